@@ -1,0 +1,42 @@
+"""The optimizer cases behind the golden vectors: one table read by the generator
+(make_golden.py, which runs the reference) and by the tests (which run the oracle and the CUDA path).
+
+name -> (optimizer, constructor kwargs, shapes, param dtype, steps, seed, options)
+options: lr_sched ("cosine5": 1e-4 -> 1e-5 over 5 steps, the C4 schedule shortened), outlier (1 % of
+the grads x100, the C3 grad distribution), sample (stride for big tensors), store_inputs, nekaon_eval.
+"""
+import math
+
+SMALL = [(48, 64), (16, 20, 3, 3), (96,), (5, 7), (130,)]
+MUON = [(48, 32), (32, 64), (40,), (8, 4, 3, 3)]
+C1 = [(1024, 1024), (320, 320, 3, 3), (1024,)]
+
+
+def cosine5(t):
+    return 1e-5 + 0.5 * (1e-4 - 1e-5) * (1 + math.cos(math.pi * t / 5))
+
+
+SCHEDULES = {"cosine5": cosine5}
+
+CASES = {
+    # Lion, the C2 settings on small shapes; "none" makes weights comparable bit for bit
+    "lion_4bit_none": ("Lion", dict(lr=2e-4, betas=(0.95, 0.98), momentum_dtype="4bit", cautious=True, bf16_method="none"), SMALL, "bf16", 6, 0, {}),
+    "lion_4bit_nogc_wd": ("Lion", dict(lr=2e-4, betas=(0.95, 0.98), weight_decay=0.1, momentum_dtype="4bit", gradient_centralization=False, bf16_method="none"), SMALL, "bf16", 6, 1, {}),
+    "lion_int8_none": ("Lion", dict(lr=2e-4, betas=(0.9, 0.99), momentum_dtype="int8", bf16_method="none"), SMALL, "bf16", 5, 2, {}),
+    "lion_bf16_nocautious": ("Lion", dict(lr=2e-4, momentum_dtype="bfloat16", cautious=False, bf16_method="none"), SMALL, "bf16", 4, 3, {}),
+    "lion_4bit_f32params": ("Lion", dict(lr=2e-4, betas=(0.95, 0.98), momentum_dtype="4bit"), SMALL, "f32", 5, 4, {}),
+    "lion_4bit_sr": ("Lion", dict(lr=2e-4, betas=(0.95, 0.98), momentum_dtype="4bit"), SMALL, "bf16", 4, 5, {}),
+    # Adakaon, the C1 settings on small shapes
+    "adakaon_int8_none": ("Adakaon", dict(lr=1e-4, betas=(0.9, 0.999), momentum_dtype="int8", bf16_method="none"), SMALL, "bf16", 6, 10, {}),
+    "adakaon_int8_sr": ("Adakaon", dict(lr=1e-4, betas=(0.9, 0.999), momentum_dtype="int8"), SMALL, "bf16", 6, 11, {}),
+    "adakaon_int8_outlier": ("Adakaon", dict(lr=1e-4, betas=(0.9, 0.999), momentum_dtype="int8", bf16_method="none"), SMALL, "bf16", 5, 12, {"outlier": True}),
+    "adakaon_4bit_wd_f32": ("Adakaon", dict(lr=1e-4, betas=(0.2, 0.999), weight_decay=0.1, momentum_dtype="4bit"), SMALL, "f32", 5, 13, {}),
+    "adakaon_bf16m_none": ("Adakaon", dict(lr=1e-4, momentum_dtype="bfloat16", bf16_method="none"), SMALL, "bf16", 4, 14, {}),
+    # Nekaon (C4 settings; fp32 params make the three writes deterministic) under a cosine LR
+    "nekaon_f32": ("Nekaon", dict(lr=1e-4, betas=(0.2, 0.999)), SMALL, "f32", 5, 20, {"lr_sched": "cosine5", "nekaon_eval": True}),
+    "nekaon_bf16": ("Nekaon", dict(lr=1e-4, betas=(0.2, 0.999)), SMALL, "bf16", 5, 21, {"lr_sched": "cosine5"}),
+    # AdaMuon (C5 settings)
+    "adamuon_int8_none": ("AdaMuon", dict(lr=1e-3, ns_steps=2, cautious=True, momentum_dtype="int8", bf16_method="none"), MUON, "bf16", 4, 30, {}),
+    # C1 at full size (the CPU-runnable correctness workload); big tensors stored strided
+    "c1_full": ("Adakaon", dict(lr=1e-4, betas=(0.9, 0.999), momentum_dtype="int8", bf16_method="stochastic_rounding"), C1, "bf16", 10, 0, {"store_inputs": False, "sample": 257}),
+}
