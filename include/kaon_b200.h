@@ -1,0 +1,159 @@
+/*
+ * kaon_b200.h — C ABI of libkaon_b200.so: the fused optimizer step of kaon (Koronos/K-Optimizers)
+ * for NVIDIA B200 (sm_100a).
+ *
+ * The reference is pure Python and has no FFI for this path; its boundary is the Python optimizer
+ * classes.  Every entry point below names the reference function whose work it replaces (path within
+ * the reference project).  Conventions: plain C types; raw DEVICE pointers unless a parameter says
+ * "host"; every call returns 0 on success or a negative KAON_E_* code and records a message readable
+ * with kaon_last_error(); nothing throws across the ABI; launches are asynchronous on the stream
+ * passed in (a cudaStream_t cast to void*); the library creates no threads.
+ */
+#ifndef KAON_B200_H
+#define KAON_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KAON_ABI_VERSION 1
+
+/* parameter / gradient element type (grads have the parameter's type) */
+#define KAON_DT_F32 0
+#define KAON_DT_BF16 1
+
+/* momentum_dtype (reference src/kaon/_momentum_codec.py:42) */
+#define KAON_M_F32 0
+#define KAON_M_BF16 1
+#define KAON_M_INT8 2 /* per-row absmax, one fp32 scale per dim-0 row, one scalar for 1-D */
+#define KAON_M_4BIT 3 /* flat blocks of `block` elements, nibble-packed, even index in the low nibble */
+#define KAON_M_NONE 4 /* betas[0] == 0: no first moment (Adakaon / AdaMuon only) */
+
+/* bf16_method (reference src/kaon/_backend.py:82-122) */
+#define KAON_W_NONE 0 /* p - bf16(delta), round to nearest even */
+#define KAON_W_SR 1   /* stochastic rounding, Philox4x32-10 keyed on (seed, step, tensor id, element) */
+
+/* optimizer kinds a plan can be built for */
+#define KAON_OPT_LION 0
+#define KAON_OPT_ADAKAON 1
+#define KAON_OPT_ADAMUON 2
+
+/* error codes */
+#define KAON_OK 0
+#define KAON_E_INVALID (-1)     /* bad argument (message says which) */
+#define KAON_E_UNSUPPORTED (-2) /* a shape / option this build has no kernel for */
+#define KAON_E_CUDA (-3)        /* a CUDA runtime call failed */
+#define KAON_E_DEVICE (-4)      /* the device status word reported a bounded wait that ran out */
+
+/* SR stream tags: which of a step's weight writes a draw belongs to */
+#define KAON_TAG_UPDATE 0
+#define KAON_TAG_REMOVE 1
+#define KAON_TAG_CLIMB 2
+#define KAON_TAG_EVAL 3
+#define KAON_TAG_TRAIN 4
+
+/* One tensor of a parameter group: a row of the descriptor table.  All pointers are device pointers
+ * that stay valid for the life of the plan, except `g`, which kaon_plan_set_grads may replace before
+ * every step.  Layout of the state tensors is the reference's state_dict layout
+ * (src/kaon/_momentum_codec.py:295-301, 350-360; src/kaon/adakaon.py:318-335). */
+typedef struct kaon_tensor_desc {
+  void* p;         /* weights, numel elements of the plan's param dtype; 16-byte aligned */
+  const void* g;   /* gradients, same dtype and shape; 16-byte aligned; may be NULL (tensor skipped) */
+  void* m;         /* momentum: fp32/bf16 [numel] | int8 [numel] | uint8 [(numel+1)/2]; NULL if none */
+  float* m_scale;  /* int8: [rows] (or [1] for 1-D); 4bit: [ceil(numel/block)]; else NULL */
+  float* stat_a;   /* Adakaon/AdaMuon: row[rows] for ndim>=2, v[numel] for 1-D; Lion: NULL */
+  float* stat_b;   /* Adakaon/AdaMuon: col[cols] for ndim>=2; else NULL */
+  int64_t numel;
+  int64_t rows;    /* shape[0] when ndim >= 2, else 0 (1-D tensor) */
+  uint32_t tensor_id; /* position in the optimizer's flattened param list: keys the SR stream */
+  uint32_t block;  /* 4-bit block size actually in use: min(momentum_4bit_block, numel) */
+} kaon_tensor_desc;
+
+typedef struct kaon_plan kaon_plan; /* opaque: descriptor table, work list and scratch on one device */
+
+/* Hyper-parameters travel as the Python doubles the reference holds in param_groups; the library casts
+ * to fp32 where the reference's torch ops do (e.g. the lerp weight is (float)(1.0 - beta)). */
+typedef struct kaon_lion_hparams {
+  double lr, beta1, beta2, weight_decay;
+  int32_t cautious, gradient_centralization, bf16_method, reserved;
+} kaon_lion_hparams;
+
+typedef struct kaon_adakaon_hparams {
+  double lr, beta1, beta2, eps1, weight_decay, clip_threshold;
+  int32_t cautious, gradient_centralization, bf16_method, reserved;
+} kaon_adakaon_hparams;
+
+/* ---- library ---- */
+int kaon_abi_version(void);
+const char* kaon_last_error(void); /* message of the calling thread's last failed call */
+
+/* ---- descriptor tables (replace the foreach batcher: src/kaon/adakaon.py:757-838,
+ *      src/kaon/lion.py:366-414, src/kaon/_backend.py:59-77) ---- */
+
+/* Build the device-side table, the work list and the scratch for `n` tensors (host array `descs`)
+ * of one parameter group on the current device.  Blocks until the table is resident. */
+int kaon_plan_create(kaon_plan** out, int optimizer, int param_dtype, int momentum_kind,
+                     const kaon_tensor_desc* descs, int n);
+/* Replace the gradient pointers (host array of n device pointers, NULL = skip that tensor this step).
+ * Asynchronous on `stream`; the host array may be reused as soon as the call returns. */
+int kaon_plan_set_grads(kaon_plan* plan, const void* const* grads, int n, void* stream);
+int kaon_plan_destroy(kaon_plan* plan);
+/* Synchronise `stream` and read the plan's device status word: 0, or KAON_E_DEVICE with a message. */
+int kaon_plan_status(kaon_plan* plan, void* stream);
+/* Bytes of device memory the plan owns (tables + scratch), and how many kernels it has launched. */
+int64_t kaon_plan_device_bytes(const kaon_plan* plan);
+int64_t kaon_plan_launch_count(const kaon_plan* plan);
+/* Per-tensor cautious kept counts of the last step, copied to a host array of n uint32 (synchronises
+ * `stream`).  Diagnostic: lets a test compare the mask population with the oracle's. */
+int kaon_plan_kept_counts(kaon_plan* plan, uint32_t* host_out, int n, void* stream);
+
+/* ---- optimizer steps ---- */
+
+/* One Lion step over every tensor of the plan whose gradient is set.
+ * Replaces Lion._step_impl / _bucket / _step_one_param (src/kaon/lion.py:322-352, 416-485) together
+ * with centralize_grads_ (src/kaon/_backend.py:147-177), the codec store (src/kaon/lion.py:244-317),
+ * cautious_batched_ (src/kaon/_backend.py:127-142) and subtract_batched_ (src/kaon/_backend.py:102-122).
+ * `step` is the 1-based step index; (seed, step, tensor_id, element) key the SR noise. */
+int kaon_lion_step(kaon_plan* plan, const kaon_lion_hparams* hp, uint64_t seed, uint32_t step,
+                   void* stream);
+
+/* One Adakaon step.  Replaces Adakaon._step_impl / _factored_bucket / _nonfactored_bucket /
+ * _step_one_param (src/kaon/adakaon.py:339-383, 840-1014), update_factored_state and
+ * factored_inv_sqrt_factors (src/kaon/_factored.py:26-83), the codec EMA
+ * (src/kaon/_momentum_codec.py:303-340, 357-389), cautious and the weight write as for Lion.
+ * If climb_remove != 0 the previous Nekaon climb is removed from each weight first and, if
+ * climb_add != 0, the new climb is applied after the update (MSAM.step, src/kaon/msam.py:374-406):
+ * e = clamp(nan_to_num(decode(m) * alpha), +-bound); see kaon_msam_apply. */
+int kaon_adakaon_step(kaon_plan* plan, const kaon_adakaon_hparams* hp, uint64_t seed, uint32_t step,
+                      void* stream);
+
+/* Nekaon climb / removal / eval / train swap over every tensor of the plan that has a momentum:
+ * p += clamp(nan_to_num(decode(m_stored) * (float)alpha), +-(float)bound), stochastic rounding for
+ * bf16 weights (stream tag `tag`), plain add for fp32.  Replaces MSAM._apply with norm="none"
+ * (src/kaon/msam.py:201-235) and _axpy_4bit_batched (src/kaon/_fused_triton.py:1145-1179). */
+int kaon_msam_apply(kaon_plan* plan, double alpha, double bound, uint32_t tag, uint64_t seed,
+                    uint32_t step, void* stream);
+
+/* ---- standalone codec (src/kaon/_momentum_codec.py:72-189; CodecBuffer.read/write,
+ *      src/kaon/_wrappers.py:56-168) ---- */
+int kaon_codec_encode_int8(const float* m, int64_t numel, int64_t rows, int8_t* codes, float* scale,
+                           void* stream);
+int kaon_codec_decode_int8(const int8_t* codes, const float* scale, int64_t numel, int64_t rows,
+                           float* m, void* stream);
+int kaon_codec_encode_4bit(const float* m, int64_t numel, int64_t block, uint8_t* packed,
+                           float* scale, void* stream);
+int kaon_codec_decode_4bit(const uint8_t* packed, const float* scale, int64_t numel, int64_t block,
+                           float* m, void* stream);
+
+/* ---- weight write on its own (src/kaon/_stochastic_rounding.py:39-103): p += alpha * delta ---- */
+int kaon_sr_add(void* p, int param_dtype, const float* delta, int64_t numel, float alpha,
+                int bf16_method, uint64_t seed, uint32_t step, uint32_t tensor_id, uint32_t tag,
+                void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KAON_B200_H */

@@ -1,0 +1,454 @@
+// Lion step for sm_100a: one persistent kernel walks the plan's work list.
+//
+// MAIN item (a run of whole rows, <= CAP elements): the gradient rows and the momentum bytes arrive in
+// shared memory through the bulk-copy engine; row means (gradient centralization) are taken from
+// shared memory; then per eight elements: decode momentum, direction sign(b1*m + (1-b1)*g), new
+// momentum b2*m + (1-b2)*g, re-encode and store it, and - when cautious masking is on - store a
+// 2-bit code per element (0 = masked out, 1/2/3 = update sign -1/0/+1) and add to the tensor's kept
+// count.  APPLY item (same run, later in the list): once every MAIN item of the tensor has finished,
+// turn the codes into the weight write with the tensor-wide rescale 1/max(kept/numel, 1e-8).
+// Quantised momentum is read once and written once; weights are read once and written once.
+#include "kaon_host.h"
+#include "kaon_ops.cuh"
+
+namespace kaon {
+
+struct LionDev {
+  float lr, b1, w1, b2, w2, wd;
+  int cautious, gc, sr, has_wd;
+  uint32_t step, k0, k1;
+};
+
+// The Lion arithmetic on eight elements: in g (centralized grads), m (decoded momentum), pvals
+// (weights, only read when has_wd).  Out: m <- new momentum, dl <- direction (+ wd*p), kept bits.
+__device__ __forceinline__ uint32_t lion_math8(const LionDev& hp, const float g[8], float m[8],
+                                               const float pvals[8], float dl[8], int sg[8],
+                                               int cnt) {
+  uint32_t kept = 0;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    float c = __fmaf_rn(g[k], hp.w1, __fmul_rn(m[k], hp.b1));
+    sg[k] = (c > 0.0f) ? 1 : ((c < 0.0f) ? -1 : 0);
+    float s = (float)sg[k];
+    m[k] = __fmaf_rn(g[k], hp.w2, __fmul_rn(m[k], hp.b2));
+    float dv = hp.has_wd ? __fmaf_rn(pvals[k], hp.wd, s) : s;
+    dl[k] = dv;
+    if (k < cnt && __fmul_rn(dv, g[k]) > 0.0f) kept |= 1u << k;
+  }
+  return kept;
+}
+
+template <typename PT, int MK>
+__device__ void lion_main(const PlanView& pv, const LionDev& hp, const Task& t, unsigned char* g_s,
+                          unsigned char* m_s, float* mean_s, unsigned* rowmax_s, float* scale_s,
+                          uint64_t* bar,
+                          unsigned& parity, unsigned* red_s, int tid) {
+  using E = Elems<PT>;
+  const DevTensor d = pv.tensors[t.tensor];
+  const unsigned char* g = reinterpret_cast<const unsigned char*>(pv.grads[t.tensor]);
+  const int n = t.n;
+  bool ok = g != nullptr;
+  if (ok) {
+    // ---- stage gradient rows and momentum bytes ----
+    const unsigned gbytes = (unsigned)n * E::BYTES;
+    unsigned mbytes;
+    const unsigned char* msrc;
+    if constexpr (MK == KAON_M_4BIT) { mbytes = (unsigned)(n + 1) >> 1; msrc = (const unsigned char*)d.m + (t.e0 >> 1); }
+    else if constexpr (MK == KAON_M_INT8) { mbytes = (unsigned)n; msrc = (const unsigned char*)d.m + t.e0; }
+    else if constexpr (MK == KAON_M_BF16) { mbytes = (unsigned)n * 2; msrc = (const unsigned char*)d.m + t.e0 * 2; }
+    else { mbytes = (unsigned)n * 4; msrc = (const unsigned char*)d.m + t.e0 * 4; }
+    const unsigned char* gsrc = g + t.e0 * E::BYTES;
+    const unsigned ghead = stage_tail(g_s, gsrc, gbytes, tid);
+    const unsigned mhead = stage_tail(m_s, msrc, mbytes, tid);
+    const bool use_bar = (ghead + mhead) != 0;
+    if (use_bar) {
+      if (tid == 0) {
+        fence_async_smem();
+        mbar_expect_tx(bar, ghead + mhead);
+        if (ghead) bulk_g2s(g_s, gsrc, ghead, bar);
+        if (mhead) bulk_g2s(m_s, msrc, mhead, bar);
+      }
+      ok = mbar_wait(bar, parity, pv.status, 1001u);
+      parity ^= 1u;
+    }
+  }
+  ok = __syncthreads_and(ok) != 0;
+  if (!ok) {  // tensor without a gradient this step, or a copy that never landed: only signal
+    __syncthreads();
+    if (tid == 0) signal_counter(pv.done + t.tensor, 1u);
+    return;
+  }
+
+  // ---- gradient centralization: bf16-rounded (bf16 grads) mean of each staged row ----
+  const bool do_gc = hp.gc && d.rows > 0;
+  const int C = d.cols;
+  const int nrows = d.rows > 0 ? n / C : 1;
+  if (do_gc) {
+    const int warp = tid >> 5, lane = tid & 31;
+    for (int r = warp; r < nrows; r += NTHREADS / 32) {
+      const unsigned char* rowp = g_s + (size_t)r * C * E::BYTES;
+      float s = 0.0f;
+      if ((C & 7) == 0) {
+        for (int v = lane; v < (C >> 3); v += 32) {
+          float x[8];
+          E::load8(rowp + (size_t)v * 8 * E::BYTES, x);
+          s += ((x[0] + x[1]) + (x[2] + x[3])) + ((x[4] + x[5]) + (x[6] + x[7]));
+        }
+      } else {
+        for (int i = lane; i < C; i += 32) s += E::load1(rowp, i);
+      }
+      s = warp_sum(s);
+      if (lane == 0) {
+        float mean = __fdiv_rn(s, (float)C);
+        mean_s[r] = E::IS_BF16 ? round_bf16(mean) : mean;
+      }
+    }
+  }
+  if constexpr (MK == KAON_M_INT8) {
+    for (int r = tid; r < nrows; r += NTHREADS) {
+      rowmax_s[r] = 0u;
+      scale_s[r] = d.m_scale[t.row0 + r];  // old scales: the row's first vector overwrites them below
+    }
+  }
+  __syncthreads();
+
+  const int nvec = (n + 7) >> 3;
+  const int nvec_pad = (nvec + 31) & ~31;  // whole warps stay in the loop together
+  const bool row_uniform = (d.rows <= 0) || ((C & 7) == 0);
+  auto load_g = [&](int v, int cnt, float gv[8]) {
+    load8_guard<PT>(g_s + (size_t)v * 8 * E::BYTES, cnt, gv);
+    if (do_gc) {
+      if (row_uniform) {
+        float mu = mean_s[row_of((unsigned)v * 8u, d)];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          float x = __fsub_rn(gv[k], mu);
+          gv[k] = (k < cnt) ? (E::IS_BF16 ? round_bf16(x) : x) : 0.0f;
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          float x = __fsub_rn(gv[k], mean_s[k < cnt ? row_of((unsigned)(v * 8 + k), d) : 0]);
+          gv[k] = (k < cnt) ? (E::IS_BF16 ? round_bf16(x) : x) : 0.0f;
+        }
+      }
+    }
+  };
+  const bool need_p = hp.has_wd || !hp.cautious;
+  unsigned char* pbase = reinterpret_cast<unsigned char*>(d.p) + t.e0 * E::BYTES;
+  SrStream st{Philox{hp.k0, hp.k1}, hp.step, KAON_TAG_UPDATE};
+
+  // ---- int8: the row scale needs the row's absmax of the NEW momentum first ----
+  if constexpr (MK == KAON_M_INT8) {
+    for (int v = tid; v < nvec; v += NTHREADS) {
+      const int cnt = min(8, n - v * 8);
+      float gv[8], mv[8];
+      load_g(v, cnt, gv);
+      const int r0 = row_of((unsigned)v * 8u, d);
+      if (row_uniform) {
+        decode8<MK>(m_s, v, cnt, scale_s[r0], mv);
+        float a = 0.0f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) a = fmaxf(a, fabsf(__fmaf_rn(gv[k], hp.w2, __fmul_rn(mv[k], hp.b2))));
+        atomicMax(rowmax_s + r0, __float_as_uint(a));
+      } else {
+        for (int k = 0; k < cnt; ++k) {
+          const int r = row_of((unsigned)(v * 8 + k), d);
+          float mo = __fmul_rn((float)(signed char)m_s[v * 8 + k], scale_s[r]);
+          float a = fabsf(__fmaf_rn(gv[k], hp.w2, __fmul_rn(mo, hp.b2)));
+          atomicMax(rowmax_s + r, __float_as_uint(a));
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+  // ---- main pass ----
+  uint32_t kept_local = 0;
+  for (int v = tid; v < nvec_pad; v += NTHREADS) {
+    const int cnt = max(0, min(8, n - v * 8));
+    float gv[8], mv[8], pvals[8], dl[8];
+    int sg[8];
+    if (cnt > 0) load_g(v, cnt, gv);
+    else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) gv[k] = 0.0f;
+    }
+    // old momentum
+    float sc_old = 1.0f;
+    long long blk = 0;
+    if constexpr (MK == KAON_M_4BIT) {
+      blk = (d.block == 128u) ? ((t.e0 >> 7) + (v >> 4)) : 0;
+      if (cnt > 0) sc_old = d.m_scale[blk];
+    }
+    if constexpr (MK == KAON_M_INT8) {
+      if (cnt > 0 && row_uniform) sc_old = scale_s[row_of((unsigned)v * 8u, d)];
+    }
+    if (cnt > 0) {
+      if (MK == KAON_M_INT8 && !row_uniform) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          mv[k] = (k < cnt) ? __fmul_rn((float)(signed char)m_s[v * 8 + k],
+                                        scale_s[row_of((unsigned)(v * 8 + k), d)])
+                            : 0.0f;
+      } else {
+        decode8<MK>(m_s, v, cnt, sc_old, mv);
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) mv[k] = 0.0f;
+    }
+    if (need_p && cnt > 0) load8_guard<PT>(pbase + (size_t)v * 8 * E::BYTES, cnt, pvals);
+    else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) pvals[k] = 0.0f;
+    }
+    const uint32_t kept = lion_math8(hp, gv, mv, pvals, dl, sg, cnt);
+
+    // ---- store the new momentum ----
+    if constexpr (MK == KAON_M_4BIT) {
+      float a = 0.0f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) a = fmaxf(a, fabsf(mv[k]));
+      a = group_max(a, 16);
+      a = fmaxf(a, 1e-12f);
+      const float sc = __fdiv_rn(a, 7.0f);
+      const float inv = __fdividef(1.0f, sc);
+      uint32_t word = 0;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        int qi = (int)quant_round(mv[k], sc, inv, 1e-4f);
+        qi = min(max(qi, -7), 7) + 8;
+        if (k < cnt) word |= (uint32_t)qi << (4 * k);
+      }
+      if (cnt > 0) {
+        unsigned char* mdst = (unsigned char*)d.m + (t.e0 >> 1) + (size_t)v * 4;
+        if (cnt == 8) *reinterpret_cast<uint32_t*>(mdst) = word;
+        else
+          for (int b = 0; b < (cnt + 1) / 2; ++b) mdst[b] = (unsigned char)(word >> (8 * b));
+        if ((v & 15) == 0) d.m_scale[blk] = sc;
+      }
+    } else if constexpr (MK == KAON_M_INT8) {
+      if (cnt > 0) {
+        unsigned char* mdst = (unsigned char*)d.m + t.e0 + (size_t)v * 8;
+        uint32_t w0 = 0, w1 = 0;
+        float sc = 0.0f, inv = 0.0f;
+        int rprev = -1;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          if (k < cnt) {
+            const int r = row_uniform ? row_of((unsigned)v * 8u, d) : row_of((unsigned)(v * 8 + k), d);
+            if (r != rprev) {
+              sc = __fdiv_rn(fmaxf(__uint_as_float(rowmax_s[r]), 1e-12f), 127.0f);
+              inv = __fdividef(1.0f, sc);
+              rprev = r;
+              // first element of a row writes the row's scale
+              const unsigned e = (unsigned)(v * 8 + k);
+              if ((d.rows <= 0 && e == 0) || (d.rows > 0 && e == (unsigned)r * (unsigned)C)) d.m_scale[t.row0 + r] = sc;
+            }
+            int qi = (int)quant_round(mv[k], sc, inv, 1e-3f);
+            qi = min(max(qi, -127), 127);
+            uint32_t byte = (uint32_t)(qi & 0xFF);
+            if (k < 4) w0 |= byte << (8 * k); else w1 |= byte << (8 * (k - 4));
+          }
+        }
+        if (cnt == 8) *reinterpret_cast<uint2*>(mdst) = make_uint2(w0, w1);
+        else
+          for (int k = 0; k < cnt; ++k) mdst[k] = (unsigned char)((k < 4 ? w0 >> (8 * k) : w1 >> (8 * (k - 4))) & 0xFF);
+      }
+    } else if constexpr (MK == KAON_M_BF16) {
+      if (cnt > 0) {
+        unsigned char* mdst = (unsigned char*)d.m + t.e0 * 2 + (size_t)v * 16;
+        if (cnt == 8) {
+          *reinterpret_cast<uint4*>(mdst) = make_uint4(pack_bf16_rn(mv[0], mv[1]), pack_bf16_rn(mv[2], mv[3]),
+                                                      pack_bf16_rn(mv[4], mv[5]), pack_bf16_rn(mv[6], mv[7]));
+        } else {
+          for (int k = 0; k < cnt; ++k) reinterpret_cast<uint16_t*>(mdst)[k] = (uint16_t)(pack_bf16_rn(mv[k], 0.0f) & 0xffffu);
+        }
+      }
+    } else {
+      if (cnt > 0) {
+        float* mdst = reinterpret_cast<float*>((unsigned char*)d.m + t.e0 * 4) + (size_t)v * 8;
+        for (int k = 0; k < cnt; ++k) mdst[k] = mv[k];
+      }
+    }
+
+    // ---- hand the update on ----
+    if (cnt > 0) {
+      if (hp.cautious) {
+        uint32_t code16 = 0;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t code = ((kept >> k) & 1u) ? (uint32_t)(sg[k] + 2) : 0u;
+          code16 |= code << (2 * k);
+        }
+        *reinterpret_cast<uint16_t*>(pv.codes + d.code_off + (t.e0 >> 2) + (size_t)v * 2) = (uint16_t)code16;
+        kept_local += __popc(kept);
+      } else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) dl[k] = __fmul_rn(dl[k], hp.lr);
+        update8<PT>(pbase + (size_t)v * 8 * E::BYTES, cnt, dl, -1.0f, hp.sr != 0, st, d.tensor_id,
+                    (uint64_t)((t.e0 >> 3) + v));
+      }
+    }
+  }
+
+  // ---- publish: kept count, then the item's completion ----
+  if (hp.cautious) {
+    for (int o = 16; o > 0; o >>= 1) kept_local += __shfl_xor_sync(0xffffffffu, kept_local, o);
+    if ((tid & 31) == 0) red_s[tid >> 5] = kept_local;
+  }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    if (hp.cautious) {
+      unsigned tot = 0;
+      for (int w = 0; w < NTHREADS / 32; ++w) tot += red_s[w];
+      atomicAdd(pv.kept + t.tensor, tot);
+    }
+    signal_counter(pv.done + t.tensor, 1u);
+  }
+}
+
+// APPLY item: weights of the run [e0, e0+n) once the tensor's kept count is complete.
+template <typename PT>
+__device__ void lion_apply(const PlanView& pv, const LionDev& hp, const Task& t, int tid) {
+  using E = Elems<PT>;
+  const DevTensor d = pv.tensors[t.tensor];
+  if (pv.grads[t.tensor] == nullptr) return;
+  bool ok = true;
+  if (tid == 0) ok = wait_counter(pv.done + t.tensor, (unsigned)d.n_main, pv.status, 2001u);
+  ok = __syncthreads_and(ok) != 0;
+  if (!ok) return;
+  const unsigned kept = __ldcg(pv.kept + t.tensor);
+  // cautious rescale (reference src/kaon/_backend.py:127-134): mean(mask) = count / numel in fp32
+  const float denom = fmaxf(__fdiv_rn((float)kept, (float)d.numel), 1e-8f);
+  const float vpos = __fmul_rn(__fdiv_rn(1.0f, denom), hp.lr);  // |update| of a kept element, wd == 0
+  const int n = t.n;
+  const int nvec = (n + 7) >> 3;
+  unsigned char* pbase = reinterpret_cast<unsigned char*>(d.p) + t.e0 * E::BYTES;
+  const unsigned char* cbase = pv.codes + d.code_off + (t.e0 >> 2);
+  SrStream st{Philox{hp.k0, hp.k1}, hp.step, KAON_TAG_UPDATE};
+  for (int v = tid; v < nvec; v += NTHREADS) {
+    const int cnt = min(8, n - v * 8);
+    const uint32_t c16 = __ldcg(reinterpret_cast<const unsigned short*>(cbase + (size_t)v * 2));
+    float dl[8];
+    if (hp.has_wd) {
+      float pvals[8];
+      load8_guard<PT>(pbase + (size_t)v * 8 * E::BYTES, cnt, pvals);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const uint32_t code = (c16 >> (2 * k)) & 3u;
+        const float dv = __fmaf_rn(pvals[k], hp.wd, (float)((int)code - 2));
+        dl[k] = code ? __fmul_rn(__fdiv_rn(dv, denom), hp.lr) : 0.0f;
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const uint32_t code = (c16 >> (2 * k)) & 3u;
+        dl[k] = code == 3u ? vpos : (code == 1u ? -vpos : 0.0f);
+      }
+    }
+    update8<PT>(pbase + (size_t)v * 8 * E::BYTES, cnt, dl, -1.0f, hp.sr != 0, st, d.tensor_id,
+                (uint64_t)((t.e0 >> 3) + v));
+  }
+}
+
+template <typename PT, int MK>
+__global__ void __launch_bounds__(NTHREADS, 3) lion_kernel(PlanView pv, LionDev hp) {
+  extern __shared__ __align__(128) unsigned char dyn[];
+  __shared__ float mean_s[MAX_TASK_ROWS];
+  __shared__ unsigned rowmax_s[MK == KAON_M_INT8 ? MAX_TASK_ROWS : 1];
+  __shared__ float scale_s[MK == KAON_M_INT8 ? MAX_TASK_ROWS : 1];
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ int next_s[2];
+  __shared__ unsigned red_s[NTHREADS / 32];
+  unsigned char* g_s = dyn;
+  unsigned char* m_s = dyn + (size_t)CAP * Elems<PT>::BYTES;
+  const int tid = threadIdx.x;
+  auto claim_next = [&](int slot) {
+    if (tid == 0) {
+      const unsigned st = *reinterpret_cast<volatile unsigned*>(pv.status);
+      next_s[slot] = st ? 0x7fffffff : (int)atomicAdd(pv.task_counter, 1u);
+    }
+  };
+  if (tid == 0) mbar_init(&bar, 1);
+  claim_next(0);
+  __syncthreads();
+  unsigned parity = 0;
+  int slot = 0;
+  int cur = next_s[0];
+  while (cur < pv.n_tasks) {
+    claim_next(slot ^ 1);
+    const Task t = pv.tasks[cur];
+    if (t.phase == PH_LION_MAIN)
+      lion_main<PT, MK>(pv, hp, t, g_s, m_s, mean_s, rowmax_s, scale_s, &bar, parity, red_s, tid);
+    else
+      lion_apply<PT>(pv, hp, t, tid);
+    __syncthreads();
+    slot ^= 1;
+    cur = next_s[slot];
+  }
+}
+
+typedef void (*LionKernel)(PlanView, LionDev);
+
+static LionKernel pick_lion(int pdt, int mk) {
+#define KAON_PICK(PT)                                         \
+  switch (mk) {                                               \
+    case KAON_M_F32: return lion_kernel<PT, KAON_M_F32>;      \
+    case KAON_M_BF16: return lion_kernel<PT, KAON_M_BF16>;    \
+    case KAON_M_INT8: return lion_kernel<PT, KAON_M_INT8>;    \
+    case KAON_M_4BIT: return lion_kernel<PT, KAON_M_4BIT>;    \
+    default: return nullptr;                                  \
+  }
+  if (pdt == KAON_DT_BF16) { KAON_PICK(__nv_bfloat16) }
+  KAON_PICK(float)
+#undef KAON_PICK
+}
+
+int configure_launch(kaon_plan* pl, const cudaDeviceProp& prop) {
+  const size_t esz = pl->param_dtype == KAON_DT_BF16 ? 2 : 4;
+  pl->smem_bytes = (size_t)CAP * esz + momentum_bytes_per_cap(pl->momentum_kind);
+  int per_sm = 2;
+  if (pl->optimizer == KAON_OPT_LION) {
+    LionKernel k = pick_lion(pl->param_dtype, pl->momentum_kind);
+    if (!k) return fail(KAON_E_INVALID, "no Lion kernel for this dtype combination");
+    KAON_CUDA(cudaFuncSetAttribute((const void*)k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl->smem_bytes));
+    KAON_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, (const void*)k, NTHREADS, pl->smem_bytes));
+    if (per_sm < 1) return fail(KAON_E_UNSUPPORTED, "Lion kernel does not fit on an SM (shared memory %zu)", pl->smem_bytes);
+  }
+  pl->grid = prop.multiProcessorCount * per_sm;
+  return KAON_OK;
+}
+
+}  // namespace kaon
+
+using namespace kaon;
+
+extern "C" int kaon_lion_step(kaon_plan* pl, const kaon_lion_hparams* h, uint64_t seed, uint32_t step,
+                              void* stream) {
+  if (!pl || !h) return fail(KAON_E_INVALID, "kaon_lion_step: null argument");
+  if (pl->optimizer != KAON_OPT_LION) return fail(KAON_E_INVALID, "plan was not built for Lion");
+  if (h->bf16_method != KAON_W_NONE && h->bf16_method != KAON_W_SR) return fail(KAON_E_UNSUPPORTED, "bf16_method %d", h->bf16_method);
+  LionDev hp;
+  hp.lr = (float)h->lr;
+  hp.b1 = (float)h->beta1; hp.w1 = (float)(1.0 - h->beta1);
+  hp.b2 = (float)h->beta2; hp.w2 = (float)(1.0 - h->beta2);
+  hp.wd = (float)h->weight_decay;
+  hp.has_wd = h->weight_decay != 0.0;
+  hp.cautious = h->cautious != 0;
+  hp.gc = h->gradient_centralization != 0;
+  hp.sr = h->bf16_method == KAON_W_SR && pl->param_dtype == KAON_DT_BF16;
+  hp.step = step; hp.k0 = (uint32_t)seed; hp.k1 = (uint32_t)(seed >> 32);
+  cudaStream_t s = (cudaStream_t)stream;
+  PlanView v = pl->view;
+  if (hp.cautious) { v.tasks = pl->d_tasks_full; v.n_tasks = pl->n_tasks_full; }
+  else { v.tasks = pl->d_tasks_main; v.n_tasks = pl->n_tasks_main; }
+  KAON_CUDA(cudaMemsetAsync(v.task_counter, 0, pl->counters_bytes - sizeof(unsigned), s));
+  LionKernel k = pick_lion(pl->param_dtype, pl->momentum_kind);
+  k<<<pl->grid, NTHREADS, pl->smem_bytes, s>>>(v, hp);
+  KAON_CUDA(cudaGetLastError());
+  pl->launches += 1;
+  return KAON_OK;
+}

@@ -1,0 +1,247 @@
+// Host side of libkaon_b200: plans (descriptor table + work list + scratch) and error plumbing.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <deque>
+#include <string>
+#include <vector>
+
+#include "kaon_host.h"
+#include "kaon_plan.h"
+
+namespace kaon {
+
+static thread_local std::string g_err;
+
+int fail(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  g_err = buf;
+  return code;
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+  return fail(KAON_E_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+static long long gcd_ll(long long a, long long b) { return b ? gcd_ll(b, a % b) : a; }
+
+// Element alignment every work item must start on so that vector loads, the bulk copies of the
+// momentum bytes and the 4-bit blocks line up.
+static int align_unit(int momentum_kind) { return momentum_kind == KAON_M_4BIT ? 128 : 16; }
+
+size_t momentum_bytes_per_cap(int mk) {
+  switch (mk) {
+    case KAON_M_F32: return (size_t)CAP * 4;
+    case KAON_M_BF16: return (size_t)CAP * 2;
+    case KAON_M_INT8: return (size_t)CAP;
+    case KAON_M_4BIT: return (size_t)CAP / 2;
+    default: return 0;
+  }
+}
+
+// Split one tensor into work items: runs of whole rows (>=2-D) or flat runs (1-D), each at most CAP
+// elements, each starting on the alignment unit.
+static int split_tensor(const kaon_tensor_desc& d, int ti, int mk, std::vector<Task>& out) {
+  const long long n = d.numel;
+  const int A = align_unit(mk);
+  if (n == 0) return 0;
+  if (d.rows > 0) {
+    const long long C = n / d.rows;
+    if (C * d.rows != n) return fail(KAON_E_INVALID, "tensor %d: numel %lld not divisible by rows %lld", ti, n, (long long)d.rows);
+    if (n <= CAP && d.rows <= MAX_TASK_ROWS) {
+      out.push_back(Task{ti, 0, 0, (int)n, 0});
+      return 0;
+    }
+    const long long unit = A / gcd_ll(C, A);  // rows per aligned group
+    long long rpt = (CAP / C) / unit * unit;   // rows per work item
+    rpt = std::min<long long>(rpt, MAX_TASK_ROWS / unit * unit);
+    if (rpt <= 0)
+      return fail(KAON_E_UNSUPPORTED,
+                  "tensor %d: %lld rows of %lld elements cannot be cut into row-aligned work items of <= %d "
+                  "elements (row length x alignment group %lld too large)", ti, (long long)d.rows, C, CAP, unit);
+    for (long long r = 0; r < d.rows; r += rpt) {
+      long long nr = std::min<long long>(rpt, d.rows - r);
+      out.push_back(Task{ti, 0, r * C, (int)(nr * C), (int)r});
+    }
+    return 0;
+  }
+  if (mk == KAON_M_INT8 && n > CAP)
+    return fail(KAON_E_UNSUPPORTED, "tensor %d: a 1-D tensor of %lld elements with int8 momentum (one scalar scale) exceeds %d", ti, n, CAP);
+  const long long chunk = CAP / A * A;
+  for (long long e = 0; e < n; e += chunk)
+    out.push_back(Task{ti, 0, e, (int)std::min<long long>(chunk, n - e), 0});
+  return 0;
+}
+
+}  // namespace kaon
+
+using namespace kaon;
+
+extern "C" {
+
+int kaon_abi_version(void) { return KAON_ABI_VERSION; }
+const char* kaon_last_error(void) { return g_err.c_str(); }
+
+int kaon_plan_create(kaon_plan** out, int optimizer, int param_dtype, int momentum_kind,
+                     const kaon_tensor_desc* descs, int n) {
+  if (!out || !descs || n <= 0) return fail(KAON_E_INVALID, "kaon_plan_create: null argument or n <= 0");
+  if (param_dtype != KAON_DT_F32 && param_dtype != KAON_DT_BF16) return fail(KAON_E_INVALID, "param_dtype %d", param_dtype);
+  if (momentum_kind < KAON_M_F32 || momentum_kind > KAON_M_NONE) return fail(KAON_E_INVALID, "momentum_kind %d", momentum_kind);
+  if (optimizer == KAON_OPT_LION && momentum_kind == KAON_M_NONE) return fail(KAON_E_INVALID, "Lion needs a momentum");
+  *out = nullptr;
+
+  std::vector<DevTensor> tens(n);
+  std::vector<std::vector<Task>> per(n);
+  long long code_bytes = 0, total = 0;
+  for (int i = 0; i < n; ++i) {
+    const kaon_tensor_desc& d = descs[i];
+    if (!d.p || d.numel < 0) return fail(KAON_E_INVALID, "tensor %d: null weights or negative numel", i);
+    if ((uintptr_t)d.p & 15) return fail(KAON_E_INVALID, "tensor %d: weights not 16-byte aligned", i);
+    if (momentum_kind != KAON_M_NONE && !d.m && d.numel) return fail(KAON_E_INVALID, "tensor %d: momentum pointer missing", i);
+    if ((uintptr_t)d.m & 15) return fail(KAON_E_INVALID, "tensor %d: momentum not 16-byte aligned", i);
+    if ((momentum_kind == KAON_M_INT8 || momentum_kind == KAON_M_4BIT) && !d.m_scale && d.numel) return fail(KAON_E_INVALID, "tensor %d: m_scale missing", i);
+    if (d.numel >= (1ll << 40)) return fail(KAON_E_UNSUPPORTED, "tensor %d: more than 2^40 elements", i);
+    if (momentum_kind == KAON_M_4BIT && d.numel) {
+      bool ok = d.block == 128 || ((long long)d.block == d.numel && d.numel <= 128);
+      if (!ok) return fail(KAON_E_UNSUPPORTED, "tensor %d: 4-bit block size %u (numel %lld): this build handles block 128, or one block covering a tensor of <= 128 elements", i, d.block, (long long)d.numel);
+    }
+    DevTensor& t = tens[i];
+    t.p = d.p; t.m = d.m; t.m_scale = d.m_scale; t.stat_a = d.stat_a; t.stat_b = d.stat_b;
+    t.numel = d.numel;
+    t.rows = (int)d.rows;
+    t.cols = (int)(d.rows > 0 ? d.numel / d.rows : std::min<long long>(d.numel, 0x7fffffff));
+    if (d.rows > 0x7fffffffll) return fail(KAON_E_UNSUPPORTED, "tensor %d: more than 2^31 rows", i);
+    t.row_magic = t.cols > 1 ? (unsigned)((0x100000000ull + (unsigned)t.cols - 1) / (unsigned)t.cols) : 0u;
+    t.tensor_id = d.tensor_id;
+    t.block = d.block;
+    t.code_off = code_bytes;
+    code_bytes += ((d.numel + 3) / 4 + 63) / 64 * 64;  // 2 bits per element, 64-byte granules
+    total += d.numel;
+    int rc = split_tensor(d, i, momentum_kind, per[i]);
+    if (rc) return rc;
+    t.n_main = (int)per[i].size();
+  }
+
+  // Work-list order.  MAIN items in tensor order; each tensor's APPLY items follow its last MAIN item
+  // after a lag of at least `lag` other items, so that by the time an APPLY item is claimed the MAIN
+  // items it depends on have normally finished (no spinning), while the tensor's codes are still in L2.
+  int dev = 0;
+  cudaError_t ce = cudaGetDevice(&dev);
+  if (ce != cudaSuccess) return cuda_fail(ce, "cudaGetDevice");
+  cudaDeviceProp prop;
+  ce = cudaGetDeviceProperties(&prop, dev);
+  if (ce != cudaSuccess) return cuda_fail(ce, "cudaGetDeviceProperties");
+
+  kaon_plan* pl = new kaon_plan();
+  pl->device = dev;
+  pl->optimizer = optimizer; pl->param_dtype = param_dtype; pl->momentum_kind = momentum_kind;
+  pl->n_tensors = n;
+  pl->total_elems = total;
+  int rc = configure_launch(pl, prop);  // grid + shared memory for this dtype combination
+  if (rc) { delete pl; return rc; }
+
+  const size_t lag = (size_t)pl->grid * 3;
+  std::vector<Task> main_list, full_list, axpy_list;
+  std::deque<std::pair<size_t, int>> pending;  // (release position, tensor)
+  auto emit_apply = [&](int ti) {
+    for (const Task& t : per[ti]) { Task a = t; a.phase = PH_LION_APPLY; full_list.push_back(a); }
+  };
+  for (int i = 0; i < n; ++i) {
+    for (const Task& t : per[i]) {
+      while (!pending.empty() && pending.front().first <= full_list.size()) {
+        int ti = pending.front().second; pending.pop_front(); emit_apply(ti);
+      }
+      Task m = t; m.phase = PH_LION_MAIN;
+      main_list.push_back(m);
+      full_list.push_back(m);
+      Task a = t; a.phase = PH_AXPY; axpy_list.push_back(a);
+    }
+    if (!per[i].empty()) pending.emplace_back(full_list.size() + lag, i);
+  }
+  while (!pending.empty()) { int ti = pending.front().second; pending.pop_front(); emit_apply(ti); }
+
+  // One device allocation: tensors | grads | tasks(full) | tasks(main) | tasks(axpy) | counters.
+  auto up = [](size_t x) { return (x + 255) / 256 * 256; };
+  size_t o_t = 0, o_g = o_t + up(sizeof(DevTensor) * n), o_f = o_g + up(sizeof(void*) * n);
+  size_t o_m = o_f + up(sizeof(Task) * full_list.size()), o_a = o_m + up(sizeof(Task) * main_list.size());
+  size_t o_c = o_a + up(sizeof(Task) * axpy_list.size());
+  pl->counters_bytes = sizeof(unsigned) * (size_t)(2 + 2 * n);
+  size_t tot = o_c + up(pl->counters_bytes);
+  ce = cudaMalloc(&pl->d_block, tot);
+  if (ce != cudaSuccess) { delete pl; return cuda_fail(ce, "cudaMalloc(plan tables)"); }
+  ce = cudaMalloc((void**)&pl->d_codes, (size_t)std::max<long long>(code_bytes, 64));
+  if (ce != cudaSuccess) { cudaFree(pl->d_block); delete pl; return cuda_fail(ce, "cudaMalloc(code scratch)"); }
+  pl->device_bytes = (int64_t)tot + std::max<long long>(code_bytes, 64);
+  char* base = (char*)pl->d_block;
+  std::vector<const void*> grads(n);
+  for (int i = 0; i < n; ++i) grads[i] = descs[i].g;
+  cudaMemset(base + o_c, 0, up(pl->counters_bytes));
+  cudaMemcpy(base + o_t, tens.data(), sizeof(DevTensor) * n, cudaMemcpyHostToDevice);
+  cudaMemcpy(base + o_g, grads.data(), sizeof(void*) * n, cudaMemcpyHostToDevice);
+  cudaMemcpy(base + o_f, full_list.data(), sizeof(Task) * full_list.size(), cudaMemcpyHostToDevice);
+  cudaMemcpy(base + o_m, main_list.data(), sizeof(Task) * main_list.size(), cudaMemcpyHostToDevice);
+  ce = cudaMemcpy(base + o_a, axpy_list.data(), sizeof(Task) * axpy_list.size(), cudaMemcpyHostToDevice);
+  if (ce != cudaSuccess) { kaon_plan_destroy(pl); return cuda_fail(ce, "cudaMemcpy(plan tables)"); }
+  pl->d_tasks_full = (Task*)(base + o_f); pl->n_tasks_full = (int)full_list.size();
+  pl->d_tasks_main = (Task*)(base + o_m); pl->n_tasks_main = (int)main_list.size();
+  pl->d_tasks_axpy = (Task*)(base + o_a); pl->n_tasks_axpy = (int)axpy_list.size();
+  pl->d_counters = (unsigned*)(base + o_c);
+  PlanView& v = pl->view;
+  v.tensors = (const DevTensor*)(base + o_t);
+  v.grads = (const void* const*)(base + o_g);
+  v.n_tensors = n;
+  v.status = pl->d_counters;            // sticky: not cleared per step
+  v.task_counter = pl->d_counters + 1;  // cleared per step from here on
+  v.done = pl->d_counters + 2;
+  v.kept = pl->d_counters + 2 + n;
+  v.codes = pl->d_codes;
+  *out = pl;
+  return KAON_OK;
+}
+
+int kaon_plan_set_grads(kaon_plan* pl, const void* const* grads, int n, void* stream) {
+  if (!pl || !grads || n != pl->n_tensors) return fail(KAON_E_INVALID, "kaon_plan_set_grads: bad plan or n");
+  for (int i = 0; i < n; ++i)
+    if ((uintptr_t)grads[i] & 15) return fail(KAON_E_INVALID, "gradient %d not 16-byte aligned", i);
+  // pageable source: the runtime stages it before returning, so the caller's array is free at once
+  cudaError_t ce = cudaMemcpyAsync((void*)pl->view.grads, grads, sizeof(void*) * (size_t)n,
+                                   cudaMemcpyHostToDevice, (cudaStream_t)stream);
+  return ce == cudaSuccess ? KAON_OK : cuda_fail(ce, "cudaMemcpyAsync(grad pointers)");
+}
+
+int kaon_plan_destroy(kaon_plan* pl) {
+  if (!pl) return KAON_OK;
+  cudaFree(pl->d_block);
+  cudaFree(pl->d_codes);
+  delete pl;
+  return KAON_OK;
+}
+
+int kaon_plan_status(kaon_plan* pl, void* stream) {
+  if (!pl) return fail(KAON_E_INVALID, "null plan");
+  unsigned st = 0;
+  cudaError_t ce = cudaMemcpyAsync(&st, pl->view.status, 4, cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+  if (ce == cudaSuccess) ce = cudaStreamSynchronize((cudaStream_t)stream);
+  if (ce != cudaSuccess) return cuda_fail(ce, "kaon_plan_status");
+  if (st) return fail(KAON_E_DEVICE, "device status %u: a bounded wait ran out (code = 1000*phase + kind)", st);
+  return KAON_OK;
+}
+
+int64_t kaon_plan_device_bytes(const kaon_plan* pl) { return pl ? pl->device_bytes : 0; }
+int64_t kaon_plan_launch_count(const kaon_plan* pl) { return pl ? pl->launches : 0; }
+
+int kaon_plan_kept_counts(kaon_plan* pl, uint32_t* host_out, int n, void* stream) {
+  if (!pl || !host_out || n != pl->n_tensors) return fail(KAON_E_INVALID, "kaon_plan_kept_counts: bad arguments");
+  cudaError_t ce = cudaMemcpyAsync(host_out, pl->view.kept, 4 * (size_t)n, cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+  if (ce == cudaSuccess) ce = cudaStreamSynchronize((cudaStream_t)stream);
+  return ce == cudaSuccess ? KAON_OK : cuda_fail(ce, "kaon_plan_kept_counts");
+}
+
+}  // extern "C"

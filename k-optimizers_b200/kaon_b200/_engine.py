@@ -1,0 +1,242 @@
+"""Host side of the fused step: per-parameter-group plans over the C ABI.
+
+A *plan* is the device-side descriptor table that replaces the reference's foreach batcher
+(reference src/kaon/adakaon.py:757-838, src/kaon/lion.py:366-414, src/kaon/_backend.py:59-77): one row
+per tensor (weights, momentum, scales, statistics, shape), a work list and scratch, built once and
+reused every step.  Only the gradient-pointer column is refreshed per step, because
+``zero_grad(set_to_none=True)`` reallocates gradients (the stale-pointer hazard the reference guards
+against in src/kaon/_fused_triton.py:1229-1245).  Plans are dropped whenever optimizer state is
+replaced (``load_state_dict``) or the set of stepped parameters changes.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Any
+
+import torch
+
+from . import _lib as L
+
+_PARAM_DT = {torch.float32: L.DT_F32, torch.bfloat16: L.DT_BF16}
+
+
+def fourbit_block_size(numel: int, block: int) -> int:
+    """reference src/kaon/_momentum_codec.py:192-200"""
+    if block <= 0:
+        return numel
+    return min(block, numel) if numel > 0 else 1
+
+
+def init_momentum_state(state: dict[str, Any], grad: torch.Tensor, md: str, block: int) -> None:
+    """Allocate the first-moment buffer in the reference's layout
+    (src/kaon/_momentum_codec.py:263-264, 295-301, 350-360; src/kaon/lion.py:210-241)."""
+    dev = grad.device
+    if md in ("bfloat16", "float32"):
+        state["m"] = torch.zeros_like(grad, dtype=torch.bfloat16 if md == "bfloat16" else torch.float32,
+                                      memory_format=torch.contiguous_format)
+    elif md == "int8":
+        state["m"] = torch.zeros_like(grad, dtype=torch.int8, memory_format=torch.contiguous_format)
+        shape = (grad.shape[0],) + (1,) * (grad.ndim - 1) if grad.ndim >= 2 else ()
+        state["m_scale"] = torch.ones(shape, dtype=torch.float32, device=dev)
+    else:  # 4bit
+        numel = grad.numel()
+        bs = fourbit_block_size(numel, block)
+        nblocks = (numel + bs - 1) // bs
+        state["m"] = torch.full(((numel + 1) // 2,), 0x88, dtype=torch.uint8, device=dev)
+        state["m_scale"] = torch.ones(nblocks, dtype=torch.float32, device=dev)
+        state["m_numel"] = numel
+        state["m_block"] = bs
+
+
+class GroupPlan:
+    """One C-ABI plan: the tensors of one (param group, device, dtype) bucket."""
+
+    def __init__(self, optimizer_kind: int, params: list[torch.Tensor], states: list[dict[str, Any]],
+                 tensor_ids: list[int], momentum_dtype: str | None):
+        lib = L.lib()
+        p0 = params[0]
+        if not p0.is_cuda:
+            raise L.KaonError("kaon_b200 steps CUDA tensors only (there is no CPU path); got a "
+                              f"parameter on {p0.device}")
+        if p0.dtype not in _PARAM_DT:
+            raise NotImplementedError(f"kaon_b200: parameter dtype {p0.dtype} (float32 and bfloat16 are supported)")
+        self.device = p0.device
+        self.params = params
+        self.n = len(params)
+        self.param_ptrs = [p.data_ptr() for p in params]
+        mk = L.M_NONE if momentum_dtype is None else L.MOMENTUM_KIND[momentum_dtype]
+        descs = (L.TensorDesc * self.n)()
+        self._keep = []  # state tensors the table points at
+        for i, (p, st, tid) in enumerate(zip(params, states, tensor_ids)):
+            if not p.is_contiguous():
+                raise NotImplementedError("kaon_b200: non-contiguous parameter")
+            d = descs[i]
+            d.p = p.data_ptr()
+            d.g = 0
+            d.numel = p.numel()
+            d.rows = p.shape[0] if p.ndim >= 2 else 0
+            d.tensor_id = tid
+            d.block = int(st.get("m_block", 128))
+            for field, key in (("m", "m"), ("m_scale", "m_scale")):
+                t = st.get(key) if mk != L.M_NONE else None
+                if t is not None:
+                    if not t.is_contiguous() or t.device != p.device:
+                        raise L.KaonError(f"optimizer state '{key}' must be contiguous and on the parameter's device")
+                    setattr(d, field, t.data_ptr())
+                    self._keep.append(t)
+            a = st.get("row") if "row" in st else st.get("v")
+            b = st.get("col")
+            for field, t in (("stat_a", a), ("stat_b", b)):
+                if t is not None:
+                    setattr(d, field, t.data_ptr())
+                    self._keep.append(t)
+        self.handle = C.c_void_p()
+        with torch.cuda.device(self.device):
+            L.check(lib.kaon_plan_create(C.byref(self.handle), optimizer_kind, _PARAM_DT[p0.dtype], mk,
+                                         descs, self.n))
+        self._grad_ptrs: list[int] | None = None
+        self._grad_arr = (C.c_void_p * self.n)()
+
+    def set_grads(self, stream: int) -> bool:
+        """Refresh the gradient-pointer column; returns False when nothing has a gradient."""
+        ptrs = []
+        dt = self.params[0].dtype
+        for p in self.params:
+            g = p.grad
+            if g is None:
+                ptrs.append(0)
+                continue
+            if g.is_sparse:
+                raise RuntimeError("kaon_b200 does not support sparse gradients")
+            if g.dtype != dt or not g.is_contiguous():
+                raise NotImplementedError("kaon_b200: gradients must be contiguous and of the parameter's dtype")
+            ptrs.append(g.data_ptr())
+        if ptrs != self._grad_ptrs:
+            arr = self._grad_arr
+            for i, v in enumerate(ptrs):
+                arr[i] = v
+            L.check(L.lib().kaon_plan_set_grads(self.handle, arr, self.n, C.c_void_p(stream)))
+            self._grad_ptrs = ptrs
+        return any(ptrs)
+
+    def params_moved(self) -> bool:
+        return any(p.data_ptr() != q for p, q in zip(self.params, self.param_ptrs))
+
+    def status(self, stream: int) -> None:
+        L.check(L.lib().kaon_plan_status(self.handle, C.c_void_p(stream)))
+
+    def kept_counts(self, stream: int) -> list[int]:
+        out = (C.c_uint32 * self.n)()
+        L.check(L.lib().kaon_plan_kept_counts(self.handle, out, self.n, C.c_void_p(stream)))
+        return list(out)
+
+    def device_bytes(self) -> int:
+        return int(L.lib().kaon_plan_device_bytes(self.handle))
+
+    def launches(self) -> int:
+        return int(L.lib().kaon_plan_launch_count(self.handle))
+
+    def destroy(self) -> None:
+        if self.handle:
+            L.lib().kaon_plan_destroy(self.handle)
+            self.handle = C.c_void_p()
+
+    def __del__(self):  # plans own device memory
+        try:
+            self.destroy()
+        except Exception:  # noqa: BLE001 - interpreter shutdown
+            pass
+
+
+class FusedStepMixin:
+    """Plan cache and step plumbing shared by the optimizer classes.
+
+    Subclasses provide ``_OPT_KIND``, ``_init_state(p, state, group)`` and ``_launch(plan, group, step,
+    stream)``.
+    """
+
+    _OPT_KIND: int
+
+    def _fused_init(self) -> None:
+        self._plans: dict[tuple, GroupPlan] = {}
+        self._plan_members: dict[tuple, tuple[int, ...]] = {}
+        self._t = 0                 # completed steps; the SR stream uses the 1-based index
+        self.sr_seed: int | None = None  # None -> torch.initial_seed() at the first step
+
+    def _invalidate_plans(self) -> None:
+        for pl in self._plans.values():
+            pl.destroy()
+        self._plans.clear()
+        self._plan_members.clear()
+
+    def _seed(self) -> int:
+        if self.sr_seed is None:
+            self.sr_seed = int(torch.initial_seed()) & 0xFFFFFFFFFFFFFFFF
+        return self.sr_seed
+
+    def _tensor_ids(self) -> dict[int, int]:
+        ids, i = {}, 0
+        for group in self.param_groups:
+            for p in group["params"]:
+                # a sharded list may pin each tensor's global position so every rank draws the
+                # same stochastic-rounding noise for it
+                ids[id(p)] = int(getattr(p, "kaon_tensor_id", i))
+                i += 1
+        return ids
+
+    def _momentum_dtype(self, group: dict[str, Any]) -> str | None:
+        return group["momentum_dtype"]
+
+    def _group_plans(self, gi: int, group: dict[str, Any], state_of) -> list[GroupPlan]:
+        """Plans covering every parameter of the group that has a gradient now or had one before."""
+        active = [p for p in group["params"] if p.grad is not None]
+        if not active:
+            return []
+        fresh = False
+        for p in active:
+            st = state_of(p)
+            if not st:
+                self._init_state(p, st, group)
+                fresh = True
+        members = [p for p in group["params"] if state_of(p)]
+        buckets: dict[tuple, list[torch.Tensor]] = {}
+        for p in members:
+            buckets.setdefault((gi, p.device, p.dtype), []).append(p)
+        plans = []
+        ids = None
+        for key, plist in buckets.items():
+            sig = tuple(id(p) for p in plist) + (self._momentum_dtype(group),)
+            pl = self._plans.get(key)
+            if pl is None or fresh or self._plan_members.get(key) != sig or pl.params_moved():
+                if pl is not None:
+                    pl.destroy()
+                if ids is None:
+                    ids = self._tensor_ids()
+                pl = GroupPlan(self._OPT_KIND, plist, [state_of(p) for p in plist],
+                               [ids[id(p)] for p in plist], self._momentum_dtype(group))
+                self._plans[key] = pl
+                self._plan_members[key] = sig
+            plans.append(pl)
+        return plans
+
+    def _run_groups(self, state_of=None) -> None:
+        state_of = state_of or (lambda p: self.state[p])
+        self._t += 1
+        for gi, group in enumerate(self.param_groups):
+            if group.get("bf16_method") == "kahan":
+                raise NotImplementedError("kaon_b200: bf16_method='kahan' is not built yet")
+            for pl in self._group_plans(gi, group, state_of):
+                with torch.cuda.device(pl.device):
+                    stream = torch.cuda.current_stream(pl.device).cuda_stream
+                    if pl.set_grads(stream):
+                        self._launch(pl, group, self._t, stream)
+
+    def check_device_status(self) -> None:
+        """Synchronise and raise if a kernel reported a bounded wait that ran out."""
+        for pl in self._plans.values():
+            pl.status(torch.cuda.current_stream(pl.device).cuda_stream)
+
+    def stats(self) -> dict[str, int]:
+        return {"plans": len(self._plans),
+                "plan_device_bytes": sum(pl.device_bytes() for pl in self._plans.values()),
+                "kernel_launches": sum(pl.launches() for pl in self._plans.values())}

@@ -1,0 +1,73 @@
+"""ctypes binding of libkaon_b200.so (the C ABI declared in include/kaon_b200.h).
+
+There is no CPU fallback: if the library is missing or a call fails, this raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG, "libkaon_b200.so")
+
+DT_F32, DT_BF16 = 0, 1
+M_F32, M_BF16, M_INT8, M_4BIT, M_NONE = 0, 1, 2, 3, 4
+W_NONE, W_SR = 0, 1
+OPT_LION, OPT_ADAKAON, OPT_ADAMUON = 0, 1, 2
+TAG_UPDATE, TAG_REMOVE, TAG_CLIMB, TAG_EVAL, TAG_TRAIN = 0, 1, 2, 3, 4
+MOMENTUM_KIND = {"float32": M_F32, "bfloat16": M_BF16, "int8": M_INT8, "4bit": M_4BIT}
+BF16_METHOD = {"none": W_NONE, "stochastic_rounding": W_SR}
+
+
+class TensorDesc(C.Structure):
+    _fields_ = [("p", C.c_void_p), ("g", C.c_void_p), ("m", C.c_void_p), ("m_scale", C.c_void_p),
+                ("stat_a", C.c_void_p), ("stat_b", C.c_void_p), ("numel", C.c_int64),
+                ("rows", C.c_int64), ("tensor_id", C.c_uint32), ("block", C.c_uint32)]
+
+
+class LionHParams(C.Structure):
+    _fields_ = [("lr", C.c_double), ("beta1", C.c_double), ("beta2", C.c_double),
+                ("weight_decay", C.c_double), ("cautious", C.c_int32),
+                ("gradient_centralization", C.c_int32), ("bf16_method", C.c_int32),
+                ("reserved", C.c_int32)]
+
+
+class AdakaonHParams(C.Structure):
+    _fields_ = [("lr", C.c_double), ("beta1", C.c_double), ("beta2", C.c_double),
+                ("eps1", C.c_double), ("weight_decay", C.c_double), ("clip_threshold", C.c_double),
+                ("cautious", C.c_int32), ("gradient_centralization", C.c_int32),
+                ("bf16_method", C.c_int32), ("reserved", C.c_int32)]
+
+
+class KaonError(RuntimeError):
+    pass
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """Load the CUDA library; fail loudly if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise KaonError(
+                f"{LIB_PATH} is missing: build it with `python -m kaon_b200._build` (nvcc, sm_100a). "
+                "kaon_b200 has no CPU or eager fallback.")
+        _lib = C.CDLL(LIB_PATH)
+        _lib.kaon_last_error.restype = C.c_char_p
+        _lib.kaon_plan_device_bytes.restype = C.c_int64
+        _lib.kaon_plan_launch_count.restype = C.c_int64
+        _lib.kaon_plan_device_bytes.argtypes = [C.c_void_p]
+        _lib.kaon_plan_launch_count.argtypes = [C.c_void_p]
+        if _lib.kaon_abi_version() != 1:
+            raise KaonError("libkaon_b200.so ABI version mismatch")
+    return _lib
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        msg = lib().kaon_last_error().decode("utf-8", "replace")
+        if rc == -2:
+            raise NotImplementedError(msg)
+        raise KaonError(f"libkaon_b200 error {rc}: {msg}")
