@@ -84,6 +84,13 @@ typedef struct kaon_lion_hparams {
 typedef struct kaon_adakaon_hparams {
   double lr, beta1, beta2, eps1, weight_decay, clip_threshold;
   int32_t cautious, gradient_centralization, bf16_method, reserved;
+  /* Nekaon (MSAM with norm="none", reference src/kaon/msam.py:374-406) fused into the step: if
+   * msam_remove, every weight first gets  p += clamp(nan_to_num(decode(m_old) * alpha_remove),
+   * +-bound_remove)  (taking the previous climb back out); if msam_climb, after the update
+   * p += clamp(nan_to_num(decode(m_new as stored) * alpha_climb), +-bound_climb).  bf16 weights are
+   * stochastically rounded after each of the three writes (stream tags REMOVE / UPDATE / CLIMB). */
+  int32_t msam_remove, msam_climb;
+  double msam_alpha_remove, msam_bound_remove, msam_alpha_climb, msam_bound_climb;
 } kaon_adakaon_hparams;
 
 /* ---- library ---- */
@@ -123,10 +130,8 @@ int kaon_lion_step(kaon_plan* plan, const kaon_lion_hparams* hp, uint64_t seed, 
 /* One Adakaon step.  Replaces Adakaon._step_impl / _factored_bucket / _nonfactored_bucket /
  * _step_one_param (src/kaon/adakaon.py:339-383, 840-1014), update_factored_state and
  * factored_inv_sqrt_factors (src/kaon/_factored.py:26-83), the codec EMA
- * (src/kaon/_momentum_codec.py:303-340, 357-389), cautious and the weight write as for Lion.
- * If climb_remove != 0 the previous Nekaon climb is removed from each weight first and, if
- * climb_add != 0, the new climb is applied after the update (MSAM.step, src/kaon/msam.py:374-406):
- * e = clamp(nan_to_num(decode(m) * alpha), +-bound); see kaon_msam_apply. */
+ * (src/kaon/_momentum_codec.py:303-340, 357-389), cautious and the weight write as for Lion;
+ * optionally the Nekaon removal and climb (the msam_* fields of kaon_adakaon_hparams). */
 int kaon_adakaon_step(kaon_plan* plan, const kaon_adakaon_hparams* hp, uint64_t seed, uint32_t step,
                       void* stream);
 

@@ -1,17 +1,908 @@
-// Adakaon step and the Nekaon climb: entry points (kernels under construction).
+// Adakaon step (and, fused into it, the Nekaon climb/removal) for sm_100a: one persistent kernel walks
+// the plan's work list.
+//
+// Factored (>=2-D) tensor, viewed as [R, C]:
+//   STATS (a run of rows): gradient rows arrive in shared memory through the bulk-copy engine; per
+//     row: centralization mean, row mean of g^2+eps1, row EMA (stored); per column, partial sums over
+//     the run of g^2+eps1 and of g^2/row_i (thread-owned columns, fixed row order) -> scratch slot.
+//   FINAL (a strip of columns): sum the slots in order -> column EMA (stored), c_j = rsqrt(col_j);
+//     the last strip to arrive combines the partials into mean(row) and the clip divisor
+//     max(rms(u)/clip, 1) with  sum u^2 = mean(row) * sum_j (1/col_j) * sum_i g_ij^2/row_i.
+//   COUNT (same runs): recompute u and the momentum EMA, count delta*g > 0 (cautious).
+//   APPLY (same runs): recompute, encode + store the momentum, write the weights; the Nekaon removal
+//     of the previous climb and the new climb ride on the same read and write of each weight.
+// 1-D tensor: FLAT, the whole tensor in one work item.
+// Every cross-item sum is taken in a fixed order: results do not depend on scheduling.
 #include "kaon_host.h"
-#include "kaon_plan.h"
+#include "kaon_ops.cuh"
+
+namespace kaon {
+
+struct AdaDev {
+  float w1, w1m1, w2, w2m1, eps1, clip, lrwd, upd_scale;
+  int small_w1, small_w2, has_eps, has_wd, cautious, gc, sr, has_m;
+  int remove, climb;
+  float a_remove, b_remove, a_climb, b_climb;
+  uint32_t step, k0, k1;
+};
+
+constexpr int AT = ADA_THREADS;
+
+// ----------------------------------------------------------------------------- block reductions
+
+__device__ __forceinline__ double block_sum_d(double v, double* red, int tid) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if ((tid & 31) == 0) red[tid >> 5] = v;
+  __syncthreads();
+  double t = 0.0;
+  for (int w = 0; w < AT / 32; ++w) t += red[w];
+  return t;
+}
+
+__device__ __forceinline__ unsigned block_sum_u(unsigned v, double* red, int tid) {
+  return (unsigned)(block_sum_d((double)v, red, tid) + 0.5);
+}
+
+__device__ __forceinline__ float block_max_f(float v, double* red, int tid) {
+  v = group_max(v, 32);
+  __syncthreads();
+  if ((tid & 31) == 0) red[tid >> 5] = (double)v;
+  __syncthreads();
+  float t = 0.0f;
+  for (int w = 0; w < AT / 32; ++w) t = fmaxf(t, (float)red[w]);
+  return t;
+}
+
+// ----------------------------------------------------------------------------- scalar helpers
+
+// x / d for a divisor shared by many elements: rcp = RN(1/d) computed once; one Newton step on the
+// residual gives the correctly rounded quotient for normal-range operands.
+__device__ __forceinline__ float div_shared(float x, float d, float rcp) {
+  float q0 = __fmul_rn(x, rcp);
+  float r = __fmaf_rn(-q0, d, x);
+  return __fmaf_rn(r, rcp, q0);
+}
+
+// Nekaon perturbation of one element (reference src/kaon/msam.py:222-230)
+__device__ __forceinline__ float climb_e(float m_dec, float alpha, float bound) {
+  float e = __fmul_rn(m_dec, alpha);
+  if (e != e) e = 0.0f;
+  return fminf(fmaxf(e, -bound), bound);
+}
+
+// One weight write on a register value: pv <- round(pv + alpha*d).  bf16 params: stochastic rounding
+// with `noise16`, or (sr == false, alpha == -1) nearest-even of pv - bf16(d); fp32 params: one fma.
+template <typename PT>
+__device__ __forceinline__ float write_step(float pv, float d, float alpha, bool sr, uint32_t noise16) {
+  if constexpr (Elems<PT>::IS_BF16) {
+    if (sr) return __uint_as_float((__float_as_uint(__fmaf_rn(d, alpha, pv)) + noise16) & 0xFFFF0000u);
+    return round_bf16(__fadd_rn(pv, __fmul_rn(alpha, round_bf16(d))));
+  } else {
+    return __fmaf_rn(d, alpha, pv);
+  }
+}
+
+__device__ __forceinline__ uint32_t noise_lane(const uint32_t nz[4], int k) {
+  return (k & 1) ? (nz[k >> 1] >> 16) : (nz[k >> 1] & 0xffffu);
+}
+
+template <typename PT>
+__device__ __forceinline__ void store8(void* pe, int cnt, const float v[8]) {
+  if constexpr (Elems<PT>::IS_BF16) {
+    if (cnt >= 8) {
+      *reinterpret_cast<uint4*>(pe) = make_uint4(pack_bf16_rn(v[0], v[1]), pack_bf16_rn(v[2], v[3]),
+                                                 pack_bf16_rn(v[4], v[5]), pack_bf16_rn(v[6], v[7]));
+    } else {
+      for (int k = 0; k < cnt; ++k)
+        reinterpret_cast<uint16_t*>(pe)[k] = (uint16_t)(__float_as_uint(v[k]) >> 16);
+    }
+  } else {
+    for (int k = 0; k < cnt; ++k) reinterpret_cast<float*>(pe)[k] = v[k];
+  }
+}
+
+// ----------------------------------------------------------------------------- staging
+
+struct Stage {
+  unsigned char* g_s;
+  unsigned char* m_s;
+  uint64_t* bar;
+  unsigned parity;
+};
+
+// Bring `gbytes` of gradients and `mbytes` of momentum into shared memory.  All threads call.
+__device__ __forceinline__ bool stage_in(Stage& st, const unsigned char* gsrc, unsigned gbytes,
+                                         const unsigned char* msrc, unsigned mbytes, unsigned* status,
+                                         int tid) {
+  const unsigned ghead = stage_tail(st.g_s, gsrc, gbytes, tid);
+  const unsigned mhead = mbytes ? stage_tail(st.m_s, msrc, mbytes, tid) : 0u;
+  bool ok = true;
+  if (ghead + mhead) {
+    if (tid == 0) {
+      fence_async_smem();
+      mbar_expect_tx(st.bar, ghead + mhead);
+      if (ghead) bulk_g2s(st.g_s, gsrc, ghead, st.bar);
+      if (mhead) bulk_g2s(st.m_s, msrc, mhead, st.bar);
+    }
+    ok = mbar_wait(st.bar, st.parity, status, 1002u);
+    st.parity ^= 1u;
+  }
+  return __syncthreads_and(ok) != 0;
+}
+
+template <int MK>
+__device__ __forceinline__ unsigned m_bytes(long long n) {
+  if constexpr (MK == KAON_M_4BIT) return (unsigned)((n + 1) >> 1);
+  else if constexpr (MK == KAON_M_INT8) return (unsigned)n;
+  else if constexpr (MK == KAON_M_BF16) return (unsigned)(n * 2);
+  else if constexpr (MK == KAON_M_F32) return (unsigned)(n * 4);
+  else return 0u;
+}
+
+template <int MK>
+__device__ __forceinline__ const unsigned char* m_ptr(const DevTensor& d, long long e0) {
+  const unsigned char* b = reinterpret_cast<const unsigned char*>(d.m);
+  if constexpr (MK == KAON_M_4BIT) return b + (e0 >> 1);
+  else if constexpr (MK == KAON_M_INT8) return b + e0;
+  else if constexpr (MK == KAON_M_BF16) return b + e0 * 2;
+  else if constexpr (MK == KAON_M_F32) return b + e0 * 4;
+  else return nullptr;
+}
+
+// Row means of the staged chunk for gradient centralization (0 when it is off).
+template <typename PT>
+__device__ __forceinline__ float row_mean(const unsigned char* rowp, int C, int lane) {
+  using E = Elems<PT>;
+  float s = 0.0f;
+  if ((C & 7) == 0) {
+    for (int v = lane; v < (C >> 3); v += 32) {
+      float x[8];
+      E::load8(rowp + (size_t)v * 8 * E::BYTES, x);
+      s += ((x[0] + x[1]) + (x[2] + x[3])) + ((x[4] + x[5]) + (x[6] + x[7]));
+    }
+  } else {
+    for (int i = lane; i < C; i += 32) s += E::load1(rowp, i);
+  }
+  s = warp_sum(s);
+  float mean = __fdiv_rn(s, (float)C);
+  return E::IS_BF16 ? round_bf16(mean) : mean;
+}
+
+template <typename PT>
+__device__ __forceinline__ float centered(float g, float mu, bool gc) {
+  if (!gc) return g;
+  float x = __fsub_rn(g, mu);
+  return Elems<PT>::IS_BF16 ? round_bf16(x) : x;
+}
+
+// ----------------------------------------------------------------------------- STATS
+
+struct AdaSmem {
+  float* mean_s;     // [MAX_TASK_ROWS] centralization mean of each staged row
+  float* rfac_s;     // [MAX_TASK_ROWS] STATS: 1/row_i; COUNT/APPLY: r_i = rsqrt(row_i / mean(row))
+  unsigned* rowmax_s;  // [MAX_TASK_ROWS] int8: bits of the row's absmax of the new momentum
+  float* scale_s;    // [MAX_TASK_ROWS] int8: old row scales
+  float* x_s;        // region X as floats (column accumulators / cfac / flat buffer)
+  double* red;       // [AT/32]
+};
+
+template <typename PT>
+__device__ void ada_stats(const PlanView& pv, const AdaDev& hp, const Task& t, Stage& st,
+                          const AdaSmem& sm, int tid) {
+  using E = Elems<PT>;
+  const DevTensor d = pv.tensors[t.tensor];
+  const unsigned char* g = reinterpret_cast<const unsigned char*>(pv.grads[t.tensor]);
+  const int C = d.cols;
+  const int nrows = t.n / C;
+  const bool gc = hp.gc != 0;
+  bool ok = g != nullptr;
+  float* acc1 = sm.x_s;       // sum_i (g^2 + eps1)
+  float* acc2 = sm.x_s + C;   // sum_i g^2 / row_i
+  for (int j = tid; j < 2 * C; j += AT) sm.x_s[j] = 0.0f;
+  double rowsum = 0.0;  // lane 0 of each warp: sum of the new row statistics it produced
+  const int warp = tid >> 5, lane = tid & 31;
+  for (int c0 = 0; ok && c0 < nrows; c0 += d.chunk_rows) {
+    const int nrc = min(d.chunk_rows, nrows - c0);
+    const long long e0 = t.e0 + (long long)c0 * C;
+    ok = stage_in(st, g + e0 * E::BYTES, (unsigned)(nrc * C) * E::BYTES, nullptr, 0u, pv.status, tid);
+    if (!ok) break;
+    // rows: centralization mean, mean of g^2+eps1, row EMA
+    for (int r = warp; r < nrc; r += AT / 32) {
+      const unsigned char* rowp = st.g_s + (size_t)r * C * E::BYTES;
+      const float mu = gc ? row_mean<PT>(rowp, C, lane) : 0.0f;
+      float s = 0.0f;
+      for (int i = lane; i < C; i += 32) {
+        const float x = centered<PT>(E::load1(rowp, i), mu, gc);
+        float sq = __fmul_rn(x, x);
+        if (hp.has_eps) sq = __fadd_rn(sq, hp.eps1);
+        s += sq;
+      }
+      s = warp_sum(s);
+      if (lane == 0) {
+        const int row = t.row0 + c0 + r;
+        const float mean = __fdiv_rn(s, (float)C);
+        const float rn = lerp_torch(d.stat_a[row], mean, hp.w2, hp.w2m1, hp.small_w2 != 0);
+        d.stat_a[row] = rn;
+        sm.mean_s[r] = mu;
+        sm.rfac_s[r] = __fdiv_rn(1.0f, rn);
+        rowsum += (double)rn;
+      }
+    }
+    __syncthreads();
+    // columns: each thread owns columns tid, tid+AT, ... and walks the staged rows in order
+    for (int j = tid; j < C; j += AT) {
+      float a1 = 0.0f, a2 = 0.0f;
+      for (int r = 0; r < nrc; ++r) {
+        const float x = centered<PT>(E::load1(st.g_s + (size_t)r * C * E::BYTES, j), sm.mean_s[r], gc);
+        const float sq = __fmul_rn(x, x);
+        a1 += hp.has_eps ? __fadd_rn(sq, hp.eps1) : sq;
+        a2 += __fmul_rn(sq, sm.rfac_s[r]);
+      }
+      acc1[j] += a1;
+      acc2[j] += a2;
+    }
+    __syncthreads();
+  }
+  // publish the slot
+  float* slot = pv.aux + d.aux_off + 2ll * t.slot * C;
+  if (ok)
+    for (int j = tid; j < 2 * C; j += AT) slot[j] = sm.x_s[j];
+  const double rs = block_sum_d(rowsum, sm.red, tid);
+  if (tid == 0 && ok) reinterpret_cast<double*>(pv.aux + aux_rowpart(d))[t.slot] = rs;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) signal_counter(pv.done + 0 * pv.n_tensors + t.tensor, 1u);
+}
+
+// ----------------------------------------------------------------------------- FINAL
+
+__device__ void ada_final(const PlanView& pv, const AdaDev& hp, const Task& t, const AdaSmem& sm,
+                          int tid) {
+  const DevTensor d = pv.tensors[t.tensor];
+  if (pv.grads[t.tensor] == nullptr) return;
+  bool ok = true;
+  if (tid == 0) ok = wait_counter(pv.done + 0 * pv.n_tensors + t.tensor, (unsigned)d.n_stats, pv.status, 11001u);
+  ok = __syncthreads_and(ok) != 0;
+  if (!ok) return;
+  const int C = d.cols, j0 = t.row0, nc = t.n;
+  const float* part = pv.aux + d.aux_off;
+  float* cfac = pv.aux + aux_cfac(d);
+  double tl = 0.0;
+  for (int j = tid; j < nc; j += AT) {
+    float s1 = 0.0f, s2 = 0.0f;
+    for (int s = 0; s < d.n_stats; ++s) {
+      s1 += __ldcg(part + 2ll * s * C + j0 + j);
+      s2 += __ldcg(part + 2ll * s * C + C + j0 + j);
+    }
+    const float mean = __fdiv_rn(s1, (float)d.rows);
+    const float cn = lerp_torch(d.stat_b[j0 + j], mean, hp.w2, hp.w2m1, hp.small_w2 != 0);
+    d.stat_b[j0 + j] = cn;
+    cfac[j0 + j] = rsqrt_torch(cn);
+    tl += (double)s2 / (double)cn;
+  }
+  const double tot = block_sum_d(tl, sm.red, tid);
+  double* tpart = reinterpret_cast<double*>(pv.aux + aux_tpart(d));
+  if (tid == 0) tpart[t.slot] = tot;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    unsigned old;
+    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(pv.done + 1 * pv.n_tensors + t.tensor) : "memory");
+    if (old == (unsigned)d.n_strips - 1u) {  // last strip: combine, in slot order
+      __threadfence();
+      const volatile double* rowpart = reinterpret_cast<const volatile double*>(pv.aux + aux_rowpart(d));
+      const volatile double* tp = tpart;
+      double rs = 0.0, T = 0.0;
+      for (int s = 0; s < d.n_stats; ++s) rs += rowpart[s];
+      for (int s = 0; s < d.n_strips; ++s) T += tp[s];
+      const float rowmean = __fdiv_rn((float)rs, (float)d.rows);
+      const double ss = (double)rowmean * T;
+      const float rms = __fdiv_rn((float)sqrt(ss), (float)sqrt((double)d.rows * (double)C));
+      float* scal = pv.aux + aux_scal(d);
+      scal[0] = rowmean;
+      scal[1] = fmaxf(__fdiv_rn(rms, hp.clip), 1.0f);
+      scal[2] = rms;
+      __threadfence();
+      signal_counter(pv.done + 2 * pv.n_tensors + t.tensor, 1u);
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------- COUNT / APPLY
+
+// Per-item constants of the update chain.
+struct Chain {
+  float div, rcp_div;   // clip divisor and its reciprocal
+  bool use_div;
+};
+
+// u for one element: ((g*r)*c) / divisor * scale  (reference src/kaon/adakaon.py:885-888)
+__device__ __forceinline__ float update_of(float g, float r, float c, const Chain& ch, float scale) {
+  float u = __fmul_rn(__fmul_rn(g, r), c);
+  if (ch.use_div) u = div_shared(u, ch.div, ch.rcp_div);
+  return __fmul_rn(u, scale);
+}
+
+// momentum EMA on one element in the stored dtype's arithmetic
+// (reference src/kaon/_momentum_codec.py:266-270, 303-306)
+template <int MK>
+__device__ __forceinline__ float ema_of(float m_old, float u, const AdaDev& hp) {
+  if constexpr (MK == KAON_M_NONE) return u;
+  if constexpr (MK == KAON_M_BF16)
+    return round_bf16(lerp_torch(m_old, round_bf16(u), hp.w1, hp.w1m1, hp.small_w1 != 0));
+  return lerp_torch(m_old, u, hp.w1, hp.w1m1, hp.small_w1 != 0);
+}
+
+template <typename PT, int MK, bool APPLY>
+__device__ void ada_rows(const PlanView& pv, const AdaDev& hp, const Task& t, Stage& st,
+                         const AdaSmem& sm, int tid) {
+  using E = Elems<PT>;
+  const DevTensor d = pv.tensors[t.tensor];
+  const unsigned char* g = reinterpret_cast<const unsigned char*>(pv.grads[t.tensor]);
+  if (g == nullptr) {
+    if (!APPLY) {
+      __syncthreads();
+      if (tid == 0) signal_counter(pv.done + 3 * pv.n_tensors + t.tensor, 1u);
+    }
+    return;
+  }
+  bool ok = true;
+  if (tid == 0) {
+    ok = wait_counter(pv.done + 2 * pv.n_tensors + t.tensor, 1u, pv.status, 12001u);
+    if (ok && APPLY && hp.cautious)
+      ok = wait_counter(pv.done + 3 * pv.n_tensors + t.tensor, (unsigned)d.n_count, pv.status, 13001u);
+  }
+  ok = __syncthreads_and(ok) != 0;
+  const int C = d.cols;
+  const int nrows = t.n / C;
+  const bool gc = hp.gc != 0;
+  const float* scal = pv.aux + aux_scal(d);
+  const float rowmean = __ldcg(scal + 0);
+  Chain ch;
+  ch.div = __ldcg(scal + 1);
+  ch.use_div = ch.div != 1.0f;
+  ch.rcp_div = __fdiv_rn(1.0f, ch.div);
+  float denom = 1.0f, rcp_denom = 1.0f;
+  if (APPLY && hp.cautious) {
+    const unsigned kept = __ldcg(pv.kept + t.tensor);
+    denom = fmaxf(__fdiv_rn((float)kept, (float)d.numel), 1e-8f);
+    rcp_denom = __fdiv_rn(1.0f, denom);
+  }
+  // column factors of this tensor -> shared memory (after the momentum bytes in region X)
+  float* cfac_s = sm.x_s;
+  if (ok) {
+    const float* cf = pv.aux + aux_cfac(d);
+    for (int j = tid; j < C; j += AT) cfac_s[j] = __ldcg(cf + j);
+  }
+  const int warp = tid >> 5, lane = tid & 31;
+  const bool row_uniform = (C & 7) == 0;
+  SrStream s_upd{Philox{hp.k0, hp.k1}, hp.step, KAON_TAG_UPDATE};
+  SrStream s_rem{Philox{hp.k0, hp.k1}, hp.step, KAON_TAG_REMOVE};
+  SrStream s_clb{Philox{hp.k0, hp.k1}, hp.step, KAON_TAG_CLIMB};
+  const bool sr = hp.sr != 0;
+  const bool need_p = APPLY || hp.has_wd;
+  unsigned kept_local = 0;
+
+  for (int c0 = 0; ok && c0 < nrows; c0 += d.chunk_rows) {
+    const int nrc = min(d.chunk_rows, nrows - c0);
+    const int n = nrc * C;
+    const long long e0 = t.e0 + (long long)c0 * C;
+    ok = stage_in(st, g + e0 * E::BYTES, (unsigned)n * E::BYTES, m_ptr<MK>(d, e0), m_bytes<MK>(n), pv.status, tid);
+    if (!ok) break;
+    for (int r = warp; r < nrc; r += AT / 32) {
+      const float mu = gc ? row_mean<PT>(st.g_s + (size_t)r * C * E::BYTES, C, lane) : 0.0f;
+      if (lane == 0) {
+        const int row = t.row0 + c0 + r;
+        sm.mean_s[r] = mu;
+        sm.rfac_s[r] = rsqrt_torch(__fdiv_rn(__ldcg(d.stat_a + row), rowmean));
+        if constexpr (MK == KAON_M_INT8) {
+          sm.scale_s[r] = d.m_scale[row];
+          sm.rowmax_s[r] = 0u;
+        }
+      }
+    }
+    __syncthreads();
+    unsigned char* pbase = reinterpret_cast<unsigned char*>(d.p) + e0 * E::BYTES;
+    const int nvec = (n + 7) >> 3;
+    const int nvec_pad = (nvec + 31) & ~31;
+
+    // One vector of the chain: fills g', the new momentum mn[], the pre-update weights pc[] (after the
+    // Nekaon removal) and delta dl[]; returns the kept bits.
+    auto chain8 = [&](int v, int cnt, float gv[8], float mo[8], float mn[8], float pc[8], float dl[8]) -> unsigned {
+      load8_guard<PT>(st.g_s + (size_t)v * 8 * E::BYTES, cnt, gv);
+      int rl[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) rl[k] = row_uniform ? row_of((unsigned)v * 8u, d) : row_of((unsigned)(v * 8 + min(k, max(cnt - 1, 0))), d);
+      // old momentum
+      if constexpr (MK == KAON_M_4BIT) {
+        const long long blk = (d.block == 128u) ? ((e0 >> 7) + (v >> 4)) : 0;
+        decode8<MK>(st.m_s, v, cnt, cnt > 0 ? d.m_scale[blk] : 1.0f, mo);
+      } else if constexpr (MK == KAON_M_INT8) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          mo[k] = (k < cnt) ? __fmul_rn((float)(signed char)st.m_s[v * 8 + k], sm.scale_s[rl[k]]) : 0.0f;
+      } else if constexpr (MK == KAON_M_NONE) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) mo[k] = 0.0f;
+      } else {
+        decode8<MK>(st.m_s, v, cnt, 1.0f, mo);
+      }
+      if (need_p && cnt > 0) load8_guard<PT>(pbase + (size_t)v * 8 * E::BYTES, cnt, pc);
+      else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) pc[k] = 0.0f;
+      }
+      if (hp.remove && need_p && cnt > 0) {  // take the previous climb back out first
+        uint32_t nz[4] = {0u, 0u, 0u, 0u};
+        if (E::IS_BF16) s_rem.draw8(d.tensor_id, (uint64_t)((e0 >> 3) + v), nz);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          pc[k] = write_step<PT>(pc[k], climb_e(mo[k], hp.a_remove, hp.b_remove), 1.0f, true && E::IS_BF16, noise_lane(nz, k));
+      }
+      unsigned kept = 0;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float col = cfac_s[(v * 8 + k) - rl[k] * C < C ? (v * 8 + k) - rl[k] * C : 0];
+        const float x = (k < cnt) ? centered<PT>(gv[k], sm.mean_s[rl[k]], gc) : 0.0f;
+        gv[k] = x;
+        const float u = update_of(x, sm.rfac_s[rl[k]], col, ch, hp.upd_scale);
+        mn[k] = (k < cnt) ? ema_of<MK>(mo[k], u, hp) : 0.0f;
+        const float dv = hp.has_wd ? __fmaf_rn(pc[k], hp.lrwd, mn[k]) : mn[k];
+        dl[k] = dv;
+        if (k < cnt && __fmul_rn(dv, x) > 0.0f) kept |= 1u << k;
+      }
+      return kept;
+    };
+
+    if constexpr (APPLY && MK == KAON_M_INT8) {  // row absmax of the new momentum first
+      for (int v = tid; v < nvec; v += AT) {
+        const int cnt = min(8, n - v * 8);
+        float gv[8], mo[8], mn[8], pc[8], dl[8];
+        chain8(v, cnt, gv, mo, mn, pc, dl);
+        if (row_uniform) {
+          float a = 0.0f;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) a = fmaxf(a, fabsf(mn[k]));
+          atomicMax(sm.rowmax_s + row_of((unsigned)v * 8u, d), __float_as_uint(a));
+        } else {
+          for (int k = 0; k < cnt; ++k) atomicMax(sm.rowmax_s + row_of((unsigned)(v * 8 + k), d), __float_as_uint(fabsf(mn[k])));
+        }
+      }
+      __syncthreads();
+    }
+
+    for (int v = tid; v < nvec_pad; v += AT) {
+      const int cnt = max(0, min(8, n - v * 8));
+      float gv[8], mo[8], mn[8], pc[8], dl[8];
+      unsigned kept = 0;
+      if (cnt > 0) kept = chain8(v, cnt, gv, mo, mn, pc, dl);
+      else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) { mn[k] = 0.0f; mo[k] = 0.0f; pc[k] = 0.0f; dl[k] = 0.0f; gv[k] = 0.0f; }
+      }
+      if constexpr (!APPLY) {
+        kept_local += __popc(kept);
+      } else {
+        float md[8];  // the momentum as stored (decoded), for the Nekaon climb
+        // ---- encode + store the new momentum ----
+        if constexpr (MK == KAON_M_4BIT) {
+          float a = 0.0f;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) a = fmaxf(a, fabsf(mn[k]));
+          a = fmaxf(group_max(a, 16), 1e-12f);
+          const float sc = __fdiv_rn(a, 7.0f);
+          const float inv = __fdividef(1.0f, sc);
+          uint32_t word = 0;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const float q = quant_round(mn[k], sc, inv, 1e-4f);
+            const int qi = min(max((int)q, -7), 7);
+            md[k] = __fmul_rn((float)qi, sc);
+            if (k < cnt) word |= (uint32_t)(qi + 8) << (4 * k);
+          }
+          if (cnt > 0) {
+            unsigned char* mdst = (unsigned char*)d.m + (e0 >> 1) + (size_t)v * 4;
+            if (cnt == 8) *reinterpret_cast<uint32_t*>(mdst) = word;
+            else
+              for (int b = 0; b < (cnt + 1) / 2; ++b) mdst[b] = (unsigned char)(word >> (8 * b));
+            if ((v & 15) == 0) d.m_scale[(d.block == 128u) ? ((e0 >> 7) + (v >> 4)) : 0] = sc;
+          }
+        } else if constexpr (MK == KAON_M_INT8) {
+          if (cnt > 0) {
+            unsigned char* mdst = (unsigned char*)d.m + e0 + (size_t)v * 8;
+            uint32_t w0 = 0, w1 = 0;
+            float sc = 0.0f, inv = 0.0f;
+            int rprev = -1;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              md[k] = 0.0f;
+              if (k < cnt) {
+                const int r = row_uniform ? row_of((unsigned)v * 8u, d) : row_of((unsigned)(v * 8 + k), d);
+                if (r != rprev) {
+                  sc = __fdiv_rn(fmaxf(__uint_as_float(sm.rowmax_s[r]), 1e-12f), 127.0f);
+                  inv = __fdividef(1.0f, sc);
+                  rprev = r;
+                  if ((unsigned)(v * 8 + k) == (unsigned)r * (unsigned)C) d.m_scale[t.row0 + c0 + r] = sc;
+                }
+                const int qi = min(max((int)quant_round(mn[k], sc, inv, 1e-3f), -127), 127);
+                md[k] = __fmul_rn((float)qi, sc);
+                const uint32_t byte = (uint32_t)(qi & 0xFF);
+                if (k < 4) w0 |= byte << (8 * k); else w1 |= byte << (8 * (k - 4));
+              }
+            }
+            if (cnt == 8) *reinterpret_cast<uint2*>(mdst) = make_uint2(w0, w1);
+            else
+              for (int k = 0; k < cnt; ++k) mdst[k] = (unsigned char)((k < 4 ? w0 >> (8 * k) : w1 >> (8 * (k - 4))) & 0xFF);
+          }
+        } else if constexpr (MK == KAON_M_BF16 || MK == KAON_M_F32) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) md[k] = mn[k];
+          if (cnt > 0) {
+            if constexpr (MK == KAON_M_BF16) store8<__nv_bfloat16>((unsigned char*)d.m + e0 * 2 + (size_t)v * 16, cnt, mn);
+            else store8<float>((unsigned char*)d.m + e0 * 4 + (size_t)v * 32, cnt, mn);
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) md[k] = 0.0f;
+        }
+        // ---- weights: update, then the new climb ----
+        if (cnt > 0) {
+          uint32_t nz[4] = {0u, 0u, 0u, 0u};
+          if (sr) s_upd.draw8(d.tensor_id, (uint64_t)((e0 >> 3) + v), nz);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            float f = dl[k];
+            if (hp.cautious) f = ((kept >> k) & 1u) ? div_shared(f, denom, rcp_denom) : 0.0f;
+            pc[k] = write_step<PT>(pc[k], f, -1.0f, sr, noise_lane(nz, k));
+          }
+          if (hp.climb && MK != KAON_M_NONE) {
+            uint32_t nc[4] = {0u, 0u, 0u, 0u};
+            if (E::IS_BF16) s_clb.draw8(d.tensor_id, (uint64_t)((e0 >> 3) + v), nc);
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+              pc[k] = write_step<PT>(pc[k], climb_e(md[k], hp.a_climb, hp.b_climb), 1.0f, E::IS_BF16, noise_lane(nc, k));
+          }
+          store8<PT>(pbase + (size_t)v * 8 * E::BYTES, cnt, pc);
+        }
+      }
+    }
+    __syncthreads();
+  }
+  if constexpr (!APPLY) {
+    const unsigned tot = block_sum_u(kept_local, sm.red, tid);
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      if (ok) atomicAdd(pv.kept + t.tensor, tot);
+      signal_counter(pv.done + 3 * pv.n_tensors + t.tensor, 1u);
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------- FLAT (1-D tensors)
+
+// reference src/kaon/adakaon.py:908-966: full second moment v, no factoring, no centralization.
+// The whole tensor (<= CAP elements) is one work item, so every tensor-wide reduction is CTA-local.
+template <typename PT, int MK>
+__device__ void ada_flat(const PlanView& pv, const AdaDev& hp, const Task& t, Stage& st,
+                         const AdaSmem& sm, int tid) {
+  using E = Elems<PT>;
+  const DevTensor d = pv.tensors[t.tensor];
+  const unsigned char* g = reinterpret_cast<const unsigned char*>(pv.grads[t.tensor]);
+  if (g == nullptr) return;
+  const int n = t.n;
+  if (!stage_in(st, g, (unsigned)n * E::BYTES, m_ptr<MK>(d, 0), m_bytes<MK>(n), pv.status, tid)) return;
+  float* f_s = sm.x_s;  // u, then the new momentum
+  float* v = d.stat_a;
+  // 1. second moment, raw update, its rms
+  double ss = 0.0;
+  for (int i = tid; i < n; i += AT) {
+    const float x = E::load1(st.g_s, i);
+    float sq = __fmul_rn(x, x);
+    if (hp.has_eps) sq = __fadd_rn(sq, hp.eps1);
+    const float vn = lerp_torch(v[i], sq, hp.w2, hp.w2m1, hp.small_w2 != 0);
+    v[i] = vn;
+    const float u = __fmul_rn(x, rsqrt_torch(vn));
+    f_s[i] = u;
+    ss += (double)u * (double)u;
+  }
+  ss = block_sum_d(ss, sm.red, tid);
+  const float rms = __fdiv_rn((float)sqrt(ss), (float)sqrt((double)n));
+  const float div = fmaxf(__fdiv_rn(rms, hp.clip), 1.0f);
+  // 2. momentum EMA (pre-requant value kept in f_s), absmax per scale group
+  const bool one_block = MK == KAON_M_4BIT && d.block != 128u;
+  unsigned* blkmax = sm.rowmax_s;  // 4bit: one entry per 128-block (<= CAP/128); int8: entry 0
+  for (int i = tid; i < MAX_TASK_ROWS; i += AT) blkmax[i] = 0u;
+  __syncthreads();
+  auto old_m = [&](int i) -> float {
+    if constexpr (MK == KAON_M_4BIT) {
+      const unsigned byte = st.m_s[i >> 1];
+      const int nib = (i & 1) ? (byte >> 4) & 0xF : byte & 0xF;
+      return __fmul_rn((float)(nib - 8), d.m_scale[one_block ? 0 : (i >> 7)]);
+    } else if constexpr (MK == KAON_M_INT8) {
+      return __fmul_rn((float)(signed char)st.m_s[i], d.m_scale[0]);
+    } else if constexpr (MK == KAON_M_BF16) {
+      return Elems<__nv_bfloat16>::load1(st.m_s, i);
+    } else if constexpr (MK == KAON_M_F32) {
+      return reinterpret_cast<const float*>(st.m_s)[i];
+    } else {
+      return 0.0f;
+    }
+  };
+  for (int i = tid; i < n; i += AT) {
+    const float u = __fmul_rn(__fdiv_rn(f_s[i], div), hp.upd_scale);
+    const float mn = ema_of<MK>(old_m(i), u, hp);
+    f_s[i] = mn;
+    if constexpr (MK == KAON_M_4BIT) atomicMax(blkmax + (one_block ? 0 : (i >> 7)), __float_as_uint(fabsf(mn)));
+    if constexpr (MK == KAON_M_INT8) atomicMax(blkmax, __float_as_uint(fabsf(mn)));
+  }
+  __syncthreads();
+  // 3. weights before the update (Nekaon removal), delta, kept count
+  SrStream s_upd{Philox{hp.k0, hp.k1}, hp.step, KAON_TAG_UPDATE};
+  SrStream s_rem{Philox{hp.k0, hp.k1}, hp.step, KAON_TAG_REMOVE};
+  SrStream s_clb{Philox{hp.k0, hp.k1}, hp.step, KAON_TAG_CLIMB};
+  auto noise_of = [&](const SrStream& s, int i) -> uint32_t {
+    uint32_t nz[4];
+    s.draw8(d.tensor_id, (uint64_t)(i >> 3), nz);
+    return noise_lane(nz, i & 7);
+  };
+  auto p_before = [&](int i) -> float {
+    float pv0 = E::load1(d.p, i);
+    if (hp.remove && MK != KAON_M_NONE)
+      pv0 = write_step<PT>(pv0, climb_e(old_m(i), hp.a_remove, hp.b_remove), 1.0f, E::IS_BF16,
+                           E::IS_BF16 ? noise_of(s_rem, i) : 0u);
+    return pv0;
+  };
+  unsigned kept_local = 0;
+  if (hp.cautious) {
+    for (int i = tid; i < n; i += AT) {
+      const float dv = hp.has_wd ? __fmaf_rn(p_before(i), hp.lrwd, f_s[i]) : f_s[i];
+      if (__fmul_rn(dv, E::load1(st.g_s, i)) > 0.0f) ++kept_local;
+    }
+  }
+  const unsigned kept = block_sum_u(kept_local, sm.red, tid);
+  if (tid == 0) pv.kept[t.tensor] = kept;
+  const float denom = fmaxf(__fdiv_rn((float)kept, (float)n), 1e-8f);
+  // 4. encode the momentum, write the weights
+  auto scale_of = [&](int i) -> float {
+    if constexpr (MK == KAON_M_4BIT) return __fdiv_rn(fmaxf(__uint_as_float(blkmax[one_block ? 0 : (i >> 7)]), 1e-12f), 7.0f);
+    else if constexpr (MK == KAON_M_INT8) return __fdiv_rn(fmaxf(__uint_as_float(blkmax[0]), 1e-12f), 127.0f);
+    else return 1.0f;
+  };
+  auto code_of = [&](int i, float sc) -> int {
+    const float lim = MK == KAON_M_4BIT ? 7.0f : 127.0f;
+    return (int)fminf(fmaxf(rintf(__fdiv_rn(f_s[i], sc)), -lim), lim);
+  };
+  for (int i = tid; i < n; i += AT) {
+    const float pv0 = p_before(i);
+    float dv = hp.has_wd ? __fmaf_rn(pv0, hp.lrwd, f_s[i]) : f_s[i];
+    if (hp.cautious) dv = (__fmul_rn(dv, E::load1(st.g_s, i)) > 0.0f) ? __fdiv_rn(dv, denom) : 0.0f;
+    float pn = write_step<PT>(pv0, dv, -1.0f, hp.sr != 0, hp.sr ? noise_of(s_upd, i) : 0u);
+    if (hp.climb && MK != KAON_M_NONE) {
+      float md;
+      if constexpr (MK == KAON_M_4BIT || MK == KAON_M_INT8) {
+        const float sc = scale_of(i);
+        md = __fmul_rn((float)code_of(i, sc), sc);
+      } else {
+        md = f_s[i];
+      }
+      pn = write_step<PT>(pn, climb_e(md, hp.a_climb, hp.b_climb), 1.0f, E::IS_BF16, E::IS_BF16 ? noise_of(s_clb, i) : 0u);
+    }
+    if constexpr (E::IS_BF16) reinterpret_cast<uint16_t*>(d.p)[i] = (uint16_t)(__float_as_uint(pn) >> 16);
+    else reinterpret_cast<float*>(d.p)[i] = pn;
+  }
+  __syncthreads();  // every read of the old scales is done before they are replaced
+  if constexpr (MK == KAON_M_4BIT) {
+    for (int b = tid; b < (n + 1) / 2; b += AT) {
+      const int i0 = 2 * b, i1 = 2 * b + 1;
+      unsigned lo = (unsigned)(code_of(i0, scale_of(i0)) + 8);
+      unsigned hi = i1 < n ? (unsigned)(code_of(i1, scale_of(i1)) + 8) : 0u;
+      reinterpret_cast<unsigned char*>(d.m)[b] = (unsigned char)(lo | (hi << 4));
+    }
+    const int nb = one_block ? 1 : (n + 127) >> 7;
+    for (int b = tid; b < nb; b += AT) d.m_scale[b] = scale_of(b << 7);
+  } else if constexpr (MK == KAON_M_INT8) {
+    const float sc = scale_of(0);
+    for (int i = tid; i < n; i += AT) reinterpret_cast<signed char*>(d.m)[i] = (signed char)code_of(i, sc);
+    __syncthreads();  // every thread has read the old scale (old_m) before it is replaced
+    if (tid == 0) d.m_scale[0] = sc;
+  } else if constexpr (MK == KAON_M_BF16) {
+    for (int i = tid; i < n; i += AT) reinterpret_cast<uint16_t*>(d.m)[i] = (uint16_t)(__float_as_uint(f_s[i]) >> 16);
+  } else if constexpr (MK == KAON_M_F32) {
+    for (int i = tid; i < n; i += AT) reinterpret_cast<float*>(d.m)[i] = f_s[i];
+  }
+}
+
+// ----------------------------------------------------------------------------- kernels
+
+template <typename PT, int MK>
+__global__ void __launch_bounds__(AT, 1) adakaon_kernel(PlanView pv, AdaDev hp, int x_off_rows) {
+  extern __shared__ __align__(128) unsigned char dyn[];
+  __shared__ float mean_s[MAX_TASK_ROWS];
+  __shared__ float rfac_s[MAX_TASK_ROWS];
+  __shared__ unsigned rowmax_s[MAX_TASK_ROWS];
+  __shared__ float scale_s[MAX_TASK_ROWS];
+  __shared__ double red[AT / 32];
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ int next_s[2];
+  const int tid = threadIdx.x;
+  Stage st{dyn, dyn + (size_t)CAP * Elems<PT>::BYTES, &bar, 0u};
+  // region after the gradient stage: STATS overlays its column accumulators on the momentum bytes;
+  // COUNT/APPLY/FLAT keep the momentum bytes and put cfac / the flat buffer after them.
+  AdaSmem sm_stats{mean_s, rfac_s, rowmax_s, scale_s, reinterpret_cast<float*>(st.m_s), red};
+  AdaSmem sm_rows{mean_s, rfac_s, rowmax_s, scale_s, reinterpret_cast<float*>(st.m_s + x_off_rows), red};
+  auto claim_next = [&](int slot) {
+    if (tid == 0) {
+      const unsigned s = *reinterpret_cast<volatile unsigned*>(pv.status);
+      next_s[slot] = s ? 0x7fffffff : (int)atomicAdd(pv.task_counter, 1u);
+    }
+  };
+  if (tid == 0) mbar_init(&bar, 1);
+  claim_next(0);
+  __syncthreads();
+  int slot = 0;
+  int cur = next_s[0];
+  while (cur < pv.n_tasks) {
+    claim_next(slot ^ 1);
+    const Task t = pv.tasks[cur];
+    switch (t.phase) {
+      case PH_ADA_STATS: ada_stats<PT>(pv, hp, t, st, sm_stats, tid); break;
+      case PH_ADA_FINAL: ada_final(pv, hp, t, sm_stats, tid); break;
+      case PH_ADA_COUNT: ada_rows<PT, MK, false>(pv, hp, t, st, sm_rows, tid); break;
+      case PH_ADA_APPLY: ada_rows<PT, MK, true>(pv, hp, t, st, sm_rows, tid); break;
+      case PH_ADA_FLAT: ada_flat<PT, MK>(pv, hp, t, st, sm_rows, tid); break;
+      default: break;
+    }
+    __syncthreads();
+    slot ^= 1;
+    cur = next_s[slot];
+  }
+}
+
+// Nekaon climb / removal / eval / train swap on its own (reference src/kaon/msam.py:201-235):
+// p += clamp(nan_to_num(decode(m) * alpha), +-bound) over the plan's flat work items.
+template <typename PT, int MK>
+__global__ void __launch_bounds__(256) msam_axpy_kernel(PlanView pv, float alpha, float bound,
+                                                        SrStream st) {
+  using E = Elems<PT>;
+  for (int ti = blockIdx.x; ti < pv.n_tasks; ti += gridDim.x) {
+    const Task t = pv.tasks[ti];
+    const DevTensor d = pv.tensors[t.tensor];
+    const int nvec = (t.n + 7) >> 3;
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+      const int cnt = min(8, t.n - v * 8);
+      const long long e = t.e0 + (long long)v * 8;
+      float md[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        float x = 0.0f;
+        if (k < cnt) {
+          const long long i = e + k;
+          if constexpr (MK == KAON_M_4BIT) {
+            const unsigned byte = reinterpret_cast<const unsigned char*>(d.m)[i >> 1];
+            const int nib = (i & 1) ? (byte >> 4) & 0xF : byte & 0xF;
+            x = __fmul_rn((float)(nib - 8), d.m_scale[d.block == 128u ? (i >> 7) : 0]);
+          } else if constexpr (MK == KAON_M_INT8) {
+            const int row = d.rows > 0 ? (int)(i / d.cols) : 0;
+            x = __fmul_rn((float)reinterpret_cast<const signed char*>(d.m)[i], d.m_scale[row]);
+          } else if constexpr (MK == KAON_M_BF16) {
+            x = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(d.m)[i]);
+          } else {
+            x = reinterpret_cast<const float*>(d.m)[i];
+          }
+        }
+        md[k] = climb_e(x, alpha, bound);
+      }
+      update8<PT>(reinterpret_cast<unsigned char*>(d.p) + e * E::BYTES, cnt, md, 1.0f, E::IS_BF16, st,
+                  d.tensor_id, (uint64_t)(e >> 3));
+    }
+  }
+}
+
+typedef void (*AdaKernel)(PlanView, AdaDev, int);
+typedef void (*AxpyKernel)(PlanView, float, float, SrStream);
+
+template <typename PT>
+static AdaKernel pick_ada_pt(int mk) {
+  switch (mk) {
+    case KAON_M_F32: return adakaon_kernel<PT, KAON_M_F32>;
+    case KAON_M_BF16: return adakaon_kernel<PT, KAON_M_BF16>;
+    case KAON_M_INT8: return adakaon_kernel<PT, KAON_M_INT8>;
+    case KAON_M_4BIT: return adakaon_kernel<PT, KAON_M_4BIT>;
+    case KAON_M_NONE: return adakaon_kernel<PT, KAON_M_NONE>;
+    default: return nullptr;
+  }
+}
+static AdaKernel pick_ada(int pdt, int mk) {
+  return pdt == KAON_DT_BF16 ? pick_ada_pt<__nv_bfloat16>(mk) : pick_ada_pt<float>(mk);
+}
+
+template <typename PT>
+static AxpyKernel pick_axpy_pt(int mk) {
+  switch (mk) {
+    case KAON_M_F32: return msam_axpy_kernel<PT, KAON_M_F32>;
+    case KAON_M_BF16: return msam_axpy_kernel<PT, KAON_M_BF16>;
+    case KAON_M_INT8: return msam_axpy_kernel<PT, KAON_M_INT8>;
+    case KAON_M_4BIT: return msam_axpy_kernel<PT, KAON_M_4BIT>;
+    default: return nullptr;
+  }
+}
+
+static size_t x_offset_rows(int mk) { return (momentum_bytes_per_cap(mk) + 127) / 128 * 128; }
+
+int configure_launch_adakaon(kaon_plan* pl, const cudaDeviceProp& prop, int max_cols) {
+  const size_t esz = pl->param_dtype == KAON_DT_BF16 ? 2 : 4;
+  const size_t xr = x_offset_rows(pl->momentum_kind);
+  const size_t region = std::max<size_t>(xr + (size_t)max_cols * 4, (size_t)max_cols * 8);
+  pl->smem_bytes = (size_t)CAP * esz + region + 128;
+  pl->threads = AT;
+  AdaKernel k = pick_ada(pl->param_dtype, pl->momentum_kind);
+  if (!k) return fail(KAON_E_INVALID, "no Adakaon kernel for this dtype combination");
+  if (pl->smem_bytes > (size_t)prop.sharedMemPerBlockOptin - 40 * 1024)
+    return fail(KAON_E_UNSUPPORTED, "Adakaon kernel needs %zu bytes of shared memory for rows of %d elements", pl->smem_bytes, max_cols);
+  KAON_CUDA(cudaFuncSetAttribute((const void*)k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl->smem_bytes));
+  int per_sm = 1;
+  KAON_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, (const void*)k, AT, pl->smem_bytes));
+  if (per_sm < 1) return fail(KAON_E_UNSUPPORTED, "Adakaon kernel does not fit on an SM");
+  pl->grid = prop.multiProcessorCount * per_sm;
+  return KAON_OK;
+}
+
+}  // namespace kaon
 
 using namespace kaon;
 
 extern "C" int kaon_adakaon_step(kaon_plan* pl, const kaon_adakaon_hparams* h, uint64_t seed,
                                  uint32_t step, void* stream) {
-  (void)pl; (void)h; (void)seed; (void)step; (void)stream;
-  return fail(KAON_E_UNSUPPORTED, "kaon_adakaon_step: not built yet");
+  if (!pl || !h) return fail(KAON_E_INVALID, "kaon_adakaon_step: null argument");
+  if (pl->optimizer != KAON_OPT_ADAKAON) return fail(KAON_E_INVALID, "plan was not built for Adakaon");
+  if (h->bf16_method != KAON_W_NONE && h->bf16_method != KAON_W_SR) return fail(KAON_E_UNSUPPORTED, "bf16_method %d", h->bf16_method);
+  if (!(h->clip_threshold > 0.0)) return fail(KAON_E_INVALID, "clip_threshold must be > 0");
+  const bool has_m = pl->momentum_kind != KAON_M_NONE;
+  if (has_m != (h->beta1 > 0.0)) return fail(KAON_E_INVALID, "beta1 %g does not match the plan's momentum kind", h->beta1);
+  AdaDev hp{};
+  hp.w1 = (float)(1.0 - h->beta1); hp.w1m1 = hp.w1 - 1.0f; hp.small_w1 = hp.w1 < 0.5f;
+  hp.w2 = (float)(1.0 - h->beta2); hp.w2m1 = hp.w2 - 1.0f; hp.small_w2 = hp.w2 < 0.5f;
+  hp.eps1 = (float)h->eps1; hp.has_eps = h->eps1 > 0.0;
+  hp.clip = (float)h->clip_threshold;
+  hp.lrwd = (float)(h->lr * h->weight_decay); hp.has_wd = h->weight_decay != 0.0;
+  hp.upd_scale = (float)h->lr;
+  hp.cautious = h->cautious != 0;
+  hp.gc = h->gradient_centralization != 0;
+  hp.sr = h->bf16_method == KAON_W_SR && pl->param_dtype == KAON_DT_BF16;
+  hp.has_m = has_m;
+  hp.remove = h->msam_remove != 0 && has_m;
+  hp.climb = h->msam_climb != 0 && has_m;
+  hp.a_remove = (float)h->msam_alpha_remove; hp.b_remove = (float)h->msam_bound_remove;
+  hp.a_climb = (float)h->msam_alpha_climb; hp.b_climb = (float)h->msam_bound_climb;
+  hp.step = step; hp.k0 = (uint32_t)seed; hp.k1 = (uint32_t)(seed >> 32);
+  cudaStream_t s = (cudaStream_t)stream;
+  PlanView v = pl->view;
+  if (hp.cautious) { v.tasks = pl->d_tasks_full; v.n_tasks = pl->n_tasks_full; }
+  else { v.tasks = pl->d_tasks_main; v.n_tasks = pl->n_tasks_main; }
+  KAON_CUDA(cudaMemsetAsync(v.task_counter, 0, pl->counters_bytes - sizeof(unsigned), s));
+  AdaKernel k = pick_ada(pl->param_dtype, pl->momentum_kind);
+  k<<<pl->grid, AT, pl->smem_bytes, s>>>(v, hp, (int)x_offset_rows(pl->momentum_kind));
+  KAON_CUDA(cudaGetLastError());
+  pl->launches += 1;
+  return KAON_OK;
 }
 
 extern "C" int kaon_msam_apply(kaon_plan* pl, double alpha, double bound, uint32_t tag, uint64_t seed,
                                uint32_t step, void* stream) {
-  (void)pl; (void)alpha; (void)bound; (void)tag; (void)seed; (void)step; (void)stream;
-  return fail(KAON_E_UNSUPPORTED, "kaon_msam_apply: not built yet");
+  if (!pl) return fail(KAON_E_INVALID, "kaon_msam_apply: null plan");
+  if (pl->momentum_kind == KAON_M_NONE || pl->n_tasks_axpy == 0) return KAON_OK;  // nothing carries a momentum
+  AxpyKernel k = pl->param_dtype == KAON_DT_BF16 ? pick_axpy_pt<__nv_bfloat16>(pl->momentum_kind)
+                                                 : pick_axpy_pt<float>(pl->momentum_kind);
+  if (!k) return fail(KAON_E_INVALID, "no climb kernel for this dtype combination");
+  PlanView v = pl->view;
+  v.tasks = pl->d_tasks_axpy; v.n_tasks = pl->n_tasks_axpy;
+  SrStream st{Philox{(uint32_t)seed, (uint32_t)(seed >> 32)}, step, tag};
+  const int grid = std::min(pl->n_tasks_axpy, 148 * 8);
+  k<<<grid, 256, 0, (cudaStream_t)stream>>>(v, (float)alpha, (float)bound, st);
+  KAON_CUDA(cudaGetLastError());
+  pl->launches += 1;
+  return KAON_OK;
 }

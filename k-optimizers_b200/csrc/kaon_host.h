@@ -11,7 +11,8 @@ namespace kaon {
 int fail(int code, const char* fmt, ...);           // records the message, returns code
 int cuda_fail(cudaError_t e, const char* what);     // KAON_E_CUDA with the runtime's message
 size_t momentum_bytes_per_cap(int momentum_kind);   // bytes of momentum storage per CAP elements
-int configure_launch(kaon_plan* pl, const cudaDeviceProp& prop);  // grid + dynamic shared memory
+int configure_launch(kaon_plan* pl, const cudaDeviceProp& prop);  // Lion: grid + dynamic shared memory
+int configure_launch_adakaon(kaon_plan* pl, const cudaDeviceProp& prop, int max_cols);
 
 #define KAON_CUDA(call)                                              \
   do {                                                               \

@@ -17,7 +17,15 @@ constexpr int NTHREADS = 256;
 // Work-item kinds.  Lion: MAIN does everything up to the momentum store and records, per element,
 // a 2-bit code (sign of the update / masked out); APPLY turns the codes into the weight write once
 // the tensor's kept count is complete.
-enum : int { PH_LION_MAIN = 0, PH_LION_APPLY = 1, PH_AXPY = 2 };
+enum : int { PH_LION_MAIN = 0, PH_LION_APPLY = 1, PH_AXPY = 2,
+              // Adakaon / AdaMuon (factored tensors): STATS = row statistics + column partial sums over a
+              // run of rows; FINAL = column statistics, clip divisor (one item per column strip);
+              // COUNT = cautious kept count; APPLY = momentum store + weight write.  FLAT = a whole 1-D
+              // tensor in one item.
+              PH_ADA_STATS = 10, PH_ADA_FINAL = 11, PH_ADA_COUNT = 12, PH_ADA_APPLY = 13, PH_ADA_FLAT = 14 };
+
+constexpr int ADA_THREADS = 512;
+constexpr int FINAL_STRIP = 2048;  // columns per FINAL item
 
 // One tensor as the kernels see it (device copy of kaon_tensor_desc plus planner-derived fields).
 struct DevTensor {
@@ -34,14 +42,31 @@ struct DevTensor {
   unsigned tensor_id;
   unsigned block;       // 4-bit block size in use
   int n_main;           // number of MAIN work items of this tensor (what `done` must reach)
+  // Adakaon / AdaMuon only
+  int chunk_rows;       // rows staged at a time (chunk_rows * cols <= CAP, aligned)
+  int n_stats;          // STATS items (= slots of column partials)
+  int n_strips;         // FINAL items
+  int n_count;          // COUNT items
+  long long aux_off;    // float index of this tensor's scratch in `aux`:
+                        //   colpart[n_stats][2][cols] | cfac[cols] | rowpart[n_stats] (double) |
+                        //   tpart[n_strips] (double) | scal[4] = {rowmean, divisor, rms, -}
 };
+
+// float offsets inside a tensor's aux block
+__host__ __device__ inline long long aux_cfac(const DevTensor& d) { return d.aux_off + 2ll * d.n_stats * d.cols; }
+__host__ __device__ inline long long aux_rowpart(const DevTensor& d) { return (aux_cfac(d) + d.cols + 1) / 2 * 2; }
+__host__ __device__ inline long long aux_tpart(const DevTensor& d) { return aux_rowpart(d) + 2ll * d.n_stats; }
+__host__ __device__ inline long long aux_scal(const DevTensor& d) { return aux_tpart(d) + 2ll * d.n_strips; }
+__host__ __device__ inline long long aux_size(const DevTensor& d) { return aux_scal(d) + 4 - d.aux_off; }
 
 struct Task {
   int tensor;
   int phase;
   long long e0;  // first element (flat index); multiple of the plan's alignment unit and a row start
   int n;         // elements (<= CAP); whole rows for >=2-D tensors
-  int row0;      // first row (>=2-D tensors)
+  int row0;      // first row (>=2-D tensors); FINAL items: first column of the strip
+  int slot;      // STATS items: index of the column-partial slot; otherwise 0
+  int pad;
 };
 
 // Device pointers handed to the kernels by value.
@@ -52,8 +77,10 @@ struct PlanView {
   int n_tasks;
   int n_tensors;
   unsigned* task_counter;  // claims
-  unsigned* done;          // [n_tensors] MAIN items finished
+  unsigned* done;          // Lion: [n_tensors] MAIN items finished.  Adakaon: [4][n_tensors] =
+                           //   STATS items done | FINAL strips arrived | FINAL complete | COUNT items done
   unsigned* kept;          // [n_tensors] cautious kept count
+  float* aux;              // Adakaon scratch (see DevTensor::aux_off)
   unsigned* status;        // 0 = ok; else the code of the first bounded wait that ran out
   unsigned char* codes;    // 2 bits per element
 };
@@ -74,6 +101,10 @@ struct kaon_plan {
   kaon::Task* d_tasks_axpy = nullptr;
   void* d_block = nullptr;      // one allocation holding tables and counters
   unsigned char* d_codes = nullptr;
+  float* d_aux = nullptr;
+  kaon::Task* d_tasks_nocount = nullptr;  // Adakaon work list without the COUNT items (cautious off)
+  int n_tasks_nocount = 0;
+  int threads = 0;
   unsigned* d_counters = nullptr;  // task_counter, status, done[n], kept[n] (contiguous; memset per step)
   size_t counters_bytes = 0;
   int64_t device_bytes = 0;

@@ -129,9 +129,6 @@ int kaon_plan_create(kaon_plan** out, int optimizer, int param_dtype, int moment
     t.n_main = (int)per[i].size();
   }
 
-  // Work-list order.  MAIN items in tensor order; each tensor's APPLY items follow its last MAIN item
-  // after a lag of at least `lag` other items, so that by the time an APPLY item is claimed the MAIN
-  // items it depends on have normally finished (no spinning), while the tensor's codes are still in L2.
   int dev = 0;
   cudaError_t ce = cudaGetDevice(&dev);
   if (ce != cudaSuccess) return cuda_fail(ce, "cudaGetDevice");
@@ -144,41 +141,109 @@ int kaon_plan_create(kaon_plan** out, int optimizer, int param_dtype, int moment
   pl->optimizer = optimizer; pl->param_dtype = param_dtype; pl->momentum_kind = momentum_kind;
   pl->n_tensors = n;
   pl->total_elems = total;
-  int rc = configure_launch(pl, prop);  // grid + shared memory for this dtype combination
+
+  // Per-tensor stages.  Lion: MAIN, APPLY.  Adakaon (factored): STATS, FINAL, COUNT, APPLY; (1-D): FLAT.
+  std::vector<std::vector<std::vector<Task>>> stages(n);
+  long long aux_floats = 0;
+  int max_cols = 1;
+  if (optimizer == KAON_OPT_LION) {
+    for (int i = 0; i < n; ++i) {
+      stages[i].resize(2);
+      for (const Task& t : per[i]) {
+        Task m = t; m.phase = PH_LION_MAIN; stages[i][0].push_back(m);
+        Task a = t; a.phase = PH_LION_APPLY; stages[i][1].push_back(a);
+      }
+    }
+  } else {
+    for (int i = 0; i < n; ++i) {
+      DevTensor& t = tens[i];
+      if (per[i].empty()) continue;
+      if (t.rows <= 0) {
+        if (t.numel > CAP) { delete pl; return fail(KAON_E_UNSUPPORTED, "tensor %d: a 1-D tensor of %lld elements exceeds %d (Adakaon/AdaMuon step 1-D tensors in one work item)", i, t.numel, CAP); }
+        stages[i].resize(1);
+        Task f = per[i][0]; f.phase = PH_ADA_FLAT; stages[i][0].push_back(f);
+        t.aux_off = aux_floats; t.n_stats = 0; t.n_strips = 0; t.chunk_rows = 0;
+        aux_floats += 8;
+        continue;
+      }
+      const long long C = t.cols;
+      max_cols = std::max<int>(max_cols, (int)C);
+      t.chunk_rows = (int)(per[i][0].n / C);
+      // rows per run: column partials (8 B per column per run) stay under ~10 % of the run's gradient
+      // bytes, and a run is at least ~128 K elements
+      long long run_rows = std::max<long long>(40, (131072 + C - 1) / C);
+      run_rows = (run_rows + t.chunk_rows - 1) / t.chunk_rows * t.chunk_rows;
+      stages[i].resize(4);
+      int slot = 0;
+      for (long long r = 0; r < t.rows; r += run_rows, ++slot) {
+        long long nr = std::min<long long>(run_rows, t.rows - r);
+        Task k{i, PH_ADA_STATS, r * C, (int)(nr * C), (int)r, slot, 0};
+        stages[i][0].push_back(k);
+        k.phase = PH_ADA_COUNT; stages[i][2].push_back(k);
+        k.phase = PH_ADA_APPLY; stages[i][3].push_back(k);
+      }
+      t.n_stats = slot;
+      t.n_count = slot;
+      t.n_strips = (int)((C + FINAL_STRIP - 1) / FINAL_STRIP);
+      for (int s = 0; s < t.n_strips; ++s)
+        stages[i][1].push_back(Task{i, PH_ADA_FINAL, 0, (int)std::min<long long>(FINAL_STRIP, C - (long long)s * FINAL_STRIP), s * FINAL_STRIP, s, 0});
+      t.aux_off = aux_floats;
+      aux_floats += aux_size(t);
+      aux_floats = (aux_floats + 63) / 64 * 64;
+    }
+  }
+  int rc = optimizer == KAON_OPT_LION ? configure_launch(pl, prop) : configure_launch_adakaon(pl, prop, max_cols);
   if (rc) { delete pl; return rc; }
 
+  // Work-list order: a tensor's next stage is released once at least `lag` other items have been
+  // listed after its previous stage, so that an item's dependencies have normally finished when it is
+  // claimed (claims are in list order, so a waiting item can never block the items it waits for),
+  // while what the previous stage left in L2 is still there.
   const size_t lag = (size_t)pl->grid * 3;
-  std::vector<Task> main_list, full_list, axpy_list;
-  std::deque<std::pair<size_t, int>> pending;  // (release position, tensor)
-  auto emit_apply = [&](int ti) {
-    for (const Task& t : per[ti]) { Task a = t; a.phase = PH_LION_APPLY; full_list.push_back(a); }
-  };
-  for (int i = 0; i < n; ++i) {
-    for (const Task& t : per[i]) {
-      while (!pending.empty() && pending.front().first <= full_list.size()) {
-        int ti = pending.front().second; pending.pop_front(); emit_apply(ti);
+  std::vector<Task> full_list, main_list, axpy_list;
+  {
+    std::deque<std::pair<size_t, std::pair<int, int>>> pending;  // (release position, (tensor, stage))
+    auto emit = [&](int ti, int st) {
+      for (const Task& t : stages[ti][st]) full_list.push_back(t);
+      if (st + 1 < (int)stages[ti].size()) pending.push_back({full_list.size() + lag, {ti, st + 1}});
+    };
+    auto drain = [&](bool all) {
+      while (!pending.empty() && (all || pending.front().first <= full_list.size())) {
+        auto pr = pending.front().second; pending.pop_front(); emit(pr.first, pr.second);
       }
-      Task m = t; m.phase = PH_LION_MAIN;
-      main_list.push_back(m);
-      full_list.push_back(m);
-      Task a = t; a.phase = PH_AXPY; axpy_list.push_back(a);
+    };
+    for (int i = 0; i < n; ++i) {
+      if (stages[i].empty()) continue;
+      // release what is due before each new item of this tensor's first stage
+      std::vector<Task> first = stages[i][0];
+      stages[i][0].clear();
+      for (const Task& t : first) { drain(false); full_list.push_back(t); }
+      if (stages[i].size() > 1) pending.push_back({full_list.size() + lag, {i, 1}});
     }
-    if (!per[i].empty()) pending.emplace_back(full_list.size() + lag, i);
+    drain(true);
   }
-  while (!pending.empty()) { int ti = pending.front().second; pending.pop_front(); emit_apply(ti); }
+  for (const Task& t : full_list)
+    if (t.phase != PH_LION_APPLY && t.phase != PH_ADA_COUNT) main_list.push_back(t);
+  for (int i = 0; i < n; ++i)
+    if (tens[i].m)
+      for (const Task& t : per[i]) { Task a = t; a.phase = PH_AXPY; axpy_list.push_back(a); }
 
   // One device allocation: tensors | grads | tasks(full) | tasks(main) | tasks(axpy) | counters.
   auto up = [](size_t x) { return (x + 255) / 256 * 256; };
   size_t o_t = 0, o_g = o_t + up(sizeof(DevTensor) * n), o_f = o_g + up(sizeof(void*) * n);
   size_t o_m = o_f + up(sizeof(Task) * full_list.size()), o_a = o_m + up(sizeof(Task) * main_list.size());
   size_t o_c = o_a + up(sizeof(Task) * axpy_list.size());
-  pl->counters_bytes = sizeof(unsigned) * (size_t)(2 + 2 * n);
+  pl->counters_bytes = sizeof(unsigned) * (size_t)(2 + 5 * n);
   size_t tot = o_c + up(pl->counters_bytes);
   ce = cudaMalloc(&pl->d_block, tot);
   if (ce != cudaSuccess) { delete pl; return cuda_fail(ce, "cudaMalloc(plan tables)"); }
   ce = cudaMalloc((void**)&pl->d_codes, (size_t)std::max<long long>(code_bytes, 64));
   if (ce != cudaSuccess) { cudaFree(pl->d_block); delete pl; return cuda_fail(ce, "cudaMalloc(code scratch)"); }
-  pl->device_bytes = (int64_t)tot + std::max<long long>(code_bytes, 64);
+  if (optimizer != KAON_OPT_LION) {
+    ce = cudaMalloc((void**)&pl->d_aux, sizeof(float) * (size_t)std::max<long long>(aux_floats, 64));
+    if (ce != cudaSuccess) { cudaFree(pl->d_block); cudaFree(pl->d_codes); delete pl; return cuda_fail(ce, "cudaMalloc(aux scratch)"); }
+  }
+  pl->device_bytes = (int64_t)tot + std::max<long long>(code_bytes, 64) + (pl->d_aux ? 4 * std::max<long long>(aux_floats, 64) : 0);
   char* base = (char*)pl->d_block;
   std::vector<const void*> grads(n);
   for (int i = 0; i < n; ++i) grads[i] = descs[i].g;
@@ -200,8 +265,9 @@ int kaon_plan_create(kaon_plan** out, int optimizer, int param_dtype, int moment
   v.status = pl->d_counters;            // sticky: not cleared per step
   v.task_counter = pl->d_counters + 1;  // cleared per step from here on
   v.done = pl->d_counters + 2;
-  v.kept = pl->d_counters + 2 + n;
+  v.kept = pl->d_counters + 2 + 4 * n;
   v.codes = pl->d_codes;
+  v.aux = pl->d_aux;
   *out = pl;
   return KAON_OK;
 }
@@ -220,6 +286,7 @@ int kaon_plan_destroy(kaon_plan* pl) {
   if (!pl) return KAON_OK;
   cudaFree(pl->d_block);
   cudaFree(pl->d_codes);
+  cudaFree(pl->d_aux);
   delete pl;
   return KAON_OK;
 }

@@ -5,6 +5,8 @@ Drop-in for the reference's ``kaon`` classes on the fused-step path: same constr
 through a C ABI (``libkaon_b200.so``, declared in ``include/kaon_b200.h``).  CUDA tensors only.
 """
 from ._version import __version__
+from .adakaon import Adakaon
 from .lion import Lion
+from .nekaon import Nekaon
 
-__all__ = ["Lion", "__version__"]
+__all__ = ["Adakaon", "Lion", "Nekaon", "__version__"]

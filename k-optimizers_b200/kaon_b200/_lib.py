@@ -36,7 +36,10 @@ class AdakaonHParams(C.Structure):
     _fields_ = [("lr", C.c_double), ("beta1", C.c_double), ("beta2", C.c_double),
                 ("eps1", C.c_double), ("weight_decay", C.c_double), ("clip_threshold", C.c_double),
                 ("cautious", C.c_int32), ("gradient_centralization", C.c_int32),
-                ("bf16_method", C.c_int32), ("reserved", C.c_int32)]
+                ("bf16_method", C.c_int32), ("reserved", C.c_int32),
+                ("msam_remove", C.c_int32), ("msam_climb", C.c_int32),
+                ("msam_alpha_remove", C.c_double), ("msam_bound_remove", C.c_double),
+                ("msam_alpha_climb", C.c_double), ("msam_bound_climb", C.c_double)]
 
 
 class KaonError(RuntimeError):

@@ -1,0 +1,139 @@
+"""Adakaon (conv-aware factored second moment, quantised momentum) on the fused sm_100a step.
+
+Same constructor, param-group keys, state layout and errors as the reference class
+(src/kaon/adakaon.py:195-292, 318-335); ``step()`` launches one persistent CUDA kernel per parameter
+group instead of the foreach buckets (src/kaon/adakaon.py:339-383, 793-1014).  ``foreach*``, ``fused`` and
+``fused_tile_cap`` are accepted and ignored.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from collections.abc import Iterable
+from typing import Any
+
+import torch
+from torch import Tensor
+from torch.optim import Optimizer
+
+from . import _lib as L
+from ._autolr import DEFAULT_FUSE_REL, AutoLRMixin
+from ._engine import FusedStepMixin, GroupPlan, init_momentum_state
+from ._state import load_state_dict_exact
+
+__all__ = ["Adakaon"]
+
+_FOURBIT_BLOCK = 128
+FOREACH_BATCH_CUTOFF = 2_000_000
+
+
+def init_second_moment_state(p: Tensor, state: dict[str, Any]) -> None:
+    """row/col statistics of the matrixised tensor for ndim >= 2, full v for 1-D
+    (reference src/kaon/adakaon.py:318-331)."""
+    if p.ndim >= 2:
+        state["row"] = torch.zeros(p.shape[0], dtype=torch.float32, device=p.device)
+        state["col"] = torch.zeros(p.numel() // p.shape[0], dtype=torch.float32, device=p.device)
+    else:
+        state["v"] = torch.zeros(p.shape, dtype=torch.float32, device=p.device)
+
+
+class Adakaon(FusedStepMixin, AutoLRMixin, Optimizer):
+    _OPT_KIND = L.OPT_ADAKAON
+
+    def __init__(
+        self,
+        params: Iterable[Any],
+        lr: float = 1e-3,
+        betas: tuple[float, float] = (0.9, 0.999),
+        eps: tuple[float, float] = (1e-30, 1e-3),
+        weight_decay: float = 0.0,
+        *,
+        clip_threshold: float = 1.0,
+        momentum_dtype: str = "bfloat16",
+        momentum_4bit_block: int = _FOURBIT_BLOCK,
+        cautious: bool = True,
+        gradient_centralization: bool = True,
+        bf16_method: str = "stochastic_rounding",
+        foreach: bool = True,
+        foreach_batch_cutoff: int = FOREACH_BATCH_CUTOFF,
+        foreach_stack_budget: int | None = None,
+        fused: bool = False,
+        fused_tile_cap: int | None = None,
+        auto_lr: bool = False,
+        auto_lr_scale: float = 1.0,
+        auto_lr_fuse_rel: float = DEFAULT_FUSE_REL,
+        auto_lr_d0: float | None = None,
+    ) -> None:
+        beta1, beta2 = float(betas[0]), float(betas[1])
+        if not 0.0 <= beta1 < 1.0:
+            raise ValueError(f"betas[0] must be in [0, 1), got {beta1}")
+        if not 0.0 <= beta2 < 1.0:
+            raise ValueError(f"betas[1] must be in [0, 1), got {beta2}")
+        if lr < 0.0:
+            raise ValueError(f"lr must be >= 0, got {lr}")
+        if clip_threshold <= 0.0:
+            raise ValueError(f"clip_threshold must be > 0, got {clip_threshold}")
+        if momentum_dtype not in ("bfloat16", "float32", "int8", "4bit"):
+            raise ValueError(f"momentum_dtype must be bfloat16/float32/int8/4bit, got {momentum_dtype!r}")
+        if bf16_method not in ("stochastic_rounding", "kahan", "none"):
+            raise ValueError(f"bf16_method must be stochastic_rounding/kahan/none, got {bf16_method!r}")
+        if foreach_batch_cutoff < 1:
+            raise ValueError(f"foreach_batch_cutoff must be >= 1, got {foreach_batch_cutoff}")
+        defaults = {
+            "lr": lr,
+            "betas": (beta1, beta2),
+            "eps": (float(eps[0]), float(eps[1])),
+            "weight_decay": weight_decay,
+            "clip_threshold": clip_threshold,
+            "momentum_dtype": momentum_dtype,
+            "momentum_4bit_block": momentum_4bit_block,
+            "cautious": cautious,
+            "gradient_centralization": gradient_centralization,
+            "bf16_method": bf16_method,
+        }
+        super().__init__(params, defaults)
+        self._foreach = foreach
+        self._foreach_batch_cutoff = foreach_batch_cutoff
+        self._foreach_stack_budget = foreach_stack_budget
+        self._fused = bool(fused)
+        self._fused_init()
+        self._msam: dict[int, dict[str, float]] = {}  # per group id: climb/removal riding on this step
+        self._init_autolr(auto_lr, auto_lr_scale, auto_lr_fuse_rel, auto_lr_d0)
+
+    def _momentum_dtype(self, group: dict[str, Any]) -> str | None:
+        return group["momentum_dtype"] if group["betas"][0] > 0 else None
+
+    @torch.no_grad()
+    def _init_state(self, p: Tensor, state: dict[str, Any], group: dict[str, Any]) -> None:
+        init_second_moment_state(p, state)
+        if group["betas"][0] > 0:
+            init_momentum_state(state, p.grad, group["momentum_dtype"], group["momentum_4bit_block"])
+
+    def _launch(self, plan: GroupPlan, group: dict[str, Any], step: int, stream: int) -> None:
+        ms = self._msam.get(id(group), {})
+        hp = L.AdakaonHParams(
+            lr=group["lr"], beta1=group["betas"][0], beta2=group["betas"][1], eps1=group["eps"][0],
+            weight_decay=group["weight_decay"], clip_threshold=group["clip_threshold"],
+            cautious=int(bool(group["cautious"])),
+            gradient_centralization=int(bool(group["gradient_centralization"])),
+            bf16_method=L.BF16_METHOD[group["bf16_method"]], reserved=0,
+            msam_remove=int("remove" in ms), msam_climb=int("climb" in ms),
+            msam_alpha_remove=ms.get("remove", (0.0, 0.0))[0], msam_bound_remove=ms.get("remove", (0.0, 0.0))[1],
+            msam_alpha_climb=ms.get("climb", (0.0, 0.0))[0], msam_bound_climb=ms.get("climb", (0.0, 0.0))[1])
+        L.check(L.lib().kaon_adakaon_step(plan.handle, C.byref(hp), C.c_uint64(self._seed()),
+                                          C.c_uint32(step), C.c_void_p(stream)))
+
+    @torch.no_grad()
+    def _step_impl(self, closure: Any = None) -> Any:
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        self._run_groups()
+        return loss
+
+    def state_dict(self) -> dict[str, Any]:
+        return self._autolr_state_dict(super().state_dict())
+
+    def load_state_dict(self, state_dict: dict[str, Any]) -> None:
+        self._autolr_load(state_dict, lambda sd: load_state_dict_exact(self, sd))
+        self._invalidate_plans()

@@ -1,0 +1,203 @@
+"""Parity of the CUDA Adakaon / Nekaon step (through the C ABI) with the reference's golden vectors
+and the CPU oracle.  Everything here sits downstream of order-dependent fp32 reductions (row/col means,
+the clip rms, the GC row mean), so the gates are: statistics rel <= 1e-5, quantised codes within one
+level with a small flip rate, weights within one bf16 ulp ("none") or one ulp per stochastic write."""
+import numpy as np
+import pytest
+import torch
+
+import kaon_oracle as ko
+from _golden import Fixture, rel_err, sr_close, ulp_diff_bf16
+from golden.cases import CASES, SCHEDULES
+
+pytestmark = pytest.mark.gpu
+
+
+def _code_diff(md, got, want):
+    if md == "int8":
+        return np.abs(got.view(np.int8).astype(np.int32) - want.view(np.int8).astype(np.int32))
+    g8, w8 = got.view(np.uint8), want.view(np.uint8)
+    return np.maximum(np.abs((g8 & 15).astype(np.int32) - (w8 & 15)), np.abs((g8 >> 4).astype(np.int32) - (w8 >> 4)))
+
+
+def _check_against_fixture(name, writes_per_step=1):
+    from _gpu import run_case_gpu, state_np, to_bits
+    kw = CASES[name][1]
+    md = kw.get("momentum_dtype", "bfloat16")
+    sr = kw.get("bf16_method", "stochastic_rounding") == "stochastic_rounding"
+    flips = total = 0
+    last = None
+    for step, f, opt, params in run_case_gpu(name):
+        inner = getattr(opt, "base_optimizer", opt)
+        for i, p in enumerate(params):
+            st = inner.state[p]
+            for key in ("row", "col", "v"):
+                want = f.state(step, i, key)
+                if want is not None:
+                    assert rel_err(state_np(st, key), want) <= 1e-5, (step, i, key, rel_err(state_np(st, key), want))
+            want_m = f.state(step, i, "m")
+            if want_m is not None:
+                got_m = state_np(st, "m")
+                if md in ("int8", "4bit"):
+                    assert rel_err(state_np(st, "m_scale"), f.state(step, i, "m_scale").reshape(-1)) <= 1e-5, (step, i)
+                    d = _code_diff(md, got_m, want_m)
+                    assert d.max() <= 1, (step, i, int(d.max()))
+                    flips += int((d != 0).sum()); total += d.size
+                elif md == "bfloat16":
+                    assert ulp_diff_bf16(got_m, want_m).max() <= 1
+            got, want = to_bits(p), f.weights(step, i)
+            if want.dtype == np.uint16:
+                if sr or writes_per_step > 1:
+                    assert sr_close(got, want, writes_per_step * step, 1e-3), (step, i)
+                else:
+                    assert ulp_diff_bf16(got, want).max() <= 1, (step, i)
+            else:
+                np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-9)
+        last = (f, opt, params)
+    if total:
+        assert flips / total < 2e-3, (flips, total)
+    return last
+
+
+@pytest.mark.parametrize("name", ["adakaon_int8_none", "adakaon_int8_sr", "adakaon_int8_outlier",
+                                  "adakaon_4bit_wd_f32", "adakaon_bf16m_none"])
+def test_adakaon_matches_reference(name):
+    _check_against_fixture(name)
+
+
+def test_nekaon_fp32_matches_reference_including_eval():
+    from _gpu import to_bits
+    f, opt, params = _check_against_fixture("nekaon_f32")
+    opt.eval()
+    torch.cuda.synchronize()
+    for i, p in enumerate(params):
+        np.testing.assert_allclose(to_bits(p), f[f"p_eval_t{i}"], rtol=1e-5, atol=1e-9)
+    with pytest.raises(RuntimeError, match="outside train mode"):
+        opt.step()
+    opt.train()
+    torch.cuda.synchronize()
+    for i, p in enumerate(params):
+        np.testing.assert_allclose(to_bits(p), f.weights(5, i), rtol=1e-5, atol=1e-9)
+
+
+def test_nekaon_bf16_matches_reference():
+    _check_against_fixture("nekaon_bf16", writes_per_step=3)
+
+
+def test_nekaon_fused_equals_three_pass_path():
+    """The fused removal+update+climb and the three separate passes draw the same noise and must give
+    identical weights (bf16, stochastic rounding)."""
+    import kaon_b200
+    from _gpu import from_bits, to_bits
+    name = "nekaon_bf16"
+    _, kw, shapes, _, steps, _, _ = CASES[name]
+    f = Fixture(name)
+    results = []
+    for mode in ("fused", "three_pass"):
+        params = [torch.nn.Parameter(from_bits(b, s)) for b, s in zip(f.params(), shapes)]
+        opt = kaon_b200.Nekaon(params, **kw)
+        opt.sr_seed = 5
+        if mode == "three_pass":
+            opt._all_momentum_tensors_have_grads = lambda: False
+        for step in range(1, steps + 1):
+            for g in opt.param_groups:
+                g["lr"] = SCHEDULES["cosine5"](step - 1)
+            for p, gb, s in zip(params, f.grads(step), shapes):
+                p.grad = from_bits(gb, s)
+            opt.step()
+        torch.cuda.synchronize()
+        opt.check_device_status()
+        results.append([to_bits(p) for p in params])
+    for a, b in zip(*results):
+        assert np.array_equal(a, b)
+
+
+def test_c1_full_size():
+    """BASELINE config 1: Adakaon-int8 + SR, [1024,1024] + [320,320,3,3] + [1024], 10 steps."""
+    import kaon_b200
+    from _gpu import state_np
+    _, kw, shapes, _, steps, seed, o = CASES["c1_full"]
+    f = Fixture("c1_full")
+    stride = o["sample"]
+    gen = torch.Generator().manual_seed(seed)
+    params = [torch.nn.Parameter((torch.randn(s, generator=gen) * 0.02).bfloat16().cuda()) for s in shapes]
+    opt = kaon_b200.Adakaon(params, **kw)
+    opt.sr_seed = 0
+    flips = total = 0
+    for step in range(1, steps + 1):
+        gen = torch.Generator().manual_seed(seed + step)
+        for p, s in zip(params, shapes):
+            p.grad = (torch.randn(s, generator=gen) * 1e-3).bfloat16().cuda()
+        opt.step()
+        torch.cuda.synchronize()
+        opt.check_device_status()
+        for i, p in enumerate(params):
+            st = opt.state[p]
+            for key in ("row", "col", "v", "m_scale"):
+                want = f.state(step, i, key)
+                if want is None:
+                    continue
+                got = state_np(st, key).astype(np.float64)
+                err = np.abs(got - want.reshape(-1)) / np.abs(want.reshape(-1))
+                if key == "m_scale":
+                    assert np.mean(err > 5e-5) < 0.02 and err.max() < 2e-2, (step, i, err.max())
+                else:
+                    assert err.max() <= 1e-5, (step, i, key, err.max())
+            want_m = f.state(step, i, "m").view(np.int8)
+            got_m = state_np(st, "m")
+            got_m = got_m[::stride] if got_m.size > 20000 else got_m
+            d = np.abs(got_m.astype(np.int32) - want_m.astype(np.int32))
+            assert d.max() <= 1
+            flips += int((d != 0).sum()); total += d.size
+    assert flips / total < 2e-3, (flips, total)
+
+
+BIG = [(640, 2560), (320, 320, 3, 3), (1280,), (5120, 640), (333, 77), (3, 16384), (4000, 1), (7,), (96, 4100)]
+
+
+@pytest.mark.parametrize("md,wd,method", [("int8", 0.0, "stochastic_rounding"), ("4bit", 0.1, "none"),
+                                          ("bfloat16", 0.0, "none"), ("float32", 0.01, "stochastic_rounding"),
+                                          (None, 0.0, "none")])
+@pytest.mark.parametrize("dtype", ["bf16", "f32"])
+def test_adakaon_vs_oracle_bigger_shapes(md, wd, method, dtype):
+    import kaon_b200
+    from _gpu import state_np, to_bits
+    tdt = torch.bfloat16 if dtype == "bf16" else torch.float32
+    gen = torch.Generator().manual_seed(9)
+    host = [(torch.randn(s, generator=gen) * 0.02).to(tdt) for s in BIG]
+    params = [torch.nn.Parameter(h.clone().cuda()) for h in host]
+    kw = dict(lr=1e-4, betas=(0.9 if md else 0.0, 0.999), weight_decay=wd, bf16_method=method)
+    if md:
+        kw["momentum_dtype"] = md
+    opt = kaon_b200.Adakaon(params, **kw)
+    opt.sr_seed = 4
+    orc = ko.OracleAdakaon([to_bits(h) for h in host], BIG, seed=4, **kw)
+    flips = total = 0
+    for step in range(1, 4):
+        grads = [(torch.randn(s, generator=gen) * 1e-3).to(tdt) for s in BIG]
+        for p, g in zip(params, grads):
+            p.grad = g.clone().cuda()
+        opt.step()
+        torch.cuda.synchronize()
+        opt.check_device_status()
+        orc.step([to_bits(g) for g in grads])
+        (plan,) = opt._plans.values()
+        kept = plan.kept_counts(torch.cuda.current_stream().cuda_stream)
+        for i, p in enumerate(params):
+            st, ot = opt.state[p], orc.tensors[i]
+            for key in ("row", "col", "v"):
+                if key in ot.state:
+                    assert rel_err(state_np(st, key), ot.state[key]) <= 1e-5, (step, i, key, BIG[i])
+            assert abs(kept[i] - orc.kept[i]) <= max(4, 2e-3 * ot.n), (step, i, kept[i], orc.kept[i])
+            if md in ("int8", "4bit"):
+                assert rel_err(state_np(st, "m_scale"), ot.state["m_scale"]) <= 2e-5, (step, i, BIG[i])
+                d = _code_diff(md, state_np(st, "m"), ot.state["m"])
+                assert d.max() <= 1, (step, i, BIG[i])
+                flips += int((d != 0).sum()); total += d.size
+            got, want = to_bits(p), ot.p
+            if dtype == "bf16":
+                assert np.mean(got != want) < 5e-3, (step, i, BIG[i], np.mean(got != want))
+            else:
+                np.testing.assert_allclose(got, want, rtol=2e-5, atol=1e-9)
+    if total:
+        assert flips / total < 2e-3, (flips, total)
