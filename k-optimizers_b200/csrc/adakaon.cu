@@ -840,8 +840,11 @@ int configure_launch_adakaon(kaon_plan* pl, const cudaDeviceProp& prop, int max_
   pl->threads = AT;
   AdaKernel k = pick_ada(pl->param_dtype, pl->momentum_kind);
   if (!k) return fail(KAON_E_INVALID, "no Adakaon kernel for this dtype combination");
-  if (pl->smem_bytes > (size_t)prop.sharedMemPerBlockOptin - 40 * 1024)
-    return fail(KAON_E_UNSUPPORTED, "Adakaon kernel needs %zu bytes of shared memory for rows of %d elements", pl->smem_bytes, max_cols);
+  cudaFuncAttributes fa;
+  KAON_CUDA(cudaFuncGetAttributes(&fa, (const void*)k));
+  if (pl->smem_bytes + fa.sharedSizeBytes > (size_t)prop.sharedMemPerBlockOptin)
+    return fail(KAON_E_UNSUPPORTED, "Adakaon kernel needs %zu + %zu bytes of shared memory for rows of %d elements (limit %zu)",
+                pl->smem_bytes, (size_t)fa.sharedSizeBytes, max_cols, (size_t)prop.sharedMemPerBlockOptin);
   KAON_CUDA(cudaFuncSetAttribute((const void*)k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl->smem_bytes));
   int per_sm = 1;
   KAON_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, (const void*)k, AT, pl->smem_bytes));

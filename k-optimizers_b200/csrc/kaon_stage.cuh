@@ -58,11 +58,21 @@ __device__ __forceinline__ void fence_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
-// Copy `bytes` from global to shared: the 16-byte-multiple head through the bulk engine (thread 0
-// issues it; completion lands on `bar`), the tail of < 16 bytes with plain byte loads by the first
-// threads.  Call with all threads; returns the bytes the barrier must expect (0 if none).
+// Copy `bytes` from global to shared.  Source 16-byte aligned: the 16-byte-multiple head goes through
+// the bulk engine (the caller's thread 0 issues it; completion lands on the barrier) and the tail of
+// < 16 bytes is copied with plain loads.  Source only 8-byte aligned (a run of int8 / bf16 momentum that
+// starts on an odd 8-element group): everything is copied with plain 8-byte loads.  Call with all
+// threads; returns the bytes the bulk engine must move (0 if none).
 __device__ __forceinline__ unsigned stage_tail(unsigned char* dst, const unsigned char* src,
                                                unsigned bytes, int tid) {
+  if (reinterpret_cast<uintptr_t>(src) & 15) {
+    const unsigned words = bytes >> 3;
+    for (unsigned i = tid; i < words; i += blockDim.x)
+      reinterpret_cast<uint2*>(dst)[i] = reinterpret_cast<const uint2*>(src)[i];
+    const unsigned done = words << 3;
+    if ((unsigned)tid < bytes - done) dst[done + tid] = src[done + tid];
+    return 0u;
+  }
   unsigned head = bytes & ~15u;
   unsigned tail = bytes - head;
   if ((unsigned)tid < tail) dst[head + tid] = src[head + tid];

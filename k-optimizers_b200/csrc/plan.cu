@@ -34,7 +34,7 @@ static long long gcd_ll(long long a, long long b) { return b ? gcd_ll(b, a % b) 
 
 // Element alignment every work item must start on so that vector loads, the bulk copies of the
 // momentum bytes and the 4-bit blocks line up.
-static int align_unit(int momentum_kind) { return momentum_kind == KAON_M_4BIT ? 128 : 16; }
+static int align_unit(int momentum_kind) { return momentum_kind == KAON_M_4BIT ? 128 : 8; }
 
 size_t momentum_bytes_per_cap(int mk) {
   switch (mk) {
