@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import subprocess
 import sys
@@ -23,13 +24,22 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(ROOT, "k-optimizers_b200"))
 
 WORKLOADS = {
-    # name: (optimizer, kwargs, shape list, algorithmic bytes per parameter)
-    # Lion-4bit: g 2 + p 2+2 + m 0.5+0.5 + scales 2*4/128
+    # optimizer, constructor kwargs, shape list, algorithmic bytes per parameter, options
+    # Lion-4bit (BASELINE config 2): g 2 + p 2+2 + m 0.5+0.5 + scales 2*4/128
     "lion4bit_unet2p6b": ("Lion", dict(lr=2e-4, betas=(0.95, 0.98), momentum_dtype="4bit", cautious=True),
-                          "unet_2p6b", 7.0625),
+                          "unet_2p6b", 7.0625, {}),
     "lion4bit_sample": ("Lion", dict(lr=2e-4, betas=(0.95, 0.98), momentum_dtype="4bit", cautious=True),
-                        "unet_sample", 7.0625),
+                        "unet_sample", 7.0625, {}),
+    # Adakaon-int8 (config 3): g 2 + p 2+2 + m 1+1 + row scales, row/col stats, 1-D v; 1 % of grads x100
+    "adakaon_int8_unet2p6b": ("Adakaon", dict(lr=1e-4, betas=(0.9, 0.999), momentum_dtype="int8"),
+                              "unet_2p6b", 8.015, {"outlier": True}),
+    "adakaon_int8_sample": ("Adakaon", dict(lr=1e-4, betas=(0.9, 0.999), momentum_dtype="int8"),
+                            "unet_sample", 8.015, {"outlier": True}),
+    # Nekaon-4bit (config 4): as Lion-4bit + stats; climb and removal ride on the same weight access
+    "nekaon4bit_unet2p6b": ("Nekaon", dict(lr=1e-4, betas=(0.2, 0.999)), "unet_2p6b", 7.073, {"cosine": (1e-4, 1e-5, 50)}),
+    "nekaon4bit_sample": ("Nekaon", dict(lr=1e-4, betas=(0.2, 0.999)), "unet_sample", 7.073, {"cosine": (1e-4, 1e-5, 50)}),
 }
+KERNEL_NAME = {"Lion": "lion_kernel<bf16,4bit>", "Adakaon": "adakaon_kernel<bf16,int8>", "Nekaon": "adakaon_kernel<bf16,4bit>"}
 
 
 def measured_peaks():
@@ -89,7 +99,7 @@ def cpu_baseline(workload: str, steps: int = 2):
     import numpy as np
     import kaon_oracle as ko
     from kaon_b200 import workloads as W
-    opt_name, kw, _, _ = WORKLOADS[workload]
+    opt_name, kw, _, _, _ = WORKLOADS[workload]
     shapes = W.unet_sample()
     n = W.numel(shapes)
     rng = np.random.default_rng(0)
@@ -144,7 +154,7 @@ def run_ours(args):
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    opt_name, kw, shape_key, bytes_per_param = WORKLOADS[args.workload]
+    opt_name, kw, shape_key, bytes_per_param, wopt = WORKLOADS[args.workload]
     shapes = W.WORKLOADS[shape_key]()
     total = W.numel(shapes)
     sw = ShardedWeights(shapes, world, rank, torch.bfloat16, dev)
@@ -156,7 +166,10 @@ def run_ours(args):
     # two gradient sets, alternated per step (a real loop reallocates grads: set_to_none=True)
     gsets = []
     for k in range(2):
-        flat_g = (torch.randn(sw.part.shard_len, generator=gen, device=dev) * 1e-3).to(torch.bfloat16)
+        flat_g = torch.randn(sw.part.shard_len, generator=gen, device=dev) * 1e-3
+        if wopt.get("outlier"):
+            flat_g = torch.where(torch.rand(sw.part.shard_len, generator=gen, device=dev) < 0.01, flat_g * 100.0, flat_g)
+        flat_g = flat_g.to(torch.bfloat16)
         gsets.append((flat_g, [flat_g[sw.part.offset[i]:sw.part.offset[i] + sw.views[i].numel()].view(shapes[i]) for i in owned]))
     params = []
     for i in owned:
@@ -166,8 +179,13 @@ def run_ours(args):
     opt = getattr(kaon_b200, opt_name)(params, **kw)
     opt.sr_seed = 0
 
+    cos = wopt.get("cosine")
+
     def one_step(k, ev=None):
         gv = gsets[k & 1][1]
+        if cos:
+            for grp in opt.param_groups:
+                grp["lr"] = cos[1] + 0.5 * (cos[0] - cos[1]) * (1.0 + math.cos(math.pi * (k % cos[2]) / cos[2]))
         for p, g in zip(params, gv):
             p.grad = g
         if ev:
@@ -268,7 +286,7 @@ def run_ours(args):
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "frac_of_nominal_8TBs": achieved / 8000.0,
                          "peak_kind": f"{peak_kind} copy bandwidth", "traffic": None,
-                         "bytes_per_param": bytes_per_param, "kernel": "lion_kernel<bf16,4bit>"},
+                         "bytes_per_param": bytes_per_param, "kernel": KERNEL_NAME[opt_name]},
             "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
         }
         if world == 1 and not args.no_cpu:
