@@ -127,6 +127,20 @@ int kaon_plan_kept_counts(kaon_plan* plan, uint32_t* host_out, int n, void* stre
 int kaon_lion_step(kaon_plan* plan, const kaon_lion_hparams* hp, uint64_t seed, uint32_t step,
                    void* stream);
 
+/* One Lion step over ONE tensor that allocates nothing (no counterpart in the reference: it exists for
+ * callers that may not call cudaMalloc where they step the optimizer - code under a memory pool it must
+ * not disturb, launch-only real-time paths, hosts that own every allocation).  Same arithmetic and the
+ * same kernel as kaon_lion_step, but the table, work list, counters and code scratch that
+ * kaon_plan_create would allocate live in a device array built into the library (about 1.3 MiB on every
+ * GPU that loads it).  `tensor` is a HOST struct; weights, gradient, momentum (4-bit, block 128 or one
+ * block for <= 128 elements) and m_scale must be set; numel <= KAON_NOALLOC_MAX_NUMEL, else
+ * KAON_E_UNSUPPORTED.  Calls no cudaMalloc/cudaFree.  The first call on a device resolves the array's
+ * address and configures the kernel: make it before any stream capture.  All calls on a device share
+ * the array: calls whose kernels overlap on the GPU race; calls ordered on one stream do not. */
+#define KAON_NOALLOC_MAX_NUMEL (1 << 22)
+int kaon_lion_step_noalloc(const kaon_tensor_desc* tensor, int param_dtype, const kaon_lion_hparams* hp,
+                           uint64_t seed, uint32_t step, void* stream);
+
 /* One Adakaon step.  Replaces Adakaon._step_impl / _factored_bucket / _nonfactored_bucket /
  * _step_one_param (src/kaon/adakaon.py:339-383, 840-1014), update_factored_state and
  * factored_inv_sqrt_factors (src/kaon/_factored.py:26-83), the codec EMA

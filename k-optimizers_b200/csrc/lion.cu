@@ -452,3 +452,187 @@ extern "C" int kaon_lion_step(kaon_plan* pl, const kaon_lion_hparams* h, uint64_
   pl->launches += 1;
   return KAON_OK;
 }
+
+// ---------------------------------------------------------------------------------------------------
+// Lion step for ONE tensor that allocates nothing.
+//
+// Some callers cannot call cudaMalloc at the point where they step the optimizer: code that runs
+// under a memory pool it must not disturb, a real-time or fault-handling path that may only launch
+// work, a host framework that hands this library raw pointers but keeps every allocation for itself.
+// kaon_plan_create allocates the descriptor table, the work list, the counters and the 2-bit code
+// scratch with cudaMalloc; the entry point below needs none of that.  Its table, work list, counters and
+// code scratch live in the file-scope device array g_noalloc, which every GPU that loads this library
+// holds (about 1.3 MiB) until the process exits; a small set-up kernel fills it from the call's
+// arguments, then the same persistent kernel as kaon_lion_step runs over it.
+//
+// Limits and rules: one tensor per call, at most KAON_NOALLOC_MAX_NUMEL elements, 4-bit momentum
+// (block 128, or one block for a tensor of <= 128 elements), bf16 or fp32 weights.  All calls on a
+// device share the array, and it keeps what the last call left there: the set-up kernel rewrites every
+// field the step reads and zeroes the counters, so calls that follow each other on one stream are
+// independent, but two calls whose kernels overlap on the GPU (different streams) race on it.  The
+// first call on a device looks the array's address up and configures the kernel (no allocation, but
+// synchronous driver work); make that first call outside any stream capture.
+// ---------------------------------------------------------------------------------------------------
+namespace kaon {
+
+constexpr long long NOALLOC_MAX_NUMEL = KAON_NOALLOC_MAX_NUMEL;
+constexpr int NOALLOC_MAX_ITEMS = 4096;  // work items per phase
+constexpr size_t NA_OFF_COUNTERS = 0;    // status @0, task counter @64, done @68, kept @72
+constexpr size_t NA_OFF_TENSOR = 256;
+constexpr size_t NA_OFF_GRAD = 512;
+constexpr size_t NA_OFF_TASKS = 1024;
+constexpr size_t NA_OFF_CODES = NA_OFF_TASKS + 2 * (size_t)NOALLOC_MAX_ITEMS * sizeof(Task);
+constexpr size_t NA_BYTES = NA_OFF_CODES + (size_t)NOALLOC_MAX_NUMEL / 4 + 256;
+
+static __device__ __align__(256) unsigned char g_noalloc[NA_BYTES];
+
+// Fills the table, the gradient pointer, the work list (all MAIN items, then all APPLY items) and
+// clears the counters.  Device code names the array directly.
+__global__ void noalloc_setup_kernel(DevTensor d, const void* grad, long long item_elems, int item_rows,
+                                     int n_items) {
+  unsigned* counters = reinterpret_cast<unsigned*>(g_noalloc + NA_OFF_COUNTERS);
+  Task* tasks = reinterpret_cast<Task*>(g_noalloc + NA_OFF_TASKS);
+  if (threadIdx.x == 0) {
+    *reinterpret_cast<DevTensor*>(g_noalloc + NA_OFF_TENSOR) = d;
+    *reinterpret_cast<const void**>(g_noalloc + NA_OFF_GRAD) = grad;
+    counters[16] = 0u;  // task counter
+    counters[17] = 0u;  // done
+    counters[18] = 0u;  // kept
+  }
+  for (int i = threadIdx.x; i < n_items; i += blockDim.x) {
+    const long long e0 = (long long)i * item_elems;
+    Task t;
+    t.tensor = 0;
+    t.phase = PH_LION_MAIN;
+    t.e0 = e0;
+    t.n = (int)min(item_elems, d.numel - e0);
+    t.row0 = i * item_rows;
+    t.slot = 0;
+    t.pad = 0;
+    tasks[i] = t;
+    t.phase = PH_LION_APPLY;
+    tasks[n_items + i] = t;
+  }
+}
+
+struct NoAllocDevice {
+  bool ready = false;
+  unsigned char* base = nullptr;  // device address of g_noalloc on this device
+  int grid[2] = {0, 0};           // per param dtype
+  size_t smem[2] = {0, 0};
+};
+static NoAllocDevice g_na_dev[64];
+
+// Once per device, with that device current: the array's name is a host-side stand-in, so the address
+// the kernels get must come from cudaGetSymbolAddress.
+static int noalloc_setup_device(int dev) {
+  NoAllocDevice& nd = g_na_dev[dev];
+  void* ptr = nullptr;
+  cudaError_t ce = cudaGetSymbolAddress(&ptr, g_noalloc);
+  if (ce != cudaSuccess) return cuda_fail(ce, "cudaGetSymbolAddress(g_noalloc)");
+  if (!ptr) return fail(KAON_E_CUDA, "cudaGetSymbolAddress(g_noalloc) returned a null address");
+  cudaDeviceProp prop;
+  KAON_CUDA(cudaGetDeviceProperties(&prop, dev));
+  for (int pdt = 0; pdt < 2; ++pdt) {
+    LionKernel k = pick_lion(pdt, KAON_M_4BIT);
+    nd.smem[pdt] = (size_t)CAP * (pdt == KAON_DT_BF16 ? 2 : 4) + momentum_bytes_per_cap(KAON_M_4BIT);
+    KAON_CUDA(cudaFuncSetAttribute((const void*)k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)nd.smem[pdt]));
+    int per_sm = 0;
+    KAON_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, (const void*)k, NTHREADS, nd.smem[pdt]));
+    if (per_sm < 1) return fail(KAON_E_UNSUPPORTED, "Lion kernel does not fit on an SM");
+    nd.grid[pdt] = prop.multiProcessorCount * per_sm;
+  }
+  nd.base = reinterpret_cast<unsigned char*>(ptr);
+  nd.ready = true;
+  return KAON_OK;
+}
+
+}  // namespace kaon
+
+extern "C" int kaon_lion_step_noalloc(const kaon_tensor_desc* t, int param_dtype, const kaon_lion_hparams* h,
+                                      uint64_t seed, uint32_t step, void* stream) {
+  if (!t || !h) return fail(KAON_E_INVALID, "kaon_lion_step_noalloc: null argument");
+  if (param_dtype != KAON_DT_F32 && param_dtype != KAON_DT_BF16) return fail(KAON_E_INVALID, "param_dtype %d", param_dtype);
+  if (h->bf16_method != KAON_W_NONE && h->bf16_method != KAON_W_SR) return fail(KAON_E_UNSUPPORTED, "bf16_method %d", h->bf16_method);
+  if (!t->p || !t->g || !t->m || !t->m_scale) return fail(KAON_E_INVALID, "kaon_lion_step_noalloc: weights, gradient, momentum and m_scale must all be set");
+  if (((uintptr_t)t->p | (uintptr_t)t->g | (uintptr_t)t->m) & 15) return fail(KAON_E_INVALID, "kaon_lion_step_noalloc: pointers must be 16-byte aligned");
+  const long long n = t->numel;
+  if (n <= 0) return n == 0 ? KAON_OK : fail(KAON_E_INVALID, "negative numel");
+  if (n > NOALLOC_MAX_NUMEL)
+    return fail(KAON_E_UNSUPPORTED, "kaon_lion_step_noalloc: %lld elements exceed the built-in scratch (KAON_NOALLOC_MAX_NUMEL = %lld); use a plan (kaon_plan_create + kaon_lion_step) for larger tensors", n, NOALLOC_MAX_NUMEL);
+  if (!(t->block == 128 || ((long long)t->block == n && n <= 128)))
+    return fail(KAON_E_UNSUPPORTED, "kaon_lion_step_noalloc: 4-bit block size %u (numel %lld) is not handled", t->block, n);
+  // work items: the same cut as a plan makes (whole rows, each item starting on a 4-bit block boundary)
+  long long item_elems;
+  int item_rows = 0;
+  long long C = n;
+  if (t->rows > 0) {
+    C = n / t->rows;
+    if (C * t->rows != n || t->rows > 0x7fffffffll) return fail(KAON_E_INVALID, "numel %lld not divisible by rows %lld", n, (long long)t->rows);
+    if (n <= CAP && t->rows <= MAX_TASK_ROWS) {
+      item_elems = n; item_rows = (int)t->rows;
+    } else {
+      long long g = C, b = 128;
+      while (b) { long long r = g % b; g = b; b = r; }
+      const long long unit = 128 / g;
+      long long rpt = (CAP / C) / unit * unit;
+      rpt = std::min<long long>(rpt, MAX_TASK_ROWS / unit * unit);
+      if (rpt <= 0) return fail(KAON_E_UNSUPPORTED, "kaon_lion_step_noalloc: rows of %lld elements cannot be cut into block-aligned work items", C);
+      item_rows = (int)rpt; item_elems = rpt * C;
+    }
+  } else {
+    item_elems = CAP;
+  }
+  const long long n_items = (n + item_elems - 1) / item_elems;
+  if (n_items > NOALLOC_MAX_ITEMS) return fail(KAON_E_UNSUPPORTED, "kaon_lion_step_noalloc: %lld work items exceed the built-in work list (%d)", n_items, NOALLOC_MAX_ITEMS);
+
+  int dev = 0;
+  KAON_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(KAON_E_UNSUPPORTED, "device index %d", dev);
+  if (!g_na_dev[dev].ready) {
+    int rc = noalloc_setup_device(dev);
+    if (rc) return rc;
+  }
+  const NoAllocDevice& nd = g_na_dev[dev];
+
+  DevTensor d{};
+  d.p = t->p; d.m = t->m; d.m_scale = t->m_scale;
+  d.numel = n; d.code_off = 0;
+  d.rows = (int)t->rows;
+  d.cols = (int)std::min<long long>(C, 0x7fffffff);
+  d.row_magic = d.cols > 1 ? (unsigned)((0x100000000ull + (unsigned)d.cols - 1) / (unsigned)d.cols) : 0u;
+  d.tensor_id = t->tensor_id; d.block = t->block;
+  d.n_main = (int)n_items;
+
+  LionDev hp;
+  hp.lr = (float)h->lr;
+  hp.b1 = (float)h->beta1; hp.w1 = (float)(1.0 - h->beta1);
+  hp.b2 = (float)h->beta2; hp.w2 = (float)(1.0 - h->beta2);
+  hp.wd = (float)h->weight_decay;
+  hp.has_wd = h->weight_decay != 0.0;
+  hp.cautious = h->cautious != 0;
+  hp.gc = h->gradient_centralization != 0;
+  hp.sr = h->bf16_method == KAON_W_SR && param_dtype == KAON_DT_BF16;
+  hp.step = step; hp.k0 = (uint32_t)seed; hp.k1 = (uint32_t)(seed >> 32);
+
+  unsigned* counters = reinterpret_cast<unsigned*>(nd.base + NA_OFF_COUNTERS);
+  PlanView v{};
+  v.tensors = reinterpret_cast<const DevTensor*>(nd.base + NA_OFF_TENSOR);
+  v.grads = reinterpret_cast<const void* const*>(nd.base + NA_OFF_GRAD);
+  v.tasks = reinterpret_cast<const Task*>(nd.base + NA_OFF_TASKS);
+  v.n_tasks = (int)(hp.cautious ? 2 * n_items : n_items);
+  v.n_tensors = 1;
+  v.status = counters;
+  v.task_counter = counters + 16;
+  v.done = counters + 17;
+  v.kept = counters + 18;
+  v.aux = nullptr;
+  v.codes = nd.base + NA_OFF_CODES;
+  cudaStream_t s = (cudaStream_t)stream;
+  noalloc_setup_kernel<<<1, 256, 0, s>>>(d, t->g, item_elems, item_rows, (int)n_items);
+  KAON_CUDA(cudaGetLastError());
+  LionKernel k = pick_lion(param_dtype, KAON_M_4BIT);
+  k<<<nd.grid[param_dtype], NTHREADS, nd.smem[param_dtype], s>>>(v, hp);
+  KAON_CUDA(cudaGetLastError());
+  return KAON_OK;
+}
