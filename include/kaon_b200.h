@@ -93,6 +93,11 @@ typedef struct kaon_adakaon_hparams {
   double msam_alpha_remove, msam_bound_remove, msam_alpha_climb, msam_bound_climb;
 } kaon_adakaon_hparams;
 
+typedef struct kaon_adamuon_hparams {
+  double lr, beta1, beta2, eps1, weight_decay, clip_threshold;
+  int32_t ns_steps, cautious, gradient_centralization, bf16_method;
+} kaon_adamuon_hparams;
+
 /* ---- library ---- */
 int kaon_abi_version(void);
 const char* kaon_last_error(void); /* message of the calling thread's last failed call */
@@ -149,12 +154,35 @@ int kaon_lion_step_noalloc(const kaon_tensor_desc* tensor, int param_dtype, cons
 int kaon_adakaon_step(kaon_plan* plan, const kaon_adakaon_hparams* hp, uint64_t seed, uint32_t step,
                       void* stream);
 
+/* One AdaMuon step.  Replaces AdaMuon._run_step / _factored_bucket / _nonfactored_bucket /
+ * _step_one_param (src/kaon/adamuon.py:327-352, 434-615): per >=2-D tensor the EMA of the raw gradient
+ * through the codec, Newton-Schulz of the fp32 momentum (tcgen05 GEMMs), factored second moment of the
+ * orthogonalised signal, clip, 0.2*lr scale, weight decay, cautious mask against the raw gradient,
+ * weight write; 1-D tensors take the Adam-style branch.  `workspace` (device, 256-byte aligned, at least
+ * kaon_adamuon_workspace_bytes(plan)) holds the orthogonalised matrices between the kernels; the caller
+ * owns it and may reuse it between steps and plans. */
+int64_t kaon_adamuon_workspace_bytes(const kaon_plan* plan);
+/* Byte offset, inside the workspace, of tensor `tensor`'s orthogonalised matrix (bf16 [rows, cols]) as
+ * the last step left it; -1 for 1-D tensors.  Diagnostic: lets a test feed the same matrix to the oracle. */
+int64_t kaon_adamuon_signal_offset(const kaon_plan* plan, int tensor);
+int kaon_adamuon_step(kaon_plan* plan, const kaon_adamuon_hparams* hp, void* workspace,
+                      int64_t workspace_bytes, uint64_t seed, uint32_t step, void* stream);
+
 /* Nekaon climb / removal / eval / train swap over every tensor of the plan that has a momentum:
  * p += clamp(nan_to_num(decode(m_stored) * (float)alpha), +-(float)bound), stochastic rounding for
  * bf16 weights (stream tag `tag`), plain add for fp32.  Replaces MSAM._apply with norm="none"
  * (src/kaon/msam.py:201-235) and _axpy_4bit_batched (src/kaon/_fused_triton.py:1145-1179). */
 int kaon_msam_apply(kaon_plan* plan, double alpha, double bound, uint32_t tag, uint64_t seed,
                     uint32_t step, void* stream);
+
+/* ---- Newton-Schulz orthogonalisation (zeropower_via_newtonschulz5, src/kaon/adamuon.py:97-149) ----
+ * x_bf16 [rows, cols] (bf16, row-major, unnormalised) -> out_bf16 [rows, cols]: X = x/(||x||_F + 1e-7),
+ * steps x { A = X X^T; B = b A + c A A; X = a X + B X } as tcgen05 bf16 GEMMs with fp32 accumulation.
+ * The workspace (256-byte aligned, kaon_newton_schulz_workspace_bytes) holds the iterates; its first
+ * word is the call's device status (non-zero: a bounded wait ran out).  out may not alias x. */
+int64_t kaon_newton_schulz_workspace_bytes(int64_t rows, int64_t cols);
+int kaon_newton_schulz(const void* x_bf16, int64_t rows, int64_t cols, int steps, void* out_bf16,
+                       void* workspace, int64_t workspace_bytes, void* stream);
 
 /* ---- standalone codec (src/kaon/_momentum_codec.py:72-189; CodecBuffer.read/write,
  *      src/kaon/_wrappers.py:56-168) ---- */

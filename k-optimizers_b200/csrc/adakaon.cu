@@ -13,18 +13,14 @@
 //     of the previous climb and the new climb ride on the same read and write of each weight.
 // 1-D tensor: FLAT, the whole tensor in one work item.
 // Every cross-item sum is taken in a fixed order: results do not depend on scheduling.
+#include <type_traits>
+
+#include "adakaon_dev.h"
 #include "kaon_host.h"
 #include "kaon_ops.cuh"
 
 namespace kaon {
 
-struct AdaDev {
-  float w1, w1m1, w2, w2m1, eps1, clip, lrwd, upd_scale;
-  int small_w1, small_w2, has_eps, has_wd, cautious, gc, sr, has_m;
-  int remove, climb;
-  float a_remove, b_remove, a_climb, b_climb;
-  uint32_t step, k0, k1;
-};
 
 constexpr int AT = ADA_THREADS;
 
@@ -188,15 +184,19 @@ struct AdaSmem {
   double* red;       // [AT/32]
 };
 
-template <typename PT>
+// ST = element type of the signal whose second moment is tracked: the gradient (Adakaon) or the
+// orthogonalised momentum in bf16 (AdaMuon, `pv.signal`).
+template <typename ST>
 __device__ void ada_stats(const PlanView& pv, const AdaDev& hp, const Task& t, Stage& st,
                           const AdaSmem& sm, int tid) {
-  using E = Elems<PT>;
+  using E = Elems<ST>;
+  using PT = ST;
   const DevTensor d = pv.tensors[t.tensor];
   const unsigned char* g = reinterpret_cast<const unsigned char*>(pv.grads[t.tensor]);
+  if (g != nullptr && pv.signal != nullptr) g = reinterpret_cast<const unsigned char*>(pv.signal[t.tensor]);
   const int C = d.cols;
   const int nrows = t.n / C;
-  const bool gc = hp.gc != 0;
+  const bool gc = hp.gc != 0 && pv.signal == nullptr;
   bool ok = g != nullptr;
   float* acc1 = sm.x_s;       // sum_i (g^2 + eps1)
   float* acc2 = sm.x_s + C;   // sum_i g^2 / row_i
@@ -335,12 +335,21 @@ __device__ __forceinline__ float ema_of(float m_old, float u, const AdaDev& hp) 
   return lerp_torch(m_old, u, hp.w1, hp.w1m1, hp.small_w1 != 0);
 }
 
-template <typename PT, int MK, bool APPLY>
+// MUON (AdaMuon's factored tensors): the signal is the orthogonalised momentum O (bf16, `pv.signal`), the
+// momentum itself was already updated by the EMA pre-pass (so the chain carries none: delta = u), and
+// the cautious mask compares delta with the RAW gradient, which is staged where the momentum bytes go
+// otherwise (reference src/kaon/adamuon.py:460-497, 605-613).
+template <typename PT, int MKP, bool APPLY, bool MUON>
 __device__ void ada_rows(const PlanView& pv, const AdaDev& hp, const Task& t, Stage& st,
                          const AdaSmem& sm, int tid) {
   using E = Elems<PT>;
+  using S = Elems<typename std::conditional<MUON, __nv_bfloat16, PT>::type>;
+  using ST = typename std::conditional<MUON, __nv_bfloat16, PT>::type;
+  constexpr int MK = MUON ? KAON_M_NONE : MKP;
   const DevTensor d = pv.tensors[t.tensor];
   const unsigned char* g = reinterpret_cast<const unsigned char*>(pv.grads[t.tensor]);
+  const unsigned char* sig = g;
+  if (MUON && g != nullptr) sig = reinterpret_cast<const unsigned char*>(pv.signal[t.tensor]);
   if (g == nullptr) {
     if (!APPLY) {
       __syncthreads();
@@ -357,7 +366,7 @@ __device__ void ada_rows(const PlanView& pv, const AdaDev& hp, const Task& t, St
   ok = __syncthreads_and(ok) != 0;
   const int C = d.cols;
   const int nrows = t.n / C;
-  const bool gc = hp.gc != 0;
+  const bool gc = hp.gc != 0 && !MUON;
   const float* scal = pv.aux + aux_scal(d);
   const float rowmean = __ldcg(scal + 0);
   Chain ch;
@@ -389,7 +398,8 @@ __device__ void ada_rows(const PlanView& pv, const AdaDev& hp, const Task& t, St
     const int nrc = min(d.chunk_rows, nrows - c0);
     const int n = nrc * C;
     const long long e0 = t.e0 + (long long)c0 * C;
-    ok = stage_in(st, g + e0 * E::BYTES, (unsigned)n * E::BYTES, m_ptr<MK>(d, e0), m_bytes<MK>(n), pv.status, tid);
+    if (MUON) ok = stage_in(st, sig + e0 * S::BYTES, (unsigned)n * S::BYTES, g + e0 * E::BYTES, (unsigned)n * E::BYTES, pv.status, tid);
+    else ok = stage_in(st, g + e0 * E::BYTES, (unsigned)n * E::BYTES, m_ptr<MK>(d, e0), m_bytes<MK>(n), pv.status, tid);
     if (!ok) break;
     for (int r = warp; r < nrc; r += AT / 32) {
       const float mu = gc ? row_mean<PT>(st.g_s + (size_t)r * C * E::BYTES, C, lane) : 0.0f;
@@ -411,7 +421,9 @@ __device__ void ada_rows(const PlanView& pv, const AdaDev& hp, const Task& t, St
     // One vector of the chain: fills g', the new momentum mn[], the pre-update weights pc[] (after the
     // Nekaon removal) and delta dl[]; returns the kept bits.
     auto chain8 = [&](int v, int cnt, float gv[8], float mo[8], float mn[8], float pc[8], float dl[8]) -> unsigned {
-      load8_guard<PT>(st.g_s + (size_t)v * 8 * E::BYTES, cnt, gv);
+      load8_guard<ST>(st.g_s + (size_t)v * 8 * S::BYTES, cnt, gv);
+      float raw[8];  // MUON: the raw gradient, the cautious mask's reference
+      if (MUON) load8_guard<PT>(st.m_s + (size_t)v * 8 * E::BYTES, cnt, raw);
       int rl[8];
 #pragma unroll
       for (int k = 0; k < 8; ++k) rl[k] = row_uniform ? row_of((unsigned)v * 8u, d) : row_of((unsigned)(v * 8 + min(k, max(cnt - 1, 0))), d);
@@ -451,7 +463,7 @@ __device__ void ada_rows(const PlanView& pv, const AdaDev& hp, const Task& t, St
         mn[k] = (k < cnt) ? ema_of<MK>(mo[k], u, hp) : 0.0f;
         const float dv = hp.has_wd ? __fmaf_rn(pc[k], hp.lrwd, mn[k]) : mn[k];
         dl[k] = dv;
-        if (k < cnt && __fmul_rn(dv, x) > 0.0f) kept |= 1u << k;
+        if (k < cnt && __fmul_rn(dv, MUON ? raw[k] : x) > 0.0f) kept |= 1u << k;
       }
       return kept;
     };
@@ -717,7 +729,7 @@ __device__ void ada_flat(const PlanView& pv, const AdaDev& hp, const Task& t, St
 
 // ----------------------------------------------------------------------------- kernels
 
-template <typename PT, int MK>
+template <typename PT, int MK, bool MUON>
 __global__ void __launch_bounds__(AT, 1) adakaon_kernel(PlanView pv, AdaDev hp, int x_off_rows) {
   extern __shared__ __align__(128) unsigned char dyn[];
   __shared__ float mean_s[MAX_TASK_ROWS];
@@ -748,10 +760,10 @@ __global__ void __launch_bounds__(AT, 1) adakaon_kernel(PlanView pv, AdaDev hp, 
     claim_next(slot ^ 1);
     const Task t = pv.tasks[cur];
     switch (t.phase) {
-      case PH_ADA_STATS: ada_stats<PT>(pv, hp, t, st, sm_stats, tid); break;
+      case PH_ADA_STATS: ada_stats<typename std::conditional<MUON, __nv_bfloat16, PT>::type>(pv, hp, t, st, sm_stats, tid); break;
       case PH_ADA_FINAL: ada_final(pv, hp, t, sm_stats, tid); break;
-      case PH_ADA_COUNT: ada_rows<PT, MK, false>(pv, hp, t, st, sm_rows, tid); break;
-      case PH_ADA_APPLY: ada_rows<PT, MK, true>(pv, hp, t, st, sm_rows, tid); break;
+      case PH_ADA_COUNT: ada_rows<PT, MK, false, MUON>(pv, hp, t, st, sm_rows, tid); break;
+      case PH_ADA_APPLY: ada_rows<PT, MK, true, MUON>(pv, hp, t, st, sm_rows, tid); break;
       case PH_ADA_FLAT: ada_flat<PT, MK>(pv, hp, t, st, sm_rows, tid); break;
       default: break;
     }
@@ -801,22 +813,22 @@ __global__ void __launch_bounds__(256) msam_axpy_kernel(PlanView pv, float alpha
   }
 }
 
-typedef void (*AdaKernel)(PlanView, AdaDev, int);
 typedef void (*AxpyKernel)(PlanView, float, float, SrStream);
 
-template <typename PT>
+template <typename PT, bool MUON>
 static AdaKernel pick_ada_pt(int mk) {
   switch (mk) {
-    case KAON_M_F32: return adakaon_kernel<PT, KAON_M_F32>;
-    case KAON_M_BF16: return adakaon_kernel<PT, KAON_M_BF16>;
-    case KAON_M_INT8: return adakaon_kernel<PT, KAON_M_INT8>;
-    case KAON_M_4BIT: return adakaon_kernel<PT, KAON_M_4BIT>;
-    case KAON_M_NONE: return adakaon_kernel<PT, KAON_M_NONE>;
+    case KAON_M_F32: return adakaon_kernel<PT, KAON_M_F32, MUON>;
+    case KAON_M_BF16: return adakaon_kernel<PT, KAON_M_BF16, MUON>;
+    case KAON_M_INT8: return adakaon_kernel<PT, KAON_M_INT8, MUON>;
+    case KAON_M_4BIT: return adakaon_kernel<PT, KAON_M_4BIT, MUON>;
+    case KAON_M_NONE: return adakaon_kernel<PT, KAON_M_NONE, MUON>;
     default: return nullptr;
   }
 }
-static AdaKernel pick_ada(int pdt, int mk) {
-  return pdt == KAON_DT_BF16 ? pick_ada_pt<__nv_bfloat16>(mk) : pick_ada_pt<float>(mk);
+AdaKernel pick_ada(int pdt, int mk, bool muon) {
+  if (muon) return pdt == KAON_DT_BF16 ? pick_ada_pt<__nv_bfloat16, true>(mk) : pick_ada_pt<float, true>(mk);
+  return pdt == KAON_DT_BF16 ? pick_ada_pt<__nv_bfloat16, false>(mk) : pick_ada_pt<float, false>(mk);
 }
 
 template <typename PT>
@@ -830,15 +842,20 @@ static AxpyKernel pick_axpy_pt(int mk) {
   }
 }
 
-static size_t x_offset_rows(int mk) { return (momentum_bytes_per_cap(mk) + 127) / 128 * 128; }
+// bytes reserved after the gradient stage for the momentum bytes (AdaMuon: the raw gradient) of a chunk
+size_t x_offset_rows(const kaon_plan* pl) {
+  size_t b = momentum_bytes_per_cap(pl->momentum_kind);
+  if (pl->optimizer == KAON_OPT_ADAMUON) b = std::max<size_t>(b, (size_t)CAP * (pl->param_dtype == KAON_DT_BF16 ? 2 : 4));
+  return (b + 127) / 128 * 128;
+}
 
 int configure_launch_adakaon(kaon_plan* pl, const cudaDeviceProp& prop, int max_cols) {
   const size_t esz = pl->param_dtype == KAON_DT_BF16 ? 2 : 4;
-  const size_t xr = x_offset_rows(pl->momentum_kind);
+  const size_t xr = x_offset_rows(pl);
   const size_t region = std::max<size_t>(xr + (size_t)max_cols * 4, (size_t)max_cols * 8);
   pl->smem_bytes = (size_t)CAP * esz + region + 128;
   pl->threads = AT;
-  AdaKernel k = pick_ada(pl->param_dtype, pl->momentum_kind);
+  AdaKernel k = pick_ada(pl->param_dtype, pl->momentum_kind, pl->optimizer == KAON_OPT_ADAMUON);
   if (!k) return fail(KAON_E_INVALID, "no Adakaon kernel for this dtype combination");
   cudaFuncAttributes fa;
   KAON_CUDA(cudaFuncGetAttributes(&fa, (const void*)k));
@@ -886,8 +903,8 @@ extern "C" int kaon_adakaon_step(kaon_plan* pl, const kaon_adakaon_hparams* h, u
   if (hp.cautious) { v.tasks = pl->d_tasks_full; v.n_tasks = pl->n_tasks_full; }
   else { v.tasks = pl->d_tasks_main; v.n_tasks = pl->n_tasks_main; }
   KAON_CUDA(cudaMemsetAsync(v.task_counter, 0, pl->counters_bytes - sizeof(unsigned), s));
-  AdaKernel k = pick_ada(pl->param_dtype, pl->momentum_kind);
-  k<<<pl->grid, AT, pl->smem_bytes, s>>>(v, hp, (int)x_offset_rows(pl->momentum_kind));
+  AdaKernel k = pick_ada(pl->param_dtype, pl->momentum_kind, false);
+  k<<<pl->grid, AT, pl->smem_bytes, s>>>(v, hp, (int)x_offset_rows(pl));
   KAON_CUDA(cudaGetLastError());
   pl->launches += 1;
   return KAON_OK;

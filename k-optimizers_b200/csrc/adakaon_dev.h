@@ -1,0 +1,24 @@
+// Device-side hyper-parameter block of the Adakaon / AdaMuon kernels and the launch helpers other
+// translation units use.
+#pragma once
+
+#include <stddef.h>
+#include <stdint.h>
+
+#include "kaon_plan.h"
+
+namespace kaon {
+
+struct AdaDev {
+  float w1, w1m1, w2, w2m1, eps1, clip, lrwd, upd_scale;
+  int small_w1, small_w2, has_eps, has_wd, cautious, gc, sr, has_m;
+  int remove, climb;
+  float a_remove, b_remove, a_climb, b_climb;
+  uint32_t step, k0, k1;
+};
+
+typedef void (*AdaKernel)(PlanView, AdaDev, int);
+AdaKernel pick_ada(int param_dtype, int momentum_kind, bool muon);
+size_t x_offset_rows(const kaon_plan* pl);
+
+}  // namespace kaon

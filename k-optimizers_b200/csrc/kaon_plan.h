@@ -4,6 +4,8 @@
 
 #include <stdint.h>
 
+#include <vector>
+
 #include "../../include/kaon_b200.h"
 
 namespace kaon {
@@ -81,6 +83,7 @@ struct PlanView {
                            //   STATS items done | FINAL strips arrived | FINAL complete | COUNT items done
   unsigned* kept;          // [n_tensors] cautious kept count
   float* aux;              // Adakaon scratch (see DevTensor::aux_off)
+  const void* const* signal;  // AdaMuon: per-tensor orthogonalised momentum (bf16); null otherwise
   unsigned* status;        // 0 = ok; else the code of the first bounded wait that ran out
   unsigned char* codes;    // 2 bits per element
 };
@@ -105,6 +108,13 @@ struct kaon_plan {
   kaon::Task* d_tasks_nocount = nullptr;  // Adakaon work list without the COUNT items (cautious off)
   int n_tasks_nocount = 0;
   int threads = 0;
+  std::vector<kaon::DevTensor> h_tensors;   // host copy of the table
+  std::vector<const void*> h_grads;         // host copy of the gradient-pointer column
+  // AdaMuon only (built lazily by the first step)
+  kaon::Task* d_tasks_ema = nullptr;         // row-chunk items of the factored tensors, tensor by tensor
+  std::vector<int> ema_begin;                // [n_tensors + 1] ranges into d_tasks_ema
+  const void** d_signal = nullptr;           // per-tensor pointer to O in the caller's workspace
+  const void* signal_base = nullptr;         // workspace the pointers were computed for
   unsigned* d_counters = nullptr;  // task_counter, status, done[n], kept[n] (contiguous; memset per step)
   size_t counters_bytes = 0;
   int64_t device_bytes = 0;

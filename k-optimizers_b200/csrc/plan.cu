@@ -254,6 +254,8 @@ int kaon_plan_create(kaon_plan** out, int optimizer, int param_dtype, int moment
   cudaMemcpy(base + o_m, main_list.data(), sizeof(Task) * main_list.size(), cudaMemcpyHostToDevice);
   ce = cudaMemcpy(base + o_a, axpy_list.data(), sizeof(Task) * axpy_list.size(), cudaMemcpyHostToDevice);
   if (ce != cudaSuccess) { kaon_plan_destroy(pl); return cuda_fail(ce, "cudaMemcpy(plan tables)"); }
+  pl->h_tensors = tens;
+  pl->h_grads = grads;
   pl->d_tasks_full = (Task*)(base + o_f); pl->n_tasks_full = (int)full_list.size();
   pl->d_tasks_main = (Task*)(base + o_m); pl->n_tasks_main = (int)main_list.size();
   pl->d_tasks_axpy = (Task*)(base + o_a); pl->n_tasks_axpy = (int)axpy_list.size();
@@ -277,6 +279,7 @@ int kaon_plan_set_grads(kaon_plan* pl, const void* const* grads, int n, void* st
   for (int i = 0; i < n; ++i)
     if ((uintptr_t)grads[i] & 15) return fail(KAON_E_INVALID, "gradient %d not 16-byte aligned", i);
   // pageable source: the runtime stages it before returning, so the caller's array is free at once
+  pl->h_grads.assign(grads, grads + n);
   cudaError_t ce = cudaMemcpyAsync((void*)pl->view.grads, grads, sizeof(void*) * (size_t)n,
                                    cudaMemcpyHostToDevice, (cudaStream_t)stream);
   return ce == cudaSuccess ? KAON_OK : cuda_fail(ce, "cudaMemcpyAsync(grad pointers)");
@@ -287,6 +290,8 @@ int kaon_plan_destroy(kaon_plan* pl) {
   cudaFree(pl->d_block);
   cudaFree(pl->d_codes);
   cudaFree(pl->d_aux);
+  cudaFree(pl->d_tasks_ema);
+  cudaFree((void*)pl->d_signal);
   delete pl;
   return KAON_OK;
 }

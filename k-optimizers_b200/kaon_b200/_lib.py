@@ -42,6 +42,13 @@ class AdakaonHParams(C.Structure):
                 ("msam_alpha_climb", C.c_double), ("msam_bound_climb", C.c_double)]
 
 
+class AdaMuonHParams(C.Structure):
+    _fields_ = [("lr", C.c_double), ("beta1", C.c_double), ("beta2", C.c_double),
+                ("eps1", C.c_double), ("weight_decay", C.c_double), ("clip_threshold", C.c_double),
+                ("ns_steps", C.c_int32), ("cautious", C.c_int32),
+                ("gradient_centralization", C.c_int32), ("bf16_method", C.c_int32)]
+
+
 class KaonError(RuntimeError):
     pass
 
@@ -61,6 +68,11 @@ def lib() -> C.CDLL:
         _lib.kaon_last_error.restype = C.c_char_p
         _lib.kaon_plan_device_bytes.restype = C.c_int64
         _lib.kaon_plan_launch_count.restype = C.c_int64
+        _lib.kaon_adamuon_workspace_bytes.restype = C.c_int64
+        _lib.kaon_adamuon_workspace_bytes.argtypes = [C.c_void_p]
+        _lib.kaon_adamuon_signal_offset.restype = C.c_int64
+        _lib.kaon_adamuon_signal_offset.argtypes = [C.c_void_p, C.c_int]
+        _lib.kaon_newton_schulz_workspace_bytes.restype = C.c_int64
         _lib.kaon_plan_device_bytes.argtypes = [C.c_void_p]
         _lib.kaon_plan_launch_count.argtypes = [C.c_void_p]
         if _lib.kaon_abi_version() != 1:
