@@ -37,9 +37,15 @@ WORKLOADS = {
                             "unet_sample", 8.015, {"outlier": True}),
     # Nekaon-4bit (config 4): as Lion-4bit + stats; climb and removal ride on the same weight access
     "nekaon4bit_unet2p6b": ("Nekaon", dict(lr=1e-4, betas=(0.2, 0.999)), "unet_2p6b", 7.073, {"cosine": (1e-4, 1e-5, 50)}),
+    # AdaMuon-int8 (config 5): 11.3 B-parameter DiT list; the non-NS passes move 8.006 B/param, the
+    # Newton-Schulz GEMMs are 3.24e14 flop per step
+    "adamuon_int8_dit11b": ("AdaMuon", dict(lr=1e-3, ns_steps=2, cautious=True, momentum_dtype="int8"),
+                            "dit_11b", 8.006, {"one_grad_set": True}),
+    "adamuon_int8_ditblock": ("AdaMuon", dict(lr=1e-3, ns_steps=2, cautious=True, momentum_dtype="int8"),
+                              "dit_block", 8.006, {}),
     "nekaon4bit_sample": ("Nekaon", dict(lr=1e-4, betas=(0.2, 0.999)), "unet_sample", 7.073, {"cosine": (1e-4, 1e-5, 50)}),
 }
-KERNEL_NAME = {"Lion": "lion_kernel<bf16,4bit>", "Adakaon": "adakaon_kernel<bf16,int8>", "Nekaon": "adakaon_kernel<bf16,4bit>"}
+KERNEL_NAME = {"AdaMuon": "ns_gemm_kernel", "Lion": "lion_kernel<bf16,4bit>", "Adakaon": "adakaon_kernel<bf16,int8>", "Nekaon": "adakaon_kernel<bf16,4bit>"}
 
 
 def measured_peaks():
@@ -105,7 +111,7 @@ def cpu_baseline(workload: str, steps: int = 2):
     rng = np.random.default_rng(0)
     ps = [ko.f32_to_bf16_bits(rng.standard_normal(int(np.prod(s)), dtype=np.float32) * 0.02) for s in shapes]
     gs = [ko.f32_to_bf16_bits(rng.standard_normal(int(np.prod(s)), dtype=np.float32) * 1e-3) for s in shapes]
-    cls = {"Lion": ko.OracleLion, "Adakaon": ko.OracleAdakaon, "Nekaon": ko.OracleNekaon}[opt_name]
+    cls = {"Lion": ko.OracleLion, "Adakaon": ko.OracleAdakaon, "Nekaon": ko.OracleNekaon, "AdaMuon": ko.OracleAdaMuon}[opt_name]
     opt = cls(ps, shapes, **kw)
     opt.step(gs)  # warm-up: allocates state
     times = []
@@ -161,15 +167,23 @@ def run_ours(args):
     owned = sw.part.owned(rank)
     owned_elems = sum(sw.views[i].numel() for i in owned)
     gen = torch.Generator(device=dev).manual_seed(1234 + rank)
-    sw.shard.copy_((torch.randn(sw.part.shard_len, generator=gen, device=dev) * 0.02).to(torch.bfloat16))
+
+    def fill_normal(dst, std, outlier=False, chunk=1 << 28):
+        """dst (bf16, flat) <- N(0, std), generated in fp32 chunks so that no 4x-sized temporary exists"""
+        for a in range(0, dst.numel(), chunk):
+            b = min(dst.numel(), a + chunk)
+            t = torch.randn(b - a, generator=gen, device=dev) * std
+            if outlier:
+                t = torch.where(torch.rand(b - a, generator=gen, device=dev) < 0.01, t * 100.0, t)
+            dst[a:b].copy_(t)
+
+    fill_normal(sw.shard, 0.02)
     sw.all_gather()
     # two gradient sets, alternated per step (a real loop reallocates grads: set_to_none=True)
     gsets = []
-    for k in range(2):
-        flat_g = torch.randn(sw.part.shard_len, generator=gen, device=dev) * 1e-3
-        if wopt.get("outlier"):
-            flat_g = torch.where(torch.rand(sw.part.shard_len, generator=gen, device=dev) < 0.01, flat_g * 100.0, flat_g)
-        flat_g = flat_g.to(torch.bfloat16)
+    for k in range(1 if wopt.get("one_grad_set") else 2):
+        flat_g = torch.empty(sw.part.shard_len, dtype=torch.bfloat16, device=dev)
+        fill_normal(flat_g, 1e-3, outlier=bool(wopt.get("outlier")))
         gsets.append((flat_g, [flat_g[sw.part.offset[i]:sw.part.offset[i] + sw.views[i].numel()].view(shapes[i]) for i in owned]))
     params = []
     for i in owned:
@@ -182,7 +196,7 @@ def run_ours(args):
     cos = wopt.get("cosine")
 
     def one_step(k, ev=None):
-        gv = gsets[k & 1][1]
+        gv = gsets[k % len(gsets)][1]
         if cos:
             for grp in opt.param_groups:
                 grp["lr"] = cos[1] + 0.5 * (cos[0] - cos[1]) * (1.0 + math.cos(math.pi * (k % cos[2]) / cos[2]))
@@ -245,8 +259,8 @@ def run_ours(args):
         esteps = max(1, min(args.steps, args.e2e_steps))
 
         def e2e_step(k):
-            gsets[k & 1][0].copy_(host_g, non_blocking=True)
-            for p, g in zip(params, gsets[k & 1][1]):
+            gsets[k % len(gsets)][0].copy_(host_g, non_blocking=True)
+            for p, g in zip(params, gsets[k % len(gsets)][1]):
                 p.grad = g
             opt.step()
             sw.all_gather()
@@ -267,6 +281,33 @@ def run_ours(args):
         nbytes = sw.part.shard_len * 2 * world
         e2e = {"value": total / (ems * 1e-3), "unit": "params/s", "ms_per_step": ems, "steps": esteps,
                "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes}
+
+    ns_info = None
+    if opt_name == "AdaMuon":
+        # Newton-Schulz alone, per distinct matrix shape of this rank's tensors: CUDA events around the
+        # GEMM chain (2 + 3*steps launches) of kaon_newton_schulz
+        from kaon_b200.adamuon import zeropower_via_newtonschulz5 as ns
+        steps_ns = kw.get("ns_steps", 2)
+        shapes2d = sorted({(s[0], W.numel([s]) // s[0]) for i, s in enumerate(shapes) if len(s) >= 2 and i in set(owned)})
+        counts = {sh: sum(1 for i in owned if len(shapes[i]) >= 2 and (shapes[i][0], W.numel([shapes[i]]) // shapes[i][0]) == sh) for sh in shapes2d}
+        ns_info, tot_flop, tot_ms = {}, 0.0, 0.0
+        for (R, Cc) in shapes2d:
+            x = torch.randn(R, Cc, device=dev, dtype=torch.bfloat16)
+            ns(x, steps_ns)
+            a_, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a_.record()
+            for _ in range(3):
+                ns(x, steps_ns)
+            b_.record()
+            torch.cuda.synchronize()
+            ms = a_.elapsed_time(b_) / 3
+            r_, k_ = min(R, Cc), max(R, Cc)
+            flop = steps_ns * (4.0 * r_ * r_ * k_ + 2.0 * r_ ** 3)
+            ns_info[f"{R}x{Cc}"] = {"ms": ms, "tflops": flop / (ms * 1e-3) / 1e12, "count": counts[(R, Cc)]}
+            tot_flop += flop * counts[(R, Cc)]
+            tot_ms += ms * counts[(R, Cc)]
+        ns_info["total"] = {"flop_per_step": tot_flop, "ms_per_step": tot_ms, "tflops": tot_flop / (tot_ms * 1e-3) / 1e12}
 
     if rank == 0:
         peak, peak_kind = measured_peaks()
@@ -289,6 +330,19 @@ def run_ours(args):
                          "bytes_per_param": bytes_per_param, "kernel": KERNEL_NAME[opt_name]},
             "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
         }
+        if ns_info is not None:
+            tpeak = 1678.7
+            try:
+                with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
+                    tpeak = float(json.load(fh)["bf16_tflops"])
+            except (OSError, KeyError, ValueError):
+                pass
+            line["hbm_passes"] = line["roofline"]
+            line["roofline"] = {"bound": "tensor", "achieved": ns_info["total"]["tflops"], "peak": tpeak,
+                                "unit": "TFLOP/s", "frac": ns_info["total"]["tflops"] / tpeak, "traffic": None,
+                                "peak_kind": "measured cuBLAS bf16 burst", "kernel": "ns_gemm_kernel",
+                                "note": "Newton-Schulz GEMM chain timed alone per shape (CUDA events); hbm_passes has the whole-step algorithmic-bytes view"}
+            line["newton_schulz"] = ns_info
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"], _, _ = cpu_baseline(args.workload)
         print(json.dumps(line), flush=True)

@@ -33,6 +33,11 @@ def dit_11b() -> list[tuple[int, ...]]:
     return shapes
 
 
+def dit_block() -> list[tuple[int, ...]]:
+    """One width-3072 DiT block (113 M parameters)."""
+    return [(9216, 3072), (3072, 3072), (12288, 3072), (3072, 12288), (3072,), (3072,)]
+
+
 def unet_sample() -> list[tuple[int, ...]]:
     """One width-1280 block plus one [1280,1280,3,3] conv: the bounded sample the CPU baseline times."""
     return _block(1280) + [(1280, 1280, 3, 3)]
@@ -42,4 +47,4 @@ def numel(shapes) -> int:
     return sum(math.prod(s) for s in shapes)
 
 
-WORKLOADS = {"unet_2p6b": unet_2p6b, "dit_11b": dit_11b, "unet_sample": unet_sample}
+WORKLOADS = {"unet_2p6b": unet_2p6b, "dit_11b": dit_11b, "dit_block": dit_block, "unet_sample": unet_sample}
