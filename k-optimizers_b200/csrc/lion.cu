@@ -17,7 +17,116 @@ struct LionDev {
   float lr, b1, w1, b2, w2, wd;
   int cautious, gc, sr, has_wd;
   uint32_t step, k0, k1;
+  uint32_t rk0[10], rk1[10];  // Philox round keys (k + r * Weyl), precomputed on the host
 };
+
+// Philox4x32-10 with the round keys read from the kernel's parameter block.
+__device__ __forceinline__ void philox_rk(const LionDev& hp, uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3,
+                                          uint32_t out[4]) {
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const unsigned long long p0 = (unsigned long long)0xD2511F53u * c0;
+    const unsigned long long p1 = (unsigned long long)0xCD9E8D57u * c2;
+    const uint32_t n0 = (uint32_t)(p1 >> 32) ^ c1 ^ hp.rk0[r];
+    const uint32_t n2 = (uint32_t)(p0 >> 32) ^ c3 ^ hp.rk1[r];
+    c1 = (uint32_t)p1;
+    c3 = (uint32_t)p0;
+    c0 = n0;
+    c2 = n2;
+  }
+  out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
+}
+
+// Full-vector fast path of the MAIN item for 4-bit momentum, no weight decay, cautious on, rows that are
+// a multiple of 8 elements: no per-element guards, the eight 4-bit codes assembled with one shift-add
+// each, one exactness check per vector.  Codes of the update go out as two byte masks per eight
+// elements: bit k of the low byte = kept with sign >= 0, bit k of the high byte = kept with sign <= 0.
+template <typename PT, bool GC>
+__device__ __forceinline__ unsigned lion_fast4(const PlanView& pv, const LionDev& hp, const Task& t,
+                                               const DevTensor& d, const unsigned char* g_s,
+                                               const unsigned char* m_s, const float* mean_s, int tid) {
+  using E = Elems<PT>;
+  const int nvec = t.n >> 3;
+  const int nvec_pad = (nvec + 31) & ~31;
+  const bool blk128 = d.block == 128u;
+  uint16_t* cdst = reinterpret_cast<uint16_t*>(pv.codes + d.code_off + (t.e0 >> 2));
+  uint32_t* mdst = reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned char*>(d.m) + (t.e0 >> 1));
+  const uint32_t* msrc = reinterpret_cast<const uint32_t*>(m_s);
+  unsigned kept_local = 0;
+  // sum over k of ((bits(1.5*2^23) - 8) << 4k) mod 2^32: what the shift-add packing must give back
+  constexpr uint32_t PACK_BIAS = (uint32_t)(0x4B3FFFF8ull * 0x11111111ull);
+  for (int v = tid; v < nvec_pad; v += NTHREADS) {
+    const bool act = v < nvec;
+    float g[8];
+    uint32_t w = 0x88888888u;
+    float sc_old = 1.0f;
+    const long long blk = blk128 ? ((t.e0 >> 7) + (v >> 4)) : 0;
+    if (act) {
+      E::load8(g_s + (size_t)v * 8 * E::BYTES, g);
+      w = msrc[v];
+      sc_old = d.m_scale[blk];
+      if (GC) {
+        const float mu = mean_s[row_of((unsigned)v * 8u, d)];
+#pragma unroll
+        for (int k = 0; k < 8; k += 2) {
+          const float x0 = __fsub_rn(g[k], mu), x1 = __fsub_rn(g[k + 1], mu);
+          if (E::IS_BF16) {
+            const uint32_t pk = pack_bf16_rn(x0, x1);
+            g[k] = bf16lo(pk);
+            g[k + 1] = bf16hi(pk);
+          } else {
+            g[k] = x0;
+            g[k + 1] = x1;
+          }
+        }
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) g[k] = 0.0f;
+    }
+    float mn[8];
+    uint32_t pos = 0, neg = 0;
+    float amax = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float mo = __fmul_rn(__uint_as_float(0x4B000000u | ((w >> (4 * k)) & 0xFu)) - 8388616.0f, sc_old);
+      const float c = __fmaf_rn(g[k], hp.w1, __fmul_rn(mo, hp.b1));
+      mn[k] = __fmaf_rn(g[k], hp.w2, __fmul_rn(mo, hp.b2));
+      amax = fmaxf(amax, fabsf(mn[k]));
+      if (fminf(c, g[k]) > 0.0f) pos |= 1u << k;
+      if (fmaxf(c, g[k]) < 0.0f) neg |= 1u << k;
+    }
+    amax = fmaxf(group_max(amax, 16), 1e-12f);
+    const float sc = __fdiv_rn(amax, 7.0f);
+    const float inv = __fdividef(1.0f, sc);
+    const float magic = 12582912.0f;
+    uint32_t word = 0;
+    float worst = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float tq = __fmul_rn(mn[k], inv);
+      const float r = __fadd_rn(tq, magic);
+      worst = fmaxf(worst, fabsf(__fsub_rn(tq, __fsub_rn(r, magic))));
+      word += __float_as_uint(r) << (4 * k);
+    }
+    word -= PACK_BIAS;
+    if (worst > 0.5f - 1e-4f) {  // some product sits near a rounding boundary: redo with the true division
+      word = 0;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const int qi = min(max((int)rintf(__fdiv_rn(mn[k], sc)), -7), 7);
+        word |= (uint32_t)(qi + 8) << (4 * k);
+      }
+    }
+    if (act) {
+      mdst[v] = word;
+      if ((v & 15) == 0) d.m_scale[blk] = sc;
+      cdst[v] = (uint16_t)(pos | (neg << 8));
+      kept_local += __popc(pos | neg);
+    }
+  }
+  return kept_local;
+}
 
 // The Lion arithmetic on eight elements: in g (centralized grads), m (decoded momentum), pvals
 // (weights, only read when has_wd).  Out: m <- new momentum, dl <- direction (+ wd*p), kept bits.
@@ -165,6 +274,13 @@ __device__ void lion_main(const PlanView& pv, const LionDev& hp, const Task& t, 
 
   // ---- main pass ----
   uint32_t kept_local = 0;
+  bool fast = false;
+  if constexpr (MK == KAON_M_4BIT) fast = !hp.has_wd && hp.cautious && (n & 7) == 0 && row_uniform;
+  if (fast) {
+    if constexpr (MK == KAON_M_4BIT)
+      kept_local = do_gc ? lion_fast4<PT, true>(pv, hp, t, d, g_s, m_s, mean_s, tid)
+                         : lion_fast4<PT, false>(pv, hp, t, d, g_s, m_s, mean_s, tid);
+  } else
   for (int v = tid; v < nvec_pad; v += NTHREADS) {
     const int cnt = max(0, min(8, n - v * 8));
     float gv[8], mv[8], pvals[8], dl[8];
@@ -276,11 +392,10 @@ __device__ void lion_main(const PlanView& pv, const LionDev& hp, const Task& t, 
     // ---- hand the update on ----
     if (cnt > 0) {
       if (hp.cautious) {
-        uint32_t code16 = 0;
+        uint32_t code16 = 0;  // low byte: kept with sign >= 0; high byte: kept with sign <= 0
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          const uint32_t code = ((kept >> k) & 1u) ? (uint32_t)(sg[k] + 2) : 0u;
-          code16 |= code << (2 * k);
+          if ((kept >> k) & 1u) code16 |= (sg[k] >= 0 ? (1u << k) : 0u) | (sg[k] <= 0 ? (256u << k) : 0u);
         }
         *reinterpret_cast<uint16_t*>(pv.codes + d.code_off + (t.e0 >> 2) + (size_t)v * 2) = (uint16_t)code16;
         kept_local += __popc(kept);
@@ -329,24 +444,46 @@ __device__ void lion_apply(const PlanView& pv, const LionDev& hp, const Task& t,
   unsigned char* pbase = reinterpret_cast<unsigned char*>(d.p) + t.e0 * E::BYTES;
   const unsigned char* cbase = pv.codes + d.code_off + (t.e0 >> 2);
   SrStream st{Philox{hp.k0, hp.k1}, hp.step, KAON_TAG_UPDATE};
+  const bool fast_sr = E::IS_BF16 && hp.sr && !hp.has_wd;
   for (int v = tid; v < nvec; v += NTHREADS) {
     const int cnt = min(8, n - v * 8);
     const uint32_t c16 = __ldcg(reinterpret_cast<const unsigned short*>(cbase + (size_t)v * 2));
+    const uint32_t pos = c16 & 0xFFu, neg = c16 >> 8;
+    if (fast_sr && cnt == 8) {
+      // eight bf16 weights: p - (+-vpos | 0), noise from the Philox stream, truncate
+      const uint64_t q = (uint64_t)((t.e0 >> 3) + v);
+      uint32_t nz[4];
+      philox_rk(hp, (uint32_t)q, d.tensor_id, hp.step, (uint32_t)KAON_TAG_UPDATE | ((uint32_t)(q >> 32) << 8), nz);
+      uint4* pp = reinterpret_cast<uint4*>(pbase + (size_t)v * 16);
+      const uint4 pw4 = *pp;
+      uint32_t pw[4] = {pw4.x, pw4.y, pw4.z, pw4.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int k0 = 2 * j, k1 = 2 * j + 1;
+        const float d0 = ((pos >> k0) & 1u) ? (((neg >> k0) & 1u) ? 0.0f : vpos) : (((neg >> k0) & 1u) ? -vpos : 0.0f);
+        const float d1 = ((pos >> k1) & 1u) ? (((neg >> k1) & 1u) ? 0.0f : vpos) : (((neg >> k1) & 1u) ? -vpos : 0.0f);
+        const uint32_t b0 = __float_as_uint(__fsub_rn(bf16lo(pw[j]), d0)) + (nz[j] & 0xffffu);
+        const uint32_t b1 = __float_as_uint(__fsub_rn(bf16hi(pw[j]), d1)) + (nz[j] >> 16);
+        pw[j] = __byte_perm(b0, b1, 0x7632);
+      }
+      *pp = make_uint4(pw[0], pw[1], pw[2], pw[3]);
+      continue;
+    }
     float dl[8];
     if (hp.has_wd) {
       float pvals[8];
       load8_guard<PT>(pbase + (size_t)v * 8 * E::BYTES, cnt, pvals);
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
-        const uint32_t code = (c16 >> (2 * k)) & 3u;
-        const float dv = __fmaf_rn(pvals[k], hp.wd, (float)((int)code - 2));
-        dl[k] = code ? __fmul_rn(__fdiv_rn(dv, denom), hp.lr) : 0.0f;
+        const int pb = (pos >> k) & 1, nb = (neg >> k) & 1;
+        const float dv = __fmaf_rn(pvals[k], hp.wd, (float)(pb - nb));
+        dl[k] = (pb | nb) ? __fmul_rn(__fdiv_rn(dv, denom), hp.lr) : 0.0f;
       }
     } else {
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
-        const uint32_t code = (c16 >> (2 * k)) & 3u;
-        dl[k] = code == 3u ? vpos : (code == 1u ? -vpos : 0.0f);
+        const int pb = (pos >> k) & 1, nb = (neg >> k) & 1;
+        dl[k] = (pb == nb) ? 0.0f : (pb ? vpos : -vpos);
       }
     }
     update8<PT>(pbase + (size_t)v * 8 * E::BYTES, cnt, dl, -1.0f, hp.sr != 0, st, d.tensor_id,
@@ -441,6 +578,7 @@ extern "C" int kaon_lion_step(kaon_plan* pl, const kaon_lion_hparams* h, uint64_
   hp.gc = h->gradient_centralization != 0;
   hp.sr = h->bf16_method == KAON_W_SR && pl->param_dtype == KAON_DT_BF16;
   hp.step = step; hp.k0 = (uint32_t)seed; hp.k1 = (uint32_t)(seed >> 32);
+  for (int r = 0; r < 10; ++r) { hp.rk0[r] = hp.k0 + 0x9E3779B9u * (uint32_t)r; hp.rk1[r] = hp.k1 + 0xBB67AE85u * (uint32_t)r; }
   cudaStream_t s = (cudaStream_t)stream;
   PlanView v = pl->view;
   if (hp.cautious) { v.tasks = pl->d_tasks_full; v.n_tasks = pl->n_tasks_full; }
@@ -614,6 +752,7 @@ extern "C" int kaon_lion_step_noalloc(const kaon_tensor_desc* t, int param_dtype
   hp.gc = h->gradient_centralization != 0;
   hp.sr = h->bf16_method == KAON_W_SR && param_dtype == KAON_DT_BF16;
   hp.step = step; hp.k0 = (uint32_t)seed; hp.k1 = (uint32_t)(seed >> 32);
+  for (int r = 0; r < 10; ++r) { hp.rk0[r] = hp.k0 + 0x9E3779B9u * (uint32_t)r; hp.rk1[r] = hp.k1 + 0xBB67AE85u * (uint32_t)r; }
 
   unsigned* counters = reinterpret_cast<unsigned*>(nd.base + NA_OFF_COUNTERS);
   PlanView v{};
