@@ -44,7 +44,8 @@ __device__ __forceinline__ void philox_rk(const LionDev& hp, uint32_t c0, uint32
 template <typename PT, bool GC>
 __device__ __forceinline__ unsigned lion_fast4(const PlanView& pv, const LionDev& hp, const Task& t,
                                                const DevTensor& d, const unsigned char* g_s,
-                                               const unsigned char* m_s, const float* mean_s, int tid) {
+                                               const unsigned char* m_s, const float* mean_s,
+                                               const float* sc_s, int tid) {
   using E = Elems<PT>;
   const int nvec = t.n >> 3;
   const int nvec_pad = (nvec + 31) & ~31;
@@ -64,7 +65,7 @@ __device__ __forceinline__ unsigned lion_fast4(const PlanView& pv, const LionDev
     if (act) {
       E::load8(g_s + (size_t)v * 8 * E::BYTES, g);
       w = msrc[v];
-      sc_old = d.m_scale[blk];
+      sc_old = sc_s[v >> 4];
       if (GC) {
         const float mu = mean_s[row_of((unsigned)v * 8u, d)];
 #pragma unroll
@@ -149,7 +150,7 @@ __device__ __forceinline__ uint32_t lion_math8(const LionDev& hp, const float g[
 
 template <typename PT, int MK>
 __device__ void lion_main(const PlanView& pv, const LionDev& hp, const Task& t, unsigned char* g_s,
-                          unsigned char* m_s, float* mean_s, unsigned* rowmax_s, float* scale_s,
+                          unsigned char* m_s, float* mean_s, unsigned* rowmax_s, float* scale_s, float* sc_s,
                           uint64_t* bar,
                           unsigned& parity, unsigned* red_s, int tid) {
   using E = Elems<PT>;
@@ -212,6 +213,11 @@ __device__ void lion_main(const PlanView& pv, const LionDev& hp, const Task& t, 
         mean_s[r] = E::IS_BF16 ? round_bf16(mean) : mean;
       }
     }
+  }
+  if constexpr (MK == KAON_M_4BIT) {  // old block scales of the chunk (the fast path reads them from here)
+    const int nblk = d.block == 128u ? (n + 127) >> 7 : 1;
+    const long long b0 = d.block == 128u ? (t.e0 >> 7) : 0;
+    for (int b = tid; b < nblk; b += NTHREADS) sc_s[b] = d.m_scale[b0 + b];
   }
   if constexpr (MK == KAON_M_INT8) {
     for (int r = tid; r < nrows; r += NTHREADS) {
@@ -278,8 +284,8 @@ __device__ void lion_main(const PlanView& pv, const LionDev& hp, const Task& t, 
   if constexpr (MK == KAON_M_4BIT) fast = !hp.has_wd && hp.cautious && (n & 7) == 0 && row_uniform;
   if (fast) {
     if constexpr (MK == KAON_M_4BIT)
-      kept_local = do_gc ? lion_fast4<PT, true>(pv, hp, t, d, g_s, m_s, mean_s, tid)
-                         : lion_fast4<PT, false>(pv, hp, t, d, g_s, m_s, mean_s, tid);
+      kept_local = do_gc ? lion_fast4<PT, true>(pv, hp, t, d, g_s, m_s, mean_s, sc_s, tid)
+                         : lion_fast4<PT, false>(pv, hp, t, d, g_s, m_s, mean_s, sc_s, tid);
   } else
   for (int v = tid; v < nvec_pad; v += NTHREADS) {
     const int cnt = max(0, min(8, n - v * 8));
@@ -445,7 +451,44 @@ __device__ void lion_apply(const PlanView& pv, const LionDev& hp, const Task& t,
   const unsigned char* cbase = pv.codes + d.code_off + (t.e0 >> 2);
   SrStream st{Philox{hp.k0, hp.k1}, hp.step, KAON_TAG_UPDATE};
   const bool fast_sr = E::IS_BF16 && hp.sr && !hp.has_wd;
-  for (int v = tid; v < nvec; v += NTHREADS) {
+  int v_begin = tid;
+  if (fast_sr) {
+    // four full vectors per trip: all loads are issued before the first use
+    const int nfull = n >> 3;
+    int v = tid;
+    for (; v + 3 * NTHREADS < nfull; v += 4 * NTHREADS) {
+      uint4 pw4[4];
+      uint32_t c16[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        pw4[u] = *reinterpret_cast<const uint4*>(pbase + (size_t)(v + u * NTHREADS) * 16);
+        c16[u] = __ldcg(reinterpret_cast<const unsigned short*>(cbase + (size_t)(v + u * NTHREADS) * 2));
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int vv = v + u * NTHREADS;
+        const uint32_t pos = c16[u] & 0xFFu, neg = c16[u] >> 8;
+        const uint64_t q = (uint64_t)((t.e0 >> 3) + vv);
+        uint32_t nz[4];
+        philox_rk(hp, (uint32_t)q, d.tensor_id, hp.step, (uint32_t)KAON_TAG_UPDATE | ((uint32_t)(q >> 32) << 8), nz);
+        uint32_t pw[4] = {pw4[u].x, pw4[u].y, pw4[u].z, pw4[u].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int k0 = 2 * j, k1 = 2 * j + 1;
+          float d0 = ((pos >> k0) & 1u) ? vpos : 0.0f;
+          d0 = ((neg >> k0) & 1u) ? -vpos : d0;
+          float d1 = ((pos >> k1) & 1u) ? vpos : 0.0f;
+          d1 = ((neg >> k1) & 1u) ? -vpos : d1;
+          const uint32_t b0 = __float_as_uint(__fsub_rn(bf16lo(pw[j]), d0)) + (nz[j] & 0xffffu);
+          const uint32_t b1 = __float_as_uint(__fsub_rn(bf16hi(pw[j]), d1)) + (nz[j] >> 16);
+          pw[j] = __byte_perm(b0, b1, 0x7632);
+        }
+        *reinterpret_cast<uint4*>(pbase + (size_t)vv * 16) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
+      }
+    }
+    v_begin = v;
+  }
+  for (int v = v_begin; v < nvec; v += NTHREADS) {
     const int cnt = min(8, n - v * 8);
     const uint32_t c16 = __ldcg(reinterpret_cast<const unsigned short*>(cbase + (size_t)v * 2));
     const uint32_t pos = c16 & 0xFFu, neg = c16 >> 8;
@@ -492,11 +535,12 @@ __device__ void lion_apply(const PlanView& pv, const LionDev& hp, const Task& t,
 }
 
 template <typename PT, int MK>
-__global__ void __launch_bounds__(NTHREADS, 3) lion_kernel(PlanView pv, LionDev hp) {
+__global__ void __launch_bounds__(NTHREADS, 4) lion_kernel(PlanView pv, LionDev hp) {
   extern __shared__ __align__(128) unsigned char dyn[];
   __shared__ float mean_s[MAX_TASK_ROWS];
   __shared__ unsigned rowmax_s[MK == KAON_M_INT8 ? MAX_TASK_ROWS : 1];
   __shared__ float scale_s[MK == KAON_M_INT8 ? MAX_TASK_ROWS : 1];
+  __shared__ float sc_s[MK == KAON_M_4BIT ? CAP / 128 : 1];
   __shared__ __align__(8) uint64_t bar;
   __shared__ int next_s[2];
   __shared__ unsigned red_s[NTHREADS / 32];
@@ -519,7 +563,7 @@ __global__ void __launch_bounds__(NTHREADS, 3) lion_kernel(PlanView pv, LionDev 
     claim_next(slot ^ 1);
     const Task t = pv.tasks[cur];
     if (t.phase == PH_LION_MAIN)
-      lion_main<PT, MK>(pv, hp, t, g_s, m_s, mean_s, rowmax_s, scale_s, &bar, parity, red_s, tid);
+      lion_main<PT, MK>(pv, hp, t, g_s, m_s, mean_s, rowmax_s, scale_s, sc_s, &bar, parity, red_s, tid);
     else
       lion_apply<PT>(pv, hp, t, tid);
     __syncthreads();
