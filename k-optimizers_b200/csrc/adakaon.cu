@@ -213,11 +213,25 @@ __device__ void ada_stats(const PlanView& pv, const AdaDev& hp, const Task& t, S
       const unsigned char* rowp = st.g_s + (size_t)r * C * E::BYTES;
       const float mu = gc ? row_mean<PT>(rowp, C, lane) : 0.0f;
       float s = 0.0f;
-      for (int i = lane; i < C; i += 32) {
-        const float x = centered<PT>(E::load1(rowp, i), mu, gc);
-        float sq = __fmul_rn(x, x);
-        if (hp.has_eps) sq = __fadd_rn(sq, hp.eps1);
-        s += sq;
+      if ((C & 7) == 0) {
+        for (int v = lane; v < (C >> 3); v += 32) {
+          float x[8];
+          E::load8(rowp + (size_t)v * 8 * E::BYTES, x);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const float y = centered<PT>(x[k], mu, gc);
+            float sq = __fmul_rn(y, y);
+            if (hp.has_eps) sq = __fadd_rn(sq, hp.eps1);
+            s += sq;
+          }
+        }
+      } else {
+        for (int i = lane; i < C; i += 32) {
+          const float x = centered<PT>(E::load1(rowp, i), mu, gc);
+          float sq = __fmul_rn(x, x);
+          if (hp.has_eps) sq = __fadd_rn(sq, hp.eps1);
+          s += sq;
+        }
       }
       s = warp_sum(s);
       if (lane == 0) {
@@ -232,6 +246,28 @@ __device__ void ada_stats(const PlanView& pv, const AdaDev& hp, const Task& t, S
     }
     __syncthreads();
     // columns: each thread owns columns tid, tid+AT, ... and walks the staged rows in order
+    if ((C & 7) == 0) {
+      // eight columns per thread, rows in order
+      for (int v = tid; v < (C >> 3); v += AT) {
+        float a1[8], a2[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) { a1[k] = 0.0f; a2[k] = 0.0f; }
+        for (int r = 0; r < nrc; ++r) {
+          float x[8];
+          E::load8(st.g_s + ((size_t)r * C + (size_t)v * 8) * E::BYTES, x);
+          const float mu = sm.mean_s[r], ri = sm.rfac_s[r];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const float y = centered<PT>(x[k], mu, gc);
+            const float sq = __fmul_rn(y, y);
+            a1[k] += hp.has_eps ? __fadd_rn(sq, hp.eps1) : sq;
+            a2[k] += __fmul_rn(sq, ri);
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) { acc1[v * 8 + k] += a1[k]; acc2[v * 8 + k] += a2[k]; }
+      }
+    } else
     for (int j = tid; j < C; j += AT) {
       float a1 = 0.0f, a2 = 0.0f;
       for (int r = 0; r < nrc; ++r) {
@@ -413,6 +449,11 @@ __device__ void ada_rows(const PlanView& pv, const AdaDev& hp, const Task& t, St
         }
       }
     }
+    if constexpr (MK == KAON_M_4BIT) {  // old block scales of the chunk
+      const int nblk = d.block == 128u ? (n + 127) >> 7 : 1;
+      const long long b0 = d.block == 128u ? (e0 >> 7) : 0;
+      for (int b = tid; b < nblk; b += AT) sm.scale_s[b] = d.m_scale[b0 + b];
+    }
     __syncthreads();
     unsigned char* pbase = reinterpret_cast<unsigned char*>(d.p) + e0 * E::BYTES;
     const int nvec = (n + 7) >> 3;
@@ -421,6 +462,57 @@ __device__ void ada_rows(const PlanView& pv, const AdaDev& hp, const Task& t, St
     // One vector of the chain: fills g', the new momentum mn[], the pre-update weights pc[] (after the
     // Nekaon removal) and delta dl[]; returns the kept bits.
     auto chain8 = [&](int v, int cnt, float gv[8], float mo[8], float mn[8], float pc[8], float dl[8]) -> unsigned {
+      if (row_uniform && cnt == 8) {
+        // full vector inside one row: one row lookup, vector loads, no guards
+        S::load8(st.g_s + (size_t)v * 8 * S::BYTES, gv);
+        float raw[8];
+        if (MUON) E::load8(st.m_s + (size_t)v * 8 * E::BYTES, raw);
+        const int r = row_of((unsigned)v * 8u, d);
+        const float rf = sm.rfac_s[r], mu = sm.mean_s[r];
+        const float4 c0 = *reinterpret_cast<const float4*>(cfac_s + (v * 8 - r * C));
+        const float4 c1 = *reinterpret_cast<const float4*>(cfac_s + (v * 8 - r * C) + 4);
+        const float cf[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+        if constexpr (MK == KAON_M_4BIT) decode8<MK>(st.m_s, v, 8, sm.scale_s[v >> 4], mo);
+        else if constexpr (MK == KAON_M_INT8) decode8<MK>(st.m_s, v, 8, sm.scale_s[r], mo);
+        else if constexpr (MK == KAON_M_NONE) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) mo[k] = 0.0f;
+        } else decode8<MK>(st.m_s, v, 8, 1.0f, mo);
+        if (need_p) E::load8(pbase + (size_t)v * 8 * E::BYTES, pc);
+        else {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) pc[k] = 0.0f;
+        }
+        if (hp.remove && need_p) {
+          uint32_t nz[4] = {0u, 0u, 0u, 0u};
+          if (E::IS_BF16) s_rem.draw8(d.tensor_id, (uint64_t)((e0 >> 3) + v), nz);
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            pc[k] = write_step<PT>(pc[k], climb_e(mo[k], hp.a_remove, hp.b_remove), 1.0f, E::IS_BF16, noise_lane(nz, k));
+        }
+        if (gc) {
+#pragma unroll
+          for (int k = 0; k < 8; k += 2) {
+            const float x0 = __fsub_rn(gv[k], mu), x1 = __fsub_rn(gv[k + 1], mu);
+            if (E::IS_BF16) {
+              const uint32_t pk = pack_bf16_rn(x0, x1);
+              gv[k] = bf16lo(pk); gv[k + 1] = bf16hi(pk);
+            } else {
+              gv[k] = x0; gv[k + 1] = x1;
+            }
+          }
+        }
+        unsigned keptf = 0;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float u = update_of(gv[k], rf, cf[k], ch, hp.upd_scale);
+          mn[k] = ema_of<MK>(mo[k], u, hp);
+          const float dv = hp.has_wd ? __fmaf_rn(pc[k], hp.lrwd, mn[k]) : mn[k];
+          dl[k] = dv;
+          if (__fmul_rn(dv, MUON ? raw[k] : gv[k]) > 0.0f) keptf |= 1u << k;
+        }
+        return keptf;
+      }
       load8_guard<ST>(st.g_s + (size_t)v * 8 * S::BYTES, cnt, gv);
       float raw[8];  // MUON: the raw gradient, the cautious mask's reference
       if (MUON) load8_guard<PT>(st.m_s + (size_t)v * 8 * E::BYTES, cnt, raw);
@@ -429,8 +521,7 @@ __device__ void ada_rows(const PlanView& pv, const AdaDev& hp, const Task& t, St
       for (int k = 0; k < 8; ++k) rl[k] = row_uniform ? row_of((unsigned)v * 8u, d) : row_of((unsigned)(v * 8 + min(k, max(cnt - 1, 0))), d);
       // old momentum
       if constexpr (MK == KAON_M_4BIT) {
-        const long long blk = (d.block == 128u) ? ((e0 >> 7) + (v >> 4)) : 0;
-        decode8<MK>(st.m_s, v, cnt, cnt > 0 ? d.m_scale[blk] : 1.0f, mo);
+        decode8<MK>(st.m_s, v, cnt, cnt > 0 ? sm.scale_s[d.block == 128u ? (v >> 4) : 0] : 1.0f, mo);
       } else if constexpr (MK == KAON_M_INT8) {
 #pragma unroll
         for (int k = 0; k < 8; ++k)
