@@ -101,30 +101,44 @@ __device__ __forceinline__ void store8(void* pe, int cnt, const float v[8]) {
 
 // ----------------------------------------------------------------------------- staging
 
+// Two staging buffers: while the CTA works on one chunk, the bulk-copy engine fills the other.
 struct Stage {
-  unsigned char* g_s;
+  unsigned char* g_s;   // buffers of the chunk being processed (set by stage_wait)
   unsigned char* m_s;
-  uint64_t* bar;
-  unsigned parity;
+  unsigned char* gbuf[2];
+  unsigned char* mbuf[2];
+  uint64_t* bar[2];
+  unsigned parity[2];
+  int nbuf;             // 2, or 1 when shared memory has no room for a second buffer
 };
 
-// Bring `gbytes` of gradients and `mbytes` of momentum into shared memory.  All threads call.
-__device__ __forceinline__ bool stage_in(Stage& st, const unsigned char* gsrc, unsigned gbytes,
-                                         const unsigned char* msrc, unsigned mbytes, unsigned* status,
-                                         int tid) {
-  const unsigned ghead = stage_tail(st.g_s, gsrc, gbytes, tid);
-  const unsigned mhead = mbytes ? stage_tail(st.m_s, msrc, mbytes, tid) : 0u;
-  bool ok = true;
-  if (ghead + mhead) {
-    if (tid == 0) {
-      fence_async_smem();
-      mbar_expect_tx(st.bar, ghead + mhead);
-      if (ghead) bulk_g2s(st.g_s, gsrc, ghead, st.bar);
-      if (mhead) bulk_g2s(st.m_s, msrc, mhead, st.bar);
-    }
-    ok = mbar_wait(st.bar, st.parity, status, 1002u);
-    st.parity ^= 1u;
+__device__ __forceinline__ unsigned bulk_head(const unsigned char* src, unsigned bytes) {
+  return (reinterpret_cast<uintptr_t>(src) & 15) ? 0u : (bytes & ~15u);
+}
+
+// Start bringing a chunk into buffer b.  All threads call (the ragged ends are plain loads).
+__device__ __forceinline__ void stage_issue(Stage& st, int b, const unsigned char* gsrc, unsigned gbytes,
+                                            const unsigned char* msrc, unsigned mbytes, int tid) {
+  const unsigned ghead = stage_tail(st.gbuf[b], gsrc, gbytes, tid);
+  const unsigned mhead = mbytes ? stage_tail(st.mbuf[b], msrc, mbytes, tid) : 0u;
+  if ((ghead + mhead) && tid == 0) {
+    fence_async_smem();
+    mbar_expect_tx(st.bar[b], ghead + mhead);
+    if (ghead) bulk_g2s(st.gbuf[b], gsrc, ghead, st.bar[b]);
+    if (mhead) bulk_g2s(st.mbuf[b], msrc, mhead, st.bar[b]);
   }
+}
+
+// Wait for the chunk issued into buffer b (same arguments) and make it the current one.
+__device__ __forceinline__ bool stage_wait(Stage& st, int b, const unsigned char* gsrc, unsigned gbytes,
+                                           const unsigned char* msrc, unsigned mbytes, unsigned* status) {
+  bool ok = true;
+  if (bulk_head(gsrc, gbytes) + (mbytes ? bulk_head(msrc, mbytes) : 0u)) {
+    ok = mbar_wait(st.bar[b], st.parity[b], status, 1002u);
+    st.parity[b] ^= 1u;
+  }
+  st.g_s = st.gbuf[b];
+  st.m_s = st.mbuf[b];
   return __syncthreads_and(ok) != 0;
 }
 
@@ -203,10 +217,18 @@ __device__ void ada_stats(const PlanView& pv, const AdaDev& hp, const Task& t, S
   for (int j = tid; j < 2 * C; j += AT) sm.x_s[j] = 0.0f;
   double rowsum = 0.0;  // lane 0 of each warp: sum of the new row statistics it produced
   const int warp = tid >> 5, lane = tid & 31;
-  for (int c0 = 0; ok && c0 < nrows; c0 += d.chunk_rows) {
+  auto issue = [&](int c0, int b) {
+    const int nrc = min(d.chunk_rows, nrows - c0);
+    stage_issue(st, b, g + (t.e0 + (long long)c0 * C) * E::BYTES, (unsigned)(nrc * C) * E::BYTES, nullptr, 0u, tid);
+  };
+  if (ok && st.nbuf == 2) issue(0, 0);
+  for (int c0 = 0, ci = 0; ok && c0 < nrows; c0 += d.chunk_rows, ++ci) {
     const int nrc = min(d.chunk_rows, nrows - c0);
     const long long e0 = t.e0 + (long long)c0 * C;
-    ok = stage_in(st, g + e0 * E::BYTES, (unsigned)(nrc * C) * E::BYTES, nullptr, 0u, pv.status, tid);
+    const int b = st.nbuf == 2 ? (ci & 1) : 0;
+    if (st.nbuf == 1) issue(c0, 0);
+    else if (c0 + d.chunk_rows < nrows) issue(c0 + d.chunk_rows, b ^ 1);
+    ok = stage_wait(st, b, g + e0 * E::BYTES, (unsigned)(nrc * C) * E::BYTES, nullptr, 0u, pv.status);
     if (!ok) break;
     // rows: centralization mean, mean of g^2+eps1, row EMA
     for (int r = warp; r < nrc; r += AT / 32) {
@@ -430,12 +452,30 @@ __device__ void ada_rows(const PlanView& pv, const AdaDev& hp, const Task& t, St
   const bool need_p = APPLY || hp.has_wd;
   unsigned kept_local = 0;
 
-  for (int c0 = 0; ok && c0 < nrows; c0 += d.chunk_rows) {
+  auto chunk_src = [&](int c0, const unsigned char*& s0, unsigned& b0, const unsigned char*& s1, unsigned& b1) {
+    const int nn = min(d.chunk_rows, nrows - c0) * C;
+    const long long ee = t.e0 + (long long)c0 * C;
+    if (MUON) { s0 = sig + ee * S::BYTES; b0 = (unsigned)nn * S::BYTES; s1 = g + ee * E::BYTES; b1 = (unsigned)nn * E::BYTES; }
+    else { s0 = g + ee * E::BYTES; b0 = (unsigned)nn * E::BYTES; s1 = m_ptr<MK>(d, ee); b1 = m_bytes<MK>(nn); }
+  };
+  auto issue = [&](int c0, int b) {
+    const unsigned char *s0, *s1; unsigned b0, b1;
+    chunk_src(c0, s0, b0, s1, b1);
+    stage_issue(st, b, s0, b0, s1, b1, tid);
+  };
+  if (ok && st.nbuf == 2) issue(0, 0);
+  for (int c0 = 0, ci = 0; ok && c0 < nrows; c0 += d.chunk_rows, ++ci) {
     const int nrc = min(d.chunk_rows, nrows - c0);
     const int n = nrc * C;
     const long long e0 = t.e0 + (long long)c0 * C;
-    if (MUON) ok = stage_in(st, sig + e0 * S::BYTES, (unsigned)n * S::BYTES, g + e0 * E::BYTES, (unsigned)n * E::BYTES, pv.status, tid);
-    else ok = stage_in(st, g + e0 * E::BYTES, (unsigned)n * E::BYTES, m_ptr<MK>(d, e0), m_bytes<MK>(n), pv.status, tid);
+    const int b = st.nbuf == 2 ? (ci & 1) : 0;
+    if (st.nbuf == 1) issue(c0, 0);
+    else if (c0 + d.chunk_rows < nrows) issue(c0 + d.chunk_rows, b ^ 1);
+    {
+      const unsigned char *s0, *s1; unsigned b0, b1;
+      chunk_src(c0, s0, b0, s1, b1);
+      ok = stage_wait(st, b, s0, b0, s1, b1, pv.status);
+    }
     if (!ok) break;
     for (int r = warp; r < nrc; r += AT / 32) {
       const float mu = gc ? row_mean<PT>(st.g_s + (size_t)r * C * E::BYTES, C, lane) : 0.0f;
@@ -696,7 +736,8 @@ __device__ void ada_flat(const PlanView& pv, const AdaDev& hp, const Task& t, St
   const unsigned char* g = reinterpret_cast<const unsigned char*>(pv.grads[t.tensor]);
   if (g == nullptr) return;
   const int n = t.n;
-  if (!stage_in(st, g, (unsigned)n * E::BYTES, m_ptr<MK>(d, 0), m_bytes<MK>(n), pv.status, tid)) return;
+  stage_issue(st, 0, g, (unsigned)n * E::BYTES, m_ptr<MK>(d, 0), m_bytes<MK>(n), tid);
+  if (!stage_wait(st, 0, g, (unsigned)n * E::BYTES, m_ptr<MK>(d, 0), m_bytes<MK>(n), pv.status)) return;
   float* f_s = sm.x_s;  // u, then the new momentum
   float* v = d.stat_a;
   // 1. second moment, raw update, its rms
@@ -828,21 +869,34 @@ __global__ void __launch_bounds__(AT, 1) adakaon_kernel(PlanView pv, AdaDev hp, 
   __shared__ unsigned rowmax_s[MAX_TASK_ROWS];
   __shared__ float scale_s[MAX_TASK_ROWS];
   __shared__ double red[AT / 32];
-  __shared__ __align__(8) uint64_t bar;
+  __shared__ __align__(8) uint64_t bar[2];
   __shared__ int next_s[2];
   const int tid = threadIdx.x;
-  Stage st{dyn, dyn + (size_t)CAP * Elems<PT>::BYTES, &bar, 0u};
-  // region after the gradient stage: STATS overlays its column accumulators on the momentum bytes;
-  // COUNT/APPLY/FLAT keep the momentum bytes and put cfac / the flat buffer after them.
-  AdaSmem sm_stats{mean_s, rfac_s, rowmax_s, scale_s, reinterpret_cast<float*>(st.m_s), red};
-  AdaSmem sm_rows{mean_s, rfac_s, rowmax_s, scale_s, reinterpret_cast<float*>(st.m_s + x_off_rows), red};
+  // dynamic shared memory: [g buffer 0][g buffer 1][m buffer 0][m buffer 1][cfac / flat buffer];
+  // x_off_rows = bytes of one m buffer (a multiple of 128) | 1 when there is room for two buffer sets.
+  const int nbuf = (x_off_rows & 1) + 1;
+  const size_t mcap = (size_t)(x_off_rows & ~127);
+  const size_t gcap = (size_t)CAP * Elems<typename std::conditional<MUON, __nv_bfloat16, PT>::type>::BYTES;
+  const size_t gcap_any = gcap > (size_t)CAP * Elems<PT>::BYTES ? gcap : (size_t)CAP * Elems<PT>::BYTES;
+  Stage st;
+  st.nbuf = nbuf;
+  st.gbuf[0] = dyn; st.gbuf[1] = nbuf == 2 ? dyn + gcap_any : dyn;
+  unsigned char* mbase = dyn + (size_t)nbuf * gcap_any;
+  st.mbuf[0] = mbase; st.mbuf[1] = nbuf == 2 ? mbase + mcap : mbase;
+  st.bar[0] = &bar[0]; st.bar[1] = &bar[1];
+  st.parity[0] = st.parity[1] = 0u;
+  st.g_s = st.gbuf[0]; st.m_s = st.mbuf[0];
+  // STATS stages gradients only and overlays its column accumulators on the momentum buffers;
+  // COUNT/APPLY/FLAT put cfac / the flat buffer after them.
+  AdaSmem sm_stats{mean_s, rfac_s, rowmax_s, scale_s, reinterpret_cast<float*>(mbase), red};
+  AdaSmem sm_rows{mean_s, rfac_s, rowmax_s, scale_s, reinterpret_cast<float*>(mbase + (size_t)nbuf * mcap), red};
   auto claim_next = [&](int slot) {
     if (tid == 0) {
       const unsigned s = *reinterpret_cast<volatile unsigned*>(pv.status);
       next_s[slot] = s ? 0x7fffffff : (int)atomicAdd(pv.task_counter, 1u);
     }
   };
-  if (tid == 0) mbar_init(&bar, 1);
+  if (tid == 0) { mbar_init(&bar[0], 1); mbar_init(&bar[1], 1); }
   claim_next(0);
   __syncthreads();
   int slot = 0;
@@ -943,13 +997,20 @@ size_t x_offset_rows(const kaon_plan* pl) {
 int configure_launch_adakaon(kaon_plan* pl, const cudaDeviceProp& prop, int max_cols) {
   const size_t esz = pl->param_dtype == KAON_DT_BF16 ? 2 : 4;
   const size_t xr = x_offset_rows(pl);
-  const size_t region = std::max<size_t>(xr + (size_t)max_cols * 4, (size_t)max_cols * 8);
-  pl->smem_bytes = (size_t)CAP * esz + region + 128;
+  // the gradient stage holds the parameter dtype, or bf16 for AdaMuon's orthogonalised signal (FLAT still
+  // stages the gradient itself there): size it for the larger
+  const size_t gcap = (size_t)CAP * esz;
+  auto total = [&](int nbuf) {
+    const size_t region = std::max<size_t>((size_t)nbuf * xr + (size_t)max_cols * 4, (size_t)max_cols * 8);
+    return (size_t)nbuf * gcap + region + 128;
+  };
   pl->threads = AT;
   AdaKernel k = pick_ada(pl->param_dtype, pl->momentum_kind, pl->optimizer == KAON_OPT_ADAMUON);
   if (!k) return fail(KAON_E_INVALID, "no Adakaon kernel for this dtype combination");
   cudaFuncAttributes fa;
   KAON_CUDA(cudaFuncGetAttributes(&fa, (const void*)k));
+  pl->double_buffer = total(2) + fa.sharedSizeBytes <= (size_t)prop.sharedMemPerBlockOptin;
+  pl->smem_bytes = total(pl->double_buffer ? 2 : 1);
   if (pl->smem_bytes + fa.sharedSizeBytes > (size_t)prop.sharedMemPerBlockOptin)
     return fail(KAON_E_UNSUPPORTED, "Adakaon kernel needs %zu + %zu bytes of shared memory for rows of %d elements (limit %zu)",
                 pl->smem_bytes, (size_t)fa.sharedSizeBytes, max_cols, (size_t)prop.sharedMemPerBlockOptin);
@@ -995,7 +1056,7 @@ extern "C" int kaon_adakaon_step(kaon_plan* pl, const kaon_adakaon_hparams* h, u
   else { v.tasks = pl->d_tasks_main; v.n_tasks = pl->n_tasks_main; }
   KAON_CUDA(cudaMemsetAsync(v.task_counter, 0, pl->counters_bytes - sizeof(unsigned), s));
   AdaKernel k = pick_ada(pl->param_dtype, pl->momentum_kind, false);
-  k<<<pl->grid, AT, pl->smem_bytes, s>>>(v, hp, (int)x_offset_rows(pl));
+  k<<<pl->grid, AT, pl->smem_bytes, s>>>(v, hp, (int)x_offset_rows(pl) | (pl->double_buffer ? 1 : 0));
   KAON_CUDA(cudaGetLastError());
   pl->launches += 1;
   return KAON_OK;

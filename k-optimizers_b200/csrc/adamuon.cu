@@ -288,7 +288,7 @@ extern "C" int kaon_adamuon_step(kaon_plan* pl, const kaon_adamuon_hparams* h, v
   else { v.tasks = pl->d_tasks_main; v.n_tasks = pl->n_tasks_main; }
   AdaKernel k = pick_ada(pl->param_dtype, pl->momentum_kind, true);
   if (!k) return fail(KAON_E_INVALID, "no AdaMuon kernel for this dtype combination");
-  k<<<pl->grid, ADA_THREADS, pl->smem_bytes, s>>>(v, hp, (int)x_offset_rows(pl));
+  k<<<pl->grid, ADA_THREADS, pl->smem_bytes, s>>>(v, hp, (int)x_offset_rows(pl) | (pl->double_buffer ? 1 : 0));
   KAON_CUDA(cudaGetLastError());
   pl->launches += 1;
   return KAON_OK;

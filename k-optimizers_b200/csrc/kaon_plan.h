@@ -108,6 +108,7 @@ struct kaon_plan {
   kaon::Task* d_tasks_nocount = nullptr;  // Adakaon work list without the COUNT items (cautious off)
   int n_tasks_nocount = 0;
   int threads = 0;
+  bool double_buffer = false;  // Adakaon/AdaMuon: shared memory holds two staging buffer sets
   std::vector<kaon::DevTensor> h_tensors;   // host copy of the table
   std::vector<const void*> h_grads;         // host copy of the gradient-pointer column
   // AdaMuon only (built lazily by the first step)

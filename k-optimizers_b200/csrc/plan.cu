@@ -161,6 +161,7 @@ int kaon_plan_create(kaon_plan** out, int optimizer, int param_dtype, int moment
       if (t.rows <= 0) {
         if (t.numel > CAP) { delete pl; return fail(KAON_E_UNSUPPORTED, "tensor %d: a 1-D tensor of %lld elements exceeds %d (Adakaon/AdaMuon step 1-D tensors in one work item)", i, t.numel, CAP); }
         stages[i].resize(1);
+        max_cols = std::max<int>(max_cols, (int)t.numel);  // FLAT keeps the whole tensor as fp32 in shared memory
         Task f = per[i][0]; f.phase = PH_ADA_FLAT; stages[i][0].push_back(f);
         t.aux_off = aux_floats; t.n_stats = 0; t.n_strips = 0; t.chunk_rows = 0;
         aux_floats += 8;
