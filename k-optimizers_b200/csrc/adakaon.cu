@@ -180,6 +180,32 @@ __device__ __forceinline__ float row_mean(const unsigned char* rowp, int C, int 
   return E::IS_BF16 ? round_bf16(mean) : mean;
 }
 
+// One warp's share of a row reduction when a row is split over G warps (part = 0..G-1): the plain sum
+// (SQ = false, for the centralization mean) or the sum of (x - mu)^2 + eps1 (SQ = true).
+template <typename PT, bool SQ>
+__device__ __forceinline__ float row_part(const unsigned char* rowp, int C, int part, int G, int lane,
+                                          float mu, bool gc, bool has_eps, float eps1) {
+  using E = Elems<PT>;
+  float s = 0.0f;
+  auto term = [&](float x) -> float {
+    if (!SQ) return x;
+    float y = x;
+    if (gc) { y = __fsub_rn(x, mu); if (E::IS_BF16) y = round_bf16(y); }
+    float sq = __fmul_rn(y, y);
+    return has_eps ? __fadd_rn(sq, eps1) : sq;
+  };
+  if ((C & 7) == 0) {
+    for (int v = part * 32 + lane; v < (C >> 3); v += G * 32) {
+      float x[8];
+      E::load8(rowp + (size_t)v * 8 * E::BYTES, x);
+      s += ((term(x[0]) + term(x[1])) + (term(x[2]) + term(x[3]))) + ((term(x[4]) + term(x[5])) + (term(x[6]) + term(x[7])));
+    }
+  } else {
+    for (int i = part * 32 + lane; i < C; i += G * 32) s += term(E::load1(rowp, i));
+  }
+  return warp_sum(s);
+}
+
 template <typename PT>
 __device__ __forceinline__ float centered(float g, float mu, bool gc) {
   if (!gc) return g;
@@ -196,6 +222,7 @@ struct AdaSmem {
   float* scale_s;    // [MAX_TASK_ROWS] int8: old row scales
   float* x_s;        // region X as floats (column accumulators / cfac / flat buffer)
   double* red;       // [AT/32]
+  float* part_s;     // [AT/32] per-warp partial sums of split rows
 };
 
 // ST = element type of the signal whose second moment is tracked: the gradient (Adakaon) or the
@@ -231,6 +258,41 @@ __device__ void ada_stats(const PlanView& pv, const AdaDev& hp, const Task& t, S
     ok = stage_wait(st, b, g + e0 * E::BYTES, (unsigned)(nrc * C) * E::BYTES, nullptr, 0u, pv.status);
     if (!ok) break;
     // rows: centralization mean, mean of g^2+eps1, row EMA
+    constexpr int NW = AT / 32;
+    if (nrc < NW) {
+      // fewer rows than warps (wide rows): split every row over G warps, combine in warp order
+      const int G = NW / nrc, r = warp / G, part = warp % G;
+      const bool act = r < nrc;
+      const unsigned char* rowp = st.g_s + (size_t)(act ? r : 0) * C * E::BYTES;
+      if (gc) {
+        const float ps = act ? row_part<PT, false>(rowp, C, part, G, lane, 0.0f, false, false, 0.0f) : 0.0f;
+        if (lane == 0) sm.part_s[warp] = ps;
+        __syncthreads();
+        if (tid < nrc) {
+          float tot = 0.0f;
+          for (int q = 0; q < G; ++q) tot += sm.part_s[tid * G + q];
+          const float mean = __fdiv_rn(tot, (float)C);
+          sm.mean_s[tid] = E::IS_BF16 ? round_bf16(mean) : mean;
+        }
+        __syncthreads();
+      } else if (tid < nrc) {
+        sm.mean_s[tid] = 0.0f;
+      }
+      const float mu = (gc && act) ? sm.mean_s[r] : 0.0f;
+      const float ps2 = act ? row_part<PT, true>(rowp, C, part, G, lane, mu, gc, hp.has_eps != 0, hp.eps1) : 0.0f;
+      if (lane == 0) sm.part_s[warp] = ps2;
+      __syncthreads();
+      if (tid < nrc) {
+        float tot = 0.0f;
+        for (int q = 0; q < G; ++q) tot += sm.part_s[tid * G + q];
+        const int row = t.row0 + c0 + tid;
+        const float mean = __fdiv_rn(tot, (float)C);
+        const float rn = lerp_torch(d.stat_a[row], mean, hp.w2, hp.w2m1, hp.small_w2 != 0);
+        d.stat_a[row] = rn;
+        sm.rfac_s[tid] = __fdiv_rn(1.0f, rn);
+        rowsum += (double)rn;
+      }
+    } else
     for (int r = warp; r < nrc; r += AT / 32) {
       const unsigned char* rowp = st.g_s + (size_t)r * C * E::BYTES;
       const float mu = gc ? row_mean<PT>(rowp, C, lane) : 0.0f;
@@ -477,15 +539,31 @@ __device__ void ada_rows(const PlanView& pv, const AdaDev& hp, const Task& t, St
       ok = stage_wait(st, b, s0, b0, s1, b1, pv.status);
     }
     if (!ok) break;
+    constexpr int NW = AT / 32;
+    if (gc && nrc < NW) {  // wide rows: split each row's mean over G warps
+      const int G = NW / nrc, r = warp / G, part = warp % G;
+      const float ps = r < nrc ? row_part<PT, false>(st.g_s + (size_t)r * C * E::BYTES, C, part, G, lane, 0.0f, false, false, 0.0f) : 0.0f;
+      if (lane == 0) sm.part_s[warp] = ps;
+      __syncthreads();
+      if (tid < nrc) {
+        float tot = 0.0f;
+        for (int q = 0; q < G; ++q) tot += sm.part_s[tid * G + q];
+        const float mean = __fdiv_rn(tot, (float)C);
+        sm.mean_s[tid] = E::IS_BF16 ? round_bf16(mean) : mean;
+      }
+      __syncthreads();
+    }
+    const bool means_done = gc && nrc < NW;
     for (int r = warp; r < nrc; r += AT / 32) {
-      const float mu = gc ? row_mean<PT>(st.g_s + (size_t)r * C * E::BYTES, C, lane) : 0.0f;
+      const float mu = means_done ? sm.mean_s[r] : (gc ? row_mean<PT>(st.g_s + (size_t)r * C * E::BYTES, C, lane) : 0.0f);
       if (lane == 0) {
         const int row = t.row0 + c0 + r;
         sm.mean_s[r] = mu;
         sm.rfac_s[r] = rsqrt_torch(__fdiv_rn(__ldcg(d.stat_a + row), rowmean));
         if constexpr (MK == KAON_M_INT8) {
           sm.scale_s[r] = d.m_scale[row];
-          sm.rowmax_s[r] = 0u;
+          // with cautious on, COUNT has already found the row's absmax of the new momentum
+          sm.rowmax_s[r] = (APPLY && hp.cautious) ? __ldcg(reinterpret_cast<const unsigned*>(pv.aux + aux_rowmax(d)) + row) : 0u;
         }
       }
     }
@@ -599,7 +677,7 @@ __device__ void ada_rows(const PlanView& pv, const AdaDev& hp, const Task& t, St
       return kept;
     };
 
-    if constexpr (APPLY && MK == KAON_M_INT8) {  // row absmax of the new momentum first
+    if constexpr (APPLY && MK == KAON_M_INT8) if (!hp.cautious) {  // row absmax of the new momentum first
       for (int v = tid; v < nvec; v += AT) {
         const int cnt = min(8, n - v * 8);
         float gv[8], mo[8], mn[8], pc[8], dl[8];
@@ -627,6 +705,18 @@ __device__ void ada_rows(const PlanView& pv, const AdaDev& hp, const Task& t, St
       }
       if constexpr (!APPLY) {
         kept_local += __popc(kept);
+        if constexpr (MK == KAON_M_INT8) {  // leave the row absmax of the new momentum for APPLY
+          if (cnt > 0) {
+            if (row_uniform) {
+              float a = 0.0f;
+#pragma unroll
+              for (int k = 0; k < 8; ++k) a = fmaxf(a, fabsf(mn[k]));
+              atomicMax(sm.rowmax_s + row_of((unsigned)v * 8u, d), __float_as_uint(a));
+            } else {
+              for (int k = 0; k < cnt; ++k) atomicMax(sm.rowmax_s + row_of((unsigned)(v * 8 + k), d), __float_as_uint(fabsf(mn[k])));
+            }
+          }
+        }
       } else {
         float md[8];  // the momentum as stored (decoded), for the Nekaon climb
         // ---- encode + store the new momentum ----
@@ -712,6 +802,11 @@ __device__ void ada_rows(const PlanView& pv, const AdaDev& hp, const Task& t, St
       }
     }
     __syncthreads();
+    if constexpr (!APPLY && MK == KAON_M_INT8) {
+      unsigned* rm = reinterpret_cast<unsigned*>(pv.aux + aux_rowmax(d)) + t.row0 + c0;
+      for (int r = tid; r < nrc; r += AT) rm[r] = sm.rowmax_s[r];
+      __syncthreads();
+    }
   }
   if constexpr (!APPLY) {
     const unsigned tot = block_sum_u(kept_local, sm.red, tid);
@@ -869,6 +964,7 @@ __global__ void __launch_bounds__(AT, 1) adakaon_kernel(PlanView pv, AdaDev hp, 
   __shared__ unsigned rowmax_s[MAX_TASK_ROWS];
   __shared__ float scale_s[MAX_TASK_ROWS];
   __shared__ double red[AT / 32];
+  __shared__ float part_s[AT / 32];
   __shared__ __align__(8) uint64_t bar[2];
   __shared__ int next_s[2];
   const int tid = threadIdx.x;
@@ -888,8 +984,8 @@ __global__ void __launch_bounds__(AT, 1) adakaon_kernel(PlanView pv, AdaDev hp, 
   st.g_s = st.gbuf[0]; st.m_s = st.mbuf[0];
   // STATS stages gradients only and overlays its column accumulators on the momentum buffers;
   // COUNT/APPLY/FLAT put cfac / the flat buffer after them.
-  AdaSmem sm_stats{mean_s, rfac_s, rowmax_s, scale_s, reinterpret_cast<float*>(mbase), red};
-  AdaSmem sm_rows{mean_s, rfac_s, rowmax_s, scale_s, reinterpret_cast<float*>(mbase + (size_t)nbuf * mcap), red};
+  AdaSmem sm_stats{mean_s, rfac_s, rowmax_s, scale_s, reinterpret_cast<float*>(mbase), red, part_s};
+  AdaSmem sm_rows{mean_s, rfac_s, rowmax_s, scale_s, reinterpret_cast<float*>(mbase + (size_t)nbuf * mcap), red, part_s};
   auto claim_next = [&](int slot) {
     if (tid == 0) {
       const unsigned s = *reinterpret_cast<volatile unsigned*>(pv.status);

@@ -51,7 +51,7 @@ struct DevTensor {
   int n_count;          // COUNT items
   long long aux_off;    // float index of this tensor's scratch in `aux`:
                         //   colpart[n_stats][2][cols] | cfac[cols] | rowpart[n_stats] (double) |
-                        //   tpart[n_strips] (double) | scal[4] = {rowmean, divisor, rms, -}
+                        //   tpart[n_strips] (double) | scal[4] = {rowmean, divisor, rms, -} | rowmax[rows]
 };
 
 // float offsets inside a tensor's aux block
@@ -59,7 +59,9 @@ __host__ __device__ inline long long aux_cfac(const DevTensor& d) { return d.aux
 __host__ __device__ inline long long aux_rowpart(const DevTensor& d) { return (aux_cfac(d) + d.cols + 1) / 2 * 2; }
 __host__ __device__ inline long long aux_tpart(const DevTensor& d) { return aux_rowpart(d) + 2ll * d.n_stats; }
 __host__ __device__ inline long long aux_scal(const DevTensor& d) { return aux_tpart(d) + 2ll * d.n_strips; }
-__host__ __device__ inline long long aux_size(const DevTensor& d) { return aux_scal(d) + 4 - d.aux_off; }
+// int8 momentum: bits of each row's absmax of the new momentum, left by COUNT for APPLY
+__host__ __device__ inline long long aux_rowmax(const DevTensor& d) { return aux_scal(d) + 4; }
+__host__ __device__ inline long long aux_size(const DevTensor& d) { return aux_rowmax(d) + d.rows - d.aux_off; }
 
 struct Task {
   int tensor;
