@@ -272,7 +272,9 @@ __device__ void ada_stats(const PlanView& pv, const AdaDev& hp, const Task& t, S
           float tot = 0.0f;
           for (int q = 0; q < G; ++q) tot += sm.part_s[tid * G + q];
           const float mean = __fdiv_rn(tot, (float)C);
-          sm.mean_s[tid] = E::IS_BF16 ? round_bf16(mean) : mean;
+          const float mr = E::IS_BF16 ? round_bf16(mean) : mean;
+          sm.mean_s[tid] = mr;
+          pv.aux[aux_mean(d) + t.row0 + c0 + tid] = mr;
         }
         __syncthreads();
       } else if (tid < nrc) {
@@ -324,6 +326,7 @@ __device__ void ada_stats(const PlanView& pv, const AdaDev& hp, const Task& t, S
         const float rn = lerp_torch(d.stat_a[row], mean, hp.w2, hp.w2m1, hp.small_w2 != 0);
         d.stat_a[row] = rn;
         sm.mean_s[r] = mu;
+        if (gc) pv.aux[aux_mean(d) + row] = mu;
         sm.rfac_s[r] = __fdiv_rn(1.0f, rn);
         rowsum += (double)rn;
       }
@@ -533,44 +536,51 @@ __device__ void ada_rows(const PlanView& pv, const AdaDev& hp, const Task& t, St
     const int b = st.nbuf == 2 ? (ci & 1) : 0;
     if (st.nbuf == 1) issue(c0, 0);
     else if (c0 + d.chunk_rows < nrows) issue(c0 + d.chunk_rows, b ^ 1);
+    // per-row scalars of this chunk: loads go out before the wait for the staged data
+    constexpr int RPT = MAX_TASK_ROWS / AT;  // rows per thread at most
+    float pre_mu[RPT], pre_row[RPT], pre_sc[RPT];
+    unsigned pre_max[RPT];
+#pragma unroll
+    for (int j = 0; j < RPT; ++j) {
+      pre_mu[j] = 0.0f; pre_row[j] = 1.0f; pre_sc[j] = 1.0f; pre_max[j] = 0u;
+      const int r = tid + j * AT;
+      if (r < nrc) {
+        const int row = t.row0 + c0 + r;
+        if (gc) pre_mu[j] = __ldcg(pv.aux + aux_mean(d) + row);
+        pre_row[j] = __ldcg(d.stat_a + row);
+        if constexpr (MK == KAON_M_INT8) {
+          pre_sc[j] = d.m_scale[row];
+          // with cautious on, COUNT has already found the row's absmax of the new momentum
+          if (APPLY && hp.cautious) pre_max[j] = __ldcg(reinterpret_cast<const unsigned*>(pv.aux + aux_rowmax(d)) + row);
+        }
+      }
+    }
+    float pre_blk = 1.0f;
+    if constexpr (MK == KAON_M_4BIT) {  // old block scales of the chunk (<= CAP/128 = 128 blocks)
+      const int nblk = d.block == 128u ? (n + 127) >> 7 : 1;
+      if (tid < nblk) pre_blk = d.m_scale[(d.block == 128u ? (e0 >> 7) : 0) + tid];
+    }
     {
       const unsigned char *s0, *s1; unsigned b0, b1;
       chunk_src(c0, s0, b0, s1, b1);
       ok = stage_wait(st, b, s0, b0, s1, b1, pv.status);
     }
     if (!ok) break;
-    constexpr int NW = AT / 32;
-    if (gc && nrc < NW) {  // wide rows: split each row's mean over G warps
-      const int G = NW / nrc, r = warp / G, part = warp % G;
-      const float ps = r < nrc ? row_part<PT, false>(st.g_s + (size_t)r * C * E::BYTES, C, part, G, lane, 0.0f, false, false, 0.0f) : 0.0f;
-      if (lane == 0) sm.part_s[warp] = ps;
-      __syncthreads();
-      if (tid < nrc) {
-        float tot = 0.0f;
-        for (int q = 0; q < G; ++q) tot += sm.part_s[tid * G + q];
-        const float mean = __fdiv_rn(tot, (float)C);
-        sm.mean_s[tid] = E::IS_BF16 ? round_bf16(mean) : mean;
-      }
-      __syncthreads();
-    }
-    const bool means_done = gc && nrc < NW;
-    for (int r = warp; r < nrc; r += AT / 32) {
-      const float mu = means_done ? sm.mean_s[r] : (gc ? row_mean<PT>(st.g_s + (size_t)r * C * E::BYTES, C, lane) : 0.0f);
-      if (lane == 0) {
-        const int row = t.row0 + c0 + r;
-        sm.mean_s[r] = mu;
-        sm.rfac_s[r] = rsqrt_torch(__fdiv_rn(__ldcg(d.stat_a + row), rowmean));
+#pragma unroll
+    for (int j = 0; j < RPT; ++j) {
+      const int r = tid + j * AT;
+      if (r < nrc) {
+        sm.mean_s[r] = pre_mu[j];
+        sm.rfac_s[r] = rsqrt_torch(__fdiv_rn(pre_row[j], rowmean));
         if constexpr (MK == KAON_M_INT8) {
-          sm.scale_s[r] = d.m_scale[row];
-          // with cautious on, COUNT has already found the row's absmax of the new momentum
-          sm.rowmax_s[r] = (APPLY && hp.cautious) ? __ldcg(reinterpret_cast<const unsigned*>(pv.aux + aux_rowmax(d)) + row) : 0u;
+          sm.scale_s[r] = pre_sc[j];
+          sm.rowmax_s[r] = pre_max[j];
         }
       }
     }
-    if constexpr (MK == KAON_M_4BIT) {  // old block scales of the chunk
+    if constexpr (MK == KAON_M_4BIT) {
       const int nblk = d.block == 128u ? (n + 127) >> 7 : 1;
-      const long long b0 = d.block == 128u ? (e0 >> 7) : 0;
-      for (int b = tid; b < nblk; b += AT) sm.scale_s[b] = d.m_scale[b0 + b];
+      if (tid < nblk) sm.scale_s[tid] = pre_blk;
     }
     __syncthreads();
     unsigned char* pbase = reinterpret_cast<unsigned char*>(d.p) + e0 * E::BYTES;

@@ -51,7 +51,7 @@ struct DevTensor {
   int n_count;          // COUNT items
   long long aux_off;    // float index of this tensor's scratch in `aux`:
                         //   colpart[n_stats][2][cols] | cfac[cols] | rowpart[n_stats] (double) |
-                        //   tpart[n_strips] (double) | scal[4] = {rowmean, divisor, rms, -} | rowmax[rows]
+                        //   tpart[n_strips] (double) | scal[4] = {rowmean, divisor, rms, -} | rowmax[rows] | mean[rows]
 };
 
 // float offsets inside a tensor's aux block
@@ -61,7 +61,9 @@ __host__ __device__ inline long long aux_tpart(const DevTensor& d) { return aux_
 __host__ __device__ inline long long aux_scal(const DevTensor& d) { return aux_tpart(d) + 2ll * d.n_strips; }
 // int8 momentum: bits of each row's absmax of the new momentum, left by COUNT for APPLY
 __host__ __device__ inline long long aux_rowmax(const DevTensor& d) { return aux_scal(d) + 4; }
-__host__ __device__ inline long long aux_size(const DevTensor& d) { return aux_rowmax(d) + d.rows - d.aux_off; }
+// centralization mean of every row, left by STATS for COUNT / APPLY
+__host__ __device__ inline long long aux_mean(const DevTensor& d) { return aux_rowmax(d) + d.rows; }
+__host__ __device__ inline long long aux_size(const DevTensor& d) { return aux_mean(d) + d.rows - d.aux_off; }
 
 struct Task {
   int tensor;
