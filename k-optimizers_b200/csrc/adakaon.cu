@@ -255,8 +255,15 @@ __device__ void ada_stats(const PlanView& pv, const AdaDev& hp, const Task& t, S
     const int b = st.nbuf == 2 ? (ci & 1) : 0;
     if (st.nbuf == 1) issue(c0, 0);
     else if (c0 + d.chunk_rows < nrows) issue(c0 + d.chunk_rows, b ^ 1);
+    const bool pre_rows = nrc <= AT;  // old row statistics: load before the wait, hand over through rfac_s
+    float pre_old = 0.0f;
+    if (pre_rows && tid < nrc) pre_old = d.stat_a[t.row0 + c0 + tid];
     ok = stage_wait(st, b, g + e0 * E::BYTES, (unsigned)(nrc * C) * E::BYTES, nullptr, 0u, pv.status);
     if (!ok) break;
+    if (pre_rows) {
+      if (tid < nrc) sm.rfac_s[tid] = pre_old;
+      __syncthreads();
+    }
     // rows: centralization mean, mean of g^2+eps1, row EMA
     constexpr int NW = AT / 32;
     if (nrc < NW) {
@@ -289,7 +296,7 @@ __device__ void ada_stats(const PlanView& pv, const AdaDev& hp, const Task& t, S
         for (int q = 0; q < G; ++q) tot += sm.part_s[tid * G + q];
         const int row = t.row0 + c0 + tid;
         const float mean = __fdiv_rn(tot, (float)C);
-        const float rn = lerp_torch(d.stat_a[row], mean, hp.w2, hp.w2m1, hp.small_w2 != 0);
+        const float rn = lerp_torch(pre_old, mean, hp.w2, hp.w2m1, hp.small_w2 != 0);
         d.stat_a[row] = rn;
         sm.rfac_s[tid] = __fdiv_rn(1.0f, rn);
         rowsum += (double)rn;
@@ -323,7 +330,7 @@ __device__ void ada_stats(const PlanView& pv, const AdaDev& hp, const Task& t, S
       if (lane == 0) {
         const int row = t.row0 + c0 + r;
         const float mean = __fdiv_rn(s, (float)C);
-        const float rn = lerp_torch(d.stat_a[row], mean, hp.w2, hp.w2m1, hp.small_w2 != 0);
+        const float rn = lerp_torch(pre_rows ? sm.rfac_s[r] : d.stat_a[row], mean, hp.w2, hp.w2m1, hp.small_w2 != 0);
         d.stat_a[row] = rn;
         sm.mean_s[r] = mu;
         if (gc) pv.aux[aux_mean(d) + row] = mu;
@@ -589,6 +596,22 @@ __device__ void ada_rows(const PlanView& pv, const AdaDev& hp, const Task& t, St
 
     // One vector of the chain: fills g', the new momentum mn[], the pre-update weights pc[] (after the
     // Nekaon removal) and delta dl[]; returns the kept bits.
+    // the weights this thread will touch in this chunk: all loads go out before the first use
+    constexpr int VPT = CAP / 8 / AT;
+    constexpr int PW = E::BYTES / 2;  // 16-byte words per eight weights
+    uint4 pre_p[VPT * PW];
+    const bool preload = need_p && row_uniform && (n & 7) == 0;
+    if (preload) {
+#pragma unroll
+      for (int j = 0; j < VPT; ++j) {
+        const int v = tid + j * AT;
+        if (v < nvec) {
+#pragma unroll
+          for (int w = 0; w < PW; ++w) pre_p[j * PW + w] = reinterpret_cast<const uint4*>(pbase + (size_t)v * 8 * E::BYTES)[w];
+        }
+      }
+    }
+
     auto chain8 = [&](int v, int cnt, float gv[8], float mo[8], float mn[8], float pc[8], float dl[8]) -> unsigned {
       if (row_uniform && cnt == 8) {
         // full vector inside one row: one row lookup, vector loads, no guards
@@ -606,8 +629,10 @@ __device__ void ada_rows(const PlanView& pv, const AdaDev& hp, const Task& t, St
 #pragma unroll
           for (int k = 0; k < 8; ++k) mo[k] = 0.0f;
         } else decode8<MK>(st.m_s, v, 8, 1.0f, mo);
-        if (need_p) E::load8(pbase + (size_t)v * 8 * E::BYTES, pc);
-        else {
+        if (need_p) {
+          if (preload) E::load8(&pre_p[((v - tid) / AT) * PW], pc);
+          else E::load8(pbase + (size_t)v * 8 * E::BYTES, pc);
+        } else {
 #pragma unroll
           for (int k = 0; k < 8; ++k) pc[k] = 0.0f;
         }
@@ -966,6 +991,11 @@ __device__ void ada_flat(const PlanView& pv, const AdaDev& hp, const Task& t, St
 
 // ----------------------------------------------------------------------------- kernels
 
+#ifdef KAON_PHASE_TIMING
+// development aid (off unless compiled in): busy cycles and item counts per work-item kind
+__device__ unsigned long long g_phase_cycles[16];
+#endif
+
 template <typename PT, int MK, bool MUON>
 __global__ void __launch_bounds__(AT, 1) adakaon_kernel(PlanView pv, AdaDev hp, int x_off_rows) {
   extern __shared__ __align__(128) unsigned char dyn[];
@@ -1010,6 +1040,9 @@ __global__ void __launch_bounds__(AT, 1) adakaon_kernel(PlanView pv, AdaDev hp, 
   while (cur < pv.n_tasks) {
     claim_next(slot ^ 1);
     const Task t = pv.tasks[cur];
+#ifdef KAON_PHASE_TIMING
+    const long long tk0 = clock64();
+#endif
     switch (t.phase) {
       case PH_ADA_STATS: ada_stats<typename std::conditional<MUON, __nv_bfloat16, PT>::type>(pv, hp, t, st, sm_stats, tid); break;
       case PH_ADA_FINAL: ada_final(pv, hp, t, sm_stats, tid); break;
@@ -1019,6 +1052,12 @@ __global__ void __launch_bounds__(AT, 1) adakaon_kernel(PlanView pv, AdaDev hp, 
       default: break;
     }
     __syncthreads();
+#ifdef KAON_PHASE_TIMING
+    if (tid == 0) {
+      atomicAdd(&g_phase_cycles[(t.phase - 10) & 7], (unsigned long long)(clock64() - tk0));
+      atomicAdd(&g_phase_cycles[8 + ((t.phase - 10) & 7)], 1ull);
+    }
+#endif
     slot ^= 1;
     cur = next_s[slot];
   }
@@ -1184,3 +1223,12 @@ extern "C" int kaon_msam_apply(kaon_plan* pl, double alpha, double bound, uint32
   pl->launches += 1;
   return KAON_OK;
 }
+
+#ifdef KAON_PHASE_TIMING
+extern "C" int kaon_debug_phase_cycles(unsigned long long* host16, int reset) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(host16, kaon::g_phase_cycles, sizeof(unsigned long long) * 16);
+  if (reset) { unsigned long long z[16] = {0}; cudaMemcpyToSymbol(kaon::g_phase_cycles, z, sizeof z); }
+  return 0;
+}
+#endif
