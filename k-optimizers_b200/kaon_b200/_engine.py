@@ -231,6 +231,21 @@ class FusedStepMixin:
                     if pl.set_grads(stream):
                         self._launch(pl, group, self._t, stream)
 
+    # ---- checkpoint extras: the stochastic-rounding stream position ----
+    def _extra_state(self, sd: dict[str, Any]) -> dict[str, Any]:
+        """Adds the one top-level key this build needs for bit-exact resume under stochastic rounding
+        (the step index and seed that key the noise).  torch's and the reference's loaders ignore it."""
+        sd["_kaon_b200"] = {"step": self._t, "sr_seed": self.sr_seed}
+        return sd
+
+    def _restore_extra(self, sd: dict[str, Any]) -> dict[str, Any]:
+        sd = dict(sd)
+        extra = sd.pop("_kaon_b200", None)
+        if extra is not None:
+            self._t = int(extra.get("step", 0))
+            self.sr_seed = extra.get("sr_seed")
+        return sd
+
     def check_device_status(self) -> None:
         """Synchronise and raise if a kernel reported a bounded wait that ran out."""
         for pl in self._plans.values():

@@ -132,8 +132,8 @@ class Adakaon(FusedStepMixin, AutoLRMixin, Optimizer):
         return loss
 
     def state_dict(self) -> dict[str, Any]:
-        return self._autolr_state_dict(super().state_dict())
+        return self._extra_state(self._autolr_state_dict(super().state_dict()))
 
     def load_state_dict(self, state_dict: dict[str, Any]) -> None:
-        self._autolr_load(state_dict, lambda sd: load_state_dict_exact(self, sd))
+        self._autolr_load(self._restore_extra(state_dict), lambda sd: load_state_dict_exact(self, sd))
         self._invalidate_plans()

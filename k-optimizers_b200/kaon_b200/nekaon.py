@@ -203,7 +203,7 @@ class Nekaon(AutoLRMixin, Optimizer):
         def _load(sd: dict[str, Any]) -> None:
             sd = dict(sd)
             sd.pop("msam", None)
-            self.inner.load_state_dict(sd)
+            self.inner.load_state_dict(sd)  # also restores the SR stream position ("_kaon_b200")
             self.param_groups = self.inner.param_groups
         self._autolr_load(state_dict, _load)
         self.base_optimizer = self.inner
