@@ -163,7 +163,8 @@ def run_ours(args):
     opt_name, kw, shape_key, bytes_per_param, wopt = WORKLOADS[args.workload]
     shapes = W.WORKLOADS[shape_key]()
     total = W.numel(shapes)
-    sw = ShardedWeights(shapes, world, rank, torch.bfloat16, dev)
+    fused_publish = world > 1 and args.publish == "fused"
+    sw = ShardedWeights(shapes, world, rank, torch.bfloat16, dev, symmetric=fused_publish)
     owned = sw.part.owned(rank)
     owned_elems = sum(sw.views[i].numel() for i in owned)
     gen = torch.Generator(device=dev).manual_seed(1234 + rank)
@@ -192,6 +193,7 @@ def run_ours(args):
         params.append(p)
     opt = getattr(kaon_b200, opt_name)(params, **kw)
     opt.sr_seed = 0
+    sw.attach(opt)  # fused publish: the step kernels store the weights into every rank's copy
 
     cos = wopt.get("cosine")
 
@@ -207,7 +209,7 @@ def run_ours(args):
         opt.step()
         if ev:
             ev[1].record()
-        sw.all_gather()
+        sw.publish()
         if ev:
             ev[2].record()
 
@@ -263,7 +265,7 @@ def run_ours(args):
             for p, g in zip(params, gsets[k % len(gsets)][1]):
                 p.grad = g
             opt.step()
-            sw.all_gather()
+            sw.publish()
             host_w.copy_(sw.shard, non_blocking=True)
 
         e2e_step(0)
@@ -322,14 +324,25 @@ def run_ours(args):
             "config": {"workload": args.workload, "optimizer": opt_name, "params": total, "tensors": len(shapes),
                        "param_dtype": "bf16", "momentum_dtype": kw.get("momentum_dtype"),
                        "sharding": "zero1" if world > 1 else "none",
+                       "publish": ("none" if world == 1 else
+                                   "peer stores fused into the step kernel + barrier" if fused_publish else
+                                   "nccl all_gather_into_tensor after the step"),
                        "l2": "inputs (18 GB per step) larger than L2; no flush needed"},
-            "step_kernel_ms": kern_ms, "all_gather_ms": gather_ms,
+            "step_kernel_ms": kern_ms, "publish_ms": gather_ms,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "frac_of_nominal_8TBs": achieved / 8000.0,
                          "peak_kind": f"{peak_kind} copy bandwidth", "traffic": None,
                          "bytes_per_param": bytes_per_param, "kernel": KERNEL_NAME[opt_name]},
             "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
         }
+        if fused_publish:
+            # the step kernel also pushes this rank's updated weights to the other ranks: its floor is
+            # the slower of the HBM pass and the NVLink egress (measured peer-copy bandwidth 770 GB/s)
+            out_bytes = 2.0 * (total / world) * (world - 1)
+            t_hbm, t_link = alg_bytes / (peak * 1e9), out_bytes / 770e9
+            line["nvlink"] = {"egress_bytes_per_rank": out_bytes, "achieved": out_bytes / (kern_ms * 1e-3) / 1e9,
+                              "peak": 770.0, "unit": "GB/s", "floor_ms": max(t_hbm, t_link) * 1e3,
+                              "frac_of_floor": max(t_hbm, t_link) * 1e3 / kern_ms}
         if ns_info is not None:
             tpeak = 1678.7
             try:
@@ -360,6 +373,8 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--publish", default="fused", choices=["fused", "allgather"],
+                    help="N>1: how the owned weights reach the other ranks")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

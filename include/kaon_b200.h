@@ -122,6 +122,18 @@ int64_t kaon_plan_launch_count(const kaon_plan* plan);
  * `stream`).  Diagnostic: lets a test compare the mask population with the oracle's. */
 int kaon_plan_kept_counts(kaon_plan* plan, uint32_t* host_out, int n, void* stream);
 
+/* Weight mirrors on other GPUs (no reference counterpart: the reference has no distributed code).
+ * After this call every step kernel of the plan stores each weight it writes at address a also at
+ * a + byte_delta[r] for r < n_peers: the ZeRO-1 publish of the owned weights is fused into the step
+ * as plain peer stores over NVLink, tile by tile, instead of an all-gather afterwards.
+ * byte_delta[r] = (address at which THIS process has rank r's weight buffer mapped) - (address of its
+ * own weight buffer); every tensor of the plan must lie in that buffer, the buffers must have the same
+ * layout on every rank, and each delta must be a multiple of 16.  The caller maps the peer memory (CUDA
+ * IPC, symmetric memory) and orders the ranks: no peer may read the weights, or start its next step,
+ * before a barrier that follows this step on every rank's stream.  n_peers = 0 switches mirroring off. */
+#define KAON_MAX_PEERS 7
+int kaon_plan_set_peers(kaon_plan* plan, const int64_t* byte_delta, int n_peers);
+
 /* ---- optimizer steps ---- */
 
 /* One Lion step over every tensor of the plan whose gradient is set.

@@ -84,18 +84,23 @@ __device__ __forceinline__ uint32_t noise_lane(const uint32_t nz[4], int k) {
   return (k & 1) ? (nz[k >> 1] >> 16) : (nz[k >> 1] & 0xffffu);
 }
 
+// Eight values out (weights: `pr` names the mirrors on other GPUs; state: none).
 template <typename PT>
-__device__ __forceinline__ void store8(void* pe, int cnt, const float v[8]) {
+__device__ __forceinline__ void store8(void* pe, int cnt, const float v[8], const Peers& pr) {
   if constexpr (Elems<PT>::IS_BF16) {
     if (cnt >= 8) {
-      *reinterpret_cast<uint4*>(pe) = make_uint4(pack_bf16_rn(v[0], v[1]), pack_bf16_rn(v[2], v[3]),
-                                                 pack_bf16_rn(v[4], v[5]), pack_bf16_rn(v[6], v[7]));
+      const uint4 out = make_uint4(pack_bf16_rn(v[0], v[1]), pack_bf16_rn(v[2], v[3]),
+                                   pack_bf16_rn(v[4], v[5]), pack_bf16_rn(v[6], v[7]));
+      *reinterpret_cast<uint4*>(pe) = out;
+      mirror16(pr, pe, out);
     } else {
       for (int k = 0; k < cnt; ++k)
         reinterpret_cast<uint16_t*>(pe)[k] = (uint16_t)(__float_as_uint(v[k]) >> 16);
+      mirror_copy(pr, pe, cnt * 2);
     }
   } else {
     for (int k = 0; k < cnt; ++k) reinterpret_cast<float*>(pe)[k] = v[k];
+    mirror_copy(pr, pe, cnt * 4);
   }
 }
 
@@ -808,8 +813,8 @@ __device__ void ada_rows(const PlanView& pv, const AdaDev& hp, const Task& t, St
 #pragma unroll
           for (int k = 0; k < 8; ++k) md[k] = mn[k];
           if (cnt > 0) {
-            if constexpr (MK == KAON_M_BF16) store8<__nv_bfloat16>((unsigned char*)d.m + e0 * 2 + (size_t)v * 16, cnt, mn);
-            else store8<float>((unsigned char*)d.m + e0 * 4 + (size_t)v * 32, cnt, mn);
+            if constexpr (MK == KAON_M_BF16) store8<__nv_bfloat16>((unsigned char*)d.m + e0 * 2 + (size_t)v * 16, cnt, mn, Peers{});
+            else store8<float>((unsigned char*)d.m + e0 * 4 + (size_t)v * 32, cnt, mn, Peers{});
           }
         } else {
 #pragma unroll
@@ -832,7 +837,7 @@ __device__ void ada_rows(const PlanView& pv, const AdaDev& hp, const Task& t, St
             for (int k = 0; k < 8; ++k)
               pc[k] = write_step<PT>(pc[k], climb_e(md[k], hp.a_climb, hp.b_climb), 1.0f, E::IS_BF16, noise_lane(nc, k));
           }
-          store8<PT>(pbase + (size_t)v * 8 * E::BYTES, cnt, pc);
+          store8<PT>(pbase + (size_t)v * 8 * E::BYTES, cnt, pc, pv.peers);
         }
       }
     }
@@ -964,8 +969,15 @@ __device__ void ada_flat(const PlanView& pv, const AdaDev& hp, const Task& t, St
       }
       pn = write_step<PT>(pn, climb_e(md, hp.a_climb, hp.b_climb), 1.0f, E::IS_BF16, E::IS_BF16 ? noise_of(s_clb, i) : 0u);
     }
-    if constexpr (E::IS_BF16) reinterpret_cast<uint16_t*>(d.p)[i] = (uint16_t)(__float_as_uint(pn) >> 16);
-    else reinterpret_cast<float*>(d.p)[i] = pn;
+    if constexpr (E::IS_BF16) {
+      uint16_t* dst = reinterpret_cast<uint16_t*>(d.p) + i;
+      *dst = (uint16_t)(__float_as_uint(pn) >> 16);
+      mirror_copy(pv.peers, dst, 2);
+    } else {
+      float* dst = reinterpret_cast<float*>(d.p) + i;
+      *dst = pn;
+      mirror_copy(pv.peers, dst, 4);
+    }
   }
   __syncthreads();  // every read of the old scales is done before they are replaced
   if constexpr (MK == KAON_M_4BIT) {
@@ -1098,7 +1110,7 @@ __global__ void __launch_bounds__(256) msam_axpy_kernel(PlanView pv, float alpha
         md[k] = climb_e(x, alpha, bound);
       }
       update8<PT>(reinterpret_cast<unsigned char*>(d.p) + e * E::BYTES, cnt, md, 1.0f, E::IS_BF16, st,
-                  d.tensor_id, (uint64_t)(e >> 3));
+                  d.tensor_id, (uint64_t)(e >> 3), pv.peers);
     }
   }
 }

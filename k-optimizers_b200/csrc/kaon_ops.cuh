@@ -11,11 +11,32 @@ __device__ __forceinline__ int row_of(unsigned e, const DevTensor& d) {
   return d.cols == 1 ? (int)e : (int)__umulhi(e, d.row_magic);
 }
 
+// ---- mirrors of the weight buffer on other GPUs (plain peer stores) ----
+
+// 16 bytes this thread just stored at `local`, repeated at every mirror.
+__device__ __forceinline__ void mirror16(const Peers& pr, void* local, uint4 v) {
+  for (int r = 0; r < pr.n; ++r)
+    *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(local) + pr.delta[r]) = v;
+}
+
+// `bytes` (a multiple of 2) this thread just stored at `local`, copied to every mirror; for the
+// ragged ends, where the value is not at hand as a vector.
+__device__ __forceinline__ void mirror_copy(const Peers& pr, const void* local, int bytes) {
+  if (pr.n == 0) return;
+  const unsigned short* src = reinterpret_cast<const unsigned short*>(local);
+  for (int r = 0; r < pr.n; ++r) {
+    unsigned short* dst = reinterpret_cast<unsigned short*>(
+        reinterpret_cast<unsigned char*>(const_cast<void*>(local)) + pr.delta[r]);
+    for (int k = 0; k < (bytes >> 1); ++k) dst[k] = src[k];
+  }
+}
+
 // p[0..cnt) += alpha * dlt[0..cnt) with the configured rounding; `q` is the global index of this
 // group of eight (element / 8), which keys the noise.
 template <typename PT>
 __device__ __forceinline__ void update8(void* pe, int cnt, const float dlt[8], float alpha, bool sr,
-                                        const SrStream& st, uint32_t tensor_id, uint64_t q) {
+                                        const SrStream& st, uint32_t tensor_id, uint64_t q,
+                                        const Peers& pr) {
   if constexpr (Elems<PT>::IS_BF16) {
     uint32_t noise[4] = {0u, 0u, 0u, 0u};
     if (sr) st.draw8(tensor_id, q, noise);
@@ -24,7 +45,9 @@ __device__ __forceinline__ void update8(void* pe, int cnt, const float dlt[8], f
       uint32_t pw[4] = {v.x, v.y, v.z, v.w};
       if (sr) write8_bf16<true>(pw, dlt, alpha, noise);
       else write8_bf16<false>(pw, dlt, alpha, noise);
-      *reinterpret_cast<uint4*>(pe) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
+      const uint4 out = make_uint4(pw[0], pw[1], pw[2], pw[3]);
+      *reinterpret_cast<uint4*>(pe) = out;
+      mirror16(pr, pe, out);
     } else {
       uint16_t* ph = reinterpret_cast<uint16_t*>(pe);
       for (int k = 0; k < cnt; ++k) {
@@ -37,6 +60,7 @@ __device__ __forceinline__ void update8(void* pe, int cnt, const float dlt[8], f
           ph[k] = (uint16_t)(pack_bf16_rn(r, 0.0f) & 0xffffu);
         }
       }
+      mirror_copy(pr, pe, cnt * 2);
     }
   } else {
     float* pf = reinterpret_cast<float*>(pe);
@@ -48,8 +72,11 @@ __device__ __forceinline__ void update8(void* pe, int cnt, const float dlt[8], f
       b.z = __fmaf_rn(dlt[6], alpha, b.z); b.w = __fmaf_rn(dlt[7], alpha, b.w);
       reinterpret_cast<float4*>(pf)[0] = a;
       reinterpret_cast<float4*>(pf)[1] = b;
+      mirror16(pr, pf, make_uint4(__float_as_uint(a.x), __float_as_uint(a.y), __float_as_uint(a.z), __float_as_uint(a.w)));
+      mirror16(pr, pf + 4, make_uint4(__float_as_uint(b.x), __float_as_uint(b.y), __float_as_uint(b.z), __float_as_uint(b.w)));
     } else {
       for (int k = 0; k < cnt; ++k) pf[k] = __fmaf_rn(dlt[k], alpha, pf[k]);
+      mirror_copy(pr, pf, cnt * 4);
     }
   }
 }

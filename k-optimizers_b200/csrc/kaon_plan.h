@@ -75,6 +75,15 @@ struct Task {
   int pad;
 };
 
+// Mirrors of the weight buffer on other GPUs (ZeRO-1 publish fused into the step): every weight the
+// kernels write at address a is also stored at a + delta[r], r < n.  delta[r] is the byte distance from
+// this rank's weight buffer to the mapping of rank r's copy (peer memory, plain stores; multiples of 16).
+struct Peers {
+  int n;
+  int pad;
+  long long delta[KAON_MAX_PEERS];
+};
+
 // Device pointers handed to the kernels by value.
 struct PlanView {
   const DevTensor* tensors;
@@ -90,6 +99,7 @@ struct PlanView {
   const void* const* signal;  // AdaMuon: per-tensor orthogonalised momentum (bf16); null otherwise
   unsigned* status;        // 0 = ok; else the code of the first bounded wait that ran out
   unsigned char* codes;    // 2 bits per element
+  Peers peers;             // n == 0: no mirrors
 };
 
 }  // namespace kaon

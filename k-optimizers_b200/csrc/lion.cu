@@ -409,7 +409,7 @@ __device__ void lion_main(const PlanView& pv, const LionDev& hp, const Task& t, 
 #pragma unroll
         for (int k = 0; k < 8; ++k) dl[k] = __fmul_rn(dl[k], hp.lr);
         update8<PT>(pbase + (size_t)v * 8 * E::BYTES, cnt, dl, -1.0f, hp.sr != 0, st, d.tensor_id,
-                    (uint64_t)((t.e0 >> 3) + v));
+                    (uint64_t)((t.e0 >> 3) + v), pv.peers);
       }
     }
   }
@@ -483,7 +483,9 @@ __device__ void lion_apply(const PlanView& pv, const LionDev& hp, const Task& t,
           const uint32_t b1 = __float_as_uint(__fsub_rn(bf16hi(pw[j]), d1)) + (nz[j] >> 16);
           pw[j] = __byte_perm(b0, b1, 0x7632);
         }
-        *reinterpret_cast<uint4*>(pbase + (size_t)vv * 16) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
+        const uint4 out = make_uint4(pw[0], pw[1], pw[2], pw[3]);
+        *reinterpret_cast<uint4*>(pbase + (size_t)vv * 16) = out;
+        mirror16(pv.peers, pbase + (size_t)vv * 16, out);
       }
     }
     v_begin = v;
@@ -509,7 +511,9 @@ __device__ void lion_apply(const PlanView& pv, const LionDev& hp, const Task& t,
         const uint32_t b1 = __float_as_uint(__fsub_rn(bf16hi(pw[j]), d1)) + (nz[j] >> 16);
         pw[j] = __byte_perm(b0, b1, 0x7632);
       }
-      *pp = make_uint4(pw[0], pw[1], pw[2], pw[3]);
+      const uint4 out = make_uint4(pw[0], pw[1], pw[2], pw[3]);
+      *pp = out;
+      mirror16(pv.peers, pp, out);
       continue;
     }
     float dl[8];
@@ -530,7 +534,7 @@ __device__ void lion_apply(const PlanView& pv, const LionDev& hp, const Task& t,
       }
     }
     update8<PT>(pbase + (size_t)v * 8 * E::BYTES, cnt, dl, -1.0f, hp.sr != 0, st, d.tensor_id,
-                (uint64_t)((t.e0 >> 3) + v));
+                (uint64_t)((t.e0 >> 3) + v), pv.peers);
   }
 }
 

@@ -310,6 +310,18 @@ int kaon_plan_status(kaon_plan* pl, void* stream) {
 int64_t kaon_plan_device_bytes(const kaon_plan* pl) { return pl ? pl->device_bytes : 0; }
 int64_t kaon_plan_launch_count(const kaon_plan* pl) { return pl ? pl->launches : 0; }
 
+int kaon_plan_set_peers(kaon_plan* pl, const int64_t* byte_delta, int n_peers) {
+  if (!pl || n_peers < 0 || n_peers > KAON_MAX_PEERS || (n_peers > 0 && !byte_delta))
+    return fail(KAON_E_INVALID, "kaon_plan_set_peers: bad arguments (at most 7 peers)");
+  for (int r = 0; r < n_peers; ++r)
+    if (byte_delta[r] == 0 || (byte_delta[r] & 15))
+      return fail(KAON_E_INVALID, "kaon_plan_set_peers: a mirror offset must be a non-zero multiple of 16 bytes");
+  pl->view.peers = kaon::Peers{};
+  pl->view.peers.n = n_peers;
+  for (int r = 0; r < n_peers; ++r) pl->view.peers.delta[r] = byte_delta[r];
+  return KAON_OK;
+}
+
 int kaon_plan_kept_counts(kaon_plan* pl, uint32_t* host_out, int n, void* stream) {
   if (!pl || !host_out || n != pl->n_tensors) return fail(KAON_E_INVALID, "kaon_plan_kept_counts: bad arguments");
   cudaError_t ce = cudaMemcpyAsync(host_out, pl->view.kept, 4 * (size_t)n, cudaMemcpyDeviceToHost, (cudaStream_t)stream);

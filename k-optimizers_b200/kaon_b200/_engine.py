@@ -125,6 +125,16 @@ class GroupPlan:
     def status(self, stream: int) -> None:
         L.check(L.lib().kaon_plan_status(self.handle, C.c_void_p(stream)))
 
+    def set_peers(self, base: int, nbytes: int, deltas: list[int]) -> None:
+        """Mirror every weight store of this plan at +delta bytes (other GPUs' copies of the weight buffer)."""
+        for p in self.params:
+            a = p.data_ptr()
+            if not (base <= a and a + p.numel() * p.element_size() <= base + nbytes):
+                raise L.KaonError("weight mirrors are set, but a stepped parameter lies outside the mirrored "
+                                  "weight buffer")
+        arr = (C.c_int64 * max(1, len(deltas)))(*deltas)
+        L.check(L.lib().kaon_plan_set_peers(self.handle, arr, len(deltas)))
+
     def kept_counts(self, stream: int) -> list[int]:
         out = (C.c_uint32 * self.n)()
         L.check(L.lib().kaon_plan_kept_counts(self.handle, out, self.n, C.c_void_p(stream)))
@@ -162,6 +172,14 @@ class FusedStepMixin:
         self._plan_members: dict[tuple, tuple[int, ...]] = {}
         self._t = 0                 # completed steps; the SR stream uses the 1-based index
         self.sr_seed: int | None = None  # None -> torch.initial_seed() at the first step
+        self._mirrors: tuple[int, int, list[int]] | None = None
+
+    def set_weight_mirrors(self, base_ptr: int, nbytes: int, byte_deltas: list[int]) -> None:
+        """Fuse the ZeRO-1 publish into the step: every weight written inside
+        [base_ptr, base_ptr + nbytes) is also stored at +delta for each delta (the same buffer as mapped
+        from the other GPUs).  The caller orders the ranks after the step (``ShardedWeights.publish``)."""
+        self._mirrors = (int(base_ptr), int(nbytes), [int(d) for d in byte_deltas]) if byte_deltas else None
+        self._invalidate_plans()
 
     def _invalidate_plans(self) -> None:
         for pl in self._plans.values():
@@ -214,6 +232,8 @@ class FusedStepMixin:
                     ids = self._tensor_ids()
                 pl = GroupPlan(self._OPT_KIND, plist, [state_of(p) for p in plist],
                                [ids[id(p)] for p in plist], self._momentum_dtype(group))
+                if self._mirrors is not None:
+                    pl.set_peers(*self._mirrors)
                 self._plans[key] = pl
                 self._plan_members[key] = sig
             plans.append(pl)

@@ -75,6 +75,7 @@ def lib() -> C.CDLL:
         _lib.kaon_newton_schulz_workspace_bytes.restype = C.c_int64
         _lib.kaon_plan_device_bytes.argtypes = [C.c_void_p]
         _lib.kaon_plan_launch_count.argtypes = [C.c_void_p]
+        _lib.kaon_plan_set_peers.argtypes = [C.c_void_p, C.POINTER(C.c_int64), C.c_int]
         if _lib.kaon_abi_version() != 1:
             raise KaonError("libkaon_b200.so ABI version mismatch")
     return _lib

@@ -97,6 +97,9 @@ class Nekaon(AutoLRMixin, Optimizer):
     def sr_seed(self, v):
         self.inner.sr_seed = v
 
+    def set_weight_mirrors(self, base_ptr: int, nbytes: int, byte_deltas: list[int]) -> None:
+        self.inner.set_weight_mirrors(base_ptr, nbytes, byte_deltas)
+
     def check_device_status(self) -> None:
         self.inner.check_device_status()
 

@@ -1,0 +1,56 @@
+"""One rank of the sharded-step test: ZeRO-1 over symmetric memory with the publish fused into the
+step kernels.  Saves every tensor's final weights as this rank sees them."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "k-optimizers_b200"))
+import kaon_b200  # noqa: E402
+from kaon_b200.zero1 import ShardedWeights  # noqa: E402
+
+SHAPES = [(640, 256), (64, 32, 3, 3), (1280,), (512, 640), (333, 77), (3, 4096), (4000, 1), (7,), (256, 1024)]
+
+
+def main():
+    opt_name, out = sys.argv[1], sys.argv[2]
+    world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    sw = ShardedWeights(SHAPES, world, rank, torch.bfloat16, dev, symmetric=True)
+    gen = torch.Generator().manual_seed(5)
+    for v, s in zip(sw.views, SHAPES):  # every rank starts from the same full weights
+        v.copy_((torch.randn(s, generator=gen) * 0.02).bfloat16())
+    owned = sw.part.owned(rank)
+    params = []
+    for i in owned:
+        p = torch.nn.Parameter(sw.views[i])
+        p.kaon_tensor_id = i
+        params.append(p)
+    kw = dict(lr=2e-4, momentum_dtype="4bit") if opt_name == "Lion" else dict(lr=1e-4, momentum_dtype="int8")
+    opt = getattr(kaon_b200, opt_name)(params, **kw)
+    opt.sr_seed = 3
+    sw.attach(opt)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    for step in range(4):
+        grads = [(torch.randn(s, generator=gen) * 1e-3).bfloat16() for s in SHAPES]
+        for p, i in zip(params, owned):
+            p.grad = grads[i].to(dev)
+        opt.step()
+        sw.publish()
+    torch.cuda.synchronize()
+    opt.check_device_status()
+    torch.save([v.detach().cpu() for v in sw.views], f"{out}.w{world}.r{rank}.pt")
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
