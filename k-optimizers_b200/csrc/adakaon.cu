@@ -86,7 +86,7 @@ __device__ __forceinline__ uint32_t noise_lane(const uint32_t nz[4], int k) {
 
 // Eight values out (weights: `pr` names the mirrors on other GPUs; state: none).
 template <typename PT>
-__device__ __forceinline__ void store8(void* pe, int cnt, const float v[8], const Peers& pr) {
+__device__ __forceinline__ void store8(void* pe, int cnt, const float v[8], const Peers* pr) {
   if constexpr (Elems<PT>::IS_BF16) {
     if (cnt >= 8) {
       const uint4 out = make_uint4(pack_bf16_rn(v[0], v[1]), pack_bf16_rn(v[2], v[3]),
@@ -813,8 +813,8 @@ __device__ void ada_rows(const PlanView& pv, const AdaDev& hp, const Task& t, St
 #pragma unroll
           for (int k = 0; k < 8; ++k) md[k] = mn[k];
           if (cnt > 0) {
-            if constexpr (MK == KAON_M_BF16) store8<__nv_bfloat16>((unsigned char*)d.m + e0 * 2 + (size_t)v * 16, cnt, mn, Peers{});
-            else store8<float>((unsigned char*)d.m + e0 * 4 + (size_t)v * 32, cnt, mn, Peers{});
+            if constexpr (MK == KAON_M_BF16) store8<__nv_bfloat16>((unsigned char*)d.m + e0 * 2 + (size_t)v * 16, cnt, mn, nullptr);
+            else store8<float>((unsigned char*)d.m + e0 * 4 + (size_t)v * 32, cnt, mn, nullptr);
           }
         } else {
 #pragma unroll
@@ -837,7 +837,7 @@ __device__ void ada_rows(const PlanView& pv, const AdaDev& hp, const Task& t, St
             for (int k = 0; k < 8; ++k)
               pc[k] = write_step<PT>(pc[k], climb_e(md[k], hp.a_climb, hp.b_climb), 1.0f, E::IS_BF16, noise_lane(nc, k));
           }
-          store8<PT>(pbase + (size_t)v * 8 * E::BYTES, cnt, pc, pv.peers);
+          store8<PT>(pbase + (size_t)v * 8 * E::BYTES, cnt, pc, &pv.peers);
         }
       }
     }
@@ -972,11 +972,11 @@ __device__ void ada_flat(const PlanView& pv, const AdaDev& hp, const Task& t, St
     if constexpr (E::IS_BF16) {
       uint16_t* dst = reinterpret_cast<uint16_t*>(d.p) + i;
       *dst = (uint16_t)(__float_as_uint(pn) >> 16);
-      mirror_copy(pv.peers, dst, 2);
+      mirror_copy(&pv.peers, dst, 2);
     } else {
       float* dst = reinterpret_cast<float*>(d.p) + i;
       *dst = pn;
-      mirror_copy(pv.peers, dst, 4);
+      mirror_copy(&pv.peers, dst, 4);
     }
   }
   __syncthreads();  // every read of the old scales is done before they are replaced
@@ -1110,7 +1110,7 @@ __global__ void __launch_bounds__(256) msam_axpy_kernel(PlanView pv, float alpha
         md[k] = climb_e(x, alpha, bound);
       }
       update8<PT>(reinterpret_cast<unsigned char*>(d.p) + e * E::BYTES, cnt, md, 1.0f, E::IS_BF16, st,
-                  d.tensor_id, (uint64_t)(e >> 3), pv.peers);
+                  d.tensor_id, (uint64_t)(e >> 3), &pv.peers);
     }
   }
 }

@@ -87,7 +87,7 @@ __global__ void sr_add_kernel(void* p, const float* __restrict__ delta, long lon
 #pragma unroll
     for (int k = 0; k < 8; ++k) d[k] = (k < cnt) ? delta[v * 8 + k] : 0.0f;
     update8<PT>(reinterpret_cast<unsigned char*>(p) + v * 8 * Elems<PT>::BYTES, cnt, d, alpha, sr != 0,
-                st, tensor_id, (uint64_t)v, Peers{});
+                st, tensor_id, (uint64_t)v, nullptr);
   }
 }
 

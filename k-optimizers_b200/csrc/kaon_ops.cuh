@@ -14,19 +14,21 @@ __device__ __forceinline__ int row_of(unsigned e, const DevTensor& d) {
 // ---- mirrors of the weight buffer on other GPUs (plain peer stores) ----
 
 // 16 bytes this thread just stored at `local`, repeated at every mirror.
-__device__ __forceinline__ void mirror16(const Peers& pr, void* local, uint4 v) {
-  for (int r = 0; r < pr.n; ++r)
-    *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(local) + pr.delta[r]) = v;
+// (pr == nullptr: no mirrors; a null constant compiles the stores out)
+__device__ __forceinline__ void mirror16(const Peers* pr, void* local, uint4 v) {
+  if (pr == nullptr) return;
+  for (int r = 0; r < pr->n; ++r)
+    *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(local) + pr->delta[r]) = v;
 }
 
 // `bytes` (a multiple of 2) this thread just stored at `local`, copied to every mirror; for the
 // ragged ends, where the value is not at hand as a vector.
-__device__ __forceinline__ void mirror_copy(const Peers& pr, const void* local, int bytes) {
-  if (pr.n == 0) return;
+__device__ __forceinline__ void mirror_copy(const Peers* pr, const void* local, int bytes) {
+  if (pr == nullptr || pr->n == 0) return;
   const unsigned short* src = reinterpret_cast<const unsigned short*>(local);
-  for (int r = 0; r < pr.n; ++r) {
+  for (int r = 0; r < pr->n; ++r) {
     unsigned short* dst = reinterpret_cast<unsigned short*>(
-        reinterpret_cast<unsigned char*>(const_cast<void*>(local)) + pr.delta[r]);
+        reinterpret_cast<unsigned char*>(const_cast<void*>(local)) + pr->delta[r]);
     for (int k = 0; k < (bytes >> 1); ++k) dst[k] = src[k];
   }
 }
@@ -36,7 +38,7 @@ __device__ __forceinline__ void mirror_copy(const Peers& pr, const void* local, 
 template <typename PT>
 __device__ __forceinline__ void update8(void* pe, int cnt, const float dlt[8], float alpha, bool sr,
                                         const SrStream& st, uint32_t tensor_id, uint64_t q,
-                                        const Peers& pr) {
+                                        const Peers* pr) {
   if constexpr (Elems<PT>::IS_BF16) {
     uint32_t noise[4] = {0u, 0u, 0u, 0u};
     if (sr) st.draw8(tensor_id, q, noise);

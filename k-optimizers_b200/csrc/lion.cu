@@ -148,7 +148,7 @@ __device__ __forceinline__ uint32_t lion_math8(const LionDev& hp, const float g[
   return kept;
 }
 
-template <typename PT, int MK>
+template <typename PT, int MK, bool MIRROR>
 __device__ void lion_main(const PlanView& pv, const LionDev& hp, const Task& t, unsigned char* g_s,
                           unsigned char* m_s, float* mean_s, unsigned* rowmax_s, float* scale_s, float* sc_s,
                           uint64_t* bar,
@@ -409,7 +409,7 @@ __device__ void lion_main(const PlanView& pv, const LionDev& hp, const Task& t, 
 #pragma unroll
         for (int k = 0; k < 8; ++k) dl[k] = __fmul_rn(dl[k], hp.lr);
         update8<PT>(pbase + (size_t)v * 8 * E::BYTES, cnt, dl, -1.0f, hp.sr != 0, st, d.tensor_id,
-                    (uint64_t)((t.e0 >> 3) + v), pv.peers);
+                    (uint64_t)((t.e0 >> 3) + v), MIRROR ? &pv.peers : nullptr);
       }
     }
   }
@@ -432,7 +432,7 @@ __device__ void lion_main(const PlanView& pv, const LionDev& hp, const Task& t, 
 }
 
 // APPLY item: weights of the run [e0, e0+n) once the tensor's kept count is complete.
-template <typename PT>
+template <typename PT, bool MIRROR>
 __device__ void lion_apply(const PlanView& pv, const LionDev& hp, const Task& t, int tid) {
   using E = Elems<PT>;
   const DevTensor d = pv.tensors[t.tensor];
@@ -485,7 +485,7 @@ __device__ void lion_apply(const PlanView& pv, const LionDev& hp, const Task& t,
         }
         const uint4 out = make_uint4(pw[0], pw[1], pw[2], pw[3]);
         *reinterpret_cast<uint4*>(pbase + (size_t)vv * 16) = out;
-        mirror16(pv.peers, pbase + (size_t)vv * 16, out);
+        mirror16(MIRROR ? &pv.peers : nullptr, pbase + (size_t)vv * 16, out);
       }
     }
     v_begin = v;
@@ -513,7 +513,7 @@ __device__ void lion_apply(const PlanView& pv, const LionDev& hp, const Task& t,
       }
       const uint4 out = make_uint4(pw[0], pw[1], pw[2], pw[3]);
       *pp = out;
-      mirror16(pv.peers, pp, out);
+      mirror16(MIRROR ? &pv.peers : nullptr, pp, out);
       continue;
     }
     float dl[8];
@@ -534,11 +534,12 @@ __device__ void lion_apply(const PlanView& pv, const LionDev& hp, const Task& t,
       }
     }
     update8<PT>(pbase + (size_t)v * 8 * E::BYTES, cnt, dl, -1.0f, hp.sr != 0, st, d.tensor_id,
-                (uint64_t)((t.e0 >> 3) + v), pv.peers);
+                (uint64_t)((t.e0 >> 3) + v), MIRROR ? &pv.peers : nullptr);
   }
 }
 
-template <typename PT, int MK>
+// MIRROR = false compiles the mirror stores out (a plan without peers pays nothing for them).
+template <typename PT, int MK, bool MIRROR>
 __global__ void __launch_bounds__(NTHREADS, 4) lion_kernel(PlanView pv, LionDev hp) {
   extern __shared__ __align__(128) unsigned char dyn[];
   __shared__ float mean_s[MAX_TASK_ROWS];
@@ -567,9 +568,9 @@ __global__ void __launch_bounds__(NTHREADS, 4) lion_kernel(PlanView pv, LionDev 
     claim_next(slot ^ 1);
     const Task t = pv.tasks[cur];
     if (t.phase == PH_LION_MAIN)
-      lion_main<PT, MK>(pv, hp, t, g_s, m_s, mean_s, rowmax_s, scale_s, sc_s, &bar, parity, red_s, tid);
+      lion_main<PT, MK, MIRROR>(pv, hp, t, g_s, m_s, mean_s, rowmax_s, scale_s, sc_s, &bar, parity, red_s, tid);
     else
-      lion_apply<PT>(pv, hp, t, tid);
+      lion_apply<PT, MIRROR>(pv, hp, t, tid);
     __syncthreads();
     slot ^= 1;
     cur = next_s[slot];
@@ -578,17 +579,21 @@ __global__ void __launch_bounds__(NTHREADS, 4) lion_kernel(PlanView pv, LionDev 
 
 typedef void (*LionKernel)(PlanView, LionDev);
 
-static LionKernel pick_lion(int pdt, int mk) {
-#define KAON_PICK(PT)                                         \
-  switch (mk) {                                               \
-    case KAON_M_F32: return lion_kernel<PT, KAON_M_F32>;      \
-    case KAON_M_BF16: return lion_kernel<PT, KAON_M_BF16>;    \
-    case KAON_M_INT8: return lion_kernel<PT, KAON_M_INT8>;    \
-    case KAON_M_4BIT: return lion_kernel<PT, KAON_M_4BIT>;    \
-    default: return nullptr;                                  \
+static LionKernel pick_lion(int pdt, int mk, bool mirror) {
+#define KAON_PICK(PT, MIR)                                         \
+  switch (mk) {                                                    \
+    case KAON_M_F32: return lion_kernel<PT, KAON_M_F32, MIR>;      \
+    case KAON_M_BF16: return lion_kernel<PT, KAON_M_BF16, MIR>;    \
+    case KAON_M_INT8: return lion_kernel<PT, KAON_M_INT8, MIR>;    \
+    case KAON_M_4BIT: return lion_kernel<PT, KAON_M_4BIT, MIR>;    \
+    default: return nullptr;                                       \
   }
-  if (pdt == KAON_DT_BF16) { KAON_PICK(__nv_bfloat16) }
-  KAON_PICK(float)
+  if (mirror) {
+    if (pdt == KAON_DT_BF16) { KAON_PICK(__nv_bfloat16, true) }
+    KAON_PICK(float, true)
+  }
+  if (pdt == KAON_DT_BF16) { KAON_PICK(__nv_bfloat16, false) }
+  KAON_PICK(float, false)
 #undef KAON_PICK
 }
 
@@ -597,9 +602,11 @@ int configure_launch(kaon_plan* pl, const cudaDeviceProp& prop) {
   pl->smem_bytes = (size_t)CAP * esz + momentum_bytes_per_cap(pl->momentum_kind);
   int per_sm = 2;
   if (pl->optimizer == KAON_OPT_LION) {
-    LionKernel k = pick_lion(pl->param_dtype, pl->momentum_kind);
+    LionKernel k = pick_lion(pl->param_dtype, pl->momentum_kind, false);
     if (!k) return fail(KAON_E_INVALID, "no Lion kernel for this dtype combination");
     KAON_CUDA(cudaFuncSetAttribute((const void*)k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl->smem_bytes));
+    KAON_CUDA(cudaFuncSetAttribute((const void*)pick_lion(pl->param_dtype, pl->momentum_kind, true),
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl->smem_bytes));
     KAON_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, (const void*)k, NTHREADS, pl->smem_bytes));
     if (per_sm < 1) return fail(KAON_E_UNSUPPORTED, "Lion kernel does not fit on an SM (shared memory %zu)", pl->smem_bytes);
   }
@@ -632,7 +639,7 @@ extern "C" int kaon_lion_step(kaon_plan* pl, const kaon_lion_hparams* h, uint64_
   if (hp.cautious) { v.tasks = pl->d_tasks_full; v.n_tasks = pl->n_tasks_full; }
   else { v.tasks = pl->d_tasks_main; v.n_tasks = pl->n_tasks_main; }
   KAON_CUDA(cudaMemsetAsync(v.task_counter, 0, pl->counters_bytes - sizeof(unsigned), s));
-  LionKernel k = pick_lion(pl->param_dtype, pl->momentum_kind);
+  LionKernel k = pick_lion(pl->param_dtype, pl->momentum_kind, v.peers.n > 0);
   k<<<pl->grid, NTHREADS, pl->smem_bytes, s>>>(v, hp);
   KAON_CUDA(cudaGetLastError());
   pl->launches += 1;
@@ -720,7 +727,7 @@ static int noalloc_setup_device(int dev) {
   cudaDeviceProp prop;
   KAON_CUDA(cudaGetDeviceProperties(&prop, dev));
   for (int pdt = 0; pdt < 2; ++pdt) {
-    LionKernel k = pick_lion(pdt, KAON_M_4BIT);
+    LionKernel k = pick_lion(pdt, KAON_M_4BIT, false);
     nd.smem[pdt] = (size_t)CAP * (pdt == KAON_DT_BF16 ? 2 : 4) + momentum_bytes_per_cap(KAON_M_4BIT);
     KAON_CUDA(cudaFuncSetAttribute((const void*)k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)nd.smem[pdt]));
     int per_sm = 0;
@@ -818,7 +825,7 @@ extern "C" int kaon_lion_step_noalloc(const kaon_tensor_desc* t, int param_dtype
   cudaStream_t s = (cudaStream_t)stream;
   noalloc_setup_kernel<<<1, 256, 0, s>>>(d, t->g, item_elems, item_rows, (int)n_items);
   KAON_CUDA(cudaGetLastError());
-  LionKernel k = pick_lion(param_dtype, KAON_M_4BIT);
+  LionKernel k = pick_lion(param_dtype, KAON_M_4BIT, false);
   k<<<nd.grid[param_dtype], NTHREADS, nd.smem[param_dtype], s>>>(v, hp);
   KAON_CUDA(cudaGetLastError());
   return KAON_OK;
