@@ -212,11 +212,15 @@ class FusedStepMixin:
             return []
         fresh = False
         for p in active:
+            if p.grad.is_sparse:
+                raise RuntimeError(f"{type(self).__name__} does not support sparse gradients")
             st = state_of(p)
             if not st:
                 self._init_state(p, st, group)
                 fresh = True
-        members = [p for p in group["params"] if state_of(p)]
+        # tensors stepped now or before (a lookup must not create state for the others); an empty tensor
+        # has state, as in the reference, but nothing to step and no address
+        members = [p for p in group["params"] if p in self.state and state_of(p) and p.numel() > 0]
         buckets: dict[tuple, list[torch.Tensor]] = {}
         for p in members:
             buckets.setdefault((gi, p.device, p.dtype), []).append(p)

@@ -8,6 +8,7 @@ group instead of the foreach buckets (src/kaon/adakaon.py:339-383, 793-1014).  `
 from __future__ import annotations
 
 import ctypes as C
+import math
 from collections.abc import Iterable
 from typing import Any
 
@@ -31,7 +32,7 @@ def init_second_moment_state(p: Tensor, state: dict[str, Any]) -> None:
     (reference src/kaon/adakaon.py:318-331)."""
     if p.ndim >= 2:
         state["row"] = torch.zeros(p.shape[0], dtype=torch.float32, device=p.device)
-        state["col"] = torch.zeros(p.numel() // p.shape[0], dtype=torch.float32, device=p.device)
+        state["col"] = torch.zeros(math.prod(p.shape[1:]), dtype=torch.float32, device=p.device)
     else:
         state["v"] = torch.zeros(p.shape, dtype=torch.float32, device=p.device)
 
