@@ -194,16 +194,23 @@ def run_ours(args):
     opt = getattr(kaon_b200, opt_name)(params, **kw)
     opt.sr_seed = 0
     sw.attach(opt)  # fused publish: the step kernels store the weights into every rank's copy
+    sg = None
+    if args.reduce_scatter and world > 1:
+        from kaon_b200.zero1 import ShardedGrads
+        sg = ShardedGrads(sw, shapes)              # full-list local gradients + the owner's reduced shard
+        fill_normal(sg.flat, 1e-3, outlier=bool(wopt.get("outlier")))
 
     cos = wopt.get("cosine")
 
     def one_step(k, ev=None):
-        gv = gsets[k % len(gsets)][1]
+        gv = sg.owned if sg is not None else gsets[k % len(gsets)][1]
         if cos:
             for grp in opt.param_groups:
                 grp["lr"] = cos[1] + 0.5 * (cos[0] - cos[1]) * (1.0 + math.cos(math.pi * (k % cos[2]) / cos[2]))
         for p, g in zip(params, gv):
             p.grad = g
+        if sg is not None:
+            sg.reduce_scatter(average=True)
         if ev:
             ev[0].record()
         opt.step()
@@ -329,6 +336,7 @@ def run_ours(args):
                                    "nccl all_gather_into_tensor after the step"),
                        "l2": "inputs (18 GB per step) larger than L2; no flush needed"},
             "step_kernel_ms": kern_ms, "publish_ms": gather_ms,
+            "gradient_reduce_scatter": "inside every step" if sg is not None else "not part of the step",
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "frac_of_nominal_8TBs": achieved / 8000.0,
                          "peak_kind": f"{peak_kind} copy bandwidth", "traffic": None,
@@ -373,6 +381,9 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--reduce-scatter", action="store_true",
+                    help="N>1: put the gradient reduce-scatter (NCCL, bf16 average) inside every step; the step "
+                         "kernels then read the collective's output buffer")
     ap.add_argument("--publish", default="fused", choices=["fused", "allgather"],
                     help="N>1: how the owned weights reach the other ranks")
     args = ap.parse_args()

@@ -104,3 +104,112 @@ class ShardedWeights:
         if self.world == 1:
             return None
         return dist.all_gather_into_tensor(self.flat, self.shard, group=group, async_op=async_op)
+
+
+class ShardedGrads:
+    """Gradients of the whole list in the weights' layout, and their reduce-scatter into this rank's
+    shard: the front half of the sharded step.  ``views[i]`` is where backward leaves tensor i's local
+    gradient; after ``reduce_scatter()`` ``owned[k]`` holds the reduced gradient of the k-th owned
+    tensor, inside the collective's own output buffer, which is what the step kernels read (the
+    gradient pointers never change, so the plan's pointer column is uploaded once)."""
+
+    def __init__(self, weights: ShardedWeights, shapes, dtype=None):
+        import torch
+        sw = self.weights = weights
+        dtype = dtype or sw.flat.dtype
+        self.flat = torch.zeros(sw.world * sw.part.shard_len, dtype=dtype, device=sw.flat.device)
+        self.shard = (self.flat if sw.world == 1 else
+                      torch.zeros(sw.part.shard_len, dtype=dtype, device=sw.flat.device))
+        self.views, self.owned = [], []
+        for i, s in enumerate(shapes):
+            n = math.prod(s)
+            start = sw.part.owner[i] * sw.part.shard_len + sw.part.offset[i]
+            self.views.append(self.flat[start:start + n].view(s))
+            if sw.part.owner[i] == sw.rank:
+                self.owned.append(self.shard[sw.part.offset[i]:sw.part.offset[i] + n].view(s))
+
+    def reduce_scatter(self, average: bool = True, async_op: bool = False):
+        import torch.distributed as dist
+        sw = self.weights
+        if sw.world == 1:
+            return None
+        if dist.get_backend(sw.group) == "gloo":
+            # gloo (CPU tests of the host flow) has no reduce-scatter: all-reduce, keep this rank's slice
+            dist.all_reduce(self.flat, group=sw.group)
+            self.shard.copy_(self.flat[sw.rank * sw.part.shard_len:(sw.rank + 1) * sw.part.shard_len])
+            if average:
+                self.shard.div_(sw.world)
+            return None
+        op = dist.ReduceOp.AVG if average else dist.ReduceOp.SUM
+        return dist.reduce_scatter_tensor(self.shard, self.flat, op=op, group=sw.group, async_op=async_op)
+
+
+# ---- checkpoints of a sharded optimizer in the single-process layout ----
+
+def _global_ids(optimizer) -> list[int]:
+    """Global list position of every parameter, in the optimizer's packed (param_groups) order."""
+    ids = []
+    for g in optimizer.param_groups:
+        for p in g["params"]:
+            if not hasattr(p, "kaon_tensor_id"):
+                raise ValueError("sharded checkpoints need p.kaon_tensor_id (the global list position) on every parameter")
+            ids.append(int(p.kaon_tensor_id))
+    return ids
+
+
+def gather_state_dict(optimizer, group=None, dst: int = 0):
+    """Every rank's optimizer state merged into ONE ``state_dict`` with the layout a single-process
+    optimizer over the whole list would save (state keyed by global list position; tensors on the CPU).
+    Returned on rank ``dst``, ``None`` elsewhere.  Collective: every rank calls it."""
+    import torch
+    import torch.distributed as dist
+    sd = optimizer.state_dict()
+    ids = _global_ids(optimizer)
+    to_cpu = lambda v: v.detach().cpu() if torch.is_tensor(v) else v  # noqa: E731
+    state = {ids[k]: {key: to_cpu(v) for key, v in st.items()} for k, st in sd["state"].items()}
+    groups, k = [], 0
+    for g in sd["param_groups"]:
+        n = len(g["params"])
+        groups.append({**g, "params": ids[k:k + n]})
+        k += n
+    payload = {"state": state, "param_groups": groups}
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if world == 1:
+        parts = [payload]
+    else:
+        parts = [None] * world if dist.get_rank(group) == dst else None
+        dist.gather_object(payload, parts, dst=dst, group=group)
+        if parts is None:
+            return None
+    merged_state, merged_groups = {}, [dict(g, params=[]) for g in parts[0]["param_groups"]]
+    for part in parts:
+        merged_state.update(part["state"])
+        for gi, g in enumerate(part["param_groups"]):
+            merged_groups[gi]["params"].extend(g["params"])
+    for g in merged_groups:
+        g["params"] = sorted(g["params"])
+    out = {k: v for k, v in sd.items() if k not in ("state", "param_groups")}
+    out["state"] = dict(sorted(merged_state.items()))
+    out["param_groups"] = merged_groups
+    return out
+
+
+def scatter_state_dict(optimizer, full_state_dict) -> None:
+    """Load this rank's part of a single-process (or gathered) ``state_dict`` into a sharded optimizer.
+    Every rank passes the same full dict (e.g. each reads the checkpoint file)."""
+    ids = _global_ids(optimizer)
+    local_state = {k: full_state_dict["state"][gid] for k, gid in enumerate(ids) if gid in full_state_dict["state"]}
+    groups, k = [], 0
+    if len(full_state_dict["param_groups"]) != len(optimizer.param_groups):
+        raise ValueError("checkpoint and optimizer have different numbers of parameter groups")
+    for g_full, g in zip(full_state_dict["param_groups"], optimizer.param_groups):
+        n = len(g["params"])
+        missing = set(ids[k:k + n]) - set(g_full["params"])
+        if missing:
+            raise ValueError(f"checkpoint group lacks tensors {sorted(missing)[:5]} of this rank's group")
+        groups.append({**g_full, "params": list(range(k, k + n))})
+        k += n
+    local = {key: v for key, v in full_state_dict.items() if key not in ("state", "param_groups")}
+    local["state"] = local_state
+    local["param_groups"] = groups
+    optimizer.load_state_dict(local)

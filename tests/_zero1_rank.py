@@ -1,5 +1,7 @@
-"""One rank of the sharded-step test: ZeRO-1 over symmetric memory with the publish fused into the
-step kernels.  Saves every tensor's final weights as this rank sees them."""
+"""One rank of the sharded-step test: gradients reduce-scattered into the owner's shard, ZeRO-1 step over
+symmetric memory with the publish fused into the step kernels, optimizer state gathered into the
+single-process checkpoint layout.  Saves every tensor's final weights as this rank sees them, and (rank 0)
+the gathered state_dict."""
 import os
 import sys
 
@@ -8,7 +10,7 @@ import torch.distributed as dist
 
 sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "k-optimizers_b200"))
 import kaon_b200  # noqa: E402
-from kaon_b200.zero1 import ShardedWeights  # noqa: E402
+from kaon_b200.zero1 import ShardedGrads, ShardedWeights, gather_state_dict  # noqa: E402
 
 SHAPES = [(640, 256), (64, 32, 3, 3), (1280,), (512, 640), (333, 77), (3, 4096), (4000, 1), (7,), (256, 1024)]
 
@@ -38,15 +40,22 @@ def main():
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
+    sg = ShardedGrads(sw, SHAPES)
+    for p, g in zip(params, sg.owned):
+        p.grad = g                                   # the reduce-scatter's output buffer, for good
     for step in range(4):
         grads = [(torch.randn(s, generator=gen) * 1e-3).bfloat16() for s in SHAPES]
-        for p, i in zip(params, owned):
-            p.grad = grads[i].to(dev)
+        for v, g in zip(sg.views, grads):            # "backward": every rank holds the same local gradient,
+            v.copy_(g)                               # so the average is exact in bf16
+        sg.reduce_scatter(average=True)
         opt.step()
         sw.publish()
     torch.cuda.synchronize()
     opt.check_device_status()
     torch.save([v.detach().cpu() for v in sw.views], f"{out}.w{world}.r{rank}.pt")
+    full = gather_state_dict(opt, dst=0)
+    if rank == 0:
+        torch.save(full, f"{out}.w{world}.state.pt")
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -99,3 +99,12 @@ def test_two_ranks_fused_publish_equals_single_gpu(opt_name, tmp_path):
         got = torch.load(out + f".w2.r{r_}.pt")
         for i, (a, b) in enumerate(zip(single, got)):
             assert torch.equal(a.view(torch.int16), b.view(torch.int16)), (r_, i)
+    # the gathered optimizer state is the single-process checkpoint, entry for entry
+    s1, s2 = torch.load(out + ".w1.state.pt"), torch.load(out + ".w2.state.pt")
+    assert s1["param_groups"] == s2["param_groups"] and s1["_kaon_b200"] == s2["_kaon_b200"]
+    assert s1["state"].keys() == s2["state"].keys()
+    for k in s1["state"]:
+        assert s1["state"][k].keys() == s2["state"][k].keys()
+        for key, v in s1["state"][k].items():
+            w = s2["state"][k][key]
+            assert torch.equal(v, w) if torch.is_tensor(v) else v == w, (k, key)
