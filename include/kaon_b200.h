@@ -19,7 +19,7 @@
 extern "C" {
 #endif
 
-#define KAON_ABI_VERSION 1
+#define KAON_ABI_VERSION 2
 
 /* parameter / gradient element type (grads have the parameter's type) */
 #define KAON_DT_F32 0
@@ -35,6 +35,7 @@ extern "C" {
 /* bf16_method (reference src/kaon/_backend.py:82-122) */
 #define KAON_W_NONE 0 /* p - bf16(delta), round to nearest even */
 #define KAON_W_SR 1   /* stochastic rounding, Philox4x32-10 keyed on (seed, step, tensor id, element) */
+#define KAON_W_KAHAN 2 /* compensated bf16 write with the per-tensor `shift` buffer (_backend.py:89-94) */
 
 /* optimizer kinds a plan can be built for */
 #define KAON_OPT_LION 0
@@ -70,6 +71,8 @@ typedef struct kaon_tensor_desc {
   int64_t rows;    /* shape[0] when ndim >= 2, else 0 (1-D tensor) */
   uint32_t tensor_id; /* position in the optimizer's flattened param list: keys the SR stream */
   uint32_t block;  /* 4-bit block size actually in use: min(momentum_4bit_block, numel) */
+  void* shift;     /* bf16_method="kahan" with bf16 weights: compensation buffer state["shift"], bf16
+                      [numel], 16-byte aligned; NULL otherwise */
 } kaon_tensor_desc;
 
 typedef struct kaon_plan kaon_plan; /* opaque: descriptor table, work list and scratch on one device */

@@ -822,13 +822,27 @@ __device__ void ada_rows(const PlanView& pv, const AdaDev& hp, const Task& t, St
         }
         // ---- weights: update, then the new climb ----
         if (cnt > 0) {
-          uint32_t nz[4] = {0u, 0u, 0u, 0u};
-          if (sr) s_upd.draw8(d.tensor_id, (uint64_t)((e0 >> 3) + v), nz);
+          if (E::IS_BF16 && hp.kahan) {
+            // compensated write: the tensor's shift buffer is read and written alongside the weights
+            unsigned char* she = reinterpret_cast<unsigned char*>(d.shift) + (size_t)e0 * 2 + (size_t)v * 16;
+            float sh[8];
+            load8_guard<__nv_bfloat16>(she, cnt, sh);
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            float f = dl[k];
-            if (hp.cautious) f = ((kept >> k) & 1u) ? div_shared(f, denom, rcp_denom) : 0.0f;
-            pc[k] = write_step<PT>(pc[k], f, -1.0f, sr, noise_lane(nz, k));
+            for (int k = 0; k < 8; ++k) {
+              float f = dl[k];
+              if (hp.cautious) f = ((kept >> k) & 1u) ? div_shared(f, denom, rcp_denom) : 0.0f;
+              kahan_step(pc[k], sh[k], f);
+            }
+            store8<__nv_bfloat16>(she, cnt, sh, nullptr);
+          } else {
+            uint32_t nz[4] = {0u, 0u, 0u, 0u};
+            if (sr) s_upd.draw8(d.tensor_id, (uint64_t)((e0 >> 3) + v), nz);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              float f = dl[k];
+              if (hp.cautious) f = ((kept >> k) & 1u) ? div_shared(f, denom, rcp_denom) : 0.0f;
+              pc[k] = write_step<PT>(pc[k], f, -1.0f, sr, noise_lane(nz, k));
+            }
           }
           if (hp.climb && MK != KAON_M_NONE) {
             uint32_t nc[4] = {0u, 0u, 0u, 0u};
@@ -958,7 +972,16 @@ __device__ void ada_flat(const PlanView& pv, const AdaDev& hp, const Task& t, St
     const float pv0 = p_before(i);
     float dv = hp.has_wd ? __fmaf_rn(pv0, hp.lrwd, f_s[i]) : f_s[i];
     if (hp.cautious) dv = (__fmul_rn(dv, E::load1(st.g_s, i)) > 0.0f) ? __fdiv_rn(dv, denom) : 0.0f;
-    float pn = write_step<PT>(pv0, dv, -1.0f, hp.sr != 0, hp.sr ? noise_of(s_upd, i) : 0u);
+    float pn;
+    if (E::IS_BF16 && hp.kahan) {
+      uint16_t* shp = reinterpret_cast<uint16_t*>(d.shift) + i;
+      float sh = __uint_as_float((uint32_t)*shp << 16);
+      pn = pv0;
+      kahan_step(pn, sh, dv);
+      *shp = (uint16_t)(__float_as_uint(sh) >> 16);
+    } else {
+      pn = write_step<PT>(pv0, dv, -1.0f, hp.sr != 0, hp.sr ? noise_of(s_upd, i) : 0u);
+    }
     if (hp.climb && MK != KAON_M_NONE) {
       float md;
       if constexpr (MK == KAON_M_4BIT || MK == KAON_M_INT8) {
@@ -1187,7 +1210,8 @@ extern "C" int kaon_adakaon_step(kaon_plan* pl, const kaon_adakaon_hparams* h, u
                                  uint32_t step, void* stream) {
   if (!pl || !h) return fail(KAON_E_INVALID, "kaon_adakaon_step: null argument");
   if (pl->optimizer != KAON_OPT_ADAKAON) return fail(KAON_E_INVALID, "plan was not built for Adakaon");
-  if (h->bf16_method != KAON_W_NONE && h->bf16_method != KAON_W_SR) return fail(KAON_E_UNSUPPORTED, "bf16_method %d", h->bf16_method);
+  if (h->bf16_method < KAON_W_NONE || h->bf16_method > KAON_W_KAHAN) return fail(KAON_E_UNSUPPORTED, "bf16_method %d", h->bf16_method);
+  if (int rc = check_kahan(pl, h->bf16_method)) return rc;
   if (!(h->clip_threshold > 0.0)) return fail(KAON_E_INVALID, "clip_threshold must be > 0");
   const bool has_m = pl->momentum_kind != KAON_M_NONE;
   if (has_m != (h->beta1 > 0.0)) return fail(KAON_E_INVALID, "beta1 %g does not match the plan's momentum kind", h->beta1);
@@ -1201,6 +1225,7 @@ extern "C" int kaon_adakaon_step(kaon_plan* pl, const kaon_adakaon_hparams* h, u
   hp.cautious = h->cautious != 0;
   hp.gc = h->gradient_centralization != 0;
   hp.sr = h->bf16_method == KAON_W_SR && pl->param_dtype == KAON_DT_BF16;
+  hp.kahan = h->bf16_method == KAON_W_KAHAN && pl->param_dtype == KAON_DT_BF16;
   hp.has_m = has_m;
   hp.remove = h->msam_remove != 0 && has_m;
   hp.climb = h->msam_climb != 0 && has_m;

@@ -206,7 +206,8 @@ extern "C" int kaon_adamuon_step(kaon_plan* pl, const kaon_adamuon_hparams* h, v
                                  int64_t workspace_bytes, uint64_t seed, uint32_t step, void* stream) {
   if (!pl || !h) return fail(KAON_E_INVALID, "kaon_adamuon_step: null argument");
   if (pl->optimizer != KAON_OPT_ADAMUON) return fail(KAON_E_INVALID, "plan was not built for AdaMuon");
-  if (h->bf16_method != KAON_W_NONE && h->bf16_method != KAON_W_SR) return fail(KAON_E_UNSUPPORTED, "bf16_method %d", h->bf16_method);
+  if (h->bf16_method < KAON_W_NONE || h->bf16_method > KAON_W_KAHAN) return fail(KAON_E_UNSUPPORTED, "bf16_method %d", h->bf16_method);
+  if (int rc = check_kahan(pl, h->bf16_method)) return rc;
   if (h->gradient_centralization) return fail(KAON_E_UNSUPPORTED, "AdaMuon with gradient_centralization=True is not built (its default is off)");
   if (!(h->clip_threshold > 0.0)) return fail(KAON_E_INVALID, "clip_threshold must be > 0");
   if (h->ns_steps < 1) return fail(KAON_E_INVALID, "ns_steps must be >= 1");
@@ -282,6 +283,7 @@ extern "C" int kaon_adamuon_step(kaon_plan* pl, const kaon_adamuon_hparams* h, v
   hp.cautious = h->cautious != 0;
   hp.gc = 0;
   hp.sr = h->bf16_method == KAON_W_SR && pl->param_dtype == KAON_DT_BF16;
+  hp.kahan = h->bf16_method == KAON_W_KAHAN && pl->param_dtype == KAON_DT_BF16;
   hp.has_m = has_m;
   hp.step = step; hp.k0 = (uint32_t)seed; hp.k1 = (uint32_t)(seed >> 32);
   if (hp.cautious) { v.tasks = pl->d_tasks_full; v.n_tasks = pl->n_tasks_full; }

@@ -122,6 +122,17 @@ __device__ __forceinline__ void write8_bf16(uint32_t pw[4], const float d[8], fl
   }
 }
 
+// Kahan-compensated bf16 write, p -= d (reference src/kaon/_backend.py:89-94).  Every line of the
+// reference is a bf16 tensor op, i.e. an fp32 operation whose result is rounded to bf16:
+//   shift -= bf16(d);  p_before = p;  p += shift;  shift += (p_before - p)
+// p and shift hold bf16 values in fp32 registers.
+__device__ __forceinline__ void kahan_step(float& p, float& shift, float d) {
+  const float s1 = round_bf16(__fsub_rn(shift, round_bf16(d)));
+  const float pn = round_bf16(__fadd_rn(p, s1));
+  shift = round_bf16(__fadd_rn(s1, round_bf16(__fsub_rn(p, pn))));
+  p = pn;
+}
+
 // ----------------------------------------------------------------------------- warp helpers
 
 __device__ __forceinline__ float warp_sum(float v) {

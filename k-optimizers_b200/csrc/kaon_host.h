@@ -13,6 +13,8 @@ int cuda_fail(cudaError_t e, const char* what);     // KAON_E_CUDA with the runt
 size_t momentum_bytes_per_cap(int momentum_kind);   // bytes of momentum storage per CAP elements
 int configure_launch(kaon_plan* pl, const cudaDeviceProp& prop);  // Lion: grid + dynamic shared memory
 int configure_launch_adakaon(kaon_plan* pl, const cudaDeviceProp& prop, int max_cols);
+// bf16_method == KAHAN with bf16 weights needs every tensor's shift buffer: KAON_OK or an error
+int check_kahan(const kaon_plan* pl, int bf16_method);
 
 #define KAON_CUDA(call)                                              \
   do {                                                               \

@@ -38,8 +38,30 @@ __device__ __forceinline__ void mirror_copy(const Peers* pr, const void* local, 
 template <typename PT>
 __device__ __forceinline__ void update8(void* pe, int cnt, const float dlt[8], float alpha, bool sr,
                                         const SrStream& st, uint32_t tensor_id, uint64_t q,
-                                        const Peers* pr) {
+                                        const Peers* pr, void* she = nullptr) {
   if constexpr (Elems<PT>::IS_BF16) {
+    if (she != nullptr) {  // Kahan: p -= dlt with the compensation buffer (alpha is -1 on this path)
+      float pv[8], sh[8];
+      load8_guard<__nv_bfloat16>(pe, cnt, pv);
+      load8_guard<__nv_bfloat16>(she, cnt, sh);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) kahan_step(pv[k], sh[k], dlt[k]);
+      if (cnt >= 8) {
+        const uint4 out = make_uint4(pack_bf16_rn(pv[0], pv[1]), pack_bf16_rn(pv[2], pv[3]),
+                                     pack_bf16_rn(pv[4], pv[5]), pack_bf16_rn(pv[6], pv[7]));
+        *reinterpret_cast<uint4*>(pe) = out;
+        mirror16(pr, pe, out);
+        *reinterpret_cast<uint4*>(she) = make_uint4(pack_bf16_rn(sh[0], sh[1]), pack_bf16_rn(sh[2], sh[3]),
+                                                    pack_bf16_rn(sh[4], sh[5]), pack_bf16_rn(sh[6], sh[7]));
+      } else {
+        for (int k = 0; k < cnt; ++k) {
+          reinterpret_cast<uint16_t*>(pe)[k] = (uint16_t)(__float_as_uint(pv[k]) >> 16);
+          reinterpret_cast<uint16_t*>(she)[k] = (uint16_t)(__float_as_uint(sh[k]) >> 16);
+        }
+        mirror_copy(pr, pe, cnt * 2);
+      }
+      return;
+    }
     uint32_t noise[4] = {0u, 0u, 0u, 0u};
     if (sr) st.draw8(tensor_id, q, noise);
     if (cnt >= 8) {

@@ -15,7 +15,7 @@ namespace kaon {
 
 struct LionDev {
   float lr, b1, w1, b2, w2, wd;
-  int cautious, gc, sr, has_wd;
+  int cautious, gc, sr, has_wd, kahan;
   uint32_t step, k0, k1;
   uint32_t rk0[10], rk1[10];  // Philox round keys (k + r * Weyl), precomputed on the host
 };
@@ -409,7 +409,8 @@ __device__ void lion_main(const PlanView& pv, const LionDev& hp, const Task& t, 
 #pragma unroll
         for (int k = 0; k < 8; ++k) dl[k] = __fmul_rn(dl[k], hp.lr);
         update8<PT>(pbase + (size_t)v * 8 * E::BYTES, cnt, dl, -1.0f, hp.sr != 0, st, d.tensor_id,
-                    (uint64_t)((t.e0 >> 3) + v), MIRROR ? &pv.peers : nullptr);
+                    (uint64_t)((t.e0 >> 3) + v), MIRROR ? &pv.peers : nullptr,
+                    (MIRROR && hp.kahan) ? reinterpret_cast<unsigned char*>(d.shift) + (size_t)t.e0 * 2 + (size_t)v * 16 : nullptr);
       }
     }
   }
@@ -534,11 +535,13 @@ __device__ void lion_apply(const PlanView& pv, const LionDev& hp, const Task& t,
       }
     }
     update8<PT>(pbase + (size_t)v * 8 * E::BYTES, cnt, dl, -1.0f, hp.sr != 0, st, d.tensor_id,
-                (uint64_t)((t.e0 >> 3) + v), MIRROR ? &pv.peers : nullptr);
+                (uint64_t)((t.e0 >> 3) + v), MIRROR ? &pv.peers : nullptr,
+                (MIRROR && hp.kahan) ? reinterpret_cast<unsigned char*>(d.shift) + (size_t)t.e0 * 2 + (size_t)v * 16 : nullptr);
   }
 }
 
-// MIRROR = false compiles the mirror stores out (a plan without peers pays nothing for them).
+// MIRROR = true is the general build: weight mirrors on other GPUs and the Kahan write.  MIRROR = false
+// compiles both out (the common single-GPU stochastic-rounding / nearest step pays nothing for them).
 template <typename PT, int MK, bool MIRROR>
 __global__ void __launch_bounds__(NTHREADS, 4) lion_kernel(PlanView pv, LionDev hp) {
   extern __shared__ __align__(128) unsigned char dyn[];
@@ -622,7 +625,8 @@ extern "C" int kaon_lion_step(kaon_plan* pl, const kaon_lion_hparams* h, uint64_
                               void* stream) {
   if (!pl || !h) return fail(KAON_E_INVALID, "kaon_lion_step: null argument");
   if (pl->optimizer != KAON_OPT_LION) return fail(KAON_E_INVALID, "plan was not built for Lion");
-  if (h->bf16_method != KAON_W_NONE && h->bf16_method != KAON_W_SR) return fail(KAON_E_UNSUPPORTED, "bf16_method %d", h->bf16_method);
+  if (h->bf16_method < KAON_W_NONE || h->bf16_method > KAON_W_KAHAN) return fail(KAON_E_UNSUPPORTED, "bf16_method %d", h->bf16_method);
+  if (int rc = check_kahan(pl, h->bf16_method)) return rc;
   LionDev hp;
   hp.lr = (float)h->lr;
   hp.b1 = (float)h->beta1; hp.w1 = (float)(1.0 - h->beta1);
@@ -632,6 +636,7 @@ extern "C" int kaon_lion_step(kaon_plan* pl, const kaon_lion_hparams* h, uint64_
   hp.cautious = h->cautious != 0;
   hp.gc = h->gradient_centralization != 0;
   hp.sr = h->bf16_method == KAON_W_SR && pl->param_dtype == KAON_DT_BF16;
+  hp.kahan = h->bf16_method == KAON_W_KAHAN && pl->param_dtype == KAON_DT_BF16;
   hp.step = step; hp.k0 = (uint32_t)seed; hp.k1 = (uint32_t)(seed >> 32);
   for (int r = 0; r < 10; ++r) { hp.rk0[r] = hp.k0 + 0x9E3779B9u * (uint32_t)r; hp.rk1[r] = hp.k1 + 0xBB67AE85u * (uint32_t)r; }
   cudaStream_t s = (cudaStream_t)stream;
@@ -639,7 +644,7 @@ extern "C" int kaon_lion_step(kaon_plan* pl, const kaon_lion_hparams* h, uint64_
   if (hp.cautious) { v.tasks = pl->d_tasks_full; v.n_tasks = pl->n_tasks_full; }
   else { v.tasks = pl->d_tasks_main; v.n_tasks = pl->n_tasks_main; }
   KAON_CUDA(cudaMemsetAsync(v.task_counter, 0, pl->counters_bytes - sizeof(unsigned), s));
-  LionKernel k = pick_lion(pl->param_dtype, pl->momentum_kind, v.peers.n > 0);
+  LionKernel k = pick_lion(pl->param_dtype, pl->momentum_kind, v.peers.n > 0 || hp.kahan);
   k<<<pl->grid, NTHREADS, pl->smem_bytes, s>>>(v, hp);
   KAON_CUDA(cudaGetLastError());
   pl->launches += 1;
@@ -806,6 +811,7 @@ extern "C" int kaon_lion_step_noalloc(const kaon_tensor_desc* t, int param_dtype
   hp.cautious = h->cautious != 0;
   hp.gc = h->gradient_centralization != 0;
   hp.sr = h->bf16_method == KAON_W_SR && param_dtype == KAON_DT_BF16;
+  hp.kahan = 0;
   hp.step = step; hp.k0 = (uint32_t)seed; hp.k1 = (uint32_t)(seed >> 32);
   for (int r = 0; r < 10; ++r) { hp.rk0[r] = hp.k0 + 0x9E3779B9u * (uint32_t)r; hp.rk1[r] = hp.k1 + 0xBB67AE85u * (uint32_t)r; }
 

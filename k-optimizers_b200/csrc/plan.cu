@@ -82,6 +82,18 @@ static int split_tensor(const kaon_tensor_desc& d, int ti, int mk, std::vector<T
 
 }  // namespace kaon
 
+namespace kaon {
+
+int check_kahan(const kaon_plan* pl, int bf16_method) {
+  if (bf16_method != KAON_W_KAHAN || pl->param_dtype != KAON_DT_BF16) return KAON_OK;
+  for (int i = 0; i < pl->n_tensors; ++i)
+    if (pl->h_tensors[i].numel > 0 && pl->h_tensors[i].shift == nullptr)
+      return fail(KAON_E_INVALID, "bf16_method kahan: tensor %d has no shift buffer", i);
+  return KAON_OK;
+}
+
+}  // namespace kaon
+
 using namespace kaon;
 
 extern "C" {
@@ -114,6 +126,8 @@ int kaon_plan_create(kaon_plan** out, int optimizer, int param_dtype, int moment
     }
     DevTensor& t = tens[i];
     t.p = d.p; t.m = d.m; t.m_scale = d.m_scale; t.stat_a = d.stat_a; t.stat_b = d.stat_b;
+    t.shift = d.shift;
+    if ((uintptr_t)d.shift & 15) return fail(KAON_E_INVALID, "tensor %d: shift buffer not 16-byte aligned", i);
     t.numel = d.numel;
     t.rows = (int)d.rows;
     t.cols = (int)(d.rows > 0 ? d.numel / d.rows : std::min<long long>(d.numel, 0x7fffffff));

@@ -48,6 +48,13 @@ def init_momentum_state(state: dict[str, Any], grad: torch.Tensor, md: str, bloc
         state["m_block"] = bs
 
 
+def init_shift_state(p: torch.Tensor, state: dict[str, Any], group: dict[str, Any]) -> None:
+    """Kahan compensation buffer for low-precision weights (reference src/kaon/lion.py:240-241,
+    src/kaon/adakaon.py:334-335, src/kaon/adamuon.py:315-316)."""
+    if group.get("bf16_method") == "kahan" and p.dtype in (torch.bfloat16, torch.float16):
+        state["shift"] = torch.zeros_like(p, memory_format=torch.contiguous_format)
+
+
 class GroupPlan:
     """One C-ABI plan: the tensors of one (param group, device, dtype) bucket."""
 
@@ -84,6 +91,12 @@ class GroupPlan:
                         raise L.KaonError(f"optimizer state '{key}' must be contiguous and on the parameter's device")
                     setattr(d, field, t.data_ptr())
                     self._keep.append(t)
+            sh = st.get("shift")
+            if sh is not None:
+                if not sh.is_contiguous() or sh.device != p.device or sh.dtype != p.dtype:
+                    raise L.KaonError("optimizer state 'shift' must be contiguous, on the parameter's device and of its dtype")
+                d.shift = sh.data_ptr()
+                self._keep.append(sh)
             a = st.get("row") if "row" in st else st.get("v")
             b = st.get("col")
             for field, t in (("stat_a", a), ("stat_b", b)):
@@ -247,8 +260,6 @@ class FusedStepMixin:
         state_of = state_of or (lambda p: self.state[p])
         self._t += 1
         for gi, group in enumerate(self.param_groups):
-            if group.get("bf16_method") == "kahan":
-                raise NotImplementedError("kaon_b200: bf16_method='kahan' is not built yet")
             for pl in self._group_plans(gi, group, state_of):
                 with torch.cuda.device(pl.device):
                     stream = torch.cuda.current_stream(pl.device).cuda_stream

@@ -12,17 +12,18 @@ LIB_PATH = os.path.join(PKG, "libkaon_b200.so")
 
 DT_F32, DT_BF16 = 0, 1
 M_F32, M_BF16, M_INT8, M_4BIT, M_NONE = 0, 1, 2, 3, 4
-W_NONE, W_SR = 0, 1
+W_NONE, W_SR, W_KAHAN = 0, 1, 2
 OPT_LION, OPT_ADAKAON, OPT_ADAMUON = 0, 1, 2
 TAG_UPDATE, TAG_REMOVE, TAG_CLIMB, TAG_EVAL, TAG_TRAIN = 0, 1, 2, 3, 4
 MOMENTUM_KIND = {"float32": M_F32, "bfloat16": M_BF16, "int8": M_INT8, "4bit": M_4BIT}
-BF16_METHOD = {"none": W_NONE, "stochastic_rounding": W_SR}
+BF16_METHOD = {"none": W_NONE, "stochastic_rounding": W_SR, "kahan": W_KAHAN}
 
 
 class TensorDesc(C.Structure):
     _fields_ = [("p", C.c_void_p), ("g", C.c_void_p), ("m", C.c_void_p), ("m_scale", C.c_void_p),
                 ("stat_a", C.c_void_p), ("stat_b", C.c_void_p), ("numel", C.c_int64),
-                ("rows", C.c_int64), ("tensor_id", C.c_uint32), ("block", C.c_uint32)]
+                ("rows", C.c_int64), ("tensor_id", C.c_uint32), ("block", C.c_uint32),
+                ("shift", C.c_void_p)]
 
 
 class LionHParams(C.Structure):
@@ -76,7 +77,7 @@ def lib() -> C.CDLL:
         _lib.kaon_plan_device_bytes.argtypes = [C.c_void_p]
         _lib.kaon_plan_launch_count.argtypes = [C.c_void_p]
         _lib.kaon_plan_set_peers.argtypes = [C.c_void_p, C.POINTER(C.c_int64), C.c_int]
-        if _lib.kaon_abi_version() != 1:
+        if _lib.kaon_abi_version() != 2:
             raise KaonError("libkaon_b200.so ABI version mismatch")
     return _lib
 

@@ -18,7 +18,7 @@ from torch.optim import Optimizer
 
 from . import _lib as L
 from ._autolr import DEFAULT_FUSE_REL, AutoLRMixin
-from ._engine import FusedStepMixin, GroupPlan, init_momentum_state
+from ._engine import FusedStepMixin, GroupPlan, init_momentum_state, init_shift_state
 from ._state import load_state_dict_exact
 
 __all__ = ["Adakaon"]
@@ -108,6 +108,7 @@ class Adakaon(FusedStepMixin, AutoLRMixin, Optimizer):
         init_second_moment_state(p, state)
         if group["betas"][0] > 0:
             init_momentum_state(state, p.grad, group["momentum_dtype"], group["momentum_4bit_block"])
+        init_shift_state(p, state, group)
 
     def _launch(self, plan: GroupPlan, group: dict[str, Any], step: int, stream: int) -> None:
         ms = self._msam.get(id(group), {})

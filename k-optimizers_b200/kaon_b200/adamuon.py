@@ -18,7 +18,7 @@ from torch.optim import Optimizer
 
 from . import _lib as L
 from ._autolr import DEFAULT_FUSE_REL, AutoLRMixin
-from ._engine import FusedStepMixin, GroupPlan, init_momentum_state
+from ._engine import FusedStepMixin, GroupPlan, init_momentum_state, init_shift_state
 from ._state import load_state_dict_exact
 from .adakaon import init_second_moment_state
 
@@ -122,6 +122,7 @@ class AdaMuon(FusedStepMixin, AutoLRMixin, Optimizer):
         init_second_moment_state(p, state)
         if group["betas"][0] > 0:
             init_momentum_state(state, p.grad, group["momentum_dtype"], group["momentum_4bit_block"])
+        init_shift_state(p, state, group)
 
     def _workspace(self, plan: GroupPlan) -> Tensor:
         """Device scratch for the orthogonalised matrices; one buffer per device, grown on demand and

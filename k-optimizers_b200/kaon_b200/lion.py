@@ -17,7 +17,7 @@ from torch.optim import Optimizer
 
 from . import _lib as L
 from ._autolr import DEFAULT_FUSE_REL, AutoLRMixin
-from ._engine import FusedStepMixin, GroupPlan, init_momentum_state
+from ._engine import FusedStepMixin, GroupPlan, init_momentum_state, init_shift_state
 from ._state import load_state_dict_exact
 
 __all__ = ["Lion"]
@@ -84,6 +84,7 @@ class Lion(FusedStepMixin, AutoLRMixin, Optimizer):
     @torch.no_grad()
     def _init_state(self, p: Tensor, state: dict[str, Any], group: dict[str, Any]) -> None:
         init_momentum_state(state, p.grad, group["momentum_dtype"], group["momentum_4bit_block"])
+        init_shift_state(p, state, group)
 
     def _launch(self, plan: GroupPlan, group: dict[str, Any], step: int, stream: int) -> None:
         if group["bf16_method"] == "stochastic_rounding" and plan.params[0].dtype == torch.float16:

@@ -22,7 +22,7 @@ _SO = os.path.join(_HERE, "libkaon_oracle.so")
 
 F32, BF16 = 0, 1
 M_F32, M_BF16, M_INT8, M_4BIT = 0, 1, 2, 3
-W_NONE, W_SR, W_SR_NOISE = 0, 1, 2
+W_NONE, W_SR, W_SR_NOISE, W_KAHAN = 0, 1, 2, 3
 MKIND = {"float32": M_F32, "bfloat16": M_BF16, "int8": M_INT8, "4bit": M_4BIT}
 METHOD = {"none": W_NONE, "stochastic_rounding": W_SR}
 
@@ -227,6 +227,21 @@ class OracleOptimizer:
     def _lazy_init(self, t: OracleTensor) -> None:
         raise NotImplementedError
 
+    def _method(self, t: OracleTensor, noise=None) -> int:
+        """Weight-write mode of this step call; for the Kahan write also hands the tensor's shift buffer
+        (state["shift"], bf16 bits; reference src/kaon/lion.py:240-241) to the C side."""
+        if noise is not None:
+            return W_SR_NOISE
+        m = self.hp["bf16_method"]
+        if m != "kahan":
+            return METHOD[m]
+        if t.p.dtype != np.uint16:
+            return W_NONE  # fp32 weights: plain subtract
+        if "shift" not in t.state:
+            t.state["shift"] = np.zeros(t.n, np.uint16)
+        lib().ko_set_kahan_shift(_p(t.state["shift"]))
+        return W_KAHAN
+
     def _args_common(self, t: OracleTensor, g: np.ndarray):
         hp = self.hp
         st = t.state
@@ -256,7 +271,7 @@ class OracleLion(OracleOptimizer):
             self._lazy_init(t)
             kept = C.c_int64(-1)
             noise = None if noises is None else noises[tid]
-            method = W_SR_NOISE if noise is not None else METHOD[hp["bf16_method"]]
+            method = self._method(t, noise)
             rc = lib().ko_lion_step(
                 *self._args_common(t, g), C.c_double(hp["lr"]), C.c_double(hp["betas"][0]),
                 C.c_double(hp["betas"][1]), C.c_double(hp["weight_decay"]),
@@ -294,7 +309,7 @@ class OracleAdakaon(OracleOptimizer):
             st = t.state
             kept, rms = C.c_int64(-1), C.c_float(0)
             noise = None if noises is None else noises[tid]
-            method = W_SR_NOISE if noise is not None else METHOD[hp["bf16_method"]]
+            method = self._method(t, noise)
             rc = lib().ko_adakaon_step(
                 *self._args_common(t, g), _p(st["row"] if t.rows else st["v"]),
                 _p(st["col"] if t.rows else None), C.c_double(hp["lr"]),
@@ -393,7 +408,7 @@ class OracleAdaMuon(OracleOptimizer):
                 C.c_double(hp["betas"][0]), C.c_double(hp["betas"][1]), C.c_double(hp["eps"][0]),
                 C.c_double(hp["weight_decay"]), C.c_double(hp["clip_threshold"]),
                 C.c_int(hp["ns_steps"]), C.c_int(bool(hp["cautious"])),
-                C.c_int(bool(hp["gradient_centralization"])), C.c_int(METHOD[hp["bf16_method"]]),
+                C.c_int(bool(hp["gradient_centralization"])), C.c_int(self._method(t)),
                 C.c_uint64(self.seed), C.c_uint32(self.t), C.c_uint32(tid), _p(None), _p(ns_in),
                 _p(ov))
             assert rc == 0

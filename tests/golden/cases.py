@@ -26,17 +26,21 @@ CASES = {
     "lion_bf16_nocautious": ("Lion", dict(lr=2e-4, momentum_dtype="bfloat16", cautious=False, bf16_method="none"), SMALL, "bf16", 4, 3, {}),
     "lion_4bit_f32params": ("Lion", dict(lr=2e-4, betas=(0.95, 0.98), momentum_dtype="4bit"), SMALL, "f32", 5, 4, {}),
     "lion_4bit_sr": ("Lion", dict(lr=2e-4, betas=(0.95, 0.98), momentum_dtype="4bit"), SMALL, "bf16", 4, 5, {}),
+    "lion_4bit_kahan": ("Lion", dict(lr=2e-4, betas=(0.95, 0.98), momentum_dtype="4bit", bf16_method="kahan"), SMALL, "bf16", 6, 6, {}),
+    "lion_int8_kahan_wd_nocautious": ("Lion", dict(lr=2e-4, momentum_dtype="int8", weight_decay=0.1, cautious=False, bf16_method="kahan"), SMALL, "bf16", 4, 7, {}),
     # Adakaon, the C1 settings on small shapes
     "adakaon_int8_none": ("Adakaon", dict(lr=1e-4, betas=(0.9, 0.999), momentum_dtype="int8", bf16_method="none"), SMALL, "bf16", 6, 10, {}),
     "adakaon_int8_sr": ("Adakaon", dict(lr=1e-4, betas=(0.9, 0.999), momentum_dtype="int8"), SMALL, "bf16", 6, 11, {}),
     "adakaon_int8_outlier": ("Adakaon", dict(lr=1e-4, betas=(0.9, 0.999), momentum_dtype="int8", bf16_method="none"), SMALL, "bf16", 5, 12, {"outlier": True}),
     "adakaon_4bit_wd_f32": ("Adakaon", dict(lr=1e-4, betas=(0.2, 0.999), weight_decay=0.1, momentum_dtype="4bit"), SMALL, "f32", 5, 13, {}),
     "adakaon_bf16m_none": ("Adakaon", dict(lr=1e-4, momentum_dtype="bfloat16", bf16_method="none"), SMALL, "bf16", 4, 14, {}),
+    "adakaon_int8_kahan": ("Adakaon", dict(lr=1e-4, betas=(0.9, 0.999), momentum_dtype="int8", bf16_method="kahan"), SMALL, "bf16", 6, 15, {}),
     # Nekaon (C4 settings; fp32 params make the three writes deterministic) under a cosine LR
     "nekaon_f32": ("Nekaon", dict(lr=1e-4, betas=(0.2, 0.999)), SMALL, "f32", 5, 20, {"lr_sched": "cosine5", "nekaon_eval": True}),
     "nekaon_bf16": ("Nekaon", dict(lr=1e-4, betas=(0.2, 0.999)), SMALL, "bf16", 5, 21, {"lr_sched": "cosine5"}),
     # AdaMuon (C5 settings)
     "adamuon_int8_none": ("AdaMuon", dict(lr=1e-3, ns_steps=2, cautious=True, momentum_dtype="int8", bf16_method="none"), MUON, "bf16", 4, 30, {}),
+    "adamuon_int8_kahan": ("AdaMuon", dict(lr=1e-3, ns_steps=2, cautious=True, momentum_dtype="int8", bf16_method="kahan"), MUON, "bf16", 3, 31, {}),
     # C1 at full size (the CPU-runnable correctness workload); big tensors stored strided
     "c1_full": ("Adakaon", dict(lr=1e-4, betas=(0.9, 0.999), momentum_dtype="int8", bf16_method="stochastic_rounding"), C1, "bf16", 10, 0, {"store_inputs": False, "sample": 257}),
 }

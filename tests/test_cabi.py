@@ -26,7 +26,7 @@ def test_library_exports_every_declared_symbol():
     lib = _lib.lib()
     missing = [n for n in _declared() if not hasattr(lib, n)]
     assert not missing, missing
-    assert lib.kaon_abi_version() == 1
+    assert lib.kaon_abi_version() == 2
 
 
 def test_host_side_argument_checks():

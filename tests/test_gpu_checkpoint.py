@@ -109,7 +109,8 @@ def test_nekaon_checkpoint_in_eval_mode_round_trips():
 
 
 @pytest.mark.parametrize("name", ["lion_4bit_none", "lion_int8_none", "adakaon_int8_none", "adakaon_4bit_wd_f32",
-                                  "adakaon_bf16m_none", "nekaon_bf16", "adamuon_int8_none"])
+                                  "adakaon_bf16m_none", "nekaon_bf16", "adamuon_int8_none", "lion_4bit_kahan",
+                                  "adakaon_int8_kahan"])
 def test_state_layout_matches_reference(name):
     """Same per-tensor state keys, dtypes and element counts as the reference's state_dict."""
     from _gpu import run_case_gpu

@@ -150,6 +150,46 @@ def test_lion_bit_exact(name):
                 assert np.array_equal(t.p, want), (step, i)
 
 
+@pytest.mark.parametrize("name", ["lion_4bit_kahan", "lion_int8_kahan_wd_nocautious"])
+def test_lion_kahan_bit_exact(name):
+    """bf16_method="kahan": weights AND the compensation buffer state["shift"] match the reference bit
+    for bit (reference src/kaon/_backend.py:89-94)."""
+    md = CASES[name][1]["momentum_dtype"]
+    for step, f, opt in _run_oracle(name):
+        _check_state(f, opt, step, exact=True, md=md)
+        for i, t in enumerate(opt.tensors):
+            assert np.array_equal(t.p, f.weights(step, i)), (step, i)
+            assert np.array_equal(t.state["shift"], f.state(step, i, "shift")), (step, i)
+
+
+def _kahan_close(p, shift, want_p, want_shift, tol_ulp=1.0):
+    """Weights within one bf16 ulp, and the compensated value p + shift within `tol_ulp` ulps of p."""
+    if ulp_diff_bf16(p, want_p).max() > 1:
+        return False
+    a = ko.as_f32(p).astype(np.float64) + ko.as_f32(shift)
+    b = ko.as_f32(want_p).astype(np.float64) + ko.as_f32(want_shift)
+    ulp = np.maximum(np.abs(ko.as_f32(want_p)), 1e-30) * 2.0 ** -7
+    return bool((np.abs(a - b) <= tol_ulp * ulp).all())
+
+
+def test_adakaon_kahan():
+    flips = total = 0
+    for step, f, opt in _run_oracle("adakaon_int8_kahan"):
+        fl, to = _check_state(f, opt, step, exact=False, md="int8")
+        flips += fl
+        total += to
+        for i, t in enumerate(opt.tensors):
+            assert _kahan_close(t.p, t.state["shift"], f.weights(step, i), f.state(step, i, "shift")), (step, i)
+    assert flips / total < 2e-3
+
+
+def test_adamuon_kahan():
+    for step, f, opt in _run_oracle("adamuon_int8_kahan"):
+        for i, t in enumerate(opt.tensors):
+            np.testing.assert_allclose(ko.as_f32(t.p), ko.as_f32(f.weights(step, i)), rtol=2e-2, atol=2e-3)
+            assert "shift" in t.state and f.state(step, i, "shift") is not None
+
+
 def test_lion_sr_state_is_weight_independent():
     """Under stochastic rounding the weights differ (different RNG) but no state depends on them."""
     for step, f, opt in _run_oracle("lion_4bit_sr"):
