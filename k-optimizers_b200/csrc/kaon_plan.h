@@ -49,10 +49,10 @@ struct DevTensor {
   int n_stats;          // STATS items (= slots of column partials)
   int n_strips;         // FINAL items
   int n_count;          // COUNT items
-  void* shift;          // Kahan compensation buffer (bf16 [numel]) or null
   long long aux_off;    // float index of this tensor's scratch in `aux`:
                         //   colpart[n_stats][2][cols] | cfac[cols] | rowpart[n_stats] (double) |
                         //   tpart[n_strips] (double) | scal[4] = {rowmean, divisor, rms, -} | rowmax[rows] | mean[rows]
+  void* shift;          // Kahan compensation buffer (bf16 [numel]) or null
 };
 
 // float offsets inside a tensor's aux block

@@ -15,9 +15,10 @@ namespace kaon {
 
 struct LionDev {
   float lr, b1, w1, b2, w2, wd;
-  int cautious, gc, sr, has_wd, kahan;
+  int cautious, gc, sr, has_wd;
   uint32_t step, k0, k1;
   uint32_t rk0[10], rk1[10];  // Philox round keys (k + r * Weyl), precomputed on the host
+  int kahan;
 };
 
 // Philox4x32-10 with the round keys read from the kernel's parameter block.
