@@ -873,6 +873,257 @@ __device__ void ada_rows(const PlanView& pv, const AdaDev& hp, const Task& t, St
   }
 }
 
+// ----------------------------------------------------------------------------- COUNT / APPLY, streaming
+
+// The same two work items for the common case - rows a multiple of 8 elements, gradient as the signal -
+// without shared-memory staging and without a barrier in the loop: every thread streams its vectors
+// straight from global memory (gradient, momentum, weights) and fetches what is per row or per column
+// (centralization mean, row statistic, column factor, int8 scales) from L2, where the earlier stages
+// left it.  Rows of an item belong to this CTA alone, so the int8 row maxima are reduced with
+// atomicMax on the tensor's scratch (COUNT) and the old row scales are set aside once per item (APPLY).
+// Results are bit-identical to ada_rows: same arithmetic, same noise indices.
+template <typename PT, int MK, bool APPLY>
+__device__ void ada_stream(const PlanView& pv, const AdaDev& hp, const Task& t, const AdaSmem& sm, int tid) {
+  using E = Elems<PT>;
+  const DevTensor d = pv.tensors[t.tensor];
+  const unsigned char* g = reinterpret_cast<const unsigned char*>(pv.grads[t.tensor]);
+  if (g == nullptr) {
+    if (!APPLY) {
+      __syncthreads();
+      if (tid == 0) signal_counter(pv.done + 3 * pv.n_tensors + t.tensor, 1u);
+    }
+    return;
+  }
+  bool ok = true;
+  if (tid == 0) {
+    ok = wait_counter(pv.done + 2 * pv.n_tensors + t.tensor, 1u, pv.status, 12001u);
+    if (ok && APPLY && hp.cautious)
+      ok = wait_counter(pv.done + 3 * pv.n_tensors + t.tensor, (unsigned)d.n_count, pv.status, 13001u);
+  }
+  ok = __syncthreads_and(ok) != 0;
+  const int C = d.cols;
+  const int nrows = t.n / C;
+  const bool gc = hp.gc != 0;
+  const float* scal = pv.aux + aux_scal(d);
+  const float rowmean = __ldcg(scal + 0);
+  Chain ch;
+  ch.div = __ldcg(scal + 1);
+  ch.use_div = ch.div != 1.0f;
+  ch.rcp_div = __fdiv_rn(1.0f, ch.div);
+  float denom = 1.0f, rcp_denom = 1.0f;
+  if (APPLY && hp.cautious) {
+    const unsigned kept = __ldcg(pv.kept + t.tensor);
+    denom = fmaxf(__fdiv_rn((float)kept, (float)d.numel), 1e-8f);
+    rcp_denom = __fdiv_rn(1.0f, denom);
+  }
+  const float* cfac = pv.aux + aux_cfac(d);
+  const float* mean = pv.aux + aux_mean(d);
+  unsigned* rowmax = reinterpret_cast<unsigned*>(pv.aux + aux_rowmax(d));
+  float* oldsc = pv.aux + aux_oldsc(d);
+  if constexpr (MK == KAON_M_INT8) {
+    if (ok) {
+      if (APPLY) {
+        for (int r = tid; r < nrows; r += AT) oldsc[t.row0 + r] = d.m_scale[t.row0 + r];
+      } else {
+        for (int r = tid; r < nrows; r += AT) rowmax[t.row0 + r] = 0u;
+      }
+    }
+    __syncthreads();
+  }
+  SrStream s_upd{Philox{hp.k0, hp.k1}, hp.step, KAON_TAG_UPDATE};
+  SrStream s_rem{Philox{hp.k0, hp.k1}, hp.step, KAON_TAG_REMOVE};
+  SrStream s_clb{Philox{hp.k0, hp.k1}, hp.step, KAON_TAG_CLIMB};
+  const bool sr = hp.sr != 0;
+  const bool need_p = APPLY || hp.has_wd;
+  const int lane = tid & 31;
+  unsigned kept_local = 0;
+
+  for (int c0 = 0; ok && c0 < nrows; c0 += d.chunk_rows) {
+    const int nrc = min(d.chunk_rows, nrows - c0);
+    const int nvec = (nrc * C) >> 3;
+    const int nvec_pad = (nvec + 31) & ~31;
+    const long long e0 = t.e0 + (long long)c0 * C;
+    const unsigned char* gbase = g + e0 * E::BYTES;
+    const unsigned char* mbase = m_ptr<MK>(d, e0);
+    unsigned char* pbase = reinterpret_cast<unsigned char*>(d.p) + e0 * E::BYTES;
+    for (int v = tid; v < nvec_pad; v += AT) {
+      const bool act = v < nvec;
+      const int vv = act ? v : 0;
+      const int r = row_of((unsigned)vv * 8u, d);
+      const int row = t.row0 + c0 + r;
+      const int col = vv * 8 - r * C;
+      float gv[8], mo[8], mn[8], pc[8], dl[8];
+      // ---- loads ----
+      E::load8(gbase + (size_t)vv * 8 * E::BYTES, gv);
+      if (need_p) E::load8(pbase + (size_t)vv * 8 * E::BYTES, pc);
+      else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) pc[k] = 0.0f;
+      }
+      const float mu = gc ? __ldcg(mean + row) : 0.0f;
+      const float rstat = __ldcg(d.stat_a + row);
+      const float4 c0v = __ldcg(reinterpret_cast<const float4*>(cfac + col));
+      const float4 c1v = __ldcg(reinterpret_cast<const float4*>(cfac + col + 4));
+      const float cf[8] = {c0v.x, c0v.y, c0v.z, c0v.w, c1v.x, c1v.y, c1v.z, c1v.w};
+      if constexpr (MK == KAON_M_4BIT) {
+        const float sc_old = d.m_scale[d.block == 128u ? ((e0 >> 7) + (vv >> 4)) : 0];
+        decode8<MK>(mbase, vv, 8, sc_old, mo);
+      } else if constexpr (MK == KAON_M_INT8) {
+        const float sc_old = APPLY ? __ldcg(oldsc + row) : d.m_scale[row];
+        decode8<MK>(mbase, vv, 8, sc_old, mo);
+      } else if constexpr (MK == KAON_M_NONE) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) mo[k] = 0.0f;
+      } else {
+        decode8<MK>(mbase, vv, 8, 1.0f, mo);
+      }
+      const float rf = rsqrt_torch(__fdiv_rn(rstat, rowmean));
+      // ---- the chain ----
+      if (hp.remove && need_p) {
+        uint32_t nz[4] = {0u, 0u, 0u, 0u};
+        if (E::IS_BF16) s_rem.draw8(d.tensor_id, (uint64_t)((e0 >> 3) + vv), nz);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          pc[k] = write_step<PT>(pc[k], climb_e(mo[k], hp.a_remove, hp.b_remove), 1.0f, E::IS_BF16, noise_lane(nz, k));
+      }
+      if (gc) {
+#pragma unroll
+        for (int k = 0; k < 8; k += 2) {
+          const float x0 = __fsub_rn(gv[k], mu), x1 = __fsub_rn(gv[k + 1], mu);
+          if (E::IS_BF16) {
+            const uint32_t pk = pack_bf16_rn(x0, x1);
+            gv[k] = bf16lo(pk); gv[k + 1] = bf16hi(pk);
+          } else {
+            gv[k] = x0; gv[k + 1] = x1;
+          }
+        }
+      }
+      unsigned kept = 0;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float u = update_of(gv[k], rf, cf[k], ch, hp.upd_scale);
+        mn[k] = ema_of<MK>(mo[k], u, hp);
+        const float dv = hp.has_wd ? __fmaf_rn(pc[k], hp.lrwd, mn[k]) : mn[k];
+        dl[k] = dv;
+        if (__fmul_rn(dv, gv[k]) > 0.0f) kept |= 1u << k;
+      }
+      if constexpr (!APPLY) {
+        if (act) kept_local += __popc(kept);
+        if constexpr (MK == KAON_M_INT8) {
+          float a = 0.0f;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) a = fmaxf(a, fabsf(mn[k]));
+          unsigned bits = act ? __float_as_uint(a) : 0u;
+          const int row_l0 = __shfl_sync(0xffffffffu, row, 0);
+          if (__all_sync(0xffffffffu, !act || row == row_l0)) {
+            bits = __reduce_max_sync(0xffffffffu, bits);
+            if (lane == 0 && bits) atomicMax(rowmax + row_l0, bits);
+          } else if (act) {
+            atomicMax(rowmax + row, bits);
+          }
+        }
+      } else {
+        float md[8];  // the momentum as stored (decoded), for the Nekaon climb
+        if constexpr (MK == KAON_M_4BIT) {
+          float a = 0.0f;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) a = fmaxf(a, act ? fabsf(mn[k]) : 0.0f);
+          a = fmaxf(group_max(a, 16), 1e-12f);
+          __syncwarp();  // every lane of the block has read the old scale before it is replaced
+          const float sc = __fdiv_rn(a, 7.0f);
+          const float inv = __fdividef(1.0f, sc);
+          uint32_t word = 0;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const float q = quant_round(mn[k], sc, inv, 1e-4f);
+            const int qi = min(max((int)q, -7), 7);
+            md[k] = __fmul_rn((float)qi, sc);
+            word |= (uint32_t)(qi + 8) << (4 * k);
+          }
+          if (act) {
+            *reinterpret_cast<uint32_t*>((unsigned char*)d.m + (e0 >> 1) + (size_t)v * 4) = word;
+            if ((v & 15) == 0) d.m_scale[(d.block == 128u) ? ((e0 >> 7) + (v >> 4)) : 0] = sc;
+          }
+        } else if constexpr (MK == KAON_M_INT8) {
+          const float sc = __fdiv_rn(fmaxf(__uint_as_float(__ldcg(rowmax + row)), 1e-12f), 127.0f);
+          const float inv = __fdividef(1.0f, sc);
+          uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const int qi = min(max((int)quant_round(mn[k], sc, inv, 1e-3f), -127), 127);
+            md[k] = __fmul_rn((float)qi, sc);
+            const uint32_t byte = (uint32_t)(qi & 0xFF);
+            if (k < 4) w0 |= byte << (8 * k); else w1 |= byte << (8 * (k - 4));
+          }
+          if (act) {
+            *reinterpret_cast<uint2*>((unsigned char*)d.m + e0 + (size_t)v * 8) = make_uint2(w0, w1);
+            if (col == 0) d.m_scale[row] = sc;
+          }
+        } else if constexpr (MK == KAON_M_BF16 || MK == KAON_M_F32) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) md[k] = mn[k];
+          if (act) {
+            if constexpr (MK == KAON_M_BF16) store8<__nv_bfloat16>((unsigned char*)d.m + e0 * 2 + (size_t)v * 16, 8, mn, nullptr);
+            else store8<float>((unsigned char*)d.m + e0 * 4 + (size_t)v * 32, 8, mn, nullptr);
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) md[k] = 0.0f;
+        }
+        if (act) {
+          if (E::IS_BF16 && hp.kahan) {
+            unsigned char* she = reinterpret_cast<unsigned char*>(d.shift) + (size_t)e0 * 2 + (size_t)v * 16;
+            float sh[8];
+            load8_guard<__nv_bfloat16>(she, 8, sh);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              float f = dl[k];
+              if (hp.cautious) f = ((kept >> k) & 1u) ? div_shared(f, denom, rcp_denom) : 0.0f;
+              kahan_step(pc[k], sh[k], f);
+            }
+            store8<__nv_bfloat16>(she, 8, sh, nullptr);
+          } else {
+            uint32_t nz[4] = {0u, 0u, 0u, 0u};
+            if (sr) s_upd.draw8(d.tensor_id, (uint64_t)((e0 >> 3) + v), nz);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              float f = dl[k];
+              if (hp.cautious) f = ((kept >> k) & 1u) ? div_shared(f, denom, rcp_denom) : 0.0f;
+              pc[k] = write_step<PT>(pc[k], f, -1.0f, sr, noise_lane(nz, k));
+            }
+          }
+          if (hp.climb && MK != KAON_M_NONE) {
+            uint32_t nc[4] = {0u, 0u, 0u, 0u};
+            if (E::IS_BF16) s_clb.draw8(d.tensor_id, (uint64_t)((e0 >> 3) + v), nc);
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+              pc[k] = write_step<PT>(pc[k], climb_e(md[k], hp.a_climb, hp.b_climb), 1.0f, E::IS_BF16, noise_lane(nc, k));
+          }
+          store8<PT>(pbase + (size_t)v * 8 * E::BYTES, 8, pc, &pv.peers);
+        }
+      }
+    }
+  }
+  if constexpr (!APPLY) {
+    const unsigned tot = block_sum_u(kept_local, sm.red, tid);
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      if (ok) atomicAdd(pv.kept + t.tensor, tot);
+      signal_counter(pv.done + 3 * pv.n_tensors + t.tensor, 1u);
+    }
+  }
+}
+
+// Whether the streaming form handles this tensor and these settings (otherwise: ada_rows).
+template <int MK>
+__device__ __forceinline__ bool stream_ok(const DevTensor& d, const AdaDev& hp) {
+  if ((d.cols & 7) != 0) return false;
+  if (MK == KAON_M_4BIT && d.block != 128u) return false;
+  if (MK == KAON_M_INT8 && !hp.cautious) return false;  // no COUNT item to find the row maxima
+  return true;
+}
+
 // ----------------------------------------------------------------------------- FLAT (1-D tensors)
 
 // reference src/kaon/adakaon.py:908-966: full second moment v, no factoring, no centralization.
@@ -1081,8 +1332,14 @@ __global__ void __launch_bounds__(AT, 1) adakaon_kernel(PlanView pv, AdaDev hp, 
     switch (t.phase) {
       case PH_ADA_STATS: ada_stats<typename std::conditional<MUON, __nv_bfloat16, PT>::type>(pv, hp, t, st, sm_stats, tid); break;
       case PH_ADA_FINAL: ada_final(pv, hp, t, sm_stats, tid); break;
-      case PH_ADA_COUNT: ada_rows<PT, MK, false, MUON>(pv, hp, t, st, sm_rows, tid); break;
-      case PH_ADA_APPLY: ada_rows<PT, MK, true, MUON>(pv, hp, t, st, sm_rows, tid); break;
+      case PH_ADA_COUNT:
+        if (!MUON && stream_ok<MK>(pv.tensors[t.tensor], hp)) ada_stream<PT, MK, false>(pv, hp, t, sm_rows, tid);
+        else ada_rows<PT, MK, false, MUON>(pv, hp, t, st, sm_rows, tid);
+        break;
+      case PH_ADA_APPLY:
+        if (!MUON && stream_ok<MK>(pv.tensors[t.tensor], hp)) ada_stream<PT, MK, true>(pv, hp, t, sm_rows, tid);
+        else ada_rows<PT, MK, true, MUON>(pv, hp, t, st, sm_rows, tid);
+        break;
       case PH_ADA_FLAT: ada_flat<PT, MK>(pv, hp, t, st, sm_rows, tid); break;
       default: break;
     }

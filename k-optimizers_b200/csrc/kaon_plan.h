@@ -64,7 +64,9 @@ __host__ __device__ inline long long aux_scal(const DevTensor& d) { return aux_t
 __host__ __device__ inline long long aux_rowmax(const DevTensor& d) { return aux_scal(d) + 4; }
 // centralization mean of every row, left by STATS for COUNT / APPLY
 __host__ __device__ inline long long aux_mean(const DevTensor& d) { return aux_rowmax(d) + d.rows; }
-__host__ __device__ inline long long aux_size(const DevTensor& d) { return aux_mean(d) + d.rows - d.aux_off; }
+// int8 momentum: the row scales as they were before this step, copied by an APPLY item for its rows
+__host__ __device__ inline long long aux_oldsc(const DevTensor& d) { return aux_mean(d) + d.rows; }
+__host__ __device__ inline long long aux_size(const DevTensor& d) { return aux_oldsc(d) + d.rows - d.aux_off; }
 
 struct Task {
   int tensor;
