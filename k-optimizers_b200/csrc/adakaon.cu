@@ -422,10 +422,12 @@ __device__ void ada_final(const PlanView& pv, const AdaDev& hp, const Task& t, c
   if (tid == 0) tpart[t.slot] = tot;
   __threadfence();
   __syncthreads();
+  int last = 0;
   if (tid == 0) {
     unsigned old;
     asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(pv.done + 1 * pv.n_tensors + t.tensor) : "memory");
     if (old == (unsigned)d.n_strips - 1u) {  // last strip: combine, in slot order
+      last = 1;
       __threadfence();
       const volatile double* rowpart = reinterpret_cast<const volatile double*>(pv.aux + aux_rowpart(d));
       const volatile double* tp = tpart;
@@ -439,9 +441,17 @@ __device__ void ada_final(const PlanView& pv, const AdaDev& hp, const Task& t, c
       scal[0] = rowmean;
       scal[1] = fmaxf(__fdiv_rn(rms, hp.clip), 1.0f);
       scal[2] = rms;
-      __threadfence();
-      signal_counter(pv.done + 2 * pv.n_tensors + t.tensor, 1u);
+      sm.part_s[0] = rowmean;
     }
+  }
+  last = __syncthreads_or(last);
+  if (last) {  // the whole CTA: r_i of every row, then release COUNT / APPLY
+    const float rowmean = sm.part_s[0];
+    float* rfac = pv.aux + aux_rfac(d);
+    for (int r = tid; r < d.rows; r += AT) rfac[r] = rsqrt_torch(__fdiv_rn(__ldcg(d.stat_a + r), rowmean));
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) signal_counter(pv.done + 2 * pv.n_tensors + t.tensor, 1u);
   }
 }
 
@@ -920,6 +930,7 @@ __device__ void ada_stream(const PlanView& pv, const AdaDev& hp, const Task& t, 
   const float* mean = pv.aux + aux_mean(d);
   unsigned* rowmax = reinterpret_cast<unsigned*>(pv.aux + aux_rowmax(d));
   float* oldsc = pv.aux + aux_oldsc(d);
+  const float* rfac = pv.aux + aux_rfac(d);
   if constexpr (MK == KAON_M_INT8) {
     if (ok) {
       if (APPLY) {
@@ -961,7 +972,7 @@ __device__ void ada_stream(const PlanView& pv, const AdaDev& hp, const Task& t, 
         for (int k = 0; k < 8; ++k) pc[k] = 0.0f;
       }
       const float mu = gc ? __ldcg(mean + row) : 0.0f;
-      const float rstat = __ldcg(d.stat_a + row);
+      const float rf = __ldcg(rfac + row);
       const float4 c0v = __ldcg(reinterpret_cast<const float4*>(cfac + col));
       const float4 c1v = __ldcg(reinterpret_cast<const float4*>(cfac + col + 4));
       const float cf[8] = {c0v.x, c0v.y, c0v.z, c0v.w, c1v.x, c1v.y, c1v.z, c1v.w};
@@ -977,7 +988,6 @@ __device__ void ada_stream(const PlanView& pv, const AdaDev& hp, const Task& t, 
       } else {
         decode8<MK>(mbase, vv, 8, 1.0f, mo);
       }
-      const float rf = rsqrt_torch(__fdiv_rn(rstat, rowmean));
       // ---- the chain ----
       if (hp.remove && need_p) {
         uint32_t nz[4] = {0u, 0u, 0u, 0u};

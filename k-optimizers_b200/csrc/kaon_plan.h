@@ -66,7 +66,9 @@ __host__ __device__ inline long long aux_rowmax(const DevTensor& d) { return aux
 __host__ __device__ inline long long aux_mean(const DevTensor& d) { return aux_rowmax(d) + d.rows; }
 // int8 momentum: the row scales as they were before this step, copied by an APPLY item for its rows
 __host__ __device__ inline long long aux_oldsc(const DevTensor& d) { return aux_mean(d) + d.rows; }
-__host__ __device__ inline long long aux_size(const DevTensor& d) { return aux_oldsc(d) + d.rows - d.aux_off; }
+// r_i = rsqrt(row_i / mean(row)) of every row, left by the last FINAL strip for COUNT / APPLY
+__host__ __device__ inline long long aux_rfac(const DevTensor& d) { return aux_oldsc(d) + d.rows; }
+__host__ __device__ inline long long aux_size(const DevTensor& d) { return aux_rfac(d) + d.rows - d.aux_off; }
 
 struct Task {
   int tensor;
