@@ -391,6 +391,155 @@ __device__ void ada_stats(const PlanView& pv, const AdaDev& hp, const Task& t, S
   if (tid == 0) signal_counter(pv.done + 0 * pv.n_tensors + t.tensor, 1u);
 }
 
+// ----------------------------------------------------------------------------- STATS, streaming
+
+// The same work item without shared-memory staging, for rows of at least 256 elements that are a
+// multiple of 8: rows are taken in groups that stay in L2 (a few hundred KB per CTA); each warp owns
+// whole rows of the group and streams them from global memory twice (mean, then the sum of squares:
+// no barrier inside), then every thread walks the group's rows for the columns it owns, with the
+// column partial sums in registers for the whole item.  Two barriers per group instead of six per
+// 16 K elements.  Sums are taken in a fixed order: results are reproducible run to run (they differ
+// from ada_stats in the last bits: another summation order).
+template <typename ST>
+__device__ void ada_stats_stream(const PlanView& pv, const AdaDev& hp, const Task& t, const AdaSmem& sm,
+                                 unsigned char* dyn, int tid) {
+  using E = Elems<ST>;
+  using PT = ST;
+  const DevTensor d = pv.tensors[t.tensor];
+  const unsigned char* g = reinterpret_cast<const unsigned char*>(pv.grads[t.tensor]);
+  if (g != nullptr && pv.signal != nullptr) g = reinterpret_cast<const unsigned char*>(pv.signal[t.tensor]);
+  const int C = d.cols;
+  const int nv = C >> 3;                 // vectors per row
+  const int nrows = t.n / C;
+  const bool gc = hp.gc != 0 && pv.signal == nullptr;
+  const bool ok = g != nullptr;
+  const int warp = tid >> 5, lane = tid & 31;
+  constexpr int NW = AT / 32;
+  // column ownership: nv >= AT: vectors tid, tid+AT, ... of every row; nv < AT: Q row groups, one vector
+  const int Q = nv >= AT ? 1 : AT / nv;
+  const int q = nv >= AT ? 0 : tid / nv;
+  const int v0 = nv >= AT ? tid : tid - q * nv;
+  const bool col_act = q < Q;
+  constexpr int VPT = CAP / 8 / AT;      // vectors per thread at most (rows are <= CAP elements)
+  float a1[VPT][8], a2[VPT][8];
+#pragma unroll
+  for (int j = 0; j < VPT; ++j)
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { a1[j][k] = 0.0f; a2[j][k] = 0.0f; }
+  double rowsum = 0.0;
+  // rows per group: about 384 KB of gradient, a multiple of the warp count, within the row arrays
+  int grp = (int)((384 * 1024) / ((long long)C * E::BYTES));
+  grp = max(NW, min(grp / NW * NW, MAX_TASK_ROWS));
+  const unsigned char* gitem = g + t.e0 * E::BYTES;
+  for (int r0 = 0; ok && r0 < nrows; r0 += grp) {
+    const int nr = min(grp, nrows - r0);
+    // ---- rows: one warp per row ----
+    for (int r = warp; r < nr; r += NW) {
+      const unsigned char* rowp = gitem + (size_t)(r0 + r) * C * E::BYTES;
+      const int row = t.row0 + r0 + r;
+      const float old = d.stat_a[row];
+      float mu = 0.0f;
+      if (gc) {
+        float s = 0.0f;
+        for (int v = lane; v < nv; v += 32) {
+          float x[8];
+          E::load8(rowp + (size_t)v * 8 * E::BYTES, x);
+          s += ((x[0] + x[1]) + (x[2] + x[3])) + ((x[4] + x[5]) + (x[6] + x[7]));
+        }
+        s = warp_sum(s);
+        const float mean = __fdiv_rn(s, (float)C);
+        mu = E::IS_BF16 ? round_bf16(mean) : mean;
+      }
+      float s2 = 0.0f;
+      for (int v = lane; v < nv; v += 32) {
+        float x[8];
+        E::load8(rowp + (size_t)v * 8 * E::BYTES, x);
+        float sq[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float y = centered<PT>(x[k], mu, gc);
+          sq[k] = __fmul_rn(y, y);
+          if (hp.has_eps) sq[k] = __fadd_rn(sq[k], hp.eps1);
+        }
+        s2 += ((sq[0] + sq[1]) + (sq[2] + sq[3])) + ((sq[4] + sq[5]) + (sq[6] + sq[7]));
+      }
+      s2 = warp_sum(s2);
+      if (lane == 0) {
+        const float mean = __fdiv_rn(s2, (float)C);
+        const float rn = lerp_torch(old, mean, hp.w2, hp.w2m1, hp.small_w2 != 0);
+        d.stat_a[row] = rn;
+        sm.mean_s[r] = mu;
+        if (gc) pv.aux[aux_mean(d) + row] = mu;
+        sm.rfac_s[r] = __fdiv_rn(1.0f, rn);
+        rowsum += (double)rn;
+      }
+    }
+    __syncthreads();
+    // ---- columns: this thread's vectors, the group's rows in order (L2 hits) ----
+    if (col_act) {
+#pragma unroll
+      for (int j = 0; j < VPT; ++j) {
+        const int v = v0 + j * AT;
+        if (v < nv && (j == 0 || Q == 1)) {
+          for (int r = q; r < nr; r += Q) {
+            float x[8];
+            E::load8(gitem + ((size_t)(r0 + r) * C + (size_t)v * 8) * E::BYTES, x);
+            const float mu = sm.mean_s[r], ri = sm.rfac_s[r];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              const float y = centered<PT>(x[k], mu, gc);
+              const float sq = __fmul_rn(y, y);
+              a1[j][k] += hp.has_eps ? __fadd_rn(sq, hp.eps1) : sq;
+              a2[j][k] += __fmul_rn(sq, ri);
+            }
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  // ---- publish the slot: column partial sums (row groups combined in order), row-statistic sum ----
+  float* slot = pv.aux + d.aux_off + 2ll * t.slot * C;
+  if (ok) {
+    if (Q == 1) {
+#pragma unroll
+      for (int j = 0; j < VPT; ++j) {
+        const int v = v0 + j * AT;
+        if (col_act && v < nv) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) { slot[v * 8 + k] = a1[j][k]; slot[C + v * 8 + k] = a2[j][k]; }
+        }
+      }
+    } else {
+      // partials of the Q row groups through shared memory: [q][2][C] floats (at most AT * 16 floats)
+      float* xs = reinterpret_cast<float*>(dyn);
+      if (col_act) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          xs[(size_t)q * 2 * C + v0 * 8 + k] = a1[0][k];
+          xs[(size_t)q * 2 * C + C + v0 * 8 + k] = a2[0][k];
+        }
+      }
+      __syncthreads();
+      for (int j = tid; j < 2 * C; j += AT) {
+        float tot = 0.0f;
+        for (int qq = 0; qq < Q; ++qq) tot += xs[(size_t)qq * 2 * C + j];
+        slot[j] = tot;
+      }
+    }
+  }
+  const double rs = block_sum_d(rowsum, sm.red, tid);
+  if (tid == 0 && ok) reinterpret_cast<double*>(pv.aux + aux_rowpart(d))[t.slot] = rs;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) signal_counter(pv.done + 0 * pv.n_tensors + t.tensor, 1u);
+}
+
+__device__ __forceinline__ bool stats_stream_ok(const DevTensor& d, const void* g, int ebytes) {
+  return (d.cols & 7) == 0 && d.cols >= 256 && (reinterpret_cast<uintptr_t>(g) & 15) == 0 &&
+         (((long long)d.cols * ebytes) & 15) == 0;
+}
+
 // ----------------------------------------------------------------------------- FINAL
 
 __device__ void ada_final(const PlanView& pv, const AdaDev& hp, const Task& t, const AdaSmem& sm,
@@ -1340,7 +1489,13 @@ __global__ void __launch_bounds__(AT, 1) adakaon_kernel(PlanView pv, AdaDev hp, 
     const long long tk0 = clock64();
 #endif
     switch (t.phase) {
-      case PH_ADA_STATS: ada_stats<typename std::conditional<MUON, __nv_bfloat16, PT>::type>(pv, hp, t, st, sm_stats, tid); break;
+      case PH_ADA_STATS: {
+        using SST = typename std::conditional<MUON, __nv_bfloat16, PT>::type;
+        const void* gsrc = (MUON && pv.grads[t.tensor] != nullptr) ? pv.signal[t.tensor] : pv.grads[t.tensor];
+        if (stats_stream_ok(pv.tensors[t.tensor], gsrc, Elems<SST>::BYTES)) ada_stats_stream<SST>(pv, hp, t, sm_stats, dyn, tid);
+        else ada_stats<SST>(pv, hp, t, st, sm_stats, tid);
+        break;
+      }
       case PH_ADA_FINAL: ada_final(pv, hp, t, sm_stats, tid); break;
       case PH_ADA_COUNT:
         if (!MUON && stream_ok<MK>(pv.tensors[t.tensor], hp)) ada_stream<PT, MK, false>(pv, hp, t, sm_rows, tid);
