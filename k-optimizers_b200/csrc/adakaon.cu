@@ -679,7 +679,6 @@ __device__ void ada_rows(const PlanView& pv, const AdaDev& hp, const Task& t, St
     const float* cf = pv.aux + aux_cfac(d);
     for (int j = tid; j < C; j += AT) cfac_s[j] = __ldcg(cf + j);
   }
-  const int warp = tid >> 5, lane = tid & 31;
   const bool row_uniform = (C & 7) == 0;
   SrStream s_upd{Philox{hp.k0, hp.k1}, hp.step, KAON_TAG_UPDATE};
   SrStream s_rem{Philox{hp.k0, hp.k1}, hp.step, KAON_TAG_REMOVE};

@@ -175,9 +175,12 @@ def ns_case(kaon):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference/src")
+    ap.add_argument("--ref", default=os.environ.get("KAON_REFERENCE_SRC", ""),
+                    help="the reference's src/ directory (holds the `kaon` package); or set KAON_REFERENCE_SRC")
     ap.add_argument("--only", default=None)
     args = ap.parse_args()
+    if not args.ref:
+        ap.error("--ref (or KAON_REFERENCE_SRC) must name the reference's src/ directory")
     sys.path.insert(0, args.ref)
     sys.path.insert(0, HERE)
     import kaon

@@ -230,3 +230,49 @@ def test_lr_schedule_between_steps_is_honoured():
     torch.cuda.synchronize()
     for p, q in zip(pa, pb):
         assert torch.equal(a.state[p]["m"], b.state[q]["m"])
+
+
+@pytest.mark.parametrize("cls_name,kw", [("Lion", dict(lr=2e-4, momentum_dtype="4bit")),
+                                         ("Adakaon", dict(lr=1e-4, momentum_dtype="int8")),
+                                         ("Nekaon", dict(lr=1e-4, betas=(0.2, 0.999)))])
+def test_results_do_not_depend_on_how_the_list_is_split(cls_name, kw):
+    """A 41 M-parameter UNet-shaped list stepped by one optimizer, and by two optimizers over interleaved
+    halves of it (what sharding does): weights and state are bit-identical, stochastic rounding
+    included - work-item scheduling, grid size and list composition do not leak into the results."""
+    import kaon_b200
+    from kaon_b200 import workloads as W
+    shapes = W.WORKLOADS["unet_sample"]()
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    base = [(torch.randn(s, generator=gen, device="cuda") * 0.02).bfloat16() for s in shapes]
+    grads = [[(torch.randn(s, generator=gen, device="cuda") * 1e-3).bfloat16() for s in shapes] for _ in range(2)]
+
+    def run(split):
+        params = [torch.nn.Parameter(b.clone()) for b in base]
+        for i, p in enumerate(params):
+            p.kaon_tensor_id = i
+        groups = [params] if not split else [params[0::2], params[1::2]]
+        opts = [getattr(kaon_b200, cls_name)(g, **kw) for g in groups]
+        for o in opts:
+            o.sr_seed = 9
+        for step in range(2):
+            for p, g in zip(params, grads[step]):
+                p.grad = g
+            for o in opts:
+                o.step()
+        torch.cuda.synchronize()
+        for o in opts:
+            o.check_device_status()
+        state = {}
+        for o in opts:
+            inner = getattr(o, "base_optimizer", o)
+            for p in inner.state:
+                state[p.kaon_tensor_id] = inner.state[p]
+        return params, state
+
+    pa, sa = run(False)
+    pb, sb = run(True)
+    for i, (a, b) in enumerate(zip(pa, pb)):
+        assert torch.equal(a.detach().view(torch.int16), b.detach().view(torch.int16)), i
+        for k, v in sa[i].items():
+            if torch.is_tensor(v):
+                assert torch.equal(v, sb[i][k]), (i, k)
