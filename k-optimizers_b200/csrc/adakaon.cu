@@ -13,6 +13,9 @@
 //     of the previous climb and the new climb ride on the same read and write of each weight.
 // 1-D tensor: FLAT, the whole tensor in one work item.
 // Every cross-item sum is taken in a fixed order: results do not depend on scheduling.
+#include <map>
+#include <mutex>
+#include <utility>
 #include <type_traits>
 
 #include "adakaon_dev.h"
@@ -1040,9 +1043,11 @@ __device__ void ada_rows(const PlanView& pv, const AdaDev& hp, const Task& t, St
 // left it.  Rows of an item belong to this CTA alone, so the int8 row maxima are reduced with
 // atomicMax on the tensor's scratch (COUNT) and the old row scales are set aside once per item (APPLY).
 // Results are bit-identical to ada_rows: same arithmetic, same noise indices.
-template <typename PT, int MK, bool APPLY>
+template <typename PT, int MKP, bool APPLY, bool MUON>
 __device__ void ada_stream(const PlanView& pv, const AdaDev& hp, const Task& t, const AdaSmem& sm, int tid) {
   using E = Elems<PT>;
+  using S = Elems<typename std::conditional<MUON, __nv_bfloat16, PT>::type>;  // the signal's element type
+  constexpr int MK = MUON ? KAON_M_NONE : MKP;
   const DevTensor d = pv.tensors[t.tensor];
   const unsigned char* g = reinterpret_cast<const unsigned char*>(pv.grads[t.tensor]);
   if (g == nullptr) {
@@ -1061,7 +1066,9 @@ __device__ void ada_stream(const PlanView& pv, const AdaDev& hp, const Task& t, 
   ok = __syncthreads_and(ok) != 0;
   const int C = d.cols;
   const int nrows = t.n / C;
-  const bool gc = hp.gc != 0;
+  const bool gc = hp.gc != 0 && !MUON;
+  // AdaMuon: the chain runs on the orthogonalised momentum, the cautious mask on the raw gradient
+  const unsigned char* sig = MUON ? reinterpret_cast<const unsigned char*>(pv.signal[t.tensor]) : g;
   const float* scal = pv.aux + aux_scal(d);
   const float rowmean = __ldcg(scal + 0);
   Chain ch;
@@ -1102,7 +1109,8 @@ __device__ void ada_stream(const PlanView& pv, const AdaDev& hp, const Task& t, 
     const int nvec = (nrc * C) >> 3;
     const int nvec_pad = (nvec + 31) & ~31;
     const long long e0 = t.e0 + (long long)c0 * C;
-    const unsigned char* gbase = g + e0 * E::BYTES;
+    const unsigned char* gbase = sig + e0 * S::BYTES;
+    const unsigned char* rawbase = g + e0 * E::BYTES;
     const unsigned char* mbase = m_ptr<MK>(d, e0);
     unsigned char* pbase = reinterpret_cast<unsigned char*>(d.p) + e0 * E::BYTES;
     for (int v = tid; v < nvec_pad; v += AT) {
@@ -1113,7 +1121,9 @@ __device__ void ada_stream(const PlanView& pv, const AdaDev& hp, const Task& t, 
       const int col = vv * 8 - r * C;
       float gv[8], mo[8], mn[8], pc[8], dl[8];
       // ---- loads ----
-      E::load8(gbase + (size_t)vv * 8 * E::BYTES, gv);
+      S::load8(gbase + (size_t)vv * 8 * S::BYTES, gv);
+      float raw[8];
+      if (MUON) E::load8(rawbase + (size_t)vv * 8 * E::BYTES, raw);
       if (need_p) E::load8(pbase + (size_t)vv * 8 * E::BYTES, pc);
       else {
 #pragma unroll
@@ -1163,7 +1173,7 @@ __device__ void ada_stream(const PlanView& pv, const AdaDev& hp, const Task& t, 
         mn[k] = ema_of<MK>(mo[k], u, hp);
         const float dv = hp.has_wd ? __fmaf_rn(pc[k], hp.lrwd, mn[k]) : mn[k];
         dl[k] = dv;
-        if (__fmul_rn(dv, gv[k]) > 0.0f) kept |= 1u << k;
+        if (__fmul_rn(dv, MUON ? raw[k] : gv[k]) > 0.0f) kept |= 1u << k;
       }
       if constexpr (!APPLY) {
         if (act) kept_local += __popc(kept);
@@ -1275,8 +1285,9 @@ __device__ void ada_stream(const PlanView& pv, const AdaDev& hp, const Task& t, 
 
 // Whether the streaming form handles this tensor and these settings (otherwise: ada_rows).
 template <int MK>
-__device__ __forceinline__ bool stream_ok(const DevTensor& d, const AdaDev& hp) {
+__device__ __forceinline__ bool stream_ok(const DevTensor& d, const AdaDev& hp, const void* g, const void* sig) {
   if ((d.cols & 7) != 0) return false;
+  if ((reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(sig)) & 15) return false;  // 16-byte vector loads
   if (MK == KAON_M_4BIT && d.block != 128u) return false;
   if (MK == KAON_M_INT8 && !hp.cautious) return false;  // no COUNT item to find the row maxima
   return true;
@@ -1497,11 +1508,13 @@ __global__ void __launch_bounds__(AT, 1) adakaon_kernel(PlanView pv, AdaDev hp, 
       }
       case PH_ADA_FINAL: ada_final(pv, hp, t, sm_stats, tid); break;
       case PH_ADA_COUNT:
-        if (!MUON && stream_ok<MK>(pv.tensors[t.tensor], hp)) ada_stream<PT, MK, false>(pv, hp, t, sm_rows, tid);
+        if (stream_ok<MUON ? KAON_M_NONE : MK>(pv.tensors[t.tensor], hp, pv.grads[t.tensor], MUON && pv.grads[t.tensor] ? pv.signal[t.tensor] : nullptr))
+          ada_stream<PT, MK, false, MUON>(pv, hp, t, sm_rows, tid);
         else ada_rows<PT, MK, false, MUON>(pv, hp, t, st, sm_rows, tid);
         break;
       case PH_ADA_APPLY:
-        if (!MUON && stream_ok<MK>(pv.tensors[t.tensor], hp)) ada_stream<PT, MK, true>(pv, hp, t, sm_rows, tid);
+        if (stream_ok<MUON ? KAON_M_NONE : MK>(pv.tensors[t.tensor], hp, pv.grads[t.tensor], MUON && pv.grads[t.tensor] ? pv.signal[t.tensor] : nullptr))
+          ada_stream<PT, MK, true, MUON>(pv, hp, t, sm_rows, tid);
         else ada_rows<PT, MK, true, MUON>(pv, hp, t, st, sm_rows, tid);
         break;
       case PH_ADA_FLAT: ada_flat<PT, MK>(pv, hp, t, st, sm_rows, tid); break;
@@ -1615,7 +1628,18 @@ int configure_launch_adakaon(kaon_plan* pl, const cudaDeviceProp& prop, int max_
   if (pl->smem_bytes + fa.sharedSizeBytes > (size_t)prop.sharedMemPerBlockOptin)
     return fail(KAON_E_UNSUPPORTED, "Adakaon kernel needs %zu + %zu bytes of shared memory for rows of %d elements (limit %zu)",
                 pl->smem_bytes, (size_t)fa.sharedSizeBytes, max_cols, (size_t)prop.sharedMemPerBlockOptin);
-  KAON_CUDA(cudaFuncSetAttribute((const void*)k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl->smem_bytes));
+  // The limit belongs to the kernel function, not to the plan: plans with narrower rows must not lower
+  // it under a plan that is still stepping, so it only ever goes up (per device).
+  {
+    static std::mutex mu;
+    static std::map<std::pair<int, const void*>, size_t> high;
+    std::lock_guard<std::mutex> lock(mu);
+    size_t& h = high[std::make_pair(pl->device, (const void*)k)];
+    if (pl->smem_bytes > h) {
+      KAON_CUDA(cudaFuncSetAttribute((const void*)k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl->smem_bytes));
+      h = pl->smem_bytes;
+    }
+  }
   int per_sm = 1;
   KAON_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, (const void*)k, AT, pl->smem_bytes));
   if (per_sm < 1) return fail(KAON_E_UNSUPPORTED, "Adakaon kernel does not fit on an SM");

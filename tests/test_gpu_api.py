@@ -276,3 +276,23 @@ def test_results_do_not_depend_on_how_the_list_is_split(cls_name, kw):
         for k, v in sa[i].items():
             if torch.is_tensor(v):
                 assert torch.equal(v, sb[i][k]), (i, k)
+
+
+@pytest.mark.parametrize("cls_name", ["Adakaon", "AdaMuon"])
+def test_plans_with_different_row_widths_coexist(cls_name):
+    """The kernels' shared-memory need grows with the widest row of a plan; a later, narrower plan must
+    not take the room away from an earlier, wider one that keeps stepping."""
+    import kaon_b200
+    wide = [torch.nn.Parameter(torch.randn(24, 12288, device="cuda").bfloat16() * 0.02)]
+    narrow = [torch.nn.Parameter(torch.randn(64, 64, device="cuda").bfloat16() * 0.02)]
+    ow = getattr(kaon_b200, cls_name)(wide, momentum_dtype="int8")
+    on = getattr(kaon_b200, cls_name)(narrow, momentum_dtype="int8")
+    for step in range(3):
+        for p in wide + narrow:
+            p.grad = (torch.randn_like(p.float()) * 1e-3).bfloat16()
+        ow.step()
+        on.step()
+    torch.cuda.synchronize()
+    ow.check_device_status()
+    on.check_device_status()
+    assert torch.isfinite(wide[0].float()).all() and torch.isfinite(narrow[0].float()).all()
