@@ -30,6 +30,9 @@ WORKLOADS = {
                           "unet_2p6b", 7.0625, {}),
     "lion4bit_sample": ("Lion", dict(lr=2e-4, betas=(0.95, 0.98), momentum_dtype="4bit", cautious=True),
                         "unet_sample", 7.0625, {}),
+    # the same without gradient centralization (no row means: the step is purely elementwise + 4-bit blocks)
+    "lion4bit_nogc_unet2p6b": ("Lion", dict(lr=2e-4, betas=(0.95, 0.98), momentum_dtype="4bit", cautious=True,
+                                            gradient_centralization=False), "unet_2p6b", 7.0625, {}),
     # Adakaon-int8 (config 3): g 2 + p 2+2 + m 1+1 + row scales, row/col stats, 1-D v; 1 % of grads x100
     "adakaon_int8_unet2p6b": ("Adakaon", dict(lr=1e-4, betas=(0.9, 0.999), momentum_dtype="int8"),
                               "unet_2p6b", 8.015, {"outlier": True}),
