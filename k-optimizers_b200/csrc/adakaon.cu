@@ -14,6 +14,7 @@
 // 1-D tensor: FLAT, the whole tensor in one work item.
 // Every cross-item sum is taken in a fixed order: results do not depend on scheduling.
 #include <map>
+#include <vector>
 #include <mutex>
 #include <utility>
 #include <type_traits>
@@ -1088,13 +1089,14 @@ __device__ void ada_stream(const PlanView& pv, const AdaDev& hp, const Task& t, 
   const float* rfac = pv.aux + aux_rfac(d);
   if constexpr (MK == KAON_M_INT8) {
     if (ok) {
-      if (APPLY) {
-        for (int r = tid; r < nrows; r += AT) oldsc[t.row0 + r] = d.m_scale[t.row0 + r];
-      } else {
-        for (int r = tid; r < nrows; r += AT) rowmax[t.row0 + r] = 0u;
+      if (!APPLY) {  // COUNT owns these rows now: reset the maxima, set the old scales aside for APPLY
+        for (int r = tid; r < nrows; r += AT) {
+          rowmax[t.row0 + r] = 0u;
+          oldsc[t.row0 + r] = d.m_scale[t.row0 + r];
+        }
       }
     }
-    __syncthreads();
+    if (!APPLY) __syncthreads();
   }
   SrStream s_upd{Philox{hp.k0, hp.k1}, hp.step, KAON_TAG_UPDATE};
   SrStream s_rem{Philox{hp.k0, hp.k1}, hp.step, KAON_TAG_REMOVE};
@@ -1572,6 +1574,254 @@ __global__ void __launch_bounds__(256) msam_axpy_kernel(PlanView pv, float alpha
   }
 }
 
+// ----------------------------------------------------------------------------- APPLY as its own kernel
+
+// When every factored tensor of the plan takes the streaming form, the APPLY stage leaves the
+// persistent kernel above and runs as a second launch built like the Lion kernel: 256-thread CTAs,
+// several per SM, each bringing one flat item of at most APPLY_CAP elements (gradient, weights,
+// momentum bytes) into shared memory with bulk copies while the other CTAs of the SM compute.  Stream
+// order replaces the completion counters: every COUNT item has finished when this kernel starts.
+// Items are flat runs (no row structure: what is per row or per column comes from the scratch in L2),
+// so the int8 row scales of the previous step are read from the copy COUNT set aside.
+constexpr int APPLY_CAP = 8192;
+constexpr int APPLY_THREADS = 256;
+
+template <typename PT, int MK>
+__global__ void __launch_bounds__(APPLY_THREADS, 3) adakaon_apply_kernel(PlanView pv, AdaDev hp) {
+  using E = Elems<PT>;
+  constexpr int GB = 8 * E::BYTES;
+  constexpr int MB = MK == KAON_M_4BIT ? 4 : MK == KAON_M_INT8 ? 8 : MK == KAON_M_BF16 ? 16 : MK == KAON_M_F32 ? 32 : 0;
+  extern __shared__ __align__(128) unsigned char dyn[];
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ int next_s[2];
+  unsigned char* g_s = dyn;
+  unsigned char* p_s = dyn + (size_t)APPLY_CAP * E::BYTES;
+  unsigned char* m_s = dyn + (size_t)2 * APPLY_CAP * E::BYTES;
+  const int tid = threadIdx.x;
+  auto claim_next = [&](int slot) {
+    if (tid == 0) {
+      const unsigned st = *reinterpret_cast<volatile unsigned*>(pv.status);
+      next_s[slot] = st ? 0x7fffffff : (int)atomicAdd(pv.task_counter, 1u);
+    }
+  };
+  if (tid == 0) mbar_init(&bar, 1);
+  claim_next(0);
+  __syncthreads();
+  unsigned parity = 0u;
+  int slot = 0;
+  int cur = next_s[0];
+  SrStream s_upd{Philox{hp.k0, hp.k1}, hp.step, KAON_TAG_UPDATE};
+  SrStream s_rem{Philox{hp.k0, hp.k1}, hp.step, KAON_TAG_REMOVE};
+  SrStream s_clb{Philox{hp.k0, hp.k1}, hp.step, KAON_TAG_CLIMB};
+  const bool sr = hp.sr != 0;
+  const bool gc = hp.gc != 0;
+  while (cur < pv.n_tasks) {
+    claim_next(slot ^ 1);
+    const Task t = pv.tasks[cur];
+    const DevTensor d = pv.tensors[t.tensor];
+    const unsigned char* g = reinterpret_cast<const unsigned char*>(pv.grads[t.tensor]);
+    bool ok = g != nullptr;
+    const int n = t.n;
+    if (ok) {
+      const unsigned char* gsrc = g + t.e0 * E::BYTES;
+      const unsigned char* psrc = reinterpret_cast<const unsigned char*>(d.p) + t.e0 * E::BYTES;
+      const unsigned ghead = stage_tail(g_s, gsrc, (unsigned)n * E::BYTES, tid);
+      const unsigned phead = stage_tail(p_s, psrc, (unsigned)n * E::BYTES, tid);
+      unsigned mhead = 0u;
+      if constexpr (MB > 0) mhead = stage_tail(m_s, m_ptr<MK>(d, t.e0), m_bytes<MK>(n), tid);
+      if (ghead + phead + mhead) {
+        if (tid == 0) {
+          fence_async_smem();
+          mbar_expect_tx(&bar, ghead + phead + mhead);
+          if (ghead) bulk_g2s(g_s, gsrc, ghead, &bar);
+          if (phead) bulk_g2s(p_s, psrc, phead, &bar);
+          if constexpr (MB > 0) { if (mhead) bulk_g2s(m_s, m_ptr<MK>(d, t.e0), mhead, &bar); }
+        }
+        ok = mbar_wait(&bar, parity, pv.status, 15001u);
+        parity ^= 1u;
+      }
+    }
+    ok = __syncthreads_and(ok) != 0;
+    if (ok) {
+      const int C = d.cols;
+      const long long row0 = t.e0 / C;
+      const int col0 = (int)(t.e0 - row0 * C);
+      const float* scal = pv.aux + aux_scal(d);
+      Chain ch;
+      ch.div = __ldcg(scal + 1);
+      ch.use_div = ch.div != 1.0f;
+      ch.rcp_div = __fdiv_rn(1.0f, ch.div);
+      float denom = 1.0f, rcp_denom = 1.0f;
+      if (hp.cautious) {
+        const unsigned kept_t = __ldcg(pv.kept + t.tensor);
+        denom = fmaxf(__fdiv_rn((float)kept_t, (float)d.numel), 1e-8f);
+        rcp_denom = __fdiv_rn(1.0f, denom);
+      }
+      const float* cfac = pv.aux + aux_cfac(d);
+      const float* mean = pv.aux + aux_mean(d);
+      const unsigned* rowmax = reinterpret_cast<const unsigned*>(pv.aux + aux_rowmax(d));
+      const float* oldsc = pv.aux + aux_oldsc(d);
+      const float* rfac = pv.aux + aux_rfac(d);
+      unsigned char* pbase = reinterpret_cast<unsigned char*>(d.p) + t.e0 * E::BYTES;
+      const int nvec = n >> 3;
+      const int nvec_pad = (nvec + 31) & ~31;
+      for (int v = tid; v < nvec_pad; v += APPLY_THREADS) {
+        const bool act = v < nvec;
+        const int vv = act ? v : 0;
+        const unsigned i = (unsigned)col0 + (unsigned)vv * 8u;  // < APPLY_CAP + cols: row_of is exact
+        const int r = row_of(i, d);
+        const int row = (int)row0 + r;
+        const int col = (int)i - r * C;
+        float gv[8], mo[8], mn[8], pc[8], dl[8];
+        const float mu = gc ? __ldcg(mean + row) : 0.0f;
+        const float rf = __ldcg(rfac + row);
+        const float4 c0v = __ldcg(reinterpret_cast<const float4*>(cfac + col));
+        const float4 c1v = __ldcg(reinterpret_cast<const float4*>(cfac + col + 4));
+        const float cf[8] = {c0v.x, c0v.y, c0v.z, c0v.w, c1v.x, c1v.y, c1v.z, c1v.w};
+        E::load8(g_s + (size_t)vv * GB, gv);
+        E::load8(p_s + (size_t)vv * GB, pc);
+        if constexpr (MK == KAON_M_4BIT) {
+          decode8<MK>(m_s, vv, 8, d.m_scale[(t.e0 >> 7) + (vv >> 4)], mo);
+        } else if constexpr (MK == KAON_M_INT8) {
+          decode8<MK>(m_s, vv, 8, __ldcg(oldsc + row), mo);
+        } else if constexpr (MK == KAON_M_NONE) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) mo[k] = 0.0f;
+        } else {
+          decode8<MK>(m_s, vv, 8, 1.0f, mo);
+        }
+        if (hp.remove) {
+          uint32_t nz[4] = {0u, 0u, 0u, 0u};
+          if (E::IS_BF16) s_rem.draw8(d.tensor_id, (uint64_t)((t.e0 >> 3) + vv), nz);
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            pc[k] = write_step<PT>(pc[k], climb_e(mo[k], hp.a_remove, hp.b_remove), 1.0f, E::IS_BF16, noise_lane(nz, k));
+        }
+        if (gc) {
+#pragma unroll
+          for (int k = 0; k < 8; k += 2) {
+            const float x0 = __fsub_rn(gv[k], mu), x1 = __fsub_rn(gv[k + 1], mu);
+            if (E::IS_BF16) {
+              const uint32_t pk = pack_bf16_rn(x0, x1);
+              gv[k] = bf16lo(pk); gv[k + 1] = bf16hi(pk);
+            } else {
+              gv[k] = x0; gv[k + 1] = x1;
+            }
+          }
+        }
+        unsigned kept = 0;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float u = update_of(gv[k], rf, cf[k], ch, hp.upd_scale);
+          mn[k] = ema_of<MK>(mo[k], u, hp);
+          const float dv = hp.has_wd ? __fmaf_rn(pc[k], hp.lrwd, mn[k]) : mn[k];
+          dl[k] = dv;
+          if (__fmul_rn(dv, gv[k]) > 0.0f) kept |= 1u << k;
+        }
+        float md[8];  // the momentum as stored (decoded), for the Nekaon climb
+        if constexpr (MK == KAON_M_4BIT) {
+          float a = 0.0f;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) a = fmaxf(a, act ? fabsf(mn[k]) : 0.0f);
+          a = fmaxf(group_max(a, 16), 1e-12f);
+          __syncwarp();  // every lane of the block has read the old scale before it is replaced
+          const float sc = __fdiv_rn(a, 7.0f);
+          const float inv = __fdividef(1.0f, sc);
+          uint32_t word = 0;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const float q = quant_round(mn[k], sc, inv, 1e-4f);
+            const int qi = min(max((int)q, -7), 7);
+            md[k] = __fmul_rn((float)qi, sc);
+            word |= (uint32_t)(qi + 8) << (4 * k);
+          }
+          if (act) {
+            *reinterpret_cast<uint32_t*>((unsigned char*)d.m + (t.e0 >> 1) + (size_t)v * 4) = word;
+            if ((v & 15) == 0) d.m_scale[(t.e0 >> 7) + (v >> 4)] = sc;
+          }
+        } else if constexpr (MK == KAON_M_INT8) {
+          const float sc = __fdiv_rn(fmaxf(__uint_as_float(__ldcg(rowmax + row)), 1e-12f), 127.0f);
+          const float inv = __fdividef(1.0f, sc);
+          uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const int qi = min(max((int)quant_round(mn[k], sc, inv, 1e-3f), -127), 127);
+            md[k] = __fmul_rn((float)qi, sc);
+            const uint32_t byte = (uint32_t)(qi & 0xFF);
+            if (k < 4) w0 |= byte << (8 * k); else w1 |= byte << (8 * (k - 4));
+          }
+          if (act) {
+            *reinterpret_cast<uint2*>((unsigned char*)d.m + t.e0 + (size_t)v * 8) = make_uint2(w0, w1);
+            if (col == 0) d.m_scale[row] = sc;
+          }
+        } else if constexpr (MK == KAON_M_BF16 || MK == KAON_M_F32) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) md[k] = mn[k];
+          if (act) {
+            if constexpr (MK == KAON_M_BF16) store8<__nv_bfloat16>((unsigned char*)d.m + t.e0 * 2 + (size_t)v * 16, 8, mn, nullptr);
+            else store8<float>((unsigned char*)d.m + t.e0 * 4 + (size_t)v * 32, 8, mn, nullptr);
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) md[k] = 0.0f;
+        }
+        if (act) {
+          if (E::IS_BF16 && hp.kahan) {
+            unsigned char* she = reinterpret_cast<unsigned char*>(d.shift) + (size_t)t.e0 * 2 + (size_t)v * 16;
+            float sh[8];
+            load8_guard<__nv_bfloat16>(she, 8, sh);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              float f = dl[k];
+              if (hp.cautious) f = ((kept >> k) & 1u) ? div_shared(f, denom, rcp_denom) : 0.0f;
+              kahan_step(pc[k], sh[k], f);
+            }
+            store8<__nv_bfloat16>(she, 8, sh, nullptr);
+          } else {
+            uint32_t nz[4] = {0u, 0u, 0u, 0u};
+            if (sr) s_upd.draw8(d.tensor_id, (uint64_t)((t.e0 >> 3) + v), nz);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              float f = dl[k];
+              if (hp.cautious) f = ((kept >> k) & 1u) ? div_shared(f, denom, rcp_denom) : 0.0f;
+              pc[k] = write_step<PT>(pc[k], f, -1.0f, sr, noise_lane(nz, k));
+            }
+          }
+          if (hp.climb && MK != KAON_M_NONE) {
+            uint32_t nc[4] = {0u, 0u, 0u, 0u};
+            if (E::IS_BF16) s_clb.draw8(d.tensor_id, (uint64_t)((t.e0 >> 3) + v), nc);
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+              pc[k] = write_step<PT>(pc[k], climb_e(md[k], hp.a_climb, hp.b_climb), 1.0f, E::IS_BF16, noise_lane(nc, k));
+          }
+          store8<PT>(pbase + (size_t)v * 8 * E::BYTES, 8, pc, &pv.peers);
+        }
+      }
+    }
+    __syncthreads();
+    slot ^= 1;
+    cur = next_s[slot];
+  }
+}
+
+typedef void (*ApplyKernel)(PlanView, AdaDev);
+
+template <typename PT>
+static ApplyKernel pick_apply_pt(int mk) {
+  switch (mk) {
+    case KAON_M_F32: return adakaon_apply_kernel<PT, KAON_M_F32>;
+    case KAON_M_BF16: return adakaon_apply_kernel<PT, KAON_M_BF16>;
+    case KAON_M_INT8: return adakaon_apply_kernel<PT, KAON_M_INT8>;
+    case KAON_M_4BIT: return adakaon_apply_kernel<PT, KAON_M_4BIT>;
+    case KAON_M_NONE: return adakaon_apply_kernel<PT, KAON_M_NONE>;
+    default: return nullptr;
+  }
+}
+
+static ApplyKernel pick_apply(int pdt, int mk) {
+  return pdt == KAON_DT_BF16 ? pick_apply_pt<__nv_bfloat16>(mk) : pick_apply_pt<float>(mk);
+}
+
 typedef void (*AxpyKernel)(PlanView, float, float, SrStream);
 
 template <typename PT, bool MUON>
@@ -1651,6 +1901,60 @@ int configure_launch_adakaon(kaon_plan* pl, const cudaDeviceProp& prop, int max_
 
 using namespace kaon;
 
+// One-time set-up of the two-launch form: eligibility, the flat APPLY items, the first launch's lists
+// without APPLY items, the second kernel's launch configuration.
+static int ensure_apply2(kaon_plan* pl) {
+  if (pl->apply2 != 0) return KAON_OK;
+  pl->apply2 = -1;
+  const int mk = pl->momentum_kind;
+  std::vector<Task> items;
+  for (int i = 0; i < pl->n_tensors; ++i) {
+    const DevTensor& t = pl->h_tensors[i];
+    if (t.rows <= 0 || t.numel == 0) continue;
+    if ((t.cols & 7) != 0) return KAON_OK;
+    if (mk == KAON_M_4BIT && t.block != 128u) return KAON_OK;
+    if (mk == KAON_M_INT8 && (t.cols & 15) != 0) return KAON_OK;
+    for (long long e = 0; e < t.numel; e += APPLY_CAP)
+      items.push_back(Task{i, PH_ADA_APPLY, e, (int)std::min<long long>(APPLY_CAP, t.numel - e), 0, 0, 0});
+  }
+  if (items.empty()) return KAON_OK;
+  ApplyKernel k = pick_apply(pl->param_dtype, mk);
+  if (!k) return KAON_OK;
+  const size_t esz = pl->param_dtype == KAON_DT_BF16 ? 2 : 4;
+  const size_t mb = mk == KAON_M_4BIT ? APPLY_CAP / 2 : mk == KAON_M_INT8 ? APPLY_CAP : mk == KAON_M_BF16 ? APPLY_CAP * 2
+                    : mk == KAON_M_F32 ? APPLY_CAP * 4 : 0;
+  pl->apply_smem = 2 * (size_t)APPLY_CAP * esz + mb;
+  KAON_CUDA(cudaFuncSetAttribute((const void*)k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl->apply_smem));
+  int per_sm = 0;
+  KAON_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, (const void*)k, APPLY_THREADS, pl->apply_smem));
+  if (per_sm < 1) return KAON_OK;
+  cudaDeviceProp prop;
+  KAON_CUDA(cudaGetDeviceProperties(&prop, pl->device));
+  pl->apply_grid = prop.multiProcessorCount * per_sm;
+  // the first launch's lists, APPLY items taken out
+  auto filtered = [&](const Task* d_list, int n, Task** out, int* n_out) -> int {
+    std::vector<Task> h((size_t)n);
+    KAON_CUDA(cudaMemcpy(h.data(), d_list, sizeof(Task) * (size_t)n, cudaMemcpyDeviceToHost));
+    std::vector<Task> keep;
+    for (const Task& t : h)
+      if (t.phase != PH_ADA_APPLY) keep.push_back(t);
+    KAON_CUDA(cudaMalloc((void**)out, sizeof(Task) * std::max<size_t>(keep.size(), 1)));
+    KAON_CUDA(cudaMemcpy(*out, keep.data(), sizeof(Task) * keep.size(), cudaMemcpyHostToDevice));
+    *n_out = (int)keep.size();
+    pl->device_bytes += (int64_t)(sizeof(Task) * keep.size());
+    return KAON_OK;
+  };
+  if (int rc = filtered(pl->d_tasks_full, pl->n_tasks_full, &pl->d_tasks_full_na, &pl->n_tasks_full_na)) return rc;
+  if (int rc = filtered(pl->d_tasks_main, pl->n_tasks_main, &pl->d_tasks_main_na, &pl->n_tasks_main_na)) return rc;
+  KAON_CUDA(cudaMalloc((void**)&pl->d_tasks_apply2, sizeof(Task) * items.size()));
+  KAON_CUDA(cudaMemcpy(pl->d_tasks_apply2, items.data(), sizeof(Task) * items.size(), cudaMemcpyHostToDevice));
+  KAON_CUDA(cudaMalloc((void**)&pl->d_counter2, 256));
+  pl->n_tasks_apply2 = (int)items.size();
+  pl->device_bytes += (int64_t)(sizeof(Task) * items.size() + 256);
+  pl->apply2 = 1;
+  return KAON_OK;
+}
+
 extern "C" int kaon_adakaon_step(kaon_plan* pl, const kaon_adakaon_hparams* h, uint64_t seed,
                                  uint32_t step, void* stream) {
   if (!pl || !h) return fail(KAON_E_INVALID, "kaon_adakaon_step: null argument");
@@ -1679,13 +1983,26 @@ extern "C" int kaon_adakaon_step(kaon_plan* pl, const kaon_adakaon_hparams* h, u
   hp.step = step; hp.k0 = (uint32_t)seed; hp.k1 = (uint32_t)(seed >> 32);
   cudaStream_t s = (cudaStream_t)stream;
   PlanView v = pl->view;
-  if (hp.cautious) { v.tasks = pl->d_tasks_full; v.n_tasks = pl->n_tasks_full; }
-  else { v.tasks = pl->d_tasks_main; v.n_tasks = pl->n_tasks_main; }
+  if (int rc = ensure_apply2(pl)) return rc;
+  // two launches when the plan is eligible (int8 momentum also needs the COUNT stage's row maxima)
+  const bool two = pl->apply2 == 1 && (pl->momentum_kind != KAON_M_INT8 || hp.cautious);
+  if (hp.cautious) { v.tasks = two ? pl->d_tasks_full_na : pl->d_tasks_full; v.n_tasks = two ? pl->n_tasks_full_na : pl->n_tasks_full; }
+  else { v.tasks = two ? pl->d_tasks_main_na : pl->d_tasks_main; v.n_tasks = two ? pl->n_tasks_main_na : pl->n_tasks_main; }
   KAON_CUDA(cudaMemsetAsync(v.task_counter, 0, pl->counters_bytes - sizeof(unsigned), s));
   AdaKernel k = pick_ada(pl->param_dtype, pl->momentum_kind, false);
   k<<<pl->grid, AT, pl->smem_bytes, s>>>(v, hp, (int)x_offset_rows(pl) | (pl->double_buffer ? 1 : 0));
   KAON_CUDA(cudaGetLastError());
   pl->launches += 1;
+  if (two) {
+    PlanView va = pl->view;
+    va.tasks = pl->d_tasks_apply2;
+    va.n_tasks = pl->n_tasks_apply2;
+    va.task_counter = pl->d_counter2;
+    KAON_CUDA(cudaMemsetAsync(pl->d_counter2, 0, sizeof(unsigned), s));
+    pick_apply(pl->param_dtype, pl->momentum_kind)<<<pl->apply_grid, APPLY_THREADS, pl->apply_smem, s>>>(va, hp);
+    KAON_CUDA(cudaGetLastError());
+    pl->launches += 1;
+  }
   return KAON_OK;
 }
 
