@@ -602,6 +602,11 @@ __device__ void ada_final(const PlanView& pv, const AdaDev& hp, const Task& t, c
     const float rowmean = sm.part_s[0];
     float* rfac = pv.aux + aux_rfac(d);
     for (int r = tid; r < d.rows; r += AT) rfac[r] = rsqrt_torch(__fdiv_rn(__ldcg(d.stat_a + r), rowmean));
+    if (hp.int8) {  // int8 momentum: COUNT starts from zeroed row maxima; APPLY decodes with the old scales
+      unsigned* rowmax = reinterpret_cast<unsigned*>(pv.aux + aux_rowmax(d));
+      float* oldsc = pv.aux + aux_oldsc(d);
+      for (int r = tid; r < d.rows; r += AT) { rowmax[r] = 0u; oldsc[r] = d.m_scale[r]; }
+    }
     __threadfence();
     __syncthreads();
     if (tid == 0) signal_counter(pv.done + 2 * pv.n_tensors + t.tensor, 1u);
@@ -1087,17 +1092,6 @@ __device__ void ada_stream(const PlanView& pv, const AdaDev& hp, const Task& t, 
   unsigned* rowmax = reinterpret_cast<unsigned*>(pv.aux + aux_rowmax(d));
   float* oldsc = pv.aux + aux_oldsc(d);
   const float* rfac = pv.aux + aux_rfac(d);
-  if constexpr (MK == KAON_M_INT8) {
-    if (ok) {
-      if (!APPLY) {  // COUNT owns these rows now: reset the maxima, set the old scales aside for APPLY
-        for (int r = tid; r < nrows; r += AT) {
-          rowmax[t.row0 + r] = 0u;
-          oldsc[t.row0 + r] = d.m_scale[t.row0 + r];
-        }
-      }
-    }
-    if (!APPLY) __syncthreads();
-  }
   SrStream s_upd{Philox{hp.k0, hp.k1}, hp.step, KAON_TAG_UPDATE};
   SrStream s_rem{Philox{hp.k0, hp.k1}, hp.step, KAON_TAG_REMOVE};
   SrStream s_clb{Philox{hp.k0, hp.k1}, hp.step, KAON_TAG_CLIMB};
@@ -1586,7 +1580,8 @@ __global__ void __launch_bounds__(256) msam_axpy_kernel(PlanView pv, float alpha
 constexpr int APPLY_CAP = 8192;
 constexpr int APPLY_THREADS = 256;
 
-template <typename PT, int MK>
+// APPLY = false is the COUNT stage in the same form (kept count, int8 row maxima; no stores but those).
+template <typename PT, int MK, bool APPLY>
 __global__ void __launch_bounds__(APPLY_THREADS, 3) adakaon_apply_kernel(PlanView pv, AdaDev hp) {
   using E = Elems<PT>;
   constexpr int GB = 8 * E::BYTES;
@@ -1594,6 +1589,8 @@ __global__ void __launch_bounds__(APPLY_THREADS, 3) adakaon_apply_kernel(PlanVie
   extern __shared__ __align__(128) unsigned char dyn[];
   __shared__ __align__(8) uint64_t bar;
   __shared__ int next_s[2];
+  __shared__ unsigned red_s[APPLY_THREADS / 32];
+  const bool need_p = APPLY || hp.has_wd;
   unsigned char* g_s = dyn;
   unsigned char* p_s = dyn + (size_t)APPLY_CAP * E::BYTES;
   unsigned char* m_s = dyn + (size_t)2 * APPLY_CAP * E::BYTES;
@@ -1626,7 +1623,7 @@ __global__ void __launch_bounds__(APPLY_THREADS, 3) adakaon_apply_kernel(PlanVie
       const unsigned char* gsrc = g + t.e0 * E::BYTES;
       const unsigned char* psrc = reinterpret_cast<const unsigned char*>(d.p) + t.e0 * E::BYTES;
       const unsigned ghead = stage_tail(g_s, gsrc, (unsigned)n * E::BYTES, tid);
-      const unsigned phead = stage_tail(p_s, psrc, (unsigned)n * E::BYTES, tid);
+      const unsigned phead = need_p ? stage_tail(p_s, psrc, (unsigned)n * E::BYTES, tid) : 0u;
       unsigned mhead = 0u;
       if constexpr (MB > 0) mhead = stage_tail(m_s, m_ptr<MK>(d, t.e0), m_bytes<MK>(n), tid);
       if (ghead + phead + mhead) {
@@ -1642,6 +1639,7 @@ __global__ void __launch_bounds__(APPLY_THREADS, 3) adakaon_apply_kernel(PlanVie
       }
     }
     ok = __syncthreads_and(ok) != 0;
+    unsigned kept_local = 0;
     if (ok) {
       const int C = d.cols;
       const long long row0 = t.e0 / C;
@@ -1652,14 +1650,14 @@ __global__ void __launch_bounds__(APPLY_THREADS, 3) adakaon_apply_kernel(PlanVie
       ch.use_div = ch.div != 1.0f;
       ch.rcp_div = __fdiv_rn(1.0f, ch.div);
       float denom = 1.0f, rcp_denom = 1.0f;
-      if (hp.cautious) {
+      if (APPLY && hp.cautious) {
         const unsigned kept_t = __ldcg(pv.kept + t.tensor);
         denom = fmaxf(__fdiv_rn((float)kept_t, (float)d.numel), 1e-8f);
         rcp_denom = __fdiv_rn(1.0f, denom);
       }
       const float* cfac = pv.aux + aux_cfac(d);
       const float* mean = pv.aux + aux_mean(d);
-      const unsigned* rowmax = reinterpret_cast<const unsigned*>(pv.aux + aux_rowmax(d));
+      unsigned* rowmax = reinterpret_cast<unsigned*>(pv.aux + aux_rowmax(d));
       const float* oldsc = pv.aux + aux_oldsc(d);
       const float* rfac = pv.aux + aux_rfac(d);
       unsigned char* pbase = reinterpret_cast<unsigned char*>(d.p) + t.e0 * E::BYTES;
@@ -1679,18 +1677,22 @@ __global__ void __launch_bounds__(APPLY_THREADS, 3) adakaon_apply_kernel(PlanVie
         const float4 c1v = __ldcg(reinterpret_cast<const float4*>(cfac + col + 4));
         const float cf[8] = {c0v.x, c0v.y, c0v.z, c0v.w, c1v.x, c1v.y, c1v.z, c1v.w};
         E::load8(g_s + (size_t)vv * GB, gv);
-        E::load8(p_s + (size_t)vv * GB, pc);
+        if (need_p) E::load8(p_s + (size_t)vv * GB, pc);
+        else {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) pc[k] = 0.0f;
+        }
         if constexpr (MK == KAON_M_4BIT) {
           decode8<MK>(m_s, vv, 8, d.m_scale[(t.e0 >> 7) + (vv >> 4)], mo);
         } else if constexpr (MK == KAON_M_INT8) {
-          decode8<MK>(m_s, vv, 8, __ldcg(oldsc + row), mo);
+          decode8<MK>(m_s, vv, 8, APPLY ? __ldcg(oldsc + row) : d.m_scale[row], mo);
         } else if constexpr (MK == KAON_M_NONE) {
 #pragma unroll
           for (int k = 0; k < 8; ++k) mo[k] = 0.0f;
         } else {
           decode8<MK>(m_s, vv, 8, 1.0f, mo);
         }
-        if (hp.remove) {
+        if (hp.remove && need_p) {
           uint32_t nz[4] = {0u, 0u, 0u, 0u};
           if (E::IS_BF16) s_rem.draw8(d.tensor_id, (uint64_t)((t.e0 >> 3) + vv), nz);
 #pragma unroll
@@ -1717,6 +1719,23 @@ __global__ void __launch_bounds__(APPLY_THREADS, 3) adakaon_apply_kernel(PlanVie
           const float dv = hp.has_wd ? __fmaf_rn(pc[k], hp.lrwd, mn[k]) : mn[k];
           dl[k] = dv;
           if (__fmul_rn(dv, gv[k]) > 0.0f) kept |= 1u << k;
+        }
+        if constexpr (!APPLY) {
+          if (act) kept_local += __popc(kept);
+          if constexpr (MK == KAON_M_INT8) {
+            float a = 0.0f;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) a = fmaxf(a, fabsf(mn[k]));
+            unsigned bits = act ? __float_as_uint(a) : 0u;
+            const int row_l0 = __shfl_sync(0xffffffffu, row, 0);
+            if (__all_sync(0xffffffffu, !act || row == row_l0)) {
+              bits = __reduce_max_sync(0xffffffffu, bits);
+              if ((tid & 31) == 0 && bits) atomicMax(rowmax + row_l0, bits);
+            } else if (act) {
+              atomicMax(rowmax + row, bits);
+            }
+          }
+          continue;
         }
         float md[8];  // the momentum as stored (decoded), for the Nekaon climb
         if constexpr (MK == KAON_M_4BIT) {
@@ -1798,7 +1817,18 @@ __global__ void __launch_bounds__(APPLY_THREADS, 3) adakaon_apply_kernel(PlanVie
         }
       }
     }
+    if constexpr (!APPLY) {  // the item's kept count
+      for (int o = 16; o > 0; o >>= 1) kept_local += __shfl_xor_sync(0xffffffffu, kept_local, o);
+      if ((tid & 31) == 0) red_s[tid >> 5] = kept_local;
+    }
     __syncthreads();
+    if constexpr (!APPLY) {
+      if (tid == 0 && ok) {
+        unsigned tot = 0;
+        for (int w = 0; w < APPLY_THREADS / 32; ++w) tot += red_s[w];
+        if (tot) atomicAdd(pv.kept + t.tensor, tot);
+      }
+    }
     slot ^= 1;
     cur = next_s[slot];
   }
@@ -1806,20 +1836,21 @@ __global__ void __launch_bounds__(APPLY_THREADS, 3) adakaon_apply_kernel(PlanVie
 
 typedef void (*ApplyKernel)(PlanView, AdaDev);
 
-template <typename PT>
+template <typename PT, bool APPLY>
 static ApplyKernel pick_apply_pt(int mk) {
   switch (mk) {
-    case KAON_M_F32: return adakaon_apply_kernel<PT, KAON_M_F32>;
-    case KAON_M_BF16: return adakaon_apply_kernel<PT, KAON_M_BF16>;
-    case KAON_M_INT8: return adakaon_apply_kernel<PT, KAON_M_INT8>;
-    case KAON_M_4BIT: return adakaon_apply_kernel<PT, KAON_M_4BIT>;
-    case KAON_M_NONE: return adakaon_apply_kernel<PT, KAON_M_NONE>;
+    case KAON_M_F32: return adakaon_apply_kernel<PT, KAON_M_F32, APPLY>;
+    case KAON_M_BF16: return adakaon_apply_kernel<PT, KAON_M_BF16, APPLY>;
+    case KAON_M_INT8: return adakaon_apply_kernel<PT, KAON_M_INT8, APPLY>;
+    case KAON_M_4BIT: return adakaon_apply_kernel<PT, KAON_M_4BIT, APPLY>;
+    case KAON_M_NONE: return adakaon_apply_kernel<PT, KAON_M_NONE, APPLY>;
     default: return nullptr;
   }
 }
 
-static ApplyKernel pick_apply(int pdt, int mk) {
-  return pdt == KAON_DT_BF16 ? pick_apply_pt<__nv_bfloat16>(mk) : pick_apply_pt<float>(mk);
+static ApplyKernel pick_apply(int pdt, int mk, bool apply) {
+  if (apply) return pdt == KAON_DT_BF16 ? pick_apply_pt<__nv_bfloat16, true>(mk) : pick_apply_pt<float, true>(mk);
+  return pdt == KAON_DT_BF16 ? pick_apply_pt<__nv_bfloat16, false>(mk) : pick_apply_pt<float, false>(mk);
 }
 
 typedef void (*AxpyKernel)(PlanView, float, float, SrStream);
@@ -1918,13 +1949,15 @@ static int ensure_apply2(kaon_plan* pl) {
       items.push_back(Task{i, PH_ADA_APPLY, e, (int)std::min<long long>(APPLY_CAP, t.numel - e), 0, 0, 0});
   }
   if (items.empty()) return KAON_OK;
-  ApplyKernel k = pick_apply(pl->param_dtype, mk);
-  if (!k) return KAON_OK;
+  ApplyKernel k = pick_apply(pl->param_dtype, mk, true);
+  ApplyKernel kc = pick_apply(pl->param_dtype, mk, false);
+  if (!k || !kc) return KAON_OK;
   const size_t esz = pl->param_dtype == KAON_DT_BF16 ? 2 : 4;
   const size_t mb = mk == KAON_M_4BIT ? APPLY_CAP / 2 : mk == KAON_M_INT8 ? APPLY_CAP : mk == KAON_M_BF16 ? APPLY_CAP * 2
                     : mk == KAON_M_F32 ? APPLY_CAP * 4 : 0;
   pl->apply_smem = 2 * (size_t)APPLY_CAP * esz + mb;
   KAON_CUDA(cudaFuncSetAttribute((const void*)k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl->apply_smem));
+  KAON_CUDA(cudaFuncSetAttribute((const void*)kc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl->apply_smem));
   int per_sm = 0;
   KAON_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, (const void*)k, APPLY_THREADS, pl->apply_smem));
   if (per_sm < 1) return KAON_OK;
@@ -1975,6 +2008,7 @@ extern "C" int kaon_adakaon_step(kaon_plan* pl, const kaon_adakaon_hparams* h, u
   hp.gc = h->gradient_centralization != 0;
   hp.sr = h->bf16_method == KAON_W_SR && pl->param_dtype == KAON_DT_BF16;
   hp.kahan = h->bf16_method == KAON_W_KAHAN && pl->param_dtype == KAON_DT_BF16;
+  hp.int8 = pl->momentum_kind == KAON_M_INT8;
   hp.has_m = has_m;
   hp.remove = h->msam_remove != 0 && has_m;
   hp.climb = h->msam_climb != 0 && has_m;
@@ -1986,8 +2020,10 @@ extern "C" int kaon_adakaon_step(kaon_plan* pl, const kaon_adakaon_hparams* h, u
   if (int rc = ensure_apply2(pl)) return rc;
   // two launches when the plan is eligible (int8 momentum also needs the COUNT stage's row maxima)
   const bool two = pl->apply2 == 1 && (pl->momentum_kind != KAON_M_INT8 || hp.cautious);
-  if (hp.cautious) { v.tasks = two ? pl->d_tasks_full_na : pl->d_tasks_full; v.n_tasks = two ? pl->n_tasks_full_na : pl->n_tasks_full; }
-  else { v.tasks = two ? pl->d_tasks_main_na : pl->d_tasks_main; v.n_tasks = two ? pl->n_tasks_main_na : pl->n_tasks_main; }
+  // first launch: STATS, FINAL, FLAT (the list without COUNT and APPLY items); then COUNT, then APPLY
+  if (two) { v.tasks = pl->d_tasks_main_na; v.n_tasks = pl->n_tasks_main_na; }
+  else if (hp.cautious) { v.tasks = pl->d_tasks_full; v.n_tasks = pl->n_tasks_full; }
+  else { v.tasks = pl->d_tasks_main; v.n_tasks = pl->n_tasks_main; }
   KAON_CUDA(cudaMemsetAsync(v.task_counter, 0, pl->counters_bytes - sizeof(unsigned), s));
   AdaKernel k = pick_ada(pl->param_dtype, pl->momentum_kind, false);
   k<<<pl->grid, AT, pl->smem_bytes, s>>>(v, hp, (int)x_offset_rows(pl) | (pl->double_buffer ? 1 : 0));
@@ -1998,8 +2034,14 @@ extern "C" int kaon_adakaon_step(kaon_plan* pl, const kaon_adakaon_hparams* h, u
     va.tasks = pl->d_tasks_apply2;
     va.n_tasks = pl->n_tasks_apply2;
     va.task_counter = pl->d_counter2;
+    if (hp.cautious) {
+      KAON_CUDA(cudaMemsetAsync(pl->d_counter2, 0, sizeof(unsigned), s));
+      pick_apply(pl->param_dtype, pl->momentum_kind, false)<<<pl->apply_grid, APPLY_THREADS, pl->apply_smem, s>>>(va, hp);
+      KAON_CUDA(cudaGetLastError());
+      pl->launches += 1;
+    }
     KAON_CUDA(cudaMemsetAsync(pl->d_counter2, 0, sizeof(unsigned), s));
-    pick_apply(pl->param_dtype, pl->momentum_kind)<<<pl->apply_grid, APPLY_THREADS, pl->apply_smem, s>>>(va, hp);
+    pick_apply(pl->param_dtype, pl->momentum_kind, true)<<<pl->apply_grid, APPLY_THREADS, pl->apply_smem, s>>>(va, hp);
     KAON_CUDA(cudaGetLastError());
     pl->launches += 1;
   }

@@ -12,7 +12,7 @@ namespace kaon {
 struct AdaDev {
   float w1, w1m1, w2, w2m1, eps1, clip, lrwd, upd_scale;
   int small_w1, small_w2, has_eps, has_wd, cautious, gc, sr, has_m;
-  int remove, climb, kahan;
+  int remove, climb, kahan, int8;
   float a_remove, b_remove, a_climb, b_climb;
   uint32_t step, k0, k1;
 };
