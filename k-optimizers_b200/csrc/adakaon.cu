@@ -1577,7 +1577,7 @@ __global__ void __launch_bounds__(256) msam_axpy_kernel(PlanView pv, float alpha
 // order replaces the completion counters: every COUNT item has finished when this kernel starts.
 // Items are flat runs (no row structure: what is per row or per column comes from the scratch in L2),
 // so the int8 row scales of the previous step are read from the copy COUNT set aside.
-constexpr int APPLY_CAP = 8192;
+constexpr int APPLY_CAP = 12288;
 constexpr int APPLY_THREADS = 256;
 
 // APPLY = false is the COUNT stage in the same form (kept count, int8 row maxima; no stores but those).
