@@ -1581,11 +1581,17 @@ constexpr int APPLY_CAP = 12288;
 constexpr int APPLY_THREADS = 256;
 
 // APPLY = false is the COUNT stage in the same form (kept count, int8 row maxima; no stores but those).
-template <typename PT, int MK, bool APPLY>
+// MUON (AdaMuon): the chain runs on the orthogonalised momentum (bf16, `pv.signal`) with no momentum of
+// its own, the cautious mask compares with the raw gradient, which is staged where the momentum bytes
+// go otherwise.
+template <typename PT, int MKP, bool APPLY, bool MUON>
 __global__ void __launch_bounds__(APPLY_THREADS, 3) adakaon_apply_kernel(PlanView pv, AdaDev hp) {
   using E = Elems<PT>;
+  using S = Elems<typename std::conditional<MUON, __nv_bfloat16, PT>::type>;
+  constexpr int MK = MUON ? KAON_M_NONE : MKP;
   constexpr int GB = 8 * E::BYTES;
-  constexpr int MB = MK == KAON_M_4BIT ? 4 : MK == KAON_M_INT8 ? 8 : MK == KAON_M_BF16 ? 16 : MK == KAON_M_F32 ? 32 : 0;
+  constexpr int SB = 8 * S::BYTES;
+  constexpr int MB = MUON ? GB : MK == KAON_M_4BIT ? 4 : MK == KAON_M_INT8 ? 8 : MK == KAON_M_BF16 ? 16 : MK == KAON_M_F32 ? 32 : 0;
   extern __shared__ __align__(128) unsigned char dyn[];
   __shared__ __align__(8) uint64_t bar;
   __shared__ int next_s[2];
@@ -1611,7 +1617,7 @@ __global__ void __launch_bounds__(APPLY_THREADS, 3) adakaon_apply_kernel(PlanVie
   SrStream s_rem{Philox{hp.k0, hp.k1}, hp.step, KAON_TAG_REMOVE};
   SrStream s_clb{Philox{hp.k0, hp.k1}, hp.step, KAON_TAG_CLIMB};
   const bool sr = hp.sr != 0;
-  const bool gc = hp.gc != 0;
+  const bool gc = hp.gc != 0 && !MUON;
   while (cur < pv.n_tasks) {
     claim_next(slot ^ 1);
     const Task t = pv.tasks[cur];
@@ -1620,19 +1626,22 @@ __global__ void __launch_bounds__(APPLY_THREADS, 3) adakaon_apply_kernel(PlanVie
     bool ok = g != nullptr;
     const int n = t.n;
     if (ok) {
-      const unsigned char* gsrc = g + t.e0 * E::BYTES;
+      const unsigned char* gsrc = MUON ? reinterpret_cast<const unsigned char*>(pv.signal[t.tensor]) + t.e0 * S::BYTES
+                                       : g + t.e0 * E::BYTES;
+      const unsigned char* msrc = MUON ? g + t.e0 * E::BYTES : m_ptr<MK>(d, t.e0);
+      const unsigned mbytes = MUON ? (unsigned)n * E::BYTES : m_bytes<MK>(n);
       const unsigned char* psrc = reinterpret_cast<const unsigned char*>(d.p) + t.e0 * E::BYTES;
-      const unsigned ghead = stage_tail(g_s, gsrc, (unsigned)n * E::BYTES, tid);
+      const unsigned ghead = stage_tail(g_s, gsrc, (unsigned)n * S::BYTES, tid);
       const unsigned phead = need_p ? stage_tail(p_s, psrc, (unsigned)n * E::BYTES, tid) : 0u;
       unsigned mhead = 0u;
-      if constexpr (MB > 0) mhead = stage_tail(m_s, m_ptr<MK>(d, t.e0), m_bytes<MK>(n), tid);
+      if constexpr (MB > 0) mhead = stage_tail(m_s, msrc, mbytes, tid);
       if (ghead + phead + mhead) {
         if (tid == 0) {
           fence_async_smem();
           mbar_expect_tx(&bar, ghead + phead + mhead);
           if (ghead) bulk_g2s(g_s, gsrc, ghead, &bar);
           if (phead) bulk_g2s(p_s, psrc, phead, &bar);
-          if constexpr (MB > 0) { if (mhead) bulk_g2s(m_s, m_ptr<MK>(d, t.e0), mhead, &bar); }
+          if constexpr (MB > 0) { if (mhead) bulk_g2s(m_s, msrc, mhead, &bar); }
         }
         ok = mbar_wait(&bar, parity, pv.status, 15001u);
         parity ^= 1u;
@@ -1676,7 +1685,9 @@ __global__ void __launch_bounds__(APPLY_THREADS, 3) adakaon_apply_kernel(PlanVie
         const float4 c0v = __ldcg(reinterpret_cast<const float4*>(cfac + col));
         const float4 c1v = __ldcg(reinterpret_cast<const float4*>(cfac + col + 4));
         const float cf[8] = {c0v.x, c0v.y, c0v.z, c0v.w, c1v.x, c1v.y, c1v.z, c1v.w};
-        E::load8(g_s + (size_t)vv * GB, gv);
+        S::load8(g_s + (size_t)vv * SB, gv);
+        float raw[8];
+        if (MUON) E::load8(m_s + (size_t)vv * GB, raw);
         if (need_p) E::load8(p_s + (size_t)vv * GB, pc);
         else {
 #pragma unroll
@@ -1718,7 +1729,7 @@ __global__ void __launch_bounds__(APPLY_THREADS, 3) adakaon_apply_kernel(PlanVie
           mn[k] = ema_of<MK>(mo[k], u, hp);
           const float dv = hp.has_wd ? __fmaf_rn(pc[k], hp.lrwd, mn[k]) : mn[k];
           dl[k] = dv;
-          if (__fmul_rn(dv, gv[k]) > 0.0f) kept |= 1u << k;
+          if (__fmul_rn(dv, MUON ? raw[k] : gv[k]) > 0.0f) kept |= 1u << k;
         }
         if constexpr (!APPLY) {
           if (act) kept_local += __popc(kept);
@@ -1839,16 +1850,21 @@ typedef void (*ApplyKernel)(PlanView, AdaDev);
 template <typename PT, bool APPLY>
 static ApplyKernel pick_apply_pt(int mk) {
   switch (mk) {
-    case KAON_M_F32: return adakaon_apply_kernel<PT, KAON_M_F32, APPLY>;
-    case KAON_M_BF16: return adakaon_apply_kernel<PT, KAON_M_BF16, APPLY>;
-    case KAON_M_INT8: return adakaon_apply_kernel<PT, KAON_M_INT8, APPLY>;
-    case KAON_M_4BIT: return adakaon_apply_kernel<PT, KAON_M_4BIT, APPLY>;
-    case KAON_M_NONE: return adakaon_apply_kernel<PT, KAON_M_NONE, APPLY>;
+    case KAON_M_F32: return adakaon_apply_kernel<PT, KAON_M_F32, APPLY, false>;
+    case KAON_M_BF16: return adakaon_apply_kernel<PT, KAON_M_BF16, APPLY, false>;
+    case KAON_M_INT8: return adakaon_apply_kernel<PT, KAON_M_INT8, APPLY, false>;
+    case KAON_M_4BIT: return adakaon_apply_kernel<PT, KAON_M_4BIT, APPLY, false>;
+    case KAON_M_NONE: return adakaon_apply_kernel<PT, KAON_M_NONE, APPLY, false>;
     default: return nullptr;
   }
 }
 
-static ApplyKernel pick_apply(int pdt, int mk, bool apply) {
+static ApplyKernel pick_apply(int pdt, int mk, bool apply, bool muon) {
+  if (muon) {
+    if (pdt == KAON_DT_BF16) return apply ? adakaon_apply_kernel<__nv_bfloat16, KAON_M_NONE, true, true>
+                                          : adakaon_apply_kernel<__nv_bfloat16, KAON_M_NONE, false, true>;
+    return apply ? adakaon_apply_kernel<float, KAON_M_NONE, true, true> : adakaon_apply_kernel<float, KAON_M_NONE, false, true>;
+  }
   if (apply) return pdt == KAON_DT_BF16 ? pick_apply_pt<__nv_bfloat16, true>(mk) : pick_apply_pt<float, true>(mk);
   return pdt == KAON_DT_BF16 ? pick_apply_pt<__nv_bfloat16, false>(mk) : pick_apply_pt<float, false>(mk);
 }
@@ -1928,16 +1944,13 @@ int configure_launch_adakaon(kaon_plan* pl, const cudaDeviceProp& prop, int max_
   return KAON_OK;
 }
 
-}  // namespace kaon
-
-using namespace kaon;
-
-// One-time set-up of the two-launch form: eligibility, the flat APPLY items, the first launch's lists
-// without APPLY items, the second kernel's launch configuration.
-static int ensure_apply2(kaon_plan* pl) {
+// One-time set-up of the three-launch form: eligibility, the flat COUNT/APPLY items, the first launch's
+// list without COUNT and APPLY items, the second kernel's launch configuration.
+int ensure_apply2(kaon_plan* pl) {
   if (pl->apply2 != 0) return KAON_OK;
   pl->apply2 = -1;
-  const int mk = pl->momentum_kind;
+  const bool muon = pl->optimizer == KAON_OPT_ADAMUON;
+  const int mk = muon ? KAON_M_NONE : pl->momentum_kind;
   std::vector<Task> items;
   for (int i = 0; i < pl->n_tensors; ++i) {
     const DevTensor& t = pl->h_tensors[i];
@@ -1949,12 +1962,13 @@ static int ensure_apply2(kaon_plan* pl) {
       items.push_back(Task{i, PH_ADA_APPLY, e, (int)std::min<long long>(APPLY_CAP, t.numel - e), 0, 0, 0});
   }
   if (items.empty()) return KAON_OK;
-  ApplyKernel k = pick_apply(pl->param_dtype, mk, true);
-  ApplyKernel kc = pick_apply(pl->param_dtype, mk, false);
+  ApplyKernel k = pick_apply(pl->param_dtype, mk, true, muon);
+  ApplyKernel kc = pick_apply(pl->param_dtype, mk, false, muon);
   if (!k || !kc) return KAON_OK;
   const size_t esz = pl->param_dtype == KAON_DT_BF16 ? 2 : 4;
-  const size_t mb = mk == KAON_M_4BIT ? APPLY_CAP / 2 : mk == KAON_M_INT8 ? APPLY_CAP : mk == KAON_M_BF16 ? APPLY_CAP * 2
-                    : mk == KAON_M_F32 ? APPLY_CAP * 4 : 0;
+  const size_t mb = muon ? APPLY_CAP * esz
+                         : mk == KAON_M_4BIT ? APPLY_CAP / 2 : mk == KAON_M_INT8 ? APPLY_CAP : mk == KAON_M_BF16 ? APPLY_CAP * 2
+                         : mk == KAON_M_F32 ? APPLY_CAP * 4 : 0;
   pl->apply_smem = 2 * (size_t)APPLY_CAP * esz + mb;
   KAON_CUDA(cudaFuncSetAttribute((const void*)k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl->apply_smem));
   KAON_CUDA(cudaFuncSetAttribute((const void*)kc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl->apply_smem));
@@ -1964,21 +1978,18 @@ static int ensure_apply2(kaon_plan* pl) {
   cudaDeviceProp prop;
   KAON_CUDA(cudaGetDeviceProperties(&prop, pl->device));
   pl->apply_grid = prop.multiProcessorCount * per_sm;
-  // the first launch's lists, APPLY items taken out
-  auto filtered = [&](const Task* d_list, int n, Task** out, int* n_out) -> int {
-    std::vector<Task> h((size_t)n);
-    KAON_CUDA(cudaMemcpy(h.data(), d_list, sizeof(Task) * (size_t)n, cudaMemcpyDeviceToHost));
+  // the first launch's list without COUNT and APPLY items
+  {
+    std::vector<Task> h((size_t)pl->n_tasks_main);
+    KAON_CUDA(cudaMemcpy(h.data(), pl->d_tasks_main, sizeof(Task) * h.size(), cudaMemcpyDeviceToHost));
     std::vector<Task> keep;
     for (const Task& t : h)
       if (t.phase != PH_ADA_APPLY) keep.push_back(t);
-    KAON_CUDA(cudaMalloc((void**)out, sizeof(Task) * std::max<size_t>(keep.size(), 1)));
-    KAON_CUDA(cudaMemcpy(*out, keep.data(), sizeof(Task) * keep.size(), cudaMemcpyHostToDevice));
-    *n_out = (int)keep.size();
+    KAON_CUDA(cudaMalloc((void**)&pl->d_tasks_main_na, sizeof(Task) * std::max<size_t>(keep.size(), 1)));
+    KAON_CUDA(cudaMemcpy(pl->d_tasks_main_na, keep.data(), sizeof(Task) * keep.size(), cudaMemcpyHostToDevice));
+    pl->n_tasks_main_na = (int)keep.size();
     pl->device_bytes += (int64_t)(sizeof(Task) * keep.size());
-    return KAON_OK;
-  };
-  if (int rc = filtered(pl->d_tasks_full, pl->n_tasks_full, &pl->d_tasks_full_na, &pl->n_tasks_full_na)) return rc;
-  if (int rc = filtered(pl->d_tasks_main, pl->n_tasks_main, &pl->d_tasks_main_na, &pl->n_tasks_main_na)) return rc;
+  }
   KAON_CUDA(cudaMalloc((void**)&pl->d_tasks_apply2, sizeof(Task) * items.size()));
   KAON_CUDA(cudaMemcpy(pl->d_tasks_apply2, items.data(), sizeof(Task) * items.size(), cudaMemcpyHostToDevice));
   KAON_CUDA(cudaMalloc((void**)&pl->d_counter2, 256));
@@ -1987,6 +1998,32 @@ static int ensure_apply2(kaon_plan* pl) {
   pl->apply2 = 1;
   return KAON_OK;
 }
+
+// The COUNT (cautious mask on) and APPLY launches over the plan's flat items; `base` carries the
+// plan's pointers (and AdaMuon's signal column).
+int launch_count_apply(kaon_plan* pl, const PlanView& base, const AdaDev& hp, cudaStream_t s) {
+  const bool muon = pl->optimizer == KAON_OPT_ADAMUON;
+  const int mk = muon ? KAON_M_NONE : pl->momentum_kind;
+  PlanView va = base;
+  va.tasks = pl->d_tasks_apply2;
+  va.n_tasks = pl->n_tasks_apply2;
+  va.task_counter = pl->d_counter2;
+  if (hp.cautious) {
+    KAON_CUDA(cudaMemsetAsync(pl->d_counter2, 0, sizeof(unsigned), s));
+    pick_apply(pl->param_dtype, mk, false, muon)<<<pl->apply_grid, APPLY_THREADS, pl->apply_smem, s>>>(va, hp);
+    KAON_CUDA(cudaGetLastError());
+    pl->launches += 1;
+  }
+  KAON_CUDA(cudaMemsetAsync(pl->d_counter2, 0, sizeof(unsigned), s));
+  pick_apply(pl->param_dtype, mk, true, muon)<<<pl->apply_grid, APPLY_THREADS, pl->apply_smem, s>>>(va, hp);
+  KAON_CUDA(cudaGetLastError());
+  pl->launches += 1;
+  return KAON_OK;
+}
+
+}  // namespace kaon
+
+using namespace kaon;
 
 extern "C" int kaon_adakaon_step(kaon_plan* pl, const kaon_adakaon_hparams* h, uint64_t seed,
                                  uint32_t step, void* stream) {
@@ -2030,20 +2067,7 @@ extern "C" int kaon_adakaon_step(kaon_plan* pl, const kaon_adakaon_hparams* h, u
   KAON_CUDA(cudaGetLastError());
   pl->launches += 1;
   if (two) {
-    PlanView va = pl->view;
-    va.tasks = pl->d_tasks_apply2;
-    va.n_tasks = pl->n_tasks_apply2;
-    va.task_counter = pl->d_counter2;
-    if (hp.cautious) {
-      KAON_CUDA(cudaMemsetAsync(pl->d_counter2, 0, sizeof(unsigned), s));
-      pick_apply(pl->param_dtype, pl->momentum_kind, false)<<<pl->apply_grid, APPLY_THREADS, pl->apply_smem, s>>>(va, hp);
-      KAON_CUDA(cudaGetLastError());
-      pl->launches += 1;
-    }
-    KAON_CUDA(cudaMemsetAsync(pl->d_counter2, 0, sizeof(unsigned), s));
-    pick_apply(pl->param_dtype, pl->momentum_kind, true)<<<pl->apply_grid, APPLY_THREADS, pl->apply_smem, s>>>(va, hp);
-    KAON_CUDA(cudaGetLastError());
-    pl->launches += 1;
+    if (int rc = launch_count_apply(pl, pl->view, hp, s)) return rc;
   }
   return KAON_OK;
 }

@@ -20,5 +20,8 @@ struct AdaDev {
 typedef void (*AdaKernel)(PlanView, AdaDev, int);
 AdaKernel pick_ada(int param_dtype, int momentum_kind, bool muon);
 size_t x_offset_rows(const kaon_plan* pl);
+// COUNT and APPLY as launches of their own (plans whose factored tensors all stream)
+int ensure_apply2(kaon_plan* pl);
+int launch_count_apply(kaon_plan* pl, const PlanView& base, const AdaDev& hp, cudaStream_t s);
 
 }  // namespace kaon

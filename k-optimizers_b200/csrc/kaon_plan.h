@@ -135,13 +135,12 @@ struct kaon_plan {
   std::vector<int> ema_begin;                // [n_tensors + 1] ranges into d_tasks_ema
   const void** d_signal = nullptr;           // per-tensor pointer to O in the caller's workspace
   const void* signal_base = nullptr;         // workspace the pointers were computed for
-  // Adakaon only (built lazily by the first step): the APPLY stage as a second launch
+  // Adakaon / AdaMuon (built lazily by the first step): COUNT and APPLY as launches of their own
   int apply2 = 0;                            // 0 = not decided, 1 = in use, -1 = this plan is not eligible
   kaon::Task* d_tasks_apply2 = nullptr;      // flat items of the factored tensors
-  kaon::Task* d_tasks_full_na = nullptr;     // the two work lists of the first launch without APPLY items
-  kaon::Task* d_tasks_main_na = nullptr;
-  int n_tasks_apply2 = 0, n_tasks_full_na = 0, n_tasks_main_na = 0;
-  unsigned* d_counter2 = nullptr;            // claim counter of the second launch
+  kaon::Task* d_tasks_main_na = nullptr;     // the first launch's work list without COUNT and APPLY items
+  int n_tasks_apply2 = 0, n_tasks_main_na = 0;
+  unsigned* d_counter2 = nullptr;            // claim counter of the COUNT / APPLY launches
   int apply_grid = 0;
   size_t apply_smem = 0;
   unsigned* d_counters = nullptr;  // task_counter, status, done[n], kept[n] (contiguous; memset per step)
