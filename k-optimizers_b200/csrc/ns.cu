@@ -72,8 +72,9 @@ static bool g_gemm_attr_set[64] = {false};
 int launch_ns_gemm(const __nv_bfloat16* A, bool a_mn, long long lda, const __nv_bfloat16* B, bool b_mn, long long ldb,
                    int M, int N, int K, float alpha, float beta, const float* dev_scale, const __nv_bfloat16* aux,
                    long long ld_aux, __nv_bfloat16* out, long long ld_out, unsigned* status, cudaStream_t stream,
-                   long long* launches) {
+                   long long* launches, bool sym = false) {
   GemmParams p{};
+  p.sym = sym && M == N ? 1 : 0;
   p.M = M; p.N = N; p.K = K; p.a_mn = a_mn; p.b_mn = b_mn;
   p.alpha = alpha; p.beta = aux ? beta : 0.0f; p.dev_scale = dev_scale;
   p.aux = aux; p.ld_aux = ld_aux; p.out = out; p.ld_out = ld_out; p.status = status;
@@ -168,11 +169,12 @@ int ns_run(const __nv_bfloat16* x_in, long long R, long long C, int steps, __nv_
     const float* sc_x = it == 0 ? scal + 2 : nullptr;
     int rc;
     // A = X X^T  [r, r]
-    if (tall) rc = launch_ns_gemm(cur, true, C, cur, true, C, (int)r, (int)r, (int)k, 1.0f, 0.0f, sc_a, nullptr, 0, Am, r, status, stream, launches);
-    else      rc = launch_ns_gemm(cur, false, C, cur, false, C, (int)r, (int)r, (int)k, 1.0f, 0.0f, sc_a, nullptr, 0, Am, r, status, stream, launches);
+    // (symmetric: only the tiles on and above the diagonal are computed)
+    if (tall) rc = launch_ns_gemm(cur, true, C, cur, true, C, (int)r, (int)r, (int)k, 1.0f, 0.0f, sc_a, nullptr, 0, Am, r, status, stream, launches, true);
+    else      rc = launch_ns_gemm(cur, false, C, cur, false, C, (int)r, (int)r, (int)k, 1.0f, 0.0f, sc_a, nullptr, 0, Am, r, status, stream, launches, true);
     if (rc) return rc;
     // B = b A + c A A   (A symmetric: A A = A A^T, both operands K-major)
-    rc = launch_ns_gemm(Am, false, r, Am, false, r, (int)r, (int)r, (int)r, c, b, nullptr, Am, r, Bm, r, status, stream, launches);
+    rc = launch_ns_gemm(Am, false, r, Am, false, r, (int)r, (int)r, (int)r, c, b, nullptr, Am, r, Bm, r, status, stream, launches, true);
     if (rc) return rc;
     // X <- a X + B X
     if (tall)  // X^T <- a X^T + X^T B : out[kk, j] = sum_i X^T[kk, i] B[j, i]

@@ -35,6 +35,9 @@ struct GemmParams {
   __nv_bfloat16* out;        // [M, ld_out]
   long long ld_out;
   unsigned* status;          // device status word (bounded waits)
+  int sym;                   // the product is symmetric (M == N, same operand on both sides): tiles that lie
+                             // wholly below the diagonal are not computed; every computed tile also stores
+                             // its transpose, which fills them
 };
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
@@ -105,6 +108,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   __shared__ int fail_s;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int m0 = blockIdx.y * G_BM, n0 = blockIdx.x * p.BN;
+  if (p.sym && n0 + p.BN <= m0) return;  // below the diagonal: the mirror of another tile (whole CTA leaves)
   const int b_bytes = p.BN * G_BK * 2;
   const int stage_bytes = G_A_BYTES + b_bytes;
   // 1024-byte aligned tile base (the swizzle pattern is a function of address bits 4..9)
@@ -199,11 +203,22 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               w[e] = pack_bf16_rn(r0, r1);
             }
             *reinterpret_cast<uint4*>(orow + q * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+            if (p.sym) {  // transpose: out[col + j, row]; lanes are consecutive rows, i.e. consecutive addresses
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                unsigned short* mlo = reinterpret_cast<unsigned short*>(p.out + (long long)(col + q * 8 + 2 * e) * p.ld_out + row);
+                unsigned short* mhi = reinterpret_cast<unsigned short*>(p.out + (long long)(col + q * 8 + 2 * e + 1) * p.ld_out + row);
+                *mlo = (unsigned short)(w[e] & 0xffffu);
+                *mhi = (unsigned short)(w[e] >> 16);
+              }
+            }
           }
         } else {
           for (int e = 0; e < 32 && col + e < p.N; ++e) {
             const float x = arow ? __bfloat162float(arow[e]) : 0.0f;
-            orow[e] = __float2bfloat16_rn(__uint_as_float(v[e]) * alpha + beta * x);
+            const __nv_bfloat16 r = __float2bfloat16_rn(__uint_as_float(v[e]) * alpha + beta * x);
+            orow[e] = r;
+            if (p.sym) p.out[(long long)(col + e) * p.ld_out + row] = r;
           }
         }
       }
