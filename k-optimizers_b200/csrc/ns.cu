@@ -87,6 +87,22 @@ int launch_ns_gemm(const __nv_bfloat16* A, bool a_mn, long long lda, const __nv_
     return KAON_OK;
   }
   p.BN = N >= 256 ? 256 : (N > 64 ? 128 : 64);
+  if (p.sym && N >= 256) {
+    // One CTA per computed tile: with 256-wide tiles a 3072-wide symmetric product has 156 of them,
+    // two waves over 148 SMs all the same; 192-wide tiles make 208 (two waves of 3/4 the work each).
+    // Take 192 when waves x width comes out clearly smaller.
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    auto cost = [&](int bn) {
+      long long tiles = 0;
+      for (int m0 = 0; m0 < M; m0 += G_BM)
+        for (int n0 = 0; n0 < N; n0 += bn)
+          if (n0 + bn > m0) ++tiles;
+      return ((tiles + sms - 1) / sms) * (long long)bn;
+    };
+    if (cost(192) * 100 < cost(256) * 90) p.BN = 192;
+  }
   CUtensorMap ma, mb;
   int rc;
   if (a_mn) rc = make_map(&ma, A, M, K, lda, 64); else rc = make_map(&ma, A, K, M, lda, G_BM);

@@ -27,7 +27,7 @@ constexpr unsigned G_WAIT_LIMIT = 1u << 22;
 struct GemmParams {
   int M, N, K;
   int a_mn, b_mn;    // 0 = K-major operand, 1 = MN-major operand
-  int BN;            // 64, 128 or 256
+  int BN;            // 64, 128, 192 or 256
   float alpha, beta;
   const float* dev_scale;    // optional device pair {alpha multiplier, beta multiplier} (e.g. 1/norm)
   const __nv_bfloat16* aux;  // [M, ld_aux] or null (beta ignored)
@@ -114,7 +114,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   // 1024-byte aligned tile base (the swizzle pattern is a function of address bits 4..9)
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(gsm) + 1023) & ~uintptr_t(1023));
   const int kblocks = (p.K + G_BK - 1) / G_BK;
-  const uint32_t ncols = p.BN < 32 ? 32u : (uint32_t)p.BN;  // power of two >= 32
+  const uint32_t ncols = p.BN <= 32 ? 32u : p.BN <= 64 ? 64u : p.BN <= 128 ? 128u : 256u;  // power of two >= BN
 
   if (tid == 0) {
     for (int s = 0; s < G_STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
