@@ -18,7 +18,7 @@ namespace kaon {
 
 constexpr int G_BM = 128;          // rows of the output tile = UMMA M
 constexpr int G_BK = 64;           // K elements per stage (one 128-byte swizzle atom of bf16)
-constexpr int G_STAGES = 4;
+constexpr int G_STAGES = 2;
 constexpr int G_A_BYTES = G_BM * G_BK * 2;  // 16 KiB
 constexpr int G_MAX_BN = 256;
 constexpr int G_THREADS = 128;
@@ -98,7 +98,7 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t v[32]) {
 
 // One CTA per 128 x BN output tile.  Thread 0 feeds TMA, thread 32 issues the MMAs, then all four
 // warps drain the accumulator (warp w owns tensor-memory lanes 32w..32w+31 = output rows).
-__global__ void __launch_bounds__(G_THREADS, 1)
+__global__ void __launch_bounds__(G_THREADS, 2)
 ns_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
   extern __shared__ __align__(1024) unsigned char gsm[];
   __shared__ __align__(8) uint64_t full_bar[G_STAGES];
