@@ -1577,7 +1577,7 @@ __global__ void __launch_bounds__(256) msam_axpy_kernel(PlanView pv, float alpha
 // order replaces the completion counters: every COUNT item has finished when this kernel starts.
 // Items are flat runs (no row structure: what is per row or per column comes from the scratch in L2),
 // so the int8 row scales of the previous step are read from the copy COUNT set aside.
-constexpr int APPLY_CAP = 12288;
+constexpr int APPLY_CAP = 8192;
 constexpr int APPLY_THREADS = 256;
 
 // APPLY = false is the COUNT stage in the same form (kept count, int8 row maxima; no stores but those).
@@ -1585,7 +1585,7 @@ constexpr int APPLY_THREADS = 256;
 // its own, the cautious mask compares with the raw gradient, which is staged where the momentum bytes
 // go otherwise.
 template <typename PT, int MKP, bool APPLY, bool MUON>
-__global__ void __launch_bounds__(APPLY_THREADS, 3) adakaon_apply_kernel(PlanView pv, AdaDev hp) {
+__global__ void __launch_bounds__(APPLY_THREADS, 4) adakaon_apply_kernel(PlanView pv, AdaDev hp) {
   using E = Elems<PT>;
   using S = Elems<typename std::conditional<MUON, __nv_bfloat16, PT>::type>;
   constexpr int MK = MUON ? KAON_M_NONE : MKP;
