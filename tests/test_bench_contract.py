@@ -1,0 +1,45 @@
+"""The JSON line bench.py prints: the reference arm runs without a GPU (it times the CPU oracle port on
+a bounded sample), so its contract can be checked here; the GPU arm's keys are checked on a GPU."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(args, timeout=600):
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), *args], capture_output=True, text=True,
+                       timeout=timeout, cwd=ROOT)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [ln for ln in r.stdout.splitlines() if ln.startswith("{")]
+    assert len(lines) == 1, r.stdout[-2000:]
+    return json.loads(lines[0])
+
+
+def test_reference_arm_line():
+    d = _run(["--impl", "reference", "--steps", "1", "--warmup", "0"])
+    assert d["impl"] == "reference" and d["metric"] == "optimizer_step_params_per_sec" and d["unit"] == "params/s"
+    assert d["higher_is_better"] is True and d["n_gpus"] == 1 and d["value"] > 0
+    assert d["config"]["workload"] == "lion4bit_unet2p6b"
+    cb = d["cpu_baseline"]
+    assert cb["kind"] == "port" and cb["cores"] >= 1 and cb["value"] == d["value"] and cb["sample"]
+    assert d["e2e"] == {"value": d["value"], "unit": "params/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+
+
+@pytest.mark.gpu
+def test_gpu_arm_line_has_the_contract_keys():
+    d = _run(["--workload", "lion4bit_sample", "--steps", "3", "--warmup", "3"])
+    for key in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling",
+                "vs_baseline", "dtype", "data", "config", "roofline", "cpu_baseline", "e2e", "gpu_launches", "clocks"):
+        assert key in d, key
+    assert d["vs_baseline"] is None and d["data"] == "synthetic" and d["config"]["workload"] == "lion4bit_sample"
+    ro = d["roofline"]
+    assert ro["bound"] == "hbm" and ro["unit"] == "GB/s" and 0 < ro["frac"] < 1.5 and ro["peak"] > 1000
+    assert abs(ro["frac"] - ro["achieved"] / ro["peak"]) < 1e-9
+    assert d["gpu_launches"] == d["steps"]           # one Lion kernel per step
+    e = d["e2e"]
+    assert e["h2d_bytes_per_step"] > 0 and e["d2h_bytes_per_step"] > 0 and e["value"] < d["value"]
+    assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1
