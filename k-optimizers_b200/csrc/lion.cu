@@ -89,9 +89,13 @@ __device__ __forceinline__ unsigned lion_fast4(const PlanView& pv, const LionDev
     float mn[8];
     uint32_t pos = 0, neg = 0;
     float amax = 0.0f;
+    // nibble k as the low mantissa bits of 2^23: one byte permute per element (even nibbles sit in the
+    // bytes of wl, odd ones in the bytes of wh)
+    const uint32_t wl = w & 0x0F0F0F0Fu, wh = (w >> 4) & 0x0F0F0F0Fu;
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
-      const float mo = __fmul_rn(__uint_as_float(0x4B000000u | ((w >> (4 * k)) & 0xFu)) - 8388616.0f, sc_old);
+      const uint32_t fb = __byte_perm((k & 1) ? wh : wl, 0x4B000000u, 0x7540u | (uint32_t)(k >> 1));
+      const float mo = __fmul_rn(__uint_as_float(fb) - 8388616.0f, sc_old);
       const float c = __fmaf_rn(g[k], hp.w1, __fmul_rn(mo, hp.b1));
       mn[k] = __fmaf_rn(g[k], hp.w2, __fmul_rn(mo, hp.b2));
       amax = fmaxf(amax, fabsf(mn[k]));
@@ -106,9 +110,9 @@ __device__ __forceinline__ unsigned lion_fast4(const PlanView& pv, const LionDev
     float worst = 0.0f;
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
-      const float tq = __fmul_rn(mn[k], inv);
-      const float r = __fadd_rn(tq, magic);
-      worst = fmaxf(worst, fabsf(__fsub_rn(tq, __fsub_rn(r, magic))));
+      // r = rint(mn*inv) + magic in one rounding; mn*inv - rint(...) exactly, by a second fma
+      const float r = __fmaf_rn(mn[k], inv, magic);
+      worst = fmaxf(worst, fabsf(__fmaf_rn(mn[k], inv, -__fsub_rn(r, magic))));
       word += __float_as_uint(r) << (4 * k);
     }
     word -= PACK_BIAS;
