@@ -15,8 +15,15 @@ from kaon_b200.zero1 import ShardedGrads, ShardedWeights, gather_state_dict  # n
 SHAPES = [(640, 256), (64, 32, 3, 3), (1280,), (512, 640), (333, 77), (3, 4096), (4000, 1), (7,), (256, 1024)]
 
 
+# rows that are multiples of 16 elements: the streaming stages and the separate COUNT / APPLY launches
+SHAPES_STREAM = [(640, 256), (64, 32, 4, 4), (1280,), (512, 640), (336, 80), (3, 4096), (4000, 16), (7,), (256, 1024)]
+
+
 def main():
+    global SHAPES
     opt_name, out = sys.argv[1], sys.argv[2]
+    if opt_name.endswith("-stream"):
+        opt_name, SHAPES = opt_name[:-len("-stream")], SHAPES_STREAM
     world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)

@@ -13,6 +13,8 @@ import torch
 pytestmark = pytest.mark.gpu
 
 SHAPES = [(96, 128), (16, 12, 3, 3), (200,), (40, 72), (7,), (33, 77), (256, 512)]
+# every row a multiple of 16 elements: the plan takes the streaming stages and the separate COUNT/APPLY launches
+SHAPES_STREAM = [(96, 128), (16, 16, 4, 4), (200,), (40, 272), (7,), (48, 4096), (256, 512)]
 
 
 def _numel(s):
@@ -22,9 +24,9 @@ def _numel(s):
     return n
 
 
-def _layout(dtype):
+def _layout(dtype, shapes=None):
     offs, cur = [], 0
-    for s in SHAPES:
+    for s in (shapes or SHAPES):
         offs.append(cur)
         cur += (_numel(s) + 127) // 128 * 128
     return offs, cur
@@ -40,9 +42,11 @@ def _layout(dtype):
     ("AdaMuon", dict(lr=1e-3, momentum_dtype="int8")),
 ])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-def test_mirror_region_tracks_the_weights(cls_name, kw, dtype):
+@pytest.mark.parametrize("shapes", [SHAPES, SHAPES_STREAM], ids=["ragged", "stream"])
+def test_mirror_region_tracks_the_weights(cls_name, kw, dtype, shapes):
     import kaon_b200
-    offs, n = _layout(dtype)
+    SHAPES = shapes  # noqa: N806 - the body below reads the list under this name
+    offs, n = _layout(dtype, shapes)
     flat = torch.zeros(3 * n, dtype=dtype, device="cuda")  # [weights | mirror 1 | mirror 2]
     gen = torch.Generator().manual_seed(11)
     params = []
@@ -81,7 +85,7 @@ def test_parameter_outside_the_mirrored_buffer_is_refused():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("opt_name", ["Lion", "Adakaon"])
+@pytest.mark.parametrize("opt_name", ["Lion", "Adakaon", "Adakaon-stream"])
 def test_two_ranks_fused_publish_equals_single_gpu(opt_name, tmp_path):
     """One process per GPU; every rank ends with the same full weight buffer as a 1-GPU run."""
     script = os.path.join(os.path.dirname(__file__), "_zero1_rank.py")
