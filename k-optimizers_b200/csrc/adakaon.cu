@@ -13,6 +13,14 @@
 //     of the previous climb and the new climb ride on the same read and write of each weight.
 // 1-D tensor: FLAT, the whole tensor in one work item.
 // Every cross-item sum is taken in a fixed order: results do not depend on scheduling.
+//
+// Each of STATS / COUNT / APPLY exists twice.  The staged form above (ada_stats, ada_rows) handles any
+// shape.  The streaming form (ada_stats_stream, ada_stream) needs rows that are a multiple of 8
+// elements and reads gradient, momentum and weights straight from global memory, with what is per row
+// or per column fetched from the scratch in L2; it has no barrier in its loops.  When every factored
+// tensor of a plan streams, COUNT and APPLY leave this kernel altogether and run as launches of
+// adakaon_apply_kernel (256-thread CTAs, four per SM, one bulk-copied flat item each), ordered by the
+// stream instead of by completion counters.
 #include <map>
 #include <vector>
 #include <mutex>
