@@ -26,18 +26,20 @@ sys.path.insert(0, os.path.join(ROOT, "k-optimizers_b200"))
 WORKLOADS = {
     # optimizer, constructor kwargs, shape list, algorithmic bytes per parameter, options
     # Lion-4bit (BASELINE config 2): g 2 + p 2+2 + m 0.5+0.5 + scales 2*4/128
+    # traffic_bpp: DRAM bytes per parameter of one step from an ncu capture of the *_sample workload
+    # (dram__bytes_read.sum + dram__bytes_write.sum over the step's kernels / 40 967 680 parameters)
     "lion4bit_unet2p6b": ("Lion", dict(lr=2e-4, betas=(0.95, 0.98), momentum_dtype="4bit", cautious=True),
-                          "unet_2p6b", 7.0625, {}),
+                          "unet_2p6b", 7.0625, {"traffic_bpp": 5.95}),
     "lion4bit_sample": ("Lion", dict(lr=2e-4, betas=(0.95, 0.98), momentum_dtype="4bit", cautious=True),
-                        "unet_sample", 7.0625, {}),
+                        "unet_sample", 7.0625, {"traffic_bpp": 5.95}),
     # the same without gradient centralization (no row means: the step is purely elementwise + 4-bit blocks)
     "lion4bit_nogc_unet2p6b": ("Lion", dict(lr=2e-4, betas=(0.95, 0.98), momentum_dtype="4bit", cautious=True,
                                             gradient_centralization=False), "unet_2p6b", 7.0625, {}),
     # Adakaon-int8 (config 3): g 2 + p 2+2 + m 1+1 + row scales, row/col stats, 1-D v; 1 % of grads x100
     "adakaon_int8_unet2p6b": ("Adakaon", dict(lr=1e-4, betas=(0.9, 0.999), momentum_dtype="int8"),
-                              "unet_2p6b", 8.015, {"outlier": True}),
+                              "unet_2p6b", 8.015, {"outlier": True, "traffic_bpp": 12.0}),
     "adakaon_int8_sample": ("Adakaon", dict(lr=1e-4, betas=(0.9, 0.999), momentum_dtype="int8"),
-                            "unet_sample", 8.015, {"outlier": True}),
+                            "unet_sample", 8.015, {"outlier": True, "traffic_bpp": 12.0}),
     # Nekaon-4bit (config 4): as Lion-4bit + stats; climb and removal ride on the same weight access
     "nekaon4bit_unet2p6b": ("Nekaon", dict(lr=1e-4, betas=(0.2, 0.999)), "unet_2p6b", 7.073, {"cosine": (1e-4, 1e-5, 50)}),
     # AdaMuon-int8 (config 5): 11.3 B-parameter DiT list; the non-NS passes move 8.006 B/param, the
@@ -374,7 +376,11 @@ def run_ours(args):
             "gradient_reduce_scatter": "inside every step" if sg is not None else "not part of the step",
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "frac_of_nominal_8TBs": achieved / 8000.0,
-                         "peak_kind": f"{peak_kind} copy bandwidth", "traffic": None,
+                         "peak_kind": f"{peak_kind} copy bandwidth",
+                         "traffic": (wopt["traffic_bpp"] * total / world) if "traffic_bpp" in wopt else None,
+                         "traffic_source": ("ncu capture of the 41 M-parameter sample of this workload, scaled by "
+                                            "parameters (a lower bound: part of the sample stays in L2 between launches)"
+                                            if "traffic_bpp" in wopt else None),
                          "bytes_per_param": bytes_per_param, "kernel": KERNEL_NAME[opt_name]},
             "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
         }
