@@ -103,3 +103,43 @@ def test_kahan_fp32_weights_have_no_shift_and_checkpoint_round_trips():
     torch.cuda.synchronize()
     assert torch.equal(pa.detach().view(torch.int16), pb.detach().view(torch.int16))
     assert torch.equal(oa.state[pa]["shift"].view(torch.int16), ob.state[pb]["shift"].view(torch.int16))
+
+
+@pytest.mark.parametrize("cls_name,okls,kw", [
+    ("Adakaon", "OracleAdakaon", dict(lr=1e-4, betas=(0.9, 0.999), momentum_dtype="int8", bf16_method="kahan")),
+    ("Adakaon", "OracleAdakaon", dict(lr=1e-4, betas=(0.9, 0.999), momentum_dtype="4bit", weight_decay=0.1, bf16_method="kahan")),
+    ("Lion", "OracleLion", dict(lr=2e-4, betas=(0.95, 0.98), momentum_dtype="4bit", bf16_method="kahan")),
+])
+def test_kahan_vs_oracle_on_streaming_shapes(cls_name, okls, kw):
+    """The compensated write on shapes whose plan takes the streaming stages and the separate COUNT / APPLY
+    launches (Adakaon) or the 4-bit fast path (Lion), against the oracle."""
+    import kaon_b200
+    from _gpu import state_np, to_bits
+    shapes = [(640, 256), (64, 32, 4, 4), (1280,), (336, 80), (3, 4096), (7,)]
+    gen = torch.Generator().manual_seed(23)
+    host = [(torch.randn(s, generator=gen) * 0.02).bfloat16() for s in shapes]
+    params = [torch.nn.Parameter(h.clone().cuda()) for h in host]
+    opt = getattr(kaon_b200, cls_name)(params, **kw)
+    orc = getattr(ko, okls)([to_bits(h) for h in host], shapes, **kw)
+    for step in range(1, 4):
+        grads = [(torch.randn(s, generator=gen) * 1e-3).bfloat16() for s in shapes]
+        for p, g in zip(params, grads):
+            p.grad = g.clone().cuda()
+        opt.step()
+        torch.cuda.synchronize()
+        opt.check_device_status()
+        orc.step([to_bits(g) for g in grads])
+        for i, p in enumerate(params):
+            st, ot = opt.state[p], orc.tensors[i]
+            got_p, got_s = to_bits(p), state_np(st, "shift")
+            if cls_name == "Lion":
+                # the only reduction upstream is the centralization mean: a handful of elements may differ
+                assert np.mean(got_p != ot.p) < 5e-3 and np.mean(got_s != ot.state["shift"]) < 5e-3, (step, i)
+            else:
+                # weights within one ulp almost everywhere; the compensated value p + shift within one ulp of p
+                a = ko.as_f32(got_p).astype(np.float64) + ko.as_f32(got_s)
+                b = ko.as_f32(ot.p).astype(np.float64) + ko.as_f32(ot.state["shift"])
+                ulp = np.maximum(np.abs(ko.as_f32(ot.p)), 1e-30) * 2.0 ** -7
+                bad = np.abs(a - b) > ulp
+                assert bad.mean() < 2e-3, (step, i, bad.mean())
+                assert ulp_diff_bf16(got_p, ot.p).max() <= 2, (step, i)
