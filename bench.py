@@ -4,14 +4,19 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
 A "step" is one optimizer step over the whole synthetic parameter list (weights N(0,0.02), grads
-N(0,1e-3), bf16).  Default workload: Lion, 4-bit momentum, betas (0.95,0.98), lr 2e-4, cautious, on the
-2.6 B-parameter UNet-shaped list.  With N > 1 the list is sharded ZeRO-1-style (each rank steps the
-tensors it owns, then one all-gather of the updated bf16 weights); total work is fixed (strong scaling).
+N(0,1e-3), bf16).  With no --workload the run measures the headline (Lion, 4-bit momentum, betas
+(0.95,0.98), lr 2e-4, cautious, on the 2.6 B-parameter UNet-shaped list) with K timed steps, and then
+the other benchmark configurations - Adakaon-int8 (K steps), Nekaon-4bit (50 steps, cosine LR) and
+AdaMuon-int8 on the 11.3 B-parameter DiT list (10 steps) - whose figures go under "workloads" in the
+same JSON line.  With N > 1 every list is sharded ZeRO-1-style (each rank steps the tensors it owns and
+publishes the updated bf16 weights to the others); total work is fixed (strong scaling).  Each workload
+is timed twice at N > 1: without any publish ("compute_only_ms") and with it ("incl_publish_ms").
 Prints ONE JSON line on rank 0.
 """
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import math
 import os
@@ -22,35 +27,46 @@ import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(ROOT, "k-optimizers_b200"))
+REF_DIR = os.path.join(ROOT, "baseline", "_ref")   # the unmodified reference package (git-ignored)
 
+LION_KW = dict(lr=2e-4, betas=(0.95, 0.98), momentum_dtype="4bit", cautious=True)
+ADAKAON_KW = dict(lr=1e-4, betas=(0.9, 0.999), momentum_dtype="int8")
+NEKAON_KW = dict(lr=1e-4, betas=(0.2, 0.999))
+ADAMUON_KW = dict(lr=1e-3, ns_steps=2, cautious=True, momentum_dtype="int8")
+# optimizer, constructor kwargs, shape list, algorithmic bytes per parameter, options.
+#  Lion-4bit (BASELINE config 2): g 2 + p 2+2 + m 0.5+0.5 + scales 2*4/128 = 7.0625
+#  Adakaon-int8 (config 3): g 2 + p 2+2 + m 1+1 + row scales, row/col stats, 1-D v; 1 % of grads x100
+#  Nekaon-4bit (config 4): as Lion-4bit + stats; climb and removal ride on the same weight access
+#  AdaMuon-int8 (config 5): the non-NS passes move 8.006 B/param; Newton-Schulz is 3.24e14 flop per step
+# traffic_bpp: DRAM bytes per parameter of one step, from the ncu capture of the *_mid workload (a list
+# of 269 M parameters, > 10x L2) summarised in profiles/; None = not captured.
 WORKLOADS = {
-    # optimizer, constructor kwargs, shape list, algorithmic bytes per parameter, options
-    # Lion-4bit (BASELINE config 2): g 2 + p 2+2 + m 0.5+0.5 + scales 2*4/128
-    # traffic_bpp: DRAM bytes per parameter of one step from an ncu capture of the *_sample workload
-    # (dram__bytes_read.sum + dram__bytes_write.sum over the step's kernels / 40 967 680 parameters)
-    "lion4bit_unet2p6b": ("Lion", dict(lr=2e-4, betas=(0.95, 0.98), momentum_dtype="4bit", cautious=True),
-                          "unet_2p6b", 7.0625, {"traffic_bpp": 5.95}),
-    "lion4bit_sample": ("Lion", dict(lr=2e-4, betas=(0.95, 0.98), momentum_dtype="4bit", cautious=True),
-                        "unet_sample", 7.0625, {"traffic_bpp": 5.95}),
-    # the same without gradient centralization (no row means: the step is purely elementwise + 4-bit blocks)
-    "lion4bit_nogc_unet2p6b": ("Lion", dict(lr=2e-4, betas=(0.95, 0.98), momentum_dtype="4bit", cautious=True,
-                                            gradient_centralization=False), "unet_2p6b", 7.0625, {}),
-    # Adakaon-int8 (config 3): g 2 + p 2+2 + m 1+1 + row scales, row/col stats, 1-D v; 1 % of grads x100
-    "adakaon_int8_unet2p6b": ("Adakaon", dict(lr=1e-4, betas=(0.9, 0.999), momentum_dtype="int8"),
-                              "unet_2p6b", 8.015, {"outlier": True, "traffic_bpp": 12.0}),
-    "adakaon_int8_sample": ("Adakaon", dict(lr=1e-4, betas=(0.9, 0.999), momentum_dtype="int8"),
-                            "unet_sample", 8.015, {"outlier": True, "traffic_bpp": 12.0}),
-    # Nekaon-4bit (config 4): as Lion-4bit + stats; climb and removal ride on the same weight access
-    "nekaon4bit_unet2p6b": ("Nekaon", dict(lr=1e-4, betas=(0.2, 0.999)), "unet_2p6b", 7.073, {"cosine": (1e-4, 1e-5, 50)}),
-    # AdaMuon-int8 (config 5): 11.3 B-parameter DiT list; the non-NS passes move 8.006 B/param, the
-    # Newton-Schulz GEMMs are 3.24e14 flop per step
-    "adamuon_int8_dit11b": ("AdaMuon", dict(lr=1e-3, ns_steps=2, cautious=True, momentum_dtype="int8"),
-                            "dit_11b", 8.006, {"one_grad_set": True}),
-    "adamuon_int8_ditblock": ("AdaMuon", dict(lr=1e-3, ns_steps=2, cautious=True, momentum_dtype="int8"),
-                              "dit_block", 8.006, {}),
-    "nekaon4bit_sample": ("Nekaon", dict(lr=1e-4, betas=(0.2, 0.999)), "unet_sample", 7.073, {"cosine": (1e-4, 1e-5, 50)}),
+    "lion4bit_unet2p6b": ("Lion", LION_KW, "unet_2p6b", 7.0625, {"traffic_bpp": None}),
+    "lion4bit_sample": ("Lion", LION_KW, "unet_sample", 7.0625, {}),
+    "lion4bit_mid": ("Lion", LION_KW, "unet_mid", 7.0625, {}),
+    "lion4bit_nogc_unet2p6b": ("Lion", dict(LION_KW, gradient_centralization=False), "unet_2p6b", 7.0625, {}),
+    "adakaon_int8_unet2p6b": ("Adakaon", ADAKAON_KW, "unet_2p6b", 8.015, {"outlier": True, "traffic_bpp": None}),
+    "adakaon_int8_sample": ("Adakaon", ADAKAON_KW, "unet_sample", 8.015, {"outlier": True}),
+    "adakaon_int8_mid": ("Adakaon", ADAKAON_KW, "unet_mid", 8.015, {"outlier": True}),
+    "nekaon4bit_unet2p6b": ("Nekaon", NEKAON_KW, "unet_2p6b", 7.073, {"cosine": (1e-4, 1e-5, 50), "steps": 50}),
+    "nekaon4bit_sample": ("Nekaon", NEKAON_KW, "unet_sample", 7.073, {"cosine": (1e-4, 1e-5, 50)}),
+    "nekaon4bit_mid": ("Nekaon", NEKAON_KW, "unet_mid", 7.073, {"cosine": (1e-4, 1e-5, 50)}),
+    "adamuon_int8_dit11b": ("AdaMuon", ADAMUON_KW, "dit_11b", 8.006, {"one_grad_set": True, "steps": 10}),
+    "adamuon_int8_ditblock": ("AdaMuon", ADAMUON_KW, "dit_block", 8.006, {}),
 }
-KERNEL_NAME = {"AdaMuon": "ns_gemm_kernel", "Lion": "lion_kernel<bf16,4bit>", "Adakaon": "adakaon_kernel<bf16,int8>", "Nekaon": "adakaon_kernel<bf16,4bit>"}
+HEADLINE = "lion4bit_unet2p6b"
+RECORD = ["adakaon_int8_unet2p6b", "nekaon4bit_unet2p6b", "adamuon_int8_dit11b"]
+KERNEL_NAME = {"AdaMuon": "ns_gemm_kernel", "Lion": "lion_kernel<bf16,4bit>", "Adakaon": "adakaon_kernel<bf16,int8>",
+               "Nekaon": "adakaon_kernel<bf16,4bit>"}
+
+
+def host_cores() -> int:
+    """Cores this process may run on (torch.distributed.run exports OMP_NUM_THREADS=1, which says
+    nothing about the host)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return os.cpu_count() or 1
 
 
 def measured_peaks():
@@ -58,8 +74,8 @@ def measured_peaks():
     if os.path.exists(path):
         with open(path) as fh:
             d = json.load(fh)
-        return float(d["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops", 1590.0)), "measured"
+    return 6650.0, 1590.0, "fallback"
 
 
 class ClockSampler:
@@ -78,6 +94,7 @@ class ClockSampler:
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
+        return self
 
     def _read(self):
         for line in self.proc.stdout:
@@ -104,74 +121,250 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def cpu_baseline(workload: str, steps: int = 2):
-    """The CPU oracle (OpenMP C port of the reference's step) on a bounded sample of the workload."""
+# ------------------------------------------------------------------------------------- CPU arms
+
+def _sample_desc(opt_name, n):
+    return f"{opt_name} on one width-1280 UNet block + one [1280,1280,3,3] conv ({n} params)"
+
+
+def cpu_port(workload: str, steps: int = 2):
+    """The CPU oracle (OpenMP C restatement of the reference's step) on a bounded sample of the workload."""
+    cores = host_cores()
+    os.environ["OMP_NUM_THREADS"] = str(cores)
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import ctypes
     import numpy as np
     import kaon_oracle as ko
     from kaon_b200 import workloads as W
-    opt_name, kw, _, _, _ = WORKLOADS[workload]
-    shapes = W.unet_sample()
+    ko.lib()
+    try:  # the variable is only read when the OpenMP runtime starts; another library may have started it
+        ctypes.CDLL("libgomp.so.1").omp_set_num_threads(cores)
+    except OSError:
+        pass
+    opt_name, kw, shape_key, _, _ = WORKLOADS[workload]
+    shapes = W.dit_block() if shape_key.startswith("dit") else W.unet_sample()
     n = W.numel(shapes)
     rng = np.random.default_rng(0)
     ps = [ko.f32_to_bf16_bits(rng.standard_normal(int(np.prod(s)), dtype=np.float32) * 0.02) for s in shapes]
     gs = [ko.f32_to_bf16_bits(rng.standard_normal(int(np.prod(s)), dtype=np.float32) * 1e-3) for s in shapes]
     cls = {"Lion": ko.OracleLion, "Adakaon": ko.OracleAdakaon, "Nekaon": ko.OracleNekaon, "AdaMuon": ko.OracleAdaMuon}[opt_name]
     opt = cls(ps, shapes, **kw)
-    opt.step(gs)  # warm-up: allocates state
+    if opt_name == "AdaMuon":
+        # the O(n^3) CPU Newton-Schulz of 3072-wide matrices is out of reach of a bounded sample: time the
+        # chain around it with the orthogonalised matrices supplied
+        ov = [None if len(s) < 2 else np.zeros(int(np.prod(s)), np.float32) + 0.01 for s in shapes]
+        step = lambda: opt.step(gs, ns_override=ov)  # noqa: E731
+    else:
+        step = lambda: opt.step(gs)  # noqa: E731
+    step()  # warm-up: allocates state
     times = []
     for _ in range(steps):
         t0 = time.perf_counter()
-        opt.step(gs)
+        step()
         times.append(time.perf_counter() - t0)
     times.sort()
     dt = times[len(times) // 2]
-    cores = int(os.environ.get("OMP_NUM_THREADS", os.cpu_count() or 1))
+    sample = (f"{opt_name} chain without Newton-Schulz on one width-3072 DiT block ({n} params)"
+              if opt_name == "AdaMuon" else _sample_desc(opt_name, n))
     return {"value": n / dt, "unit": "params/s", "cores": cores, "kind": "port",
-            "sample": f"{opt_name} on one width-1280 UNet block + one [1280,1280,3,3] conv "
-                      f"({n} params), median of {steps} steps after 1 warm-up, {dt * 1e3:.0f} ms/step"}, dt, n
+            "sample": f"{sample}, median of {steps} steps after 1 warm-up, {dt * 1e3:.0f} ms/step"}, dt, n
+
+
+def cpu_reference(workload: str, steps: int = 3, warmup: int = 1):
+    """The reference package itself (its foreach path, CPU tensors, all host threads) on the same bounded
+    sample.  Returns None when the package is not installed beside the benchmark."""
+    if not os.path.isdir(os.path.join(REF_DIR, "kaon")):
+        return None
+    sys.path.insert(0, REF_DIR)
+    import torch
+    import kaon  # the reference
+    from kaon_b200 import workloads as W
+    cores = host_cores()
+    torch.set_num_threads(cores)
+    opt_name, kw, shape_key, _, wopt = WORKLOADS[workload]
+    if opt_name == "AdaMuon":
+        return None  # a CPU Newton-Schulz of 3072-wide matrices does not fit a bounded sample
+    shapes = W.unet_sample()
+    n = W.numel(shapes)
+    gen = torch.Generator().manual_seed(0)
+    params = [torch.nn.Parameter((torch.randn(s, generator=gen) * 0.02).bfloat16()) for s in shapes]
+    grads = [(torch.randn(s, generator=gen) * 1e-3).bfloat16() for s in shapes]
+    opt = getattr(kaon, opt_name)(params, **kw)
+    times = []
+    for k in range(warmup + steps):
+        for p, g in zip(params, grads):
+            p.grad = g.clone()  # gradient centralization rewrites p.grad in place
+        t0 = time.perf_counter()
+        opt.step()
+        if k >= warmup:
+            times.append(time.perf_counter() - t0)
+    times.sort()
+    dt = times[len(times) // 2]
+    return {"value": n / dt, "unit": "params/s", "cores": cores, "kind": "reference",
+            "sample": f"kaon {kaon.__version__} {_sample_desc(opt_name, n)}, foreach=True, CPU tensors, "
+                      f"median of {steps} steps after {warmup} warm-up, {dt * 1e3:.0f} ms/step"}, dt, n
+
+
+def cpu_baseline(workload: str, steps: int = 3):
+    """Reference package when present (kind "reference"), with the C port's figure beside it."""
+    port, dt_p, n = cpu_port(workload, steps=max(2, steps))
+    ref = cpu_reference(workload, steps=steps)
+    if ref is None:
+        return port, dt_p, n
+    base, dt, n = ref
+    base["port"] = {k: port[k] for k in ("value", "unit", "cores", "sample")}
+    return base, dt, n
 
 
 def run_reference(args):
-    """--impl reference: the reference's CPU path for this workload, as the OpenMP C port in oracle/
-    (the reference is Python and does not travel to the GPU box), all host threads, bounded sample."""
+    """--impl reference: the reference's CPU path for the workload on the host cores (the reference
+    package itself when it sits in baseline/_ref, else the C port in oracle/), bounded sample."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    base, dt, n = cpu_baseline(args.workload, steps=max(1, args.steps))
+    workload = args.workload or HEADLINE
+    base, dt, n = cpu_baseline(workload, steps=max(1, min(args.steps, 5)))
     line = {"impl": "reference", "metric": "optimizer_step_params_per_sec", "value": base["value"],
             "unit": "params/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": max(1, args.warmup),
             "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
-            "config": {"workload": args.workload, "sample": base["sample"]},
+            "config": {"workload": workload, "sample": base["sample"]},
             "cpu_baseline": base,
             "e2e": {"value": base["value"], "unit": "params/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
 
-def run_ours(args):
+# ------------------------------------------------------------------------------------- GPU bar
+
+def run_gpu_bar(args):
+    """The reference's own CUDA paths on this GPU, timed with its own method (median of per-step wall
+    times with a synchronize on both sides, reference benchmarks/fused/bench_fused.py:73-89): eager foreach
+    (fused=False), optionally its Triton path (fused=True, --gpu-bar-fused), and AdaMuon's cuBLAS
+    Newton-Schulz chain (src/kaon/adamuon.py:97-118).  One JSON object on stdout."""
+    sys.path.insert(0, REF_DIR)
     import torch
-    import torch.distributed as dist
+    import kaon
+    from kaon.adamuon import zeropower_via_newtonschulz5 as ref_ns
+    from kaon_b200 import workloads as W
+    dev = torch.device("cuda", 0)
+    out = {"method": "median wall ms per step, synchronize on both sides (the reference's bench_fused.step_ms)",
+           "list": "unet_mid (8 width-1280 blocks + 4 [1280,1280,3,3] convs, 269 M params)"}
+    shapes = W.unet_mid()
+    n = W.numel(shapes)
+    gen = torch.Generator(device=dev).manual_seed(0)
+
+    def timed(fn, reps, warmup):
+        for _ in range(warmup):
+            fn()
+        ts = []
+        for _ in range(reps):
+            torch.cuda.synchronize()
+            t0 = time.time()
+            fn()
+            torch.cuda.synchronize()
+            ts.append((time.time() - t0) * 1e3)
+        ts.sort()
+        return ts[len(ts) // 2]
+
+    cases = [("lion4bit", "Lion", LION_KW, [False]),
+             ("adakaon_int8", "Adakaon", ADAKAON_KW, [False] + ([True] if args.gpu_bar_fused else [])),
+             ("nekaon4bit", "Nekaon", NEKAON_KW, [False] + ([True] if args.gpu_bar_fused else []))]
+    for key, cls, kw, fused_opts in cases:
+        for fused in fused_opts:
+            tag = f"{key}_{'triton' if fused else 'eager'}"
+            try:
+                params = [torch.nn.Parameter((torch.randn(s, generator=gen, device=dev) * 0.02).bfloat16()) for s in shapes]
+                grads = [(torch.randn(s, generator=gen, device=dev) * 1e-3).bfloat16() for s in shapes]
+                opt = getattr(kaon, cls)(params, **kw, **({"fused": True} if fused else {}))
+
+                def one():
+                    for p, g in zip(params, grads):
+                        p.grad = g  # centralization rewrites it in place: timing only
+                    opt.step()
+                ms = timed(one, 5, 2)
+                out[tag] = {"ms_per_step": ms, "params_per_s": n / (ms * 1e-3)}
+                del opt, params, grads
+            except Exception as e:  # noqa: BLE001 - a failing reference path is a finding, not a crash
+                out[tag] = {"error": f"{type(e).__name__}: {e}"[:300]}
+            gc.collect()
+            torch.cuda.empty_cache()
+    ns = {}
+    tot_ms = tot_flop = 0.0
+    for (R, Cc, count) in [(9216, 3072, 100), (3072, 3072, 100), (12288, 3072, 100), (3072, 12288, 100)]:
+        x = torch.randn(R, Cc, device=dev, dtype=torch.bfloat16)
+        ms = timed(lambda: ref_ns(x, 2), 5, 2)
+        r_, k_ = min(R, Cc), max(R, Cc)
+        flop = 2 * (4.0 * r_ * r_ * k_ + 2.0 * r_ ** 3)
+        ns[f"{R}x{Cc}"] = {"ms": ms, "tflops": flop / (ms * 1e-3) / 1e12}
+        tot_ms += ms * count
+        tot_flop += flop * count
+    ns["dit_list_total"] = {"ms_per_step": tot_ms, "tflops": tot_flop / (tot_ms * 1e-3) / 1e12}
+    out["newton_schulz_cublas"] = ns
+    print(json.dumps(out), flush=True)
+
+
+def gpu_bar_subprocess(timeout=420):
+    if not os.path.isdir(os.path.join(REF_DIR, "kaon")):
+        return {"unavailable": "the reference package is not installed in baseline/_ref"}
+    env = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK")}
+    try:
+        r = subprocess.run([sys.executable, os.path.abspath(__file__), "--gpu-bar"], capture_output=True, text=True,
+                           timeout=timeout, env=env)
+        lines = [ln for ln in r.stdout.splitlines() if ln.startswith("{")]
+        return json.loads(lines[-1]) if lines else {"error": (r.stderr or "no output")[-300:]}
+    except (subprocess.TimeoutExpired, ValueError, OSError) as e:
+        return {"error": f"{type(e).__name__}: {e}"[:300]}
+
+
+# ------------------------------------------------------------------------------------- our arm
+
+class Ctx:
+    def __init__(self, args):
+        import torch
+        import torch.distributed as dist
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        if args.gpus != self.world:
+            raise SystemExit(f"--gpus {args.gpus} needs {args.gpus} ranks (torch.distributed.run); WORLD_SIZE={self.world}")
+        torch.cuda.set_device(self.local_rank)
+        self.dev = torch.device("cuda", self.local_rank)
+        if self.world > 1:
+            dist.init_process_group("nccl", device_id=self.dev)
+        self.args = args
+
+    def fence(self):
+        import torch
+        import torch.distributed as dist
+        torch.cuda.synchronize()
+        if self.world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def reduce(self, vals, op="max"):
+        import torch
+        import torch.distributed as dist
+        t = torch.tensor(vals, device=self.dev, dtype=torch.float64)
+        if self.world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX if op == "max" else dist.ReduceOp.SUM)
+        return t.tolist()
+
+
+def measure(ctx: Ctx, workload: str, steps: int, warmup: int, e2e_steps: int = 0):
+    """One workload at ctx.world GPUs: device-timed steps (max over ranks), clocks, roofline."""
+    import torch
     import kaon_b200
     from kaon_b200 import workloads as W
     from kaon_b200.zero1 import ShardedWeights
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.gpus != world:
-        raise SystemExit(f"--gpus {args.gpus} needs {args.gpus} ranks (torch.distributed.run); WORLD_SIZE={world}")
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    opt_name, kw, shape_key, bytes_per_param, wopt = WORKLOADS[args.workload]
+    args, world, rank, dev = ctx.args, ctx.world, ctx.rank, ctx.dev
+    opt_name, kw, shape_key, bytes_per_param, wopt = WORKLOADS[workload]
     shapes = W.WORKLOADS[shape_key]()
     total = W.numel(shapes)
+    warmup = max(3, warmup)
     fused_publish = world > 1 and args.publish == "fused"
     sw = ShardedWeights(shapes, world, rank, torch.bfloat16, dev, symmetric=fused_publish)
     owned = sw.part.owned(rank)
-    owned_elems = sum(sw.views[i].numel() for i in owned)
     gen = torch.Generator(device=dev).manual_seed(1234 + rank)
 
     def fill_normal(dst, std, outlier=False, chunk=1 << 28):
@@ -187,7 +380,7 @@ def run_ours(args):
     sw.all_gather()
     # two gradient sets, alternated per step (a real loop reallocates grads: set_to_none=True)
     gsets = []
-    for k in range(1 if wopt.get("one_grad_set") else 2):
+    for _ in range(1 if wopt.get("one_grad_set") else 2):
         flat_g = torch.empty(sw.part.shard_len, dtype=torch.bfloat16, device=dev)
         fill_normal(flat_g, 1e-3, outlier=bool(wopt.get("outlier")))
         gsets.append((flat_g, [flat_g[sw.part.offset[i]:sw.part.offset[i] + sw.views[i].numel()].view(shapes[i]) for i in owned]))
@@ -198,16 +391,17 @@ def run_ours(args):
         params.append(p)
     opt = getattr(kaon_b200, opt_name)(params, **kw)
     opt.sr_seed = 0
-    sw.attach(opt)  # fused publish: the step kernels store the weights into every rank's copy
     sg = None
     if args.reduce_scatter and world > 1:
         from kaon_b200.zero1 import ShardedGrads
         sg = ShardedGrads(sw, shapes)              # full-list local gradients + the owner's reduced shard
         fill_normal(sg.flat, 1e-3, outlier=bool(wopt.get("outlier")))
-
     cos = wopt.get("cosine")
+    state = {"k": 0}
 
-    def one_step(k, ev=None):
+    def one_step(ev=None, publish=True):
+        k = state["k"]
+        state["k"] += 1
         gv = sg.owned if sg is not None else gsets[k % len(gsets)][1]
         if cos:
             for grp in opt.param_groups:
@@ -221,57 +415,51 @@ def run_ours(args):
         opt.step()
         if ev:
             ev[1].record()
-        sw.publish()
+        if publish:
+            sw.publish()
         if ev:
             ev[2].record()
 
-    def fence():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
+    def timed(nsteps, publish):
+        for _ in range(warmup):
+            one_step(publish=publish)
+        ctx.fence()
+        opt.check_device_status()
+        launches0 = opt.stats()["kernel_launches"]
+        sampler = ClockSampler(ctx.local_rank).start() if rank == 0 else None
+        evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(nsteps)]
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ctx.fence()
+        t0.record()
+        for k in range(nsteps):
+            one_step(evs[k], publish=publish)
+        t1.record()
+        ctx.fence()
+        clocks = sampler.stop() if sampler else None
+        opt.check_device_status()
+        launches = opt.stats()["kernel_launches"] - launches0
+        kern = sum(e[0].elapsed_time(e[1]) for e in evs) / nsteps
+        pub = sum(e[1].elapsed_time(e[2]) for e in evs) / nsteps
+        tot_ms, kern, pub = ctx.reduce([t0.elapsed_time(t1), kern, pub])
+        (launches,) = ctx.reduce([float(launches)], op="sum")
+        return tot_ms / nsteps, kern, pub, int(launches), clocks
 
-    for k in range(max(3, args.warmup)):
-        one_step(k)
-    fence()
-    opt.check_device_status()
-    launches0 = opt.stats()["kernel_launches"]
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
-    t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    fence()
-    t_begin.record()
-    for k in range(args.steps):
-        one_step(k, evs[k])
-    t_end.record()
-    fence()
-    clocks = sampler.stop() if rank == 0 else None
-    opt.check_device_status()
-    launches = opt.stats()["kernel_launches"] - launches0
-    ms_total = t_begin.elapsed_time(t_end)
-    kern_ms = sum(e[0].elapsed_time(e[1]) for e in evs) / args.steps
-    gather_ms = sum(e[1].elapsed_time(e[2]) for e in evs) / args.steps
-    stats = torch.tensor([ms_total, kern_ms, gather_ms, float(launches)], device=dev, dtype=torch.float64)
+    compute_only_ms = None
     if world > 1:
-        mx = stats.clone()
-        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
-        sm = stats.clone()
-        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
-        ms_total, kern_ms, gather_ms = mx[0].item(), mx[1].item(), mx[2].item()
-        launches = int(sm[3].item())
-    ms_per_step = ms_total / args.steps
+        # the step without any publish (mirrors detached, no collective): the "compute only" curve
+        compute_only_ms, _, _, _, _ = timed(min(steps, 10), publish=False)
+        sw.attach(opt)  # fused publish: the step kernels store the weights into every rank's copy
+    ms_per_step, kern_ms, pub_ms, launches, clocks = timed(steps, publish=True)
+    if compute_only_ms is None:
+        compute_only_ms = ms_per_step
 
-    # ---- end to end: pinned host grads in, step, (all-gather,) owned weights out, every step ----
+    # ---- end to end: pinned host grads in, step, (publish,) owned weights out, every step ----
     e2e = None
-    if not args.no_e2e:
+    if e2e_steps > 0:
         host_g = torch.empty(sw.part.shard_len, dtype=torch.bfloat16, pin_memory=True)
         host_w = torch.empty(sw.part.shard_len, dtype=torch.bfloat16, pin_memory=True)
         host_g.copy_(gsets[0][0])
         torch.cuda.synchronize()
-        esteps = max(1, min(args.steps, args.e2e_steps))
-
         # Three streams, as a training loop with a host-side gradient source would run it: the copy of
         # step k+1's gradients to the device (s_in) and the read-back of step k's weights (s_out) travel in
         # opposite directions over PCIe and overlap; the step itself waits for its gradients and for the
@@ -312,29 +500,29 @@ def run_ours(args):
             cur_s.wait_event(ev_out)
 
         e2e_run(1)
-        fence()
+        ctx.fence()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        e2e_run(esteps)
+        e2e_run(e2e_steps)
         b.record()
-        fence()
-        ems = torch.tensor([a.elapsed_time(b)], device=dev, dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(ems, op=dist.ReduceOp.MAX)
-        ems = ems.item() / esteps
+        ctx.fence()
+        (ems,) = ctx.reduce([a.elapsed_time(b)])
+        ems /= e2e_steps
         nbytes = sw.part.shard_len * 2 * world
-        e2e = {"value": total / (ems * 1e-3), "unit": "params/s", "ms_per_step": ems, "steps": esteps,
+        e2e = {"value": total / (ems * 1e-3), "unit": "params/s", "ms_per_step": ems, "steps": e2e_steps,
                "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes,
                "pipeline": "gradients of step k+1 go up while the weights of step k come down (3 streams); "
                            "the first upload and the last download are inside the timed region"}
+        del host_g, host_w
 
     ns_info = None
     if opt_name == "AdaMuon":
         # Newton-Schulz alone, per distinct matrix shape of this rank's tensors: CUDA events around the
-        # GEMM chain (2 + 3*steps launches) of kaon_newton_schulz
+        # GEMM chain of kaon_newton_schulz
         from kaon_b200.adamuon import zeropower_via_newtonschulz5 as ns
         steps_ns = kw.get("ns_steps", 2)
-        shapes2d = sorted({(s[0], W.numel([s]) // s[0]) for i, s in enumerate(shapes) if len(s) >= 2 and i in set(owned)})
+        oset = set(owned)
+        shapes2d = sorted({(s[0], W.numel([s]) // s[0]) for i, s in enumerate(shapes) if len(s) >= 2 and i in oset})
         counts = {sh: sum(1 for i in owned if len(shapes[i]) >= 2 and (shapes[i][0], W.numel([shapes[i]]) // shapes[i][0]) == sh) for sh in shapes2d}
         ns_info, tot_flop, tot_ms = {}, 0.0, 0.0
         for (R, Cc) in shapes2d:
@@ -355,60 +543,113 @@ def run_ours(args):
             tot_ms += ms * counts[(R, Cc)]
         ns_info["total"] = {"flop_per_step": tot_flop, "ms_per_step": tot_ms, "tflops": tot_flop / (tot_ms * 1e-3) / 1e12}
 
+    res = None
     if rank == 0:
-        peak, peak_kind = measured_peaks()
-        # the dominant (only) kernel of a step: algorithmic bytes of this rank's tensors per launch
-        alg_bytes = bytes_per_param * (total / world)
+        peak, tpeak, peak_kind = measured_peaks()
+        alg_bytes = bytes_per_param * (total / world)   # this rank's tensors, one step
         achieved = alg_bytes / (kern_ms * 1e-3) / 1e9
-        line = {
-            "metric": "optimizer_step_params_per_sec", "value": total / (ms_per_step * 1e-3), "unit": "params/s",
-            "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic",
-            "config": {"workload": args.workload, "optimizer": opt_name, "params": total, "tensors": len(shapes),
-                       "param_dtype": "bf16", "momentum_dtype": kw.get("momentum_dtype"),
+        tb = wopt.get("traffic_bpp")
+        res = {
+            "value": total / (ms_per_step * 1e-3), "unit": "params/s", "ms_per_step": ms_per_step,
+            "step_kernel_ms": kern_ms, "publish_ms": pub_ms, "compute_only_ms": compute_only_ms,
+            "incl_publish_ms": ms_per_step, "steps": steps, "warmup": warmup, "gpu_launches": launches,
+            "clocks": clocks,
+            "config": {"workload": workload, "optimizer": opt_name, "params": total, "tensors": len(shapes),
+                       "param_dtype": "bf16", "momentum_dtype": kw.get("momentum_dtype", "4bit" if opt_name == "Nekaon" else None),
                        "sharding": "zero1" if world > 1 else "none",
                        "publish": ("none" if world == 1 else
                                    "peer stores fused into the step kernel + barrier" if fused_publish else
                                    "nccl all_gather_into_tensor after the step"),
-                       "l2": "inputs (18 GB per step) larger than L2; no flush needed"},
-            "step_kernel_ms": kern_ms, "publish_ms": gather_ms,
+                       "lr_schedule": "cosine 1e-4 -> 1e-5 over 50 steps" if cos else "constant",
+                       "l2": f"inputs ({alg_bytes / 1e9:.1f} GB per step per GPU) larger than L2; no flush needed"},
             "gradient_reduce_scatter": "inside every step" if sg is not None else "not part of the step",
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "frac_of_nominal_8TBs": achieved / 8000.0,
                          "peak_kind": f"{peak_kind} copy bandwidth",
-                         "traffic": (wopt["traffic_bpp"] * total / world) if "traffic_bpp" in wopt else None,
-                         "traffic_source": ("ncu capture of the 41 M-parameter sample of this workload, scaled by "
-                                            "parameters (a lower bound: part of the sample stays in L2 between launches)"
-                                            if "traffic_bpp" in wopt else None),
+                         "traffic": (tb * total / world) if tb else None,
+                         "traffic_source": ("ncu capture of one launch of the 269 M-parameter list of the same "
+                                            "shapes (profiles/), scaled by parameters" if tb else
+                                            "not captured: the algorithmic bytes are the figure"),
                          "bytes_per_param": bytes_per_param, "kernel": KERNEL_NAME[opt_name]},
-            "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
+            "e2e": e2e,
         }
         if fused_publish:
-            # the step kernel also pushes this rank's updated weights to the other ranks: its floor is
-            # the slower of the HBM pass and the NVLink egress (measured peer-copy bandwidth 770 GB/s)
+            # the step kernel also pushes this rank's updated weights to the other ranks: its floor is the
+            # slower of the HBM pass and the NVLink traffic (measured peer-copy bandwidth 770 GB/s)
             out_bytes = 2.0 * (total / world) * (world - 1)
             t_hbm, t_link = alg_bytes / (peak * 1e9), out_bytes / 770e9
-            line["nvlink"] = {"egress_bytes_per_rank": out_bytes, "achieved": out_bytes / (kern_ms * 1e-3) / 1e9,
-                              "peak": 770.0, "unit": "GB/s", "floor_ms": max(t_hbm, t_link) * 1e3,
-                              "frac_of_floor": max(t_hbm, t_link) * 1e3 / kern_ms}
+            res["nvlink"] = {"ingress_bytes_per_rank": out_bytes, "achieved": out_bytes / (kern_ms * 1e-3) / 1e9,
+                             "peak": 770.0, "unit": "GB/s", "floor_ms": max(t_hbm, t_link) * 1e3,
+                             "frac_of_floor": max(t_hbm, t_link) * 1e3 / kern_ms}
         if ns_info is not None:
-            tpeak = 1678.7
+            rest_ms = max(kern_ms - ns_info["total"]["ms_per_step"], 1e-6)
+            res["hbm_passes"] = dict(res["roofline"], achieved=alg_bytes / (rest_ms * 1e-3) / 1e9,
+                                     frac=alg_bytes / (rest_ms * 1e-3) / 1e9 / peak, ms=rest_ms,
+                                     note="everything of the step that is not a Newton-Schulz GEMM: step time minus "
+                                          "the GEMM chains timed alone")
+            res["hbm_passes"].pop("frac_of_nominal_8TBs", None)
+            res["roofline"] = {"bound": "tensor", "achieved": ns_info["total"]["tflops"], "peak": tpeak,
+                               "unit": "TFLOP/s", "frac": ns_info["total"]["tflops"] / tpeak, "traffic": None,
+                               "peak_kind": f"{peak_kind} cuBLAS bf16 burst", "kernel": "ns_gemm_kernel",
+                               "note": "Newton-Schulz GEMM chain timed alone per shape (CUDA events); hbm_passes has the rest of the step"}
+            res["newton_schulz"] = ns_info
+    return res
+
+
+def measure_and_free(*a, **k):
+    """measure(), then release what it held (its locals die with its frame) before the next workload."""
+    import torch
+    res = measure(*a, **k)
+    gc.collect()
+    torch.cuda.empty_cache()
+    return res
+
+
+def run_ours(args):
+    import torch.distributed as dist
+    ctx = Ctx(args)
+    single = args.workload is not None
+    head_name = args.workload or HEADLINE
+    wsteps = WORKLOADS[head_name][4].get("steps") if single and args.steps_from_config else None
+    head = measure_and_free(ctx, head_name, wsteps or args.steps, args.warmup,
+                   e2e_steps=0 if args.no_e2e else max(1, min(args.steps, args.e2e_steps)))
+    extra = {}
+    if not single and not args.headline_only:
+        for name in RECORD:
+            steps = WORKLOADS[name][4].get("steps", args.steps)
             try:
-                with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
-                    tpeak = float(json.load(fh)["bf16_tflops"])
-            except (OSError, KeyError, ValueError):
-                pass
-            line["hbm_passes"] = line["roofline"]
-            line["roofline"] = {"bound": "tensor", "achieved": ns_info["total"]["tflops"], "peak": tpeak,
-                                "unit": "TFLOP/s", "frac": ns_info["total"]["tflops"] / tpeak, "traffic": None,
-                                "peak_kind": "measured cuBLAS bf16 burst", "kernel": "ns_gemm_kernel",
-                                "note": "Newton-Schulz GEMM chain timed alone per shape (CUDA events); hbm_passes has the whole-step algorithmic-bytes view"}
-            line["newton_schulz"] = ns_info
-        if world == 1 and not args.no_cpu:
-            line["cpu_baseline"], _, _ = cpu_baseline(args.workload)
+                r = measure_and_free(ctx, name, steps, args.warmup)
+            except Exception as e:  # noqa: BLE001 - the headline line must still print
+                r = {"error": f"{type(e).__name__}: {e}"[:400]}
+                if ctx.world > 1:
+                    raise
+            if ctx.rank == 0:
+                extra[name] = r
+    if ctx.rank == 0:
+        line = {"metric": "optimizer_step_params_per_sec", "value": head["value"], "unit": "params/s",
+                "n_gpus": ctx.world, "steps": head["steps"], "warmup": head["warmup"],
+                "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "f32", "data": "synthetic"}
+        for k in ("config", "step_kernel_ms", "publish_ms", "compute_only_ms", "incl_publish_ms",
+                  "gradient_reduce_scatter", "roofline", "e2e", "gpu_launches", "clocks", "nvlink", "hbm_passes",
+                  "newton_schulz"):
+            if k in head:
+                line[k] = head[k]
+        line["config"]["storage_dtype"] = "bf16 weights and gradients, arithmetic in fp32"
+        if extra:
+            line["workloads"] = extra
+            line["gpu_launches"] = head["gpu_launches"] + sum(int(r.get("gpu_launches", 0)) for r in extra.values())
+            line["gpu_launches_headline"] = head["gpu_launches"]
+        if ctx.world == 1 and not args.no_cpu:
+            line["cpu_baseline"], _, _ = cpu_baseline(head_name)
+            if extra:
+                for name in RECORD:
+                    if name in extra and "error" not in extra[name]:
+                        extra[name]["cpu_baseline"], _, _ = cpu_baseline(name)
+        if ctx.world == 1 and not single and not args.no_gpu_bar:
+            line["gpu_bar"] = gpu_bar_subprocess()
         print(json.dumps(line), flush=True)
-    if world > 1:
+    if ctx.world > 1:
         dist.destroy_process_group()
 
 
@@ -418,17 +659,26 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="lion4bit_unet2p6b", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
+                    help="measure only this workload (default: the headline, then the other configurations)")
+    ap.add_argument("--headline-only", action="store_true")
+    ap.add_argument("--steps-from-config", action="store_true",
+                    help="with --workload: use the step count the configuration names (Nekaon 50, AdaMuon 10)")
     ap.add_argument("--e2e-steps", type=int, default=6)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-gpu-bar", action="store_true")
+    ap.add_argument("--gpu-bar", action="store_true", help="time the reference's own CUDA paths (needs baseline/_ref)")
+    ap.add_argument("--gpu-bar-fused", action="store_true", help="with --gpu-bar: also the reference's Triton path")
     ap.add_argument("--reduce-scatter", action="store_true",
                     help="N>1: put the gradient reduce-scatter (NCCL, bf16 average) inside every step; the step "
                          "kernels then read the collective's output buffer")
     ap.add_argument("--publish", default="fused", choices=["fused", "allgather"],
                     help="N>1: how the owned weights reach the other ranks")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.gpu_bar:
+        run_gpu_bar(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

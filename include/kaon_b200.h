@@ -118,6 +118,14 @@ int kaon_plan_set_grads(kaon_plan* plan, const void* const* grads, int n, void* 
 int kaon_plan_destroy(kaon_plan* plan);
 /* Synchronise `stream` and read the plan's device status word: 0, or KAON_E_DEVICE with a message. */
 int kaon_plan_status(kaon_plan* plan, void* stream);
+/* Test hook (no reference counterpart): makes the bounded waits of a Lion plan observable without
+ * faulting or hanging anything.  Raises tensor `tensor`'s expected count of finished MAIN work items by
+ * one - a count the work list can never reach - and sets the number of polls a completion-counter wait
+ * makes before it gives up.  The next kaon_lion_step then returns normally with that tensor's weights
+ * not updated, kaon_plan_status reports KAON_E_DEVICE, and the plan stays drained (every later step is a
+ * no-op) until it is destroyed.  Only the completion-counter polls are shortened; waits on copies in
+ * flight keep their limit. */
+int kaon_plan_debug_stall(kaon_plan* plan, int tensor, uint32_t spin_limit);
 /* Bytes of device memory the plan owns (tables + scratch), and how many kernels it has launched. */
 int64_t kaon_plan_device_bytes(const kaon_plan* plan);
 int64_t kaon_plan_launch_count(const kaon_plan* plan);
@@ -156,10 +164,17 @@ int kaon_lion_step(kaon_plan* plan, const kaon_lion_hparams* hp, uint64_t seed, 
  * block for <= 128 elements) and m_scale must be set; numel <= KAON_NOALLOC_MAX_NUMEL, else
  * KAON_E_UNSUPPORTED.  Calls no cudaMalloc/cudaFree.  The first call on a device resolves the array's
  * address and configures the kernel: make it before any stream capture.  All calls on a device share
- * the array: calls whose kernels overlap on the GPU race; calls ordered on one stream do not. */
+ * the array: calls whose kernels overlap on the GPU race; calls ordered on one stream do not.
+ * bf16_method is KAON_W_NONE or KAON_W_SR (the Kahan write needs a plan: KAON_E_UNSUPPORTED).  Two host
+ * threads may make the first call on a device at the same time (the set-up is behind a mutex). */
 #define KAON_NOALLOC_MAX_NUMEL (1 << 22)
 int kaon_lion_step_noalloc(const kaon_tensor_desc* tensor, int param_dtype, const kaon_lion_hparams* hp,
                            uint64_t seed, uint32_t step, void* stream);
+/* Device status of the kaon_lion_step_noalloc calls made so far on the current device (no counterpart
+ * in the reference; allocates nothing).  Synchronises `stream`, returns KAON_OK, or KAON_E_DEVICE if a
+ * bounded wait ran out inside one of those calls (that call stopped early and left its tensor partly
+ * stepped; later calls ran normally), and clears the record. */
+int kaon_lion_noalloc_status(void* stream);
 
 /* One Adakaon step.  Replaces Adakaon._step_impl / _factored_bucket / _nonfactored_bucket /
  * _step_one_param (src/kaon/adakaon.py:339-383, 840-1014), update_factored_state and

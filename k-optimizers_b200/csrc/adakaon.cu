@@ -2037,6 +2037,7 @@ extern "C" int kaon_adakaon_step(kaon_plan* pl, const kaon_adakaon_hparams* h, u
                                  uint32_t step, void* stream) {
   if (!pl || !h) return fail(KAON_E_INVALID, "kaon_adakaon_step: null argument");
   if (pl->optimizer != KAON_OPT_ADAKAON) return fail(KAON_E_INVALID, "plan was not built for Adakaon");
+  if (int rc = check_device(pl)) return rc;
   if (h->bf16_method < KAON_W_NONE || h->bf16_method > KAON_W_KAHAN) return fail(KAON_E_UNSUPPORTED, "bf16_method %d", h->bf16_method);
   if (int rc = check_kahan(pl, h->bf16_method)) return rc;
   if (!(h->clip_threshold > 0.0)) return fail(KAON_E_INVALID, "clip_threshold must be > 0");
@@ -2083,6 +2084,7 @@ extern "C" int kaon_adakaon_step(kaon_plan* pl, const kaon_adakaon_hparams* h, u
 extern "C" int kaon_msam_apply(kaon_plan* pl, double alpha, double bound, uint32_t tag, uint64_t seed,
                                uint32_t step, void* stream) {
   if (!pl) return fail(KAON_E_INVALID, "kaon_msam_apply: null plan");
+  if (int rc = check_device(pl)) return rc;
   if (pl->momentum_kind == KAON_M_NONE || pl->n_tasks_axpy == 0) return KAON_OK;  // nothing carries a momentum
   AxpyKernel k = pl->param_dtype == KAON_DT_BF16 ? pick_axpy_pt<__nv_bfloat16>(pl->momentum_kind)
                                                  : pick_axpy_pt<float>(pl->momentum_kind);
@@ -2090,7 +2092,7 @@ extern "C" int kaon_msam_apply(kaon_plan* pl, double alpha, double bound, uint32
   PlanView v = pl->view;
   v.tasks = pl->d_tasks_axpy; v.n_tasks = pl->n_tasks_axpy;
   SrStream st{Philox{(uint32_t)seed, (uint32_t)(seed >> 32)}, step, tag};
-  const int grid = std::min(pl->n_tasks_axpy, 148 * 8);
+  const int grid = std::min(pl->n_tasks_axpy, pl->sm_count * 8);
   k<<<grid, 256, 0, (cudaStream_t)stream>>>(v, (float)alpha, (float)bound, st);
   KAON_CUDA(cudaGetLastError());
   pl->launches += 1;

@@ -206,6 +206,7 @@ extern "C" int kaon_adamuon_step(kaon_plan* pl, const kaon_adamuon_hparams* h, v
                                  int64_t workspace_bytes, uint64_t seed, uint32_t step, void* stream) {
   if (!pl || !h) return fail(KAON_E_INVALID, "kaon_adamuon_step: null argument");
   if (pl->optimizer != KAON_OPT_ADAMUON) return fail(KAON_E_INVALID, "plan was not built for AdaMuon");
+  if (int rc = check_device(pl)) return rc;
   if (h->bf16_method < KAON_W_NONE || h->bf16_method > KAON_W_KAHAN) return fail(KAON_E_UNSUPPORTED, "bf16_method %d", h->bf16_method);
   if (int rc = check_kahan(pl, h->bf16_method)) return rc;
   if (h->gradient_centralization) return fail(KAON_E_UNSUPPORTED, "AdaMuon with gradient_centralization=True is not built (its default is off)");
@@ -261,7 +262,7 @@ extern "C" int kaon_adamuon_step(kaon_plan* pl, const kaon_adamuon_hparams* h, v
     const DevTensor& t = pl->h_tensors[i];
     if (t.rows <= 0 || t.numel == 0 || pl->h_grads[i] == nullptr) continue;
     const int t0 = pl->ema_begin[i], t1 = pl->ema_begin[i + 1];
-    const int grid = std::min(t1 - t0, 148 * 8);
+    const int grid = std::min(t1 - t0, pl->sm_count * 8);
     ek<<<grid, ET, 0, s>>>(v, pl->d_tasks_ema, t0, t1, w1, w1 - 1.0f, w1 < 0.5f, x0);
     KAON_CUDA(cudaGetLastError());
     pl->launches += 1;

@@ -153,13 +153,14 @@ __device__ __forceinline__ float group_max(float v, int width) {
 #define KAON_SPIN_LIMIT (1u << 22)
 
 __device__ __forceinline__ bool wait_counter(const unsigned int* flag, unsigned int target,
-                                             unsigned int* status, unsigned int code) {
+                                             unsigned int* status, unsigned int code,
+                                             unsigned int limit = KAON_SPIN_LIMIT) {
   unsigned int spins = 0;
   while (true) {
     unsigned int v;
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
     if (v >= target) return true;
-    if (++spins > KAON_SPIN_LIMIT) {
+    if (++spins > limit) {
       atomicCAS(status, 0u, code);
       return false;
     }

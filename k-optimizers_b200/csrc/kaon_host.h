@@ -15,6 +15,8 @@ int configure_launch(kaon_plan* pl, const cudaDeviceProp& prop);  // Lion: grid 
 int configure_launch_adakaon(kaon_plan* pl, const cudaDeviceProp& prop, int max_cols);
 // bf16_method == KAHAN with bf16 weights needs every tensor's shift buffer: KAON_OK or an error
 int check_kahan(const kaon_plan* pl, int bf16_method);
+// the calling thread's current device must be the one the plan was built on: KAON_OK or KAON_E_INVALID
+int check_device(const kaon_plan* pl);
 
 #define KAON_CUDA(call)                                              \
   do {                                                               \

@@ -105,6 +105,7 @@ struct PlanView {
   unsigned* status;        // 0 = ok; else the code of the first bounded wait that ran out
   unsigned char* codes;    // 2 bits per element
   Peers peers;             // n == 0: no mirrors
+  unsigned spin_limit;     // polls a completion-counter wait makes before it gives up (0: the default)
 };
 
 }  // namespace kaon
@@ -148,6 +149,7 @@ struct kaon_plan {
   int64_t device_bytes = 0;
   int64_t launches = 0;
   int grid = 0;          // persistent grid size
+  int sm_count = 0;      // multiprocessors of the plan's device
   size_t smem_bytes = 0;
   int64_t total_elems = 0;
 };

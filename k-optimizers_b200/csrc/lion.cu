@@ -8,6 +8,8 @@
 // count.  APPLY item (same run, later in the list): once every MAIN item of the tensor has finished,
 // turn the codes into the weight write with the tensor-wide rescale 1/max(kept/numel, 1e-8).
 // Quantised momentum is read once and written once; weights are read once and written once.
+#include <mutex>
+
 #include "kaon_host.h"
 #include "kaon_ops.cuh"
 
@@ -444,7 +446,8 @@ __device__ void lion_apply(const PlanView& pv, const LionDev& hp, const Task& t,
   const DevTensor d = pv.tensors[t.tensor];
   if (pv.grads[t.tensor] == nullptr) return;
   bool ok = true;
-  if (tid == 0) ok = wait_counter(pv.done + t.tensor, (unsigned)d.n_main, pv.status, 2001u);
+  if (tid == 0) ok = wait_counter(pv.done + t.tensor, (unsigned)d.n_main, pv.status, 2001u,
+                                 pv.spin_limit ? pv.spin_limit : KAON_SPIN_LIMIT);
   ok = __syncthreads_and(ok) != 0;
   if (!ok) return;
   const unsigned kept = __ldcg(pv.kept + t.tensor);
@@ -630,6 +633,7 @@ extern "C" int kaon_lion_step(kaon_plan* pl, const kaon_lion_hparams* h, uint64_
                               void* stream) {
   if (!pl || !h) return fail(KAON_E_INVALID, "kaon_lion_step: null argument");
   if (pl->optimizer != KAON_OPT_LION) return fail(KAON_E_INVALID, "plan was not built for Lion");
+  if (int rc = check_device(pl)) return rc;
   if (h->bf16_method < KAON_W_NONE || h->bf16_method > KAON_W_KAHAN) return fail(KAON_E_UNSUPPORTED, "bf16_method %d", h->bf16_method);
   if (int rc = check_kahan(pl, h->bf16_method)) return rc;
   LionDev hp;
@@ -674,13 +678,17 @@ extern "C" int kaon_lion_step(kaon_plan* pl, const kaon_lion_hparams* h, uint64_
 // field the step reads and zeroes the counters, so calls that follow each other on one stream are
 // independent, but two calls whose kernels overlap on the GPU (different streams) race on it.  The
 // first call on a device looks the array's address up and configures the kernel (no allocation, but
-// synchronous driver work); make that first call outside any stream capture.
+// synchronous driver work, serialised by a host mutex); make that first call outside any stream capture.
+// Device status: if a bounded wait inside a call's kernel runs out, that call stops early (its CTAs
+// drain) and the code stays in the array; the NEXT call's set-up kernel moves it to a "last failure"
+// word and clears the live word, so later calls run normally.  kaon_lion_noalloc_status reads and
+// clears both words: a caller that must know whether every step completed calls it after the steps.
 // ---------------------------------------------------------------------------------------------------
 namespace kaon {
 
 constexpr long long NOALLOC_MAX_NUMEL = KAON_NOALLOC_MAX_NUMEL;
 constexpr int NOALLOC_MAX_ITEMS = 4096;  // work items per phase
-constexpr size_t NA_OFF_COUNTERS = 0;    // status @0, task counter @64, done @68, kept @72
+constexpr size_t NA_OFF_COUNTERS = 0;    // status @0, last failure @4, task counter @64, done @68, kept @72
 constexpr size_t NA_OFF_TENSOR = 256;
 constexpr size_t NA_OFF_GRAD = 512;
 constexpr size_t NA_OFF_TASKS = 1024;
@@ -698,6 +706,10 @@ __global__ void noalloc_setup_kernel(DevTensor d, const void* grad, long long it
   if (threadIdx.x == 0) {
     *reinterpret_cast<DevTensor*>(g_noalloc + NA_OFF_TENSOR) = d;
     *reinterpret_cast<const void**>(g_noalloc + NA_OFF_GRAD) = grad;
+    if (counters[0] != 0u) {  // an earlier call's bounded wait ran out: keep its code, run this call normally
+      if (counters[1] == 0u) counters[1] = counters[0];
+      counters[0] = 0u;
+    }
     counters[16] = 0u;  // task counter
     counters[17] = 0u;  // done
     counters[18] = 0u;  // kept
@@ -725,6 +737,7 @@ struct NoAllocDevice {
   size_t smem[2] = {0, 0};
 };
 static NoAllocDevice g_na_dev[64];
+static std::mutex g_na_mutex;  // guards the once-per-device set-up against concurrent first calls
 
 // Once per device, with that device current: the array's name is a host-side stand-in, so the address
 // the kernels get must come from cudaGetSymbolAddress.
@@ -792,9 +805,12 @@ extern "C" int kaon_lion_step_noalloc(const kaon_tensor_desc* t, int param_dtype
   int dev = 0;
   KAON_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return fail(KAON_E_UNSUPPORTED, "device index %d", dev);
-  if (!g_na_dev[dev].ready) {
-    int rc = noalloc_setup_device(dev);
-    if (rc) return rc;
+  {
+    std::lock_guard<std::mutex> lock(g_na_mutex);
+    if (!g_na_dev[dev].ready) {
+      int rc = noalloc_setup_device(dev);
+      if (rc) return rc;
+    }
   }
   const NoAllocDevice& nd = g_na_dev[dev];
 
@@ -840,4 +856,25 @@ extern "C" int kaon_lion_step_noalloc(const kaon_tensor_desc* t, int param_dtype
   k<<<nd.grid[param_dtype], NTHREADS, nd.smem[param_dtype], s>>>(v, hp);
   KAON_CUDA(cudaGetLastError());
   return KAON_OK;
+}
+
+extern "C" int kaon_lion_noalloc_status(void* stream) {
+  int dev = 0;
+  KAON_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(KAON_E_UNSUPPORTED, "device index %d", dev);
+  unsigned char* base = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_na_mutex);
+    if (!g_na_dev[dev].ready) return KAON_OK;  // no call has run on this device yet
+    base = g_na_dev[dev].base;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  unsigned st[2] = {0u, 0u};
+  KAON_CUDA(cudaMemcpyAsync(st, base + NA_OFF_COUNTERS, sizeof st, cudaMemcpyDeviceToHost, s));
+  KAON_CUDA(cudaStreamSynchronize(s));
+  if (st[0] == 0u && st[1] == 0u) return KAON_OK;
+  KAON_CUDA(cudaMemsetAsync(base + NA_OFF_COUNTERS, 0, sizeof st, s));
+  return fail(KAON_E_DEVICE, "kaon_lion_step_noalloc: device status %u: a bounded wait ran out in an earlier call "
+                             "(code = 1000*phase + kind); that call's tensor was not fully stepped",
+              st[0] ? st[0] : st[1]);
 }

@@ -92,6 +92,15 @@ int check_kahan(const kaon_plan* pl, int bf16_method) {
   return KAON_OK;
 }
 
+int check_device(const kaon_plan* pl) {
+  int dev = -1;
+  cudaError_t ce = cudaGetDevice(&dev);
+  if (ce != cudaSuccess) return cuda_fail(ce, "cudaGetDevice");
+  if (dev != pl->device)
+    return fail(KAON_E_INVALID, "the plan lives on device %d but the current device is %d", pl->device, dev);
+  return KAON_OK;
+}
+
 }  // namespace kaon
 
 using namespace kaon;
@@ -152,6 +161,7 @@ int kaon_plan_create(kaon_plan** out, int optimizer, int param_dtype, int moment
 
   kaon_plan* pl = new kaon_plan();
   pl->device = dev;
+  pl->sm_count = prop.multiProcessorCount;
   pl->optimizer = optimizer; pl->param_dtype = param_dtype; pl->momentum_kind = momentum_kind;
   pl->n_tensors = n;
   pl->total_elems = total;
@@ -252,13 +262,16 @@ int kaon_plan_create(kaon_plan** out, int optimizer, int param_dtype, int moment
   size_t tot = o_c + up(pl->counters_bytes);
   ce = cudaMalloc(&pl->d_block, tot);
   if (ce != cudaSuccess) { delete pl; return cuda_fail(ce, "cudaMalloc(plan tables)"); }
-  ce = cudaMalloc((void**)&pl->d_codes, (size_t)std::max<long long>(code_bytes, 64));
-  if (ce != cudaSuccess) { cudaFree(pl->d_block); delete pl; return cuda_fail(ce, "cudaMalloc(code scratch)"); }
+  if (optimizer != KAON_OPT_LION) code_bytes = 0;  // only Lion's MAIN/APPLY pair hands 2-bit codes over
+  if (code_bytes > 0) {
+    ce = cudaMalloc((void**)&pl->d_codes, (size_t)code_bytes);
+    if (ce != cudaSuccess) { cudaFree(pl->d_block); delete pl; return cuda_fail(ce, "cudaMalloc(code scratch)"); }
+  }
   if (optimizer != KAON_OPT_LION) {
     ce = cudaMalloc((void**)&pl->d_aux, sizeof(float) * (size_t)std::max<long long>(aux_floats, 64));
     if (ce != cudaSuccess) { cudaFree(pl->d_block); cudaFree(pl->d_codes); delete pl; return cuda_fail(ce, "cudaMalloc(aux scratch)"); }
   }
-  pl->device_bytes = (int64_t)tot + std::max<long long>(code_bytes, 64) + (pl->d_aux ? 4 * std::max<long long>(aux_floats, 64) : 0);
+  pl->device_bytes = (int64_t)tot + code_bytes + (pl->d_aux ? 4 * std::max<long long>(aux_floats, 64) : 0);
   char* base = (char*)pl->d_block;
   std::vector<const void*> grads(n);
   for (int i = 0; i < n; ++i) grads[i] = descs[i].g;
@@ -291,6 +304,7 @@ int kaon_plan_create(kaon_plan** out, int optimizer, int param_dtype, int moment
 
 int kaon_plan_set_grads(kaon_plan* pl, const void* const* grads, int n, void* stream) {
   if (!pl || !grads || n != pl->n_tensors) return fail(KAON_E_INVALID, "kaon_plan_set_grads: bad plan or n");
+  if (int rc = check_device(pl)) return rc;
   for (int i = 0; i < n; ++i)
     if ((uintptr_t)grads[i] & 15) return fail(KAON_E_INVALID, "gradient %d not 16-byte aligned", i);
   // pageable source: the runtime stages it before returning, so the caller's array is free at once
@@ -322,6 +336,16 @@ int kaon_plan_status(kaon_plan* pl, void* stream) {
   if (ce != cudaSuccess) return cuda_fail(ce, "kaon_plan_status");
   if (st) return fail(KAON_E_DEVICE, "device status %u: a bounded wait ran out (code = 1000*phase + kind)", st);
   return KAON_OK;
+}
+
+int kaon_plan_debug_stall(kaon_plan* pl, int tensor, uint32_t spin_limit) {
+  if (!pl || tensor < 0 || tensor >= pl->n_tensors) return fail(KAON_E_INVALID, "kaon_plan_debug_stall: bad plan or tensor");
+  if (pl->optimizer != KAON_OPT_LION) return fail(KAON_E_UNSUPPORTED, "kaon_plan_debug_stall: Lion plans only");
+  if (int rc = check_device(pl)) return rc;
+  pl->h_tensors[tensor].n_main += 1;  // one more MAIN item than the work list holds: APPLY's wait cannot be met
+  pl->view.spin_limit = spin_limit;
+  cudaError_t ce = cudaMemcpy((void*)(pl->view.tensors + tensor), &pl->h_tensors[tensor], sizeof(DevTensor), cudaMemcpyHostToDevice);
+  return ce == cudaSuccess ? KAON_OK : cuda_fail(ce, "kaon_plan_debug_stall");
 }
 
 int64_t kaon_plan_device_bytes(const kaon_plan* pl) { return pl ? pl->device_bytes : 0; }

@@ -1,7 +1,9 @@
 """Build libkaon_b200.so in-tree with nvcc for sm_100a.
 
-    python -m kaon_b200._build          (from the directory that holds the package)
+    python -m kaon_b200._build [--force] [-v]     (from the directory that holds the package)
 
+Every .cu file is compiled to an object of its own (in parallel, only when it or a header changed) and
+the objects are linked into the shared library.
 -fmad=false: the kernels spell out every fused multiply-add the reference's torch ops perform and
 must not get any other.  The library has no torch dependency: it is loaded with ctypes.
 """
@@ -11,14 +13,16 @@ import glob
 import os
 import subprocess
 import sys
+from concurrent.futures import ThreadPoolExecutor
 
 PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(os.path.dirname(PKG), "csrc")
+OBJ = os.path.join(CSRC, "build")
 LIB = os.path.join(PKG, "libkaon_b200.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-fmad=false",
-    "--shared", "-Xcompiler", "-fPIC",
+    "-Xcompiler", "-fPIC",
 ]
 
 
@@ -26,28 +30,49 @@ def sources() -> list[str]:
     return sorted(glob.glob(os.path.join(CSRC, "*.cu")))
 
 
+def headers() -> list[str]:
+    deps = glob.glob(os.path.join(CSRC, "*.h")) + glob.glob(os.path.join(CSRC, "*.cuh"))
+    deps += glob.glob(os.path.join(os.path.dirname(os.path.dirname(PKG)), "include", "*.h"))
+    return deps
+
+
+def _obj(src: str) -> str:
+    return os.path.join(OBJ, os.path.basename(src)[:-3] + ".o")
+
+
 def needs_build() -> bool:
     if not os.path.exists(LIB):
         return True
     t = os.path.getmtime(LIB)
-    deps = sources() + glob.glob(os.path.join(CSRC, "*.h")) + glob.glob(os.path.join(CSRC, "*.cuh"))
-    deps += glob.glob(os.path.join(os.path.dirname(os.path.dirname(PKG)), "include", "*.h"))
-    return any(os.path.getmtime(d) > t for d in deps)
+    return any(os.path.getmtime(d) > t for d in sources() + headers())
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not needs_build():
         return LIB
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-    cmd = [nvcc, *NVCC_FLAGS, "-o", LIB, *sources()]
-    if verbose:
-        cmd.insert(1, "-Xptxas")
-        cmd.insert(2, "-v")
-        print(" ".join(cmd))
     env = dict(os.environ)
     env.pop("CC", None)   # let nvcc pick its default host compiler
     env.pop("CXX", None)
-    subprocess.check_call(cmd, env=env)
+    os.makedirs(OBJ, exist_ok=True)
+    hdr_time = max(os.path.getmtime(h) for h in headers())
+
+    def compile_one(src: str) -> str:
+        obj = _obj(src)
+        if (not force and os.path.exists(obj)
+                and os.path.getmtime(obj) > max(os.path.getmtime(src), hdr_time)):
+            return obj
+        cmd = [nvcc, *NVCC_FLAGS, "-c", src, "-o", obj]
+        if verbose:
+            cmd[1:1] = ["-Xptxas", "-v"]
+            print(" ".join(cmd), flush=True)
+        subprocess.check_call(cmd, env=env)
+        return obj
+
+    with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as pool:
+        objs = list(pool.map(compile_one, sources()))
+    subprocess.check_call([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "--shared", "-o", LIB, *objs],
+                          env=env)
     return LIB
 
 

@@ -279,6 +279,10 @@ class FusedStepMixin:
         if extra is not None:
             self._t = int(extra.get("step", 0))
             self.sr_seed = extra.get("sr_seed")
+        else:
+            # a checkpoint written by the reference: the noise stream restarts at step 0; the seed in
+            # force (``sr_seed``) is kept
+            self._t = 0
         return sd
 
     def check_device_status(self) -> None:

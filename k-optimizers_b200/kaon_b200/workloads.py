@@ -43,8 +43,18 @@ def unet_sample() -> list[tuple[int, ...]]:
     return _block(1280) + [(1280, 1280, 3, 3)]
 
 
+def unet_mid() -> list[tuple[int, ...]]:
+    """Eight width-1280 blocks plus four [1280,1280,3,3] convs (269 M parameters): more than ten times the
+    L2 cache per step, yet small enough to hold a few GB on the device - the list profiler captures use."""
+    shapes: list[tuple[int, ...]] = []
+    for _ in range(8):
+        shapes += _block(1280)
+    return shapes + [(1280, 1280, 3, 3)] * 4
+
+
 def numel(shapes) -> int:
     return sum(math.prod(s) for s in shapes)
 
 
-WORKLOADS = {"unet_2p6b": unet_2p6b, "dit_11b": dit_11b, "dit_block": dit_block, "unet_sample": unet_sample}
+WORKLOADS = {"unet_2p6b": unet_2p6b, "dit_11b": dit_11b, "dit_block": dit_block, "unet_sample": unet_sample,
+             "unet_mid": unet_mid}

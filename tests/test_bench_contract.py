@@ -1,5 +1,6 @@
-"""The JSON line bench.py prints: the reference arm runs without a GPU (it times the CPU oracle port on
-a bounded sample), so its contract can be checked here; the GPU arm's keys are checked on a GPU."""
+"""The JSON line bench.py prints: the reference arm runs without a GPU (it times the reference package
+when it is installed beside the benchmark, else the CPU oracle port, on a bounded sample), so its
+contract can be checked here; the GPU arm's keys are checked on a GPU."""
 import json
 import os
 import subprocess
@@ -25,7 +26,9 @@ def test_reference_arm_line():
     assert d["higher_is_better"] is True and d["n_gpus"] == 1 and d["value"] > 0
     assert d["config"]["workload"] == "lion4bit_unet2p6b"
     cb = d["cpu_baseline"]
-    assert cb["kind"] == "port" and cb["cores"] >= 1 and cb["value"] == d["value"] and cb["sample"]
+    assert cb["kind"] in ("port", "reference") and cb["cores"] >= 1 and cb["value"] == d["value"] and cb["sample"]
+    if cb["kind"] == "reference":
+        assert cb["port"]["value"] > 0
     assert d["e2e"] == {"value": d["value"], "unit": "params/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
 
 
@@ -42,4 +45,15 @@ def test_gpu_arm_line_has_the_contract_keys():
     assert d["gpu_launches"] == d["steps"]           # one Lion kernel per step
     e = d["e2e"]
     assert e["h2d_bytes_per_step"] > 0 and e["d2h_bytes_per_step"] > 0 and e["value"] < d["value"]
-    assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1
+    assert d["cpu_baseline"]["kind"] in ("port", "reference") and d["cpu_baseline"]["cores"] >= 1
+    assert d["compute_only_ms"] == d["incl_publish_ms"] == d["ms_per_step"]   # one GPU: nothing to publish
+
+
+def test_reference_arm_uses_the_host_cores_under_a_launcher():
+    """torch.distributed.run exports OMP_NUM_THREADS=1; the CPU arm must still use every host core."""
+    env = dict(os.environ, OMP_NUM_THREADS="1")
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1",
+                        "--warmup", "0"], capture_output=True, text=True, timeout=600, cwd=ROOT, env=env)
+    assert r.returncode == 0, r.stderr[-2000:]
+    d = json.loads([ln for ln in r.stdout.splitlines() if ln.startswith("{")][0])
+    assert d["cpu_baseline"]["cores"] == len(os.sched_getaffinity(0))

@@ -49,3 +49,19 @@ def test_cpu_tensors_are_refused():
     p.grad = torch.zeros(4, 4)
     with pytest.raises(KaonError, match="CUDA tensors only"):
         opt.step()
+
+
+def test_integration_doc_structs_match_the_header():
+    """The ctypes structs printed in INTEGRATION.md have the size and field order the library uses."""
+    from kaon_b200 import _lib
+    text = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    ns = {"C": C}
+    for name in ("TensorDesc", "LionHParams"):
+        m = re.search(r"class %s\(C\.Structure\):.*?\n    _fields_ = \[(.*?)\]" % name, text, flags=re.S)
+        assert m, name
+        exec("class %s(C.Structure):\n    _fields_ = [%s]" % (name, m.group(1)), ns)  # noqa: S102
+        doc, ours = ns[name], getattr(_lib, name)
+        assert C.sizeof(doc) == C.sizeof(ours), (name, C.sizeof(doc), C.sizeof(ours))
+        assert [f[0] for f in doc._fields_] == [f[0] for f in ours._fields_]
+    assert C.sizeof(ns["TensorDesc"]) == 80
+    assert '"kahan": 2' in text
