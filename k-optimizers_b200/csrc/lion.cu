@@ -40,10 +40,224 @@ __device__ __forceinline__ void philox_rk(const LionDev& hp, uint32_t c0, uint32
   out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
 }
 
-// Full-vector fast path of the MAIN item for 4-bit momentum, no weight decay, cautious on, rows that are
-// a multiple of 8 elements: no per-element guards, the eight 4-bit codes assembled with one shift-add
-// each, one exactness check per vector.  Codes of the update go out as two byte masks per eight
-// elements: bit k of the low byte = kept with sign >= 0, bit k of the high byte = kept with sign <= 0.
+// ---- update codes: 16 bits per eight elements, one nibble per element pair ----
+// Nibble j covers elements 2j (e) and 2j+1 (o): bit 0 = kept_e, bit 1 = kept_o, bit 2 = neg_e, bit 3 = neg_o.
+// Per element (kept, neg): (0,0) masked out; (1,0) kept, update sign +1; (1,1) kept, sign -1;
+// (0,1) kept with update sign 0 (possible only with weight decay, where the mask looks at sign + wd*p).
+__device__ __forceinline__ constexpr uint32_t code_bit(int k) { return 1u << (4 * (k >> 1) + (k & 1)); }
+constexpr uint32_t CODE_KEPT_BITS = 0x3333u;
+
+// ---- packed fp32 pairs (f32x2 arithmetic of sm_100: each lane is an independent IEEE fp32 operation,
+//      so results are those of the scalar instructions; two lanes cost one issue slot) ----
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ f32x2 sub2(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+// max / min of three (sm_100 takes three inputs in one instruction)
+__device__ __forceinline__ float max3f(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ float min3f(float a, float b, float c) {
+  float d;
+  asm("min.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// Byte permute with the full selector: bit 3 of a selector nibble replicates the selected byte's top bit
+// over the whole result byte (the __byte_perm intrinsic documents only the three index bits).
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+  return d;
+}
+// a - b on two packed bf16 values, one rounding to bf16 per lane.  Equal to bf16(fp32(a) - fp32(b)): the
+// fp32 difference of two 8-bit significands is inexact only when one operand is below 2^-16 of the other,
+// and then it lies nowhere near a bf16 rounding boundary.
+__device__ __forceinline__ uint32_t sub_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+// maximum over the 16 lanes of this thread's half warp (every lane of the warp calls it; v >= 0)
+__device__ __forceinline__ float half_warp_max(float v, int tid) {
+  uint32_t r;
+  asm volatile("redux.sync.max.u32 %0, %1, %2;" : "=r"(r) : "r"(__float_as_uint(v)), "r"((tid & 16) ? 0xffff0000u : 0x0000ffffu));
+  return __uint_as_float(r);
+}
+// a / 7 correctly rounded without the division unit: quotient estimate, exact residual, one correction.
+// Equal to the IEEE quotient for every a in [1e-12, FLT_MAX] (checked exhaustively on the host).
+__device__ __forceinline__ float div7_exact(float a) {
+  const float r7 = 0.142857149243354797363281250f;  // RN(1/7)
+  const float q0 = __fmul_rn(a, r7);
+  return __fmaf_rn(__fmaf_rn(-7.0f, q0, a), r7, q0);
+}
+
+// MAIN item, fast path for bf16 weights/gradients: 4-bit momentum in blocks of 128, no weight decay,
+// cautious on, rows a multiple of 8 elements.  Eight elements per thread and trip, arithmetic on packed
+// pairs: gradient centralization as one bf16x2 subtract per pair; decode, direction c and new momentum as
+// f32x2 multiplies and FMAs; the block maximum by a half-warp reduction; the 4-bit codes packed with FMAs
+// (codes are small integers, exact in fp32) and one exactness check per vector; the update codes gathered
+// from sign bytes (byte permutes with sign replication) instead of per-element compares.
+template <bool GC>
+__device__ __forceinline__ unsigned lion_fast4_bf16(const PlanView& pv, const LionDev& hp, const Task& t,
+                                                    const DevTensor& d, const unsigned char* g_s,
+                                                    const unsigned char* m_s, const uint32_t* mean2_s,
+                                                    const float* sc_s, int tid) {
+  const int nvec = t.n >> 3;
+  const int nvec_pad = (nvec + 31) & ~31;
+  uint16_t* cdst = reinterpret_cast<uint16_t*>(pv.codes + d.code_off + (t.e0 >> 2));
+  uint32_t* mdst = reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned char*>(d.m) + (t.e0 >> 1));
+  const uint32_t* msrc = reinterpret_cast<const uint32_t*>(m_s);
+  const long long blk0 = t.e0 >> 7;
+  const f32x2 B1 = pack2(hp.b1, hp.b1), W1 = pack2(hp.w1, hp.w1), B2 = pack2(hp.b2, hp.b2), W2 = pack2(hp.w2, hp.w2);
+  const f32x2 BIAS = pack2(-8388616.0f, -8388616.0f);   // -(2^23 + 8): nibble bits under 2^23 -> nibble - 8
+  const f32x2 M8 = pack2(12582920.0f, 12582920.0f);     // 1.5 * 2^23 + 8: adding it rounds to integer, half to even
+  const f32x2 K256 = pack2(256.0f, 256.0f);
+  unsigned kept_local = 0;
+  for (int v = tid; v < nvec_pad; v += NTHREADS) {
+    const bool act = v < nvec;
+    uint32_t gw[4] = {0u, 0u, 0u, 0u};
+    uint32_t w = 0x88888888u;
+    float sc_old = 1.0f;
+    if (act) {
+      const uint4 q = *reinterpret_cast<const uint4*>(g_s + (size_t)v * 16);
+      gw[0] = q.x; gw[1] = q.y; gw[2] = q.z; gw[3] = q.w;
+      w = msrc[v];
+      sc_old = sc_s[v >> 4];
+      if (GC) {
+        const uint32_t mu2 = mean2_s[row_of((unsigned)v * 8u, d)];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) gw[j] = sub_bf16x2(gw[j], mu2);
+      }
+    }
+    // nibble 2j as the low mantissa bits of 2^23 (even nibbles are the bytes of wl, odd ones of wh)
+    const uint32_t wl = w & 0x0F0F0F0Fu, wh = (w >> 4) & 0x0F0F0F0Fu;
+    const f32x2 SC = pack2(sc_old, sc_old);
+    f32x2 G[4], C[4], N[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      G[j] = pack2(bf16lo(gw[j]), bf16hi(gw[j]));
+      const f32x2 raw = pack2(__uint_as_float(__byte_perm(wl, 0x4B000000u, 0x7540u | (uint32_t)j)),
+                              __uint_as_float(__byte_perm(wh, 0x4B000000u, 0x7540u | (uint32_t)j)));
+      const f32x2 mo = mul2(add2(raw, BIAS), SC);
+      C[j] = fma2(G[j], W1, mul2(mo, B1));
+      N[j] = fma2(G[j], W2, mul2(mo, B2));
+    }
+    float n[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) unpack2(N[j], n[2 * j], n[2 * j + 1]);
+    float amax = max3f(fabsf(n[0]), fabsf(n[1]), fabsf(n[2]));
+    amax = max3f(amax, fabsf(n[3]), fabsf(n[4]));
+    amax = max3f(amax, fabsf(n[5]), fabsf(n[6]));
+    amax = fmaxf(amax, fabsf(n[7]));
+    amax = fmaxf(half_warp_max(amax, tid), 1e-12f);
+    const float sc = div7_exact(amax);
+    float inv;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv) : "f"(sc));
+    const f32x2 INV = pack2(inv, inv);
+    // r = rint(n*inv) + 8 + magic in one rounding; t = -(rint(n*inv)); e = n*inv - rint(n*inv) exactly
+    f32x2 T[4];
+    float e[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const f32x2 r = fma2(N[j], INV, M8);
+      T[j] = sub2(M8, r);
+      unpack2(fma2(N[j], INV, T[j]), e[2 * j], e[2 * j + 1]);
+    }
+    float worst = max3f(fabsf(e[0]), fabsf(e[1]), fabsf(e[2]));
+    worst = max3f(worst, fabsf(e[3]), fabsf(e[4]));
+    worst = max3f(worst, fabsf(e[5]), fabsf(e[6]));
+    worst = fmaxf(worst, fabsf(e[7]));
+    uint32_t word;
+    if (worst > 0.5f - 1e-4f) {  // some product sits near a rounding boundary: redo with the true division
+      word = 0;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const int qi = min(max((int)rintf(__fdiv_rn(n[k], sc)), -7), 7);
+        word |= (uint32_t)(qi + 8) << (4 * k);
+      }
+    } else {
+      // t_k = -q_k in [-7, 7]: sum_k (8 - t_k) 16^k = 0x8888 - (t0 + 16 t1 + 256 t2 + 4096 t3), exact in fp32;
+      // adding 2^23 leaves it in the low 16 mantissa bits
+      float xl, xh, yl, yh;
+      unpack2(fma2(T[1], K256, T[0]), xl, xh);   // (t0 + 256 t2, t1 + 256 t3)
+      unpack2(fma2(T[3], K256, T[2]), yl, yh);
+      const float lo4 = __fsub_rn(8423560.0f, __fmaf_rn(xh, 16.0f, xl));  // 2^23 + 0x8888 - ...
+      const float hi4 = __fsub_rn(8423560.0f, __fmaf_rn(yh, 16.0f, yl));
+      word = __byte_perm(__float_as_uint(lo4), __float_as_uint(hi4), 0x5410);
+    }
+    // ---- update codes: kept <=> c*g > 0; the update's sign is then the sign of g ----
+    float a[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) unpack2(mul2(C[j], G[j]), a[2 * j], a[2 * j + 1]);
+    float amin = min3f(fabsf(a[0]), fabsf(a[1]), fabsf(a[2]));
+    amin = min3f(amin, fabsf(a[3]), fabsf(a[4]));
+    amin = min3f(amin, fabsf(a[5]), fabsf(a[6]));
+    amin = fminf(amin, fabsf(a[7]));
+    uint32_t code16;
+    if (amin > 0.0f) {
+      // bytes 0xFF where the product is negative (masked out) / where g is negative
+      const uint32_t am_lo = prmt(prmt(__float_as_uint(a[0]), __float_as_uint(a[1]), 0x00FBu),
+                                  prmt(__float_as_uint(a[2]), __float_as_uint(a[3]), 0x00FBu), 0x5410u);
+      const uint32_t am_hi = prmt(prmt(__float_as_uint(a[4]), __float_as_uint(a[5]), 0x00FBu),
+                                  prmt(__float_as_uint(a[6]), __float_as_uint(a[7]), 0x00FBu), 0x5410u);
+      const uint32_t gm_lo = prmt(gw[0], gw[1], 0xFDB9u), gm_hi = prmt(gw[2], gw[3], 0xFDB9u);
+      // element b of each group of four lives in byte b: kept bits 0,1,4,5 and neg bits 2,3,6,7 of the code byte
+      const uint32_t t_lo = ~am_lo & ((gm_lo & 0x80400804u) | 0x20100201u);
+      const uint32_t t_hi = ~am_hi & ((gm_hi & 0x80400804u) | 0x20100201u);
+      // the four bytes of t have disjoint bits: their sum (top byte of t * 0x01010101) is their OR
+      code16 = __byte_perm(t_lo * 0x01010101u, t_hi * 0x01010101u, 0x0073);
+    } else {
+      // a zero gradient, a zero direction or an underflowing product: decide element by element
+      float c[8], g[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { unpack2(C[j], c[2 * j], c[2 * j + 1]); unpack2(G[j], g[2 * j], g[2 * j + 1]); }
+      code16 = 0;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        if (c[k] > 0.0f && g[k] > 0.0f) code16 |= code_bit(k);
+        if (c[k] < 0.0f && g[k] < 0.0f) code16 |= 5u * code_bit(k);
+      }
+    }
+    if (act) {
+      mdst[v] = word;
+      if ((v & 15) == 0) d.m_scale[blk0 + (v >> 4)] = sc;
+      cdst[v] = (uint16_t)code16;
+      kept_local += __popc(code16 & CODE_KEPT_BITS);
+    }
+  }
+  return kept_local;
+}
+
+// Full-vector fast path of the MAIN item for fp32 weights (4-bit momentum, no weight decay, cautious on,
+// rows a multiple of 8 elements): no per-element guards, the eight 4-bit codes assembled with one
+// shift-add each, one exactness check per vector.
 template <typename PT, bool GC>
 __device__ __forceinline__ unsigned lion_fast4(const PlanView& pv, const LionDev& hp, const Task& t,
                                                const DevTensor& d, const unsigned char* g_s,
@@ -101,8 +315,8 @@ __device__ __forceinline__ unsigned lion_fast4(const PlanView& pv, const LionDev
       const float c = __fmaf_rn(g[k], hp.w1, __fmul_rn(mo, hp.b1));
       mn[k] = __fmaf_rn(g[k], hp.w2, __fmul_rn(mo, hp.b2));
       amax = fmaxf(amax, fabsf(mn[k]));
-      if (fminf(c, g[k]) > 0.0f) pos |= 1u << k;
-      if (fmaxf(c, g[k]) < 0.0f) neg |= 1u << k;
+      if (fminf(c, g[k]) > 0.0f) pos |= code_bit(k);
+      if (fmaxf(c, g[k]) < 0.0f) neg |= 5u * code_bit(k);
     }
     amax = fmaxf(group_max(amax, 16), 1e-12f);
     const float sc = __fdiv_rn(amax, 7.0f);
@@ -129,8 +343,8 @@ __device__ __forceinline__ unsigned lion_fast4(const PlanView& pv, const LionDev
     if (act) {
       mdst[v] = word;
       if ((v & 15) == 0) d.m_scale[blk] = sc;
-      cdst[v] = (uint16_t)(pos | (neg << 8));
-      kept_local += __popc(pos | neg);
+      cdst[v] = (uint16_t)(pos | neg);
+      kept_local += __popc((pos | neg) & CODE_KEPT_BITS);
     }
   }
   return kept_local;
@@ -200,6 +414,11 @@ __device__ void lion_main(const PlanView& pv, const LionDev& hp, const Task& t, 
   const bool do_gc = hp.gc && d.rows > 0;
   const int C = d.cols;
   const int nrows = d.rows > 0 ? n / C : 1;
+  bool fast = false;
+  if constexpr (MK == KAON_M_4BIT)
+    fast = !hp.has_wd && hp.cautious && (n & 7) == 0 && ((d.rows <= 0) || ((C & 7) == 0));
+  // the bf16 fast path subtracts the mean from packed pairs: it reads the mean as two bf16 copies
+  const bool mean_packed = fast && E::IS_BF16;
   if (do_gc) {
     const int warp = tid >> 5, lane = tid & 31;
     for (int r = warp; r < nrows; r += NTHREADS / 32) {
@@ -217,7 +436,8 @@ __device__ void lion_main(const PlanView& pv, const LionDev& hp, const Task& t, 
       s = warp_sum(s);
       if (lane == 0) {
         float mean = __fdiv_rn(s, (float)C);
-        mean_s[r] = E::IS_BF16 ? round_bf16(mean) : mean;
+        if (mean_packed) reinterpret_cast<uint32_t*>(mean_s)[r] = pack_bf16_rn(mean, mean);
+        else mean_s[r] = E::IS_BF16 ? round_bf16(mean) : mean;
       }
     }
   }
@@ -287,12 +507,15 @@ __device__ void lion_main(const PlanView& pv, const LionDev& hp, const Task& t, 
 
   // ---- main pass ----
   uint32_t kept_local = 0;
-  bool fast = false;
-  if constexpr (MK == KAON_M_4BIT) fast = !hp.has_wd && hp.cautious && (n & 7) == 0 && row_uniform;
   if (fast) {
-    if constexpr (MK == KAON_M_4BIT)
-      kept_local = do_gc ? lion_fast4<PT, true>(pv, hp, t, d, g_s, m_s, mean_s, sc_s, tid)
-                         : lion_fast4<PT, false>(pv, hp, t, d, g_s, m_s, mean_s, sc_s, tid);
+    if constexpr (MK == KAON_M_4BIT) {
+      if constexpr (E::IS_BF16)
+        kept_local = do_gc ? lion_fast4_bf16<true>(pv, hp, t, d, g_s, m_s, reinterpret_cast<const uint32_t*>(mean_s), sc_s, tid)
+                           : lion_fast4_bf16<false>(pv, hp, t, d, g_s, m_s, reinterpret_cast<const uint32_t*>(mean_s), sc_s, tid);
+      else
+        kept_local = do_gc ? lion_fast4<PT, true>(pv, hp, t, d, g_s, m_s, mean_s, sc_s, tid)
+                           : lion_fast4<PT, false>(pv, hp, t, d, g_s, m_s, mean_s, sc_s, tid);
+    }
   } else
   for (int v = tid; v < nvec_pad; v += NTHREADS) {
     const int cnt = max(0, min(8, n - v * 8));
@@ -405,10 +628,10 @@ __device__ void lion_main(const PlanView& pv, const LionDev& hp, const Task& t, 
     // ---- hand the update on ----
     if (cnt > 0) {
       if (hp.cautious) {
-        uint32_t code16 = 0;  // low byte: kept with sign >= 0; high byte: kept with sign <= 0
+        uint32_t code16 = 0;
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          if ((kept >> k) & 1u) code16 |= (sg[k] >= 0 ? (1u << k) : 0u) | (sg[k] <= 0 ? (256u << k) : 0u);
+          if ((kept >> k) & 1u) code16 |= sg[k] > 0 ? code_bit(k) : (sg[k] < 0 ? 5u * code_bit(k) : 4u * code_bit(k));
         }
         *reinterpret_cast<uint16_t*>(pv.codes + d.code_off + (t.e0 >> 2) + (size_t)v * 2) = (uint16_t)code16;
         kept_local += __popc(kept);
@@ -440,8 +663,9 @@ __device__ void lion_main(const PlanView& pv, const LionDev& hp, const Task& t, 
 }
 
 // APPLY item: weights of the run [e0, e0+n) once the tensor's kept count is complete.
+// lut_s (16 entries): for the fast path, the fp32 update pair of every value a code nibble can take.
 template <typename PT, bool MIRROR>
-__device__ void lion_apply(const PlanView& pv, const LionDev& hp, const Task& t, int tid) {
+__device__ void lion_apply(const PlanView& pv, const LionDev& hp, const Task& t, float2* lut_s, int tid) {
   using E = Elems<PT>;
   const DevTensor d = pv.tensors[t.tensor];
   if (pv.grads[t.tensor] == nullptr) return;
@@ -462,8 +686,33 @@ __device__ void lion_apply(const PlanView& pv, const LionDev& hp, const Task& t,
   const bool fast_sr = E::IS_BF16 && hp.sr && !hp.has_wd;
   int v_begin = tid;
   if (fast_sr) {
-    // four full vectors per trip: all loads are issued before the first use
+    if (tid < 16) {  // nibble = kept_e | kept_o << 1 | neg_e << 2 | neg_o << 3
+      const float de = (tid & 1) ? ((tid & 4) ? -vpos : vpos) : 0.0f;
+      const float dd = (tid & 2) ? ((tid & 8) ? -vpos : vpos) : 0.0f;
+      lut_s[tid] = make_float2(de, dd);
+    }
+    __syncthreads();
+    // full vectors, four per trip: all loads are issued before the first use.  Per pair: the update pair
+    // from the table, p - update as one packed subtract, 16 noise bits added below the kept mantissa.
     const int nfull = n >> 3;
+    auto one = [&](const uint4 pw4, const uint32_t c16, const int vv) {
+      const uint64_t q = (uint64_t)((t.e0 >> 3) + vv);
+      uint32_t nz[4];
+      philox_rk(hp, (uint32_t)q, d.tensor_id, hp.step, (uint32_t)KAON_TAG_UPDATE | ((uint32_t)(q >> 32) << 8), nz);
+      uint32_t pw[4] = {pw4.x, pw4.y, pw4.z, pw4.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 dl = lut_s[(c16 >> (4 * j)) & 15u];
+        float r0, r1;
+        unpack2(sub2(pack2(bf16lo(pw[j]), bf16hi(pw[j])), pack2(dl.x, dl.y)), r0, r1);
+        const uint32_t b0 = __float_as_uint(r0) + (nz[j] & 0xffffu);
+        const uint32_t b1 = __float_as_uint(r1) + (nz[j] >> 16);
+        pw[j] = __byte_perm(b0, b1, 0x7632);
+      }
+      const uint4 out = make_uint4(pw[0], pw[1], pw[2], pw[3]);
+      *reinterpret_cast<uint4*>(pbase + (size_t)vv * 16) = out;
+      mirror16(MIRROR ? &pv.peers : nullptr, pbase + (size_t)vv * 16, out);
+    };
     int v = tid;
     for (; v + 3 * NTHREADS < nfull; v += 4 * NTHREADS) {
       uint4 pw4[4];
@@ -474,72 +723,29 @@ __device__ void lion_apply(const PlanView& pv, const LionDev& hp, const Task& t,
         c16[u] = __ldcg(reinterpret_cast<const unsigned short*>(cbase + (size_t)(v + u * NTHREADS) * 2));
       }
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int vv = v + u * NTHREADS;
-        const uint32_t pos = c16[u] & 0xFFu, neg = c16[u] >> 8;
-        const uint64_t q = (uint64_t)((t.e0 >> 3) + vv);
-        uint32_t nz[4];
-        philox_rk(hp, (uint32_t)q, d.tensor_id, hp.step, (uint32_t)KAON_TAG_UPDATE | ((uint32_t)(q >> 32) << 8), nz);
-        uint32_t pw[4] = {pw4[u].x, pw4[u].y, pw4[u].z, pw4[u].w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int k0 = 2 * j, k1 = 2 * j + 1;
-          float d0 = ((pos >> k0) & 1u) ? vpos : 0.0f;
-          d0 = ((neg >> k0) & 1u) ? -vpos : d0;
-          float d1 = ((pos >> k1) & 1u) ? vpos : 0.0f;
-          d1 = ((neg >> k1) & 1u) ? -vpos : d1;
-          const uint32_t b0 = __float_as_uint(__fsub_rn(bf16lo(pw[j]), d0)) + (nz[j] & 0xffffu);
-          const uint32_t b1 = __float_as_uint(__fsub_rn(bf16hi(pw[j]), d1)) + (nz[j] >> 16);
-          pw[j] = __byte_perm(b0, b1, 0x7632);
-        }
-        const uint4 out = make_uint4(pw[0], pw[1], pw[2], pw[3]);
-        *reinterpret_cast<uint4*>(pbase + (size_t)vv * 16) = out;
-        mirror16(MIRROR ? &pv.peers : nullptr, pbase + (size_t)vv * 16, out);
-      }
+      for (int u = 0; u < 4; ++u) one(pw4[u], c16[u], v + u * NTHREADS);
     }
-    v_begin = v;
+    for (; v < nfull; v += NTHREADS)
+      one(*reinterpret_cast<const uint4*>(pbase + (size_t)v * 16),
+          __ldcg(reinterpret_cast<const unsigned short*>(cbase + (size_t)v * 2)), v);
+    v_begin = v;   // only a ragged last vector can be left
   }
   for (int v = v_begin; v < nvec; v += NTHREADS) {
     const int cnt = min(8, n - v * 8);
     const uint32_t c16 = __ldcg(reinterpret_cast<const unsigned short*>(cbase + (size_t)v * 2));
-    const uint32_t pos = c16 & 0xFFu, neg = c16 >> 8;
-    if (fast_sr && cnt == 8) {
-      // eight bf16 weights: p - (+-vpos | 0), noise from the Philox stream, truncate
-      const uint64_t q = (uint64_t)((t.e0 >> 3) + v);
-      uint32_t nz[4];
-      philox_rk(hp, (uint32_t)q, d.tensor_id, hp.step, (uint32_t)KAON_TAG_UPDATE | ((uint32_t)(q >> 32) << 8), nz);
-      uint4* pp = reinterpret_cast<uint4*>(pbase + (size_t)v * 16);
-      const uint4 pw4 = *pp;
-      uint32_t pw[4] = {pw4.x, pw4.y, pw4.z, pw4.w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int k0 = 2 * j, k1 = 2 * j + 1;
-        const float d0 = ((pos >> k0) & 1u) ? (((neg >> k0) & 1u) ? 0.0f : vpos) : (((neg >> k0) & 1u) ? -vpos : 0.0f);
-        const float d1 = ((pos >> k1) & 1u) ? (((neg >> k1) & 1u) ? 0.0f : vpos) : (((neg >> k1) & 1u) ? -vpos : 0.0f);
-        const uint32_t b0 = __float_as_uint(__fsub_rn(bf16lo(pw[j]), d0)) + (nz[j] & 0xffffu);
-        const uint32_t b1 = __float_as_uint(__fsub_rn(bf16hi(pw[j]), d1)) + (nz[j] >> 16);
-        pw[j] = __byte_perm(b0, b1, 0x7632);
-      }
-      const uint4 out = make_uint4(pw[0], pw[1], pw[2], pw[3]);
-      *pp = out;
-      mirror16(MIRROR ? &pv.peers : nullptr, pp, out);
-      continue;
-    }
     float dl[8];
-    if (hp.has_wd) {
-      float pvals[8];
-      load8_guard<PT>(pbase + (size_t)v * 8 * E::BYTES, cnt, pvals);
+    float pvals[8];
+    if (hp.has_wd) load8_guard<PT>(pbase + (size_t)v * 8 * E::BYTES, cnt, pvals);
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        const int pb = (pos >> k) & 1, nb = (neg >> k) & 1;
-        const float dv = __fmaf_rn(pvals[k], hp.wd, (float)(pb - nb));
-        dl[k] = (pb | nb) ? __fmul_rn(__fdiv_rn(dv, denom), hp.lr) : 0.0f;
-      }
-    } else {
-#pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        const int pb = (pos >> k) & 1, nb = (neg >> k) & 1;
-        dl[k] = (pb == nb) ? 0.0f : (pb ? vpos : -vpos);
+    for (int k = 0; k < 8; ++k) {
+      const uint32_t kb = (c16 >> (4 * (k >> 1) + (k & 1))) & 1u, nb = (c16 >> (4 * (k >> 1) + (k & 1) + 2)) & 1u;
+      if (hp.has_wd) {
+        // kept elements: (kept, neg) = (1,0) sign +1, (1,1) sign -1, (0,1) sign 0
+        const float sgn = kb ? (nb ? -1.0f : 1.0f) : 0.0f;
+        const float dv = __fmaf_rn(pvals[k], hp.wd, sgn);
+        dl[k] = (kb | nb) ? __fmul_rn(__fdiv_rn(dv, denom), hp.lr) : 0.0f;
+      } else {
+        dl[k] = kb ? (nb ? -vpos : vpos) : 0.0f;
       }
     }
     update8<PT>(pbase + (size_t)v * 8 * E::BYTES, cnt, dl, -1.0f, hp.sr != 0, st, d.tensor_id,
@@ -560,6 +766,7 @@ __global__ void __launch_bounds__(NTHREADS, 4) lion_kernel(PlanView pv, LionDev 
   __shared__ __align__(8) uint64_t bar;
   __shared__ int next_s[2];
   __shared__ unsigned red_s[NTHREADS / 32];
+  __shared__ float2 lut_s[16];
   unsigned char* g_s = dyn;
   unsigned char* m_s = dyn + (size_t)CAP * Elems<PT>::BYTES;
   const int tid = threadIdx.x;
@@ -581,7 +788,7 @@ __global__ void __launch_bounds__(NTHREADS, 4) lion_kernel(PlanView pv, LionDev 
     if (t.phase == PH_LION_MAIN)
       lion_main<PT, MK, MIRROR>(pv, hp, t, g_s, m_s, mean_s, rowmax_s, scale_s, sc_s, &bar, parity, red_s, tid);
     else
-      lion_apply<PT, MIRROR>(pv, hp, t, tid);
+      lion_apply<PT, MIRROR>(pv, hp, t, lut_s, tid);
     __syncthreads();
     slot ^= 1;
     cur = next_s[slot];
