@@ -9,6 +9,7 @@
 // turn the codes into the weight write with the tensor-wide rescale 1/max(kept/numel, 1e-8).
 // Quantised momentum is read once and written once; weights are read once and written once.
 #include <mutex>
+#include <type_traits>
 
 #include "kaon_host.h"
 #include "kaon_ops.cuh"
@@ -49,35 +50,13 @@ constexpr uint32_t CODE_KEPT_BITS = 0x3333u;
 
 // ---- packed fp32 pairs (f32x2 arithmetic of sm_100: each lane is an independent IEEE fp32 operation,
 //      so results are those of the scalar instructions; two lanes cost one issue slot) ----
-typedef unsigned long long f32x2;
-__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
-  f32x2 r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-  return r;
-}
-__device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
-  f32x2 d;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-  return d;
-}
-__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
-  f32x2 d;
-  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
-}
-__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
-  f32x2 d;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
-}
-__device__ __forceinline__ f32x2 sub2(f32x2 a, f32x2 b) {
-  f32x2 d;
-  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
-}
+typedef float2 f32x2;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) { return make_float2(lo, hi); }
+__device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) { lo = v.x; hi = v.y; }
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ f32x2 sub2(f32x2 a, f32x2 b) { return __fadd2_rn(a, make_float2(-b.x, -b.y)); }
 // max / min of three (sm_100 takes three inputs in one instruction)
 __device__ __forceinline__ float max3f(float a, float b, float c) {
   float d;
@@ -104,14 +83,30 @@ __device__ __forceinline__ uint32_t sub_bf16x2(uint32_t a, uint32_t b) {
   asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
   return d;
 }
-// maximum over the 16 lanes of this thread's half warp (every lane of the warp calls it; v >= 0)
+// maximum over the 16 lanes of this thread's half warp (every lane of the warp calls it; v >= 0, so
+// the ordering of the bit patterns is that of the values): two whole-warp reductions, one per half
 __device__ __forceinline__ float half_warp_max(float v, int tid) {
-  uint32_t r;
-  asm volatile("redux.sync.max.u32 %0, %1, %2;" : "=r"(r) : "r"(__float_as_uint(v)), "r"((tid & 16) ? 0xffff0000u : 0x0000ffffu));
-  return __uint_as_float(r);
+  const bool upper = (tid & 16) != 0;
+  const uint32_t b = __float_as_uint(v);
+  uint32_t lo, hi;
+  asm volatile("redux.sync.max.u32 %0, %1, 0xffffffff;" : "=r"(lo) : "r"(upper ? 0u : b));
+  asm volatile("redux.sync.max.u32 %0, %1, 0xffffffff;" : "=r"(hi) : "r"(upper ? b : 0u));
+  return __uint_as_float(upper ? hi : lo);
+}
+// Stores to global memory through a generic pointer.  Volatile, so they keep their order among themselves
+// and against fences and barriers; without a memory clobber, so the values the surrounding loop keeps in
+// registers stay there.
+__device__ __forceinline__ void stg_u32(void* p, uint32_t v) {
+  asm volatile("st.global.u32 [%0], %1;" ::"l"(__cvta_generic_to_global(p)), "r"(v));
+}
+__device__ __forceinline__ void stg_u16(void* p, uint32_t v) {
+  asm volatile("st.global.u16 [%0], %1;" ::"l"(__cvta_generic_to_global(p)), "h"((unsigned short)v));
+}
+__device__ __forceinline__ void stg_f32(void* p, float v) {
+  asm volatile("st.global.f32 [%0], %1;" ::"l"(__cvta_generic_to_global(p)), "f"(v));
 }
 // a / 7 correctly rounded without the division unit: quotient estimate, exact residual, one correction.
-// Equal to the IEEE quotient for every a in [1e-12, FLT_MAX] (checked exhaustively on the host).
+// Equal to the IEEE quotient for every a in [1e-12, FNTHREADS_MAX] (checked exhaustively on the host).
 __device__ __forceinline__ float div7_exact(float a) {
   const float r7 = 0.142857149243354797363281250f;  // RN(1/7)
   const float q0 = __fmul_rn(a, r7);
@@ -130,7 +125,6 @@ __device__ __forceinline__ unsigned lion_fast4_bf16(const PlanView& pv, const Li
                                                     const unsigned char* m_s, const uint32_t* mean2_s,
                                                     const float* sc_s, int tid) {
   const int nvec = t.n >> 3;
-  const int nvec_pad = (nvec + 31) & ~31;
   uint16_t* cdst = reinterpret_cast<uint16_t*>(pv.codes + d.code_off + (t.e0 >> 2));
   uint32_t* mdst = reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned char*>(d.m) + (t.e0 >> 1));
   const uint32_t* msrc = reinterpret_cast<const uint32_t*>(m_s);
@@ -140,8 +134,10 @@ __device__ __forceinline__ unsigned lion_fast4_bf16(const PlanView& pv, const Li
   const f32x2 M8 = pack2(12582920.0f, 12582920.0f);     // 1.5 * 2^23 + 8: adding it rounds to integer, half to even
   const f32x2 K256 = pack2(256.0f, 256.0f);
   unsigned kept_local = 0;
-  for (int v = tid; v < nvec_pad; v += NTHREADS) {
-    const bool act = v < nvec;
+  // one trip: eight elements of this thread.  GUARD = false: every lane of the warp has a vector.
+  auto trip = [&](const int v, auto guard_tag) {
+    constexpr bool GUARD = decltype(guard_tag)::value;
+    const bool act = !GUARD || v < nvec;
     uint32_t gw[4] = {0u, 0u, 0u, 0u};
     uint32_t w = 0x88888888u;
     float sc_old = 1.0f;
@@ -194,24 +190,14 @@ __device__ __forceinline__ unsigned lion_fast4_bf16(const PlanView& pv, const Li
     worst = max3f(worst, fabsf(e[3]), fabsf(e[4]));
     worst = max3f(worst, fabsf(e[5]), fabsf(e[6]));
     worst = fmaxf(worst, fabsf(e[7]));
-    uint32_t word;
-    if (worst > 0.5f - 1e-4f) {  // some product sits near a rounding boundary: redo with the true division
-      word = 0;
-#pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        const int qi = min(max((int)rintf(__fdiv_rn(n[k], sc)), -7), 7);
-        word |= (uint32_t)(qi + 8) << (4 * k);
-      }
-    } else {
-      // t_k = -q_k in [-7, 7]: sum_k (8 - t_k) 16^k = 0x8888 - (t0 + 16 t1 + 256 t2 + 4096 t3), exact in fp32;
-      // adding 2^23 leaves it in the low 16 mantissa bits
-      float xl, xh, yl, yh;
-      unpack2(fma2(T[1], K256, T[0]), xl, xh);   // (t0 + 256 t2, t1 + 256 t3)
-      unpack2(fma2(T[3], K256, T[2]), yl, yh);
-      const float lo4 = __fsub_rn(8423560.0f, __fmaf_rn(xh, 16.0f, xl));  // 2^23 + 0x8888 - ...
-      const float hi4 = __fsub_rn(8423560.0f, __fmaf_rn(yh, 16.0f, yl));
-      word = __byte_perm(__float_as_uint(lo4), __float_as_uint(hi4), 0x5410);
-    }
+    // t_k = -q_k in [-7, 7]: sum_k (8 - t_k) 16^k = 0x8888 - (t0 + 16 t1 + 256 t2 + 4096 t3), exact in fp32;
+    // adding 2^23 leaves it in the low 16 mantissa bits
+    float xl, xh, yl, yh;
+    unpack2(fma2(T[1], K256, T[0]), xl, xh);   // (t0 + 256 t2, t1 + 256 t3)
+    unpack2(fma2(T[3], K256, T[2]), yl, yh);
+    const float lo4 = __fsub_rn(8423560.0f, __fmaf_rn(xh, 16.0f, xl));  // 2^23 + 0x8888 - ...
+    const float hi4 = __fsub_rn(8423560.0f, __fmaf_rn(yh, 16.0f, yl));
+    uint32_t word = prmt(__float_as_uint(lo4), __float_as_uint(hi4), 0x5410u);
     // ---- update codes: kept <=> c*g > 0; the update's sign is then the sign of g ----
     float a[8];
 #pragma unroll
@@ -220,38 +206,45 @@ __device__ __forceinline__ unsigned lion_fast4_bf16(const PlanView& pv, const Li
     amin = min3f(amin, fabsf(a[3]), fabsf(a[4]));
     amin = min3f(amin, fabsf(a[5]), fabsf(a[6]));
     amin = fminf(amin, fabsf(a[7]));
-    uint32_t code16;
-    if (amin > 0.0f) {
-      // bytes 0xFF where the product is negative (masked out) / where g is negative
-      const uint32_t am_lo = prmt(prmt(__float_as_uint(a[0]), __float_as_uint(a[1]), 0x00FBu),
-                                  prmt(__float_as_uint(a[2]), __float_as_uint(a[3]), 0x00FBu), 0x5410u);
-      const uint32_t am_hi = prmt(prmt(__float_as_uint(a[4]), __float_as_uint(a[5]), 0x00FBu),
-                                  prmt(__float_as_uint(a[6]), __float_as_uint(a[7]), 0x00FBu), 0x5410u);
-      const uint32_t gm_lo = prmt(gw[0], gw[1], 0xFDB9u), gm_hi = prmt(gw[2], gw[3], 0xFDB9u);
-      // element b of each group of four lives in byte b: kept bits 0,1,4,5 and neg bits 2,3,6,7 of the code byte
-      const uint32_t t_lo = ~am_lo & ((gm_lo & 0x80400804u) | 0x20100201u);
-      const uint32_t t_hi = ~am_hi & ((gm_hi & 0x80400804u) | 0x20100201u);
-      // the four bytes of t have disjoint bits: their sum (top byte of t * 0x01010101) is their OR
-      code16 = __byte_perm(t_lo * 0x01010101u, t_hi * 0x01010101u, 0x0073);
-    } else {
-      // a zero gradient, a zero direction or an underflowing product: decide element by element
+    // bytes 0xFF where the product is negative (masked out) / where g is negative
+    const uint32_t am_lo = prmt(prmt(__float_as_uint(a[0]), __float_as_uint(a[1]), 0x00FBu),
+                                prmt(__float_as_uint(a[2]), __float_as_uint(a[3]), 0x00FBu), 0x5410u);
+    const uint32_t am_hi = prmt(prmt(__float_as_uint(a[4]), __float_as_uint(a[5]), 0x00FBu),
+                                prmt(__float_as_uint(a[6]), __float_as_uint(a[7]), 0x00FBu), 0x5410u);
+    const uint32_t gm_lo = prmt(gw[0], gw[1], 0xFDB9u), gm_hi = prmt(gw[2], gw[3], 0xFDB9u);
+    // element b of each group of four lives in byte b: kept bits 0,1,4,5 and neg bits 2,3,6,7 of the code byte
+    const uint32_t t_lo = ~am_lo & ((gm_lo & 0x80400804u) | 0x20100201u);
+    const uint32_t t_hi = ~am_hi & ((gm_hi & 0x80400804u) | 0x20100201u);
+    // the four bytes of t have disjoint bits: their sum (top byte of t * 0x01010101) is their OR
+    uint32_t code16 = prmt(t_lo * 0x01010101u, t_hi * 0x01010101u, 0x0073u);
+    // Rare cases, decided element by element: a product n*inv within 1e-5 of a rounding boundary (the
+    // reciprocal is good to 2^-22, so |n*inv - n/sc| < 2e-6: farther out both round alike) is redone with
+    // the true division; a zero gradient, a zero direction or an underflowing product c*g gets its
+    // update codes from the comparisons themselves.
+    if (worst > 0.5f - 1e-5f || !(amin > 0.0f)) {
       float c[8], g[8];
 #pragma unroll
       for (int j = 0; j < 4; ++j) { unpack2(C[j], c[2 * j], c[2 * j + 1]); unpack2(G[j], g[2 * j], g[2 * j + 1]); }
+      word = 0;
       code16 = 0;
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
+        const int qi = min(max((int)rintf(__fdiv_rn(n[k], sc)), -7), 7);
+        word |= (uint32_t)(qi + 8) << (4 * k);
         if (c[k] > 0.0f && g[k] > 0.0f) code16 |= code_bit(k);
         if (c[k] < 0.0f && g[k] < 0.0f) code16 |= 5u * code_bit(k);
       }
     }
     if (act) {
-      mdst[v] = word;
-      if ((v & 15) == 0) d.m_scale[blk0 + (v >> 4)] = sc;
-      cdst[v] = (uint16_t)code16;
+      stg_u32(mdst + v, word);
+      if ((v & 15) == 0) stg_f32(d.m_scale + blk0 + (v >> 4), sc);
+      stg_u16(cdst + v, code16);
       kept_local += __popc(code16 & CODE_KEPT_BITS);
     }
-  }
+  };
+  const int nfull = nvec & ~31;  // vectors in trips whose whole warp is active
+  for (int v = tid; v < nfull; v += NTHREADS) trip(v, std::false_type{});
+  if (nfull != nvec && tid < 32) trip(nfull + tid, std::true_type{});
   return kept_local;
 }
 
@@ -425,10 +418,21 @@ __device__ void lion_main(const PlanView& pv, const LionDev& hp, const Task& t, 
       const unsigned char* rowp = g_s + (size_t)r * C * E::BYTES;
       float s = 0.0f;
       if ((C & 7) == 0) {
-        for (int v = lane; v < (C >> 3); v += 32) {
-          float x[8];
-          E::load8(rowp + (size_t)v * 8 * E::BYTES, x);
-          s += ((x[0] + x[1]) + (x[2] + x[3])) + ((x[4] + x[5]) + (x[6] + x[7]));
+        if constexpr (E::IS_BF16) {
+          f32x2 acc = pack2(0.0f, 0.0f), acc2 = pack2(0.0f, 0.0f);
+          for (int v = lane; v < (C >> 3); v += 32) {
+            const uint4 q = *reinterpret_cast<const uint4*>(rowp + (size_t)v * 16);
+            acc = add2(acc, add2(pack2(bf16lo(q.x), bf16hi(q.x)), pack2(bf16lo(q.y), bf16hi(q.y))));
+            acc2 = add2(acc2, add2(pack2(bf16lo(q.z), bf16hi(q.z)), pack2(bf16lo(q.w), bf16hi(q.w))));
+          }
+          acc = add2(acc, acc2);
+          s = acc.x + acc.y;
+        } else {
+          for (int v = lane; v < (C >> 3); v += 32) {
+            float x[8];
+            E::load8(rowp + (size_t)v * 8 * E::BYTES, x);
+            s += ((x[0] + x[1]) + (x[2] + x[3])) + ((x[4] + x[5]) + (x[6] + x[7]));
+          }
         }
       } else {
         for (int i = lane; i < C; i += 32) s += E::load1(rowp, i);
@@ -650,9 +654,9 @@ __device__ void lion_main(const PlanView& pv, const LionDev& hp, const Task& t, 
     for (int o = 16; o > 0; o >>= 1) kept_local += __shfl_xor_sync(0xffffffffu, kept_local, o);
     if ((tid & 31) == 0) red_s[tid >> 5] = kept_local;
   }
-  __threadfence();
   __syncthreads();
   if (tid == 0) {
+    __threadfence();  // the CTA's stores of this item (ordered before the barrier) go out before the signal
     if (hp.cautious) {
       unsigned tot = 0;
       for (int w = 0; w < NTHREADS / 32; ++w) tot += red_s[w];
@@ -686,12 +690,14 @@ __device__ void lion_apply(const PlanView& pv, const LionDev& hp, const Task& t,
   const bool fast_sr = E::IS_BF16 && hp.sr && !hp.has_wd;
   int v_begin = tid;
   if (fast_sr) {
-    if (tid < 16) {  // nibble = kept_e | kept_o << 1 | neg_e << 2 | neg_o << 3
-      const float de = (tid & 1) ? ((tid & 4) ? -vpos : vpos) : 0.0f;
-      const float dd = (tid & 2) ? ((tid & 8) ? -vpos : vpos) : 0.0f;
-      lut_s[tid] = make_float2(de, dd);
+    lut_s += (tid >> 5) * 16;  // this warp's copy of the table
+    const int lane = tid & 31;
+    if (lane < 16) {  // nibble = kept_e | kept_o << 1 | neg_e << 2 | neg_o << 3
+      const float de = (lane & 1) ? ((lane & 4) ? -vpos : vpos) : 0.0f;
+      const float dd = (lane & 2) ? ((lane & 8) ? -vpos : vpos) : 0.0f;
+      lut_s[lane] = make_float2(de, dd);
     }
-    __syncthreads();
+    __syncwarp();
     // full vectors, four per trip: all loads are issued before the first use.  Per pair: the update pair
     // from the table, p - update as one packed subtract, 16 noise bits added below the kept mantissa.
     const int nfull = n >> 3;
@@ -766,7 +772,7 @@ __global__ void __launch_bounds__(NTHREADS, 4) lion_kernel(PlanView pv, LionDev 
   __shared__ __align__(8) uint64_t bar;
   __shared__ int next_s[2];
   __shared__ unsigned red_s[NTHREADS / 32];
-  __shared__ float2 lut_s[16];
+  __shared__ float2 lut_s[(NTHREADS / 32) * 16];
   unsigned char* g_s = dyn;
   unsigned char* m_s = dyn + (size_t)CAP * Elems<PT>::BYTES;
   const int tid = threadIdx.x;
@@ -785,11 +791,12 @@ __global__ void __launch_bounds__(NTHREADS, 4) lion_kernel(PlanView pv, LionDev 
   while (cur < pv.n_tasks) {
     claim_next(slot ^ 1);
     const Task t = pv.tasks[cur];
-    if (t.phase == PH_LION_MAIN)
+    if (t.phase == PH_LION_MAIN) {
       lion_main<PT, MK, MIRROR>(pv, hp, t, g_s, m_s, mean_s, rowmax_s, scale_s, sc_s, &bar, parity, red_s, tid);
-    else
+    } else {  // (a MAIN item ends with a barrier of its own)
       lion_apply<PT, MIRROR>(pv, hp, t, lut_s, tid);
-    __syncthreads();
+      __syncthreads();
+    }
     slot ^= 1;
     cur = next_s[slot];
   }
