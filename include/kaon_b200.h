@@ -34,7 +34,7 @@ extern "C" {
 
 /* bf16_method (reference src/kaon/_backend.py:82-122) */
 #define KAON_W_NONE 0 /* p - bf16(delta), round to nearest even */
-#define KAON_W_SR 1   /* stochastic rounding, Philox4x32-10 keyed on (seed, step, tensor id, element) */
+#define KAON_W_SR 1   /* stochastic rounding, Philox4x32-7 keyed on (seed, step, tensor id, element) */
 #define KAON_W_KAHAN 2 /* compensated bf16 write with the per-tensor `shift` buffer (_backend.py:89-94) */
 
 /* optimizer kinds a plan can be built for */

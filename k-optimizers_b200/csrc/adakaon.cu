@@ -30,6 +30,7 @@
 #include "adakaon_dev.h"
 #include "kaon_host.h"
 #include "kaon_ops.cuh"
+#include "kaon_packed.cuh"
 
 namespace kaon {
 
@@ -1680,6 +1681,289 @@ __global__ void __launch_bounds__(APPLY_THREADS, 4) adakaon_apply_kernel(PlanVie
       unsigned char* pbase = reinterpret_cast<unsigned char*>(d.p) + t.e0 * E::BYTES;
       const int nvec = n >> 3;
       const int nvec_pad = (nvec + 31) & ~31;
+      // ---- fast path: bf16 weights, int8 / 4-bit momentum, stochastic-rounding write (or the COUNT stage),
+      //      no Kahan buffer.  Same arithmetic as the general loop below, element for element, on packed
+      //      pairs (f32x2), with the cautious mask and the quantised codes gathered by byte permutes and
+      //      one exactness check per vector; the rare vectors that fail a check are redone the plain way. ----
+      constexpr bool FASTABLE = E::IS_BF16 && !MUON && (MK == KAON_M_INT8 || MK == KAON_M_4BIT);
+      bool fast = false;
+      if constexpr (FASTABLE) fast = !hp.kahan && (!APPLY || sr);
+      if constexpr (FASTABLE) if (fast) {
+        const f32x2 DIVN = pack2(-ch.div, -ch.div), RCPD = pack2(ch.rcp_div, ch.rcp_div);
+        const f32x2 SCALE = pack2(hp.upd_scale, hp.upd_scale);
+        const f32x2 W1 = pack2(hp.w1, hp.w1), W1M1 = pack2(hp.w1m1, hp.w1m1);
+        const f32x2 LRWD = pack2(hp.lrwd, hp.lrwd);
+        const f32x2 DENN = pack2(-denom, -denom), RCPN = pack2(rcp_denom, rcp_denom);
+        const uint32_t* gsm = reinterpret_cast<const uint32_t*>(g_s);
+        const uint32_t* psm = reinterpret_cast<const uint32_t*>(p_s);
+        const long long blk0 = t.e0 >> 7;
+        const uint64_t q0 = (uint64_t)(t.e0 >> 3);
+        auto clamp2 = [](f32x2 e, float b) { return pack2(fminf(fmaxf(e.x, -b), b), fminf(fmaxf(e.y, -b), b)); };
+        // one stochastic-rounding write of eight weights held as four pairs: P <- trunc16(bits(P + D) + noise)
+        auto sr_write = [&](f32x2 P[4], const f32x2 D[4], const SrStream& stream, uint64_t q) {
+          uint32_t nz[4];
+          stream.draw8(d.tensor_id, q, nz);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const f32x2 r = add2(P[j], D[j]);
+            P[j] = pack2(__uint_as_float((__float_as_uint(r.x) + (nz[j] & 0xffffu)) & 0xFFFF0000u),
+                         __uint_as_float((__float_as_uint(r.y) + (nz[j] >> 16)) & 0xFFFF0000u));
+          }
+        };
+        auto trip = [&](const int v, auto guard_tag, auto small_tag) {
+          constexpr bool GUARD = decltype(guard_tag)::value;
+          constexpr bool SMALL_W1 = decltype(small_tag)::value;
+          const bool act = !GUARD || v < nvec;
+          const int vv = act ? v : 0;
+          const unsigned i = (unsigned)col0 + (unsigned)vv * 8u;
+          const int r = row_of(i, d);
+          const int row = (int)row0 + r;
+          const int col = (int)i - r * C;
+          const float rf = __ldcg(rfac + row);
+          const float4 c0v = __ldcg(reinterpret_cast<const float4*>(cfac + col));
+          const float4 c1v = __ldcg(reinterpret_cast<const float4*>(cfac + col + 4));
+          const uint4 gq = *reinterpret_cast<const uint4*>(gsm + (size_t)vv * 4);
+          uint32_t gw[4] = {gq.x, gq.y, gq.z, gq.w};
+          if (gc) {
+            const float mu = __ldcg(mean + row);
+            const uint32_t mu2 = pack_bf16_rn(mu, mu);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) gw[j] = sub_bf16x2(gw[j], mu2);
+          }
+          f32x2 P[4];
+          if (need_p) {
+            const uint4 pq = *reinterpret_cast<const uint4*>(psm + (size_t)vv * 4);
+            P[0] = pack2(bf16lo(pq.x), bf16hi(pq.x)); P[1] = pack2(bf16lo(pq.y), bf16hi(pq.y));
+            P[2] = pack2(bf16lo(pq.z), bf16hi(pq.z)); P[3] = pack2(bf16lo(pq.w), bf16hi(pq.w));
+          } else {
+            P[0] = P[1] = P[2] = P[3] = pack2(0.0f, 0.0f);
+          }
+          // ---- old momentum ----
+          f32x2 MO[4];
+          float sc_old;
+          if constexpr (MK == KAON_M_4BIT) {
+            sc_old = d.m_scale[blk0 + (vv >> 4)];
+            const uint32_t w = reinterpret_cast<const uint32_t*>(m_s)[vv];
+            const uint32_t wl = w & 0x0F0F0F0Fu, wh = (w >> 4) & 0x0F0F0F0Fu;
+            const f32x2 BIAS = pack2(-8388616.0f, -8388616.0f), SC = pack2(sc_old, sc_old);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              MO[j] = mul2(add2(pack2(__uint_as_float(prmt(wl, 0x4B000000u, 0x7540u | (uint32_t)j)),
+                                      __uint_as_float(prmt(wh, 0x4B000000u, 0x7540u | (uint32_t)j))), BIAS), SC);
+          } else {
+            sc_old = APPLY ? __ldcg(oldsc + row) : d.m_scale[row];
+            const uint2 w = reinterpret_cast<const uint2*>(m_s)[vv];
+            const uint32_t x0 = w.x ^ 0x80808080u, x1 = w.y ^ 0x80808080u;  // code + 128 in every byte
+            const f32x2 BIAS = pack2(-8388736.0f, -8388736.0f), SC = pack2(sc_old, sc_old);  // -(2^23 + 128)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t x = j < 2 ? x0 : x1;
+              const uint32_t b = (uint32_t)(2 * (j & 1));
+              MO[j] = mul2(add2(pack2(__uint_as_float(prmt(x, 0x4B000000u, 0x7540u | b)),
+                                      __uint_as_float(prmt(x, 0x4B000000u, 0x7540u | (b + 1u)))), BIAS), SC);
+            }
+          }
+          const uint64_t q = q0 + (uint64_t)vv;
+          // a momentum that decodes to NaN or infinity (a corrupt scale) keeps the reference's nan_to_num
+          const bool wild = !(fabsf(sc_old) <= 3.0e38f);
+          if (hp.remove && need_p) {
+            const f32x2 AR = pack2(hp.a_remove, hp.a_remove);
+            f32x2 Dr[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              f32x2 e = mul2(MO[j], AR);
+              if (wild) { if (e.x != e.x) e.x = 0.0f; if (e.y != e.y) e.y = 0.0f; }
+              Dr[j] = clamp2(e, hp.b_remove);
+            }
+            sr_write(P, Dr, s_rem, q);
+          }
+          // ---- update chain: u = ((g r) c) / divisor * scale; m' = lerp(m, u); delta = m' + (lr wd) p ----
+          // (a divisor of 1 and a zero weight decay go through the same operations: x/1 and fma(p, 0, m')
+          //  give x and m' back; a delta of -0 that becomes +0 is masked out or subtracted either way)
+          const f32x2 RF = pack2(rf, rf);
+          const f32x2 CF[4] = {pack2(c0v.x, c0v.y), pack2(c0v.z, c0v.w), pack2(c1v.x, c1v.y), pack2(c1v.z, c1v.w)};
+          f32x2 MN[4], DV[4];
+          float a[8];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const f32x2 G = pack2(bf16lo(gw[j]), bf16hi(gw[j]));
+            f32x2 U = mul2(mul2(G, RF), CF[j]);
+            const f32x2 qq = mul2(U, RCPD);
+            U = mul2(fma2(fma2(qq, DIVN, U), RCPD, qq), SCALE);
+            const f32x2 diff = sub2(U, MO[j]);
+            MN[j] = SMALL_W1 ? fma2(W1, diff, MO[j]) : fma2(W1M1, diff, U);
+            DV[j] = fma2(P[j], LRWD, MN[j]);
+            unpack2(mul2(DV[j], G), a[2 * j], a[2 * j + 1]);
+          }
+          // ---- cautious mask: kept <=> delta * g > 0 (sign bits; a zero or underflowing product is rare
+          //      and decided by the comparison itself) ----
+          float amin = min3f(fabsf(a[0]), fabsf(a[1]), fabsf(a[2]));
+          amin = min3f(amin, fabsf(a[3]), fabsf(a[4]));
+          amin = min3f(amin, fabsf(a[5]), fabsf(a[6]));
+          amin = fminf(amin, fabsf(a[7]));
+          float amax = max3f(fabsf(MN[0].x), fabsf(MN[0].y), fabsf(MN[1].x));
+          amax = max3f(amax, fabsf(MN[1].y), fabsf(MN[2].x));
+          amax = max3f(amax, fabsf(MN[2].y), fabsf(MN[3].x));
+          amax = fmaxf(amax, fabsf(MN[3].y));
+          if constexpr (!APPLY) {
+            unsigned kept = 0;
+            if (amin > 0.0f) {
+              const uint32_t am_lo = prmt(prmt(__float_as_uint(a[0]), __float_as_uint(a[1]), 0x00FBu),
+                                          prmt(__float_as_uint(a[2]), __float_as_uint(a[3]), 0x00FBu), 0x5410u);
+              const uint32_t am_hi = prmt(prmt(__float_as_uint(a[4]), __float_as_uint(a[5]), 0x00FBu),
+                                          prmt(__float_as_uint(a[6]), __float_as_uint(a[7]), 0x00FBu), 0x5410u);
+              kept = 8u - (unsigned)__popc(am_lo & 0x01010101u) - (unsigned)__popc(am_hi & 0x01010101u);
+            } else {
+#pragma unroll
+              for (int k = 0; k < 8; ++k) kept += a[k] > 0.0f ? 1u : 0u;
+            }
+            if (act) kept_local += kept;
+            if constexpr (MK == KAON_M_INT8) {
+              unsigned bits = act ? __float_as_uint(amax) : 0u;
+              const int row_l0 = __shfl_sync(0xffffffffu, row, 0);
+              if (__all_sync(0xffffffffu, !act || row == row_l0)) {
+                bits = __reduce_max_sync(0xffffffffu, bits);
+                if ((tid & 31) == 0 && bits) atomicMax(rowmax + row_l0, bits);
+              } else if (act) {
+                atomicMax(rowmax + row, bits);
+              }
+            }
+            return;
+          } else {
+            // ---- the update: delta, or under the cautious mask (delta if kept else 0) / denom ----
+            f32x2 F[4];
+            if (hp.cautious) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const f32x2 qq = mul2(DV[j], RCPN);
+                const f32x2 f = fma2(fma2(qq, DENN, DV[j]), RCPN, qq);
+                // masked out where the product delta * g is negative (its sign bit spread over the word)
+                F[j] = pack2(__uint_as_float(__float_as_uint(f.x) & ~(uint32_t)((int)__float_as_uint(a[2 * j]) >> 31)),
+                             __uint_as_float(__float_as_uint(f.y) & ~(uint32_t)((int)__float_as_uint(a[2 * j + 1]) >> 31)));
+              }
+              if (!(amin > 0.0f)) {  // some product is zero: those elements are masked out as well
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  if (!(a[2 * j] > 0.0f)) F[j].x = 0.0f;
+                  if (!(a[2 * j + 1] > 0.0f)) F[j].y = 0.0f;
+                }
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) F[j] = DV[j];
+            }
+            // ---- quantise and store the new momentum; MD = the momentum as stored, decoded ----
+            f32x2 MD[4];
+            float sc;
+            if constexpr (MK == KAON_M_4BIT) {
+              const float am = fmaxf(half_warp_max(act ? amax : 0.0f, tid), 1e-12f);
+              __syncwarp();  // every lane of the block has read the old scale before it is replaced
+              sc = div7_exact(am);
+            } else {
+              sc = div127_exact(fmaxf(__uint_as_float(__ldcg(rowmax + row)), 1e-12f));
+            }
+            float inv;
+            asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv) : "f"(sc));
+            const f32x2 INV = pack2(inv, inv), NSC = pack2(-sc, -sc);
+            // r = rint(n*inv) (+8) + magic in one rounding; T = -rint(n*inv); e = n*inv - rint(n*inv) exactly
+            constexpr float MAGIC = MK == KAON_M_4BIT ? 12582920.0f : 12582912.0f;
+            const f32x2 MG = pack2(MAGIC, MAGIC);
+            f32x2 T[4], R[4];
+            float e8[8];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              R[j] = fma2(MN[j], INV, MG);
+              T[j] = sub2(MG, R[j]);
+              unpack2(fma2(MN[j], INV, T[j]), e8[2 * j], e8[2 * j + 1]);
+              MD[j] = mul2(T[j], NSC);
+            }
+            float worst = max3f(fabsf(e8[0]), fabsf(e8[1]), fabsf(e8[2]));
+            worst = max3f(worst, fabsf(e8[3]), fabsf(e8[4]));
+            worst = max3f(worst, fabsf(e8[5]), fabsf(e8[6]));
+            worst = fmaxf(worst, fabsf(e8[7]));
+            uint32_t w0, w1 = 0u;
+            if constexpr (MK == KAON_M_4BIT) {
+              const f32x2 K256 = pack2(256.0f, 256.0f);
+              const f32x2 X = fma2(T[1], K256, T[0]), Y = fma2(T[3], K256, T[2]);
+              const float lo4 = __fsub_rn(8423560.0f, __fmaf_rn(X.y, 16.0f, X.x));
+              const float hi4 = __fsub_rn(8423560.0f, __fmaf_rn(Y.y, 16.0f, Y.x));
+              w0 = prmt(__float_as_uint(lo4), __float_as_uint(hi4), 0x5410u);
+            } else {  // the low byte of every r is the code in two's complement
+              w0 = prmt(prmt(__float_as_uint(R[0].x), __float_as_uint(R[0].y), 0x0040u),
+                        prmt(__float_as_uint(R[1].x), __float_as_uint(R[1].y), 0x0040u), 0x5410u);
+              w1 = prmt(prmt(__float_as_uint(R[2].x), __float_as_uint(R[2].y), 0x0040u),
+                        prmt(__float_as_uint(R[3].x), __float_as_uint(R[3].y), 0x0040u), 0x5410u);
+            }
+            // Rare: a product n*inv too close to a rounding boundary to trust the reciprocal (it is good to
+            // 2^-22: |n*inv - n/sc| < 127 * 2^-22 = 3e-5, 7 * 2^-22 for 4 bits), or a scale that is not
+            // finite: the codes of this vector again, by the true division.
+            if (worst > 0.5f - (MK == KAON_M_4BIT ? 1e-5f : 1e-4f) || !(sc <= 3.0e38f)) {
+              const float inv2 = __fdividef(1.0f, sc);
+              float n8[8], md8[8];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) unpack2(MN[j], n8[2 * j], n8[2 * j + 1]);
+              w0 = 0u; w1 = 0u;
+#pragma unroll
+              for (int k = 0; k < 8; ++k) {
+                if constexpr (MK == KAON_M_4BIT) {
+                  const int qi = min(max((int)quant_round(n8[k], sc, inv2, 1e-4f), -7), 7);
+                  md8[k] = __fmul_rn((float)qi, sc);
+                  w0 |= (uint32_t)(qi + 8) << (4 * k);
+                } else {
+                  const int qi = min(max((int)quant_round(n8[k], sc, inv2, 1e-3f), -127), 127);
+                  md8[k] = __fmul_rn((float)qi, sc);
+                  const uint32_t byte = (uint32_t)(qi & 0xFF);
+                  if (k < 4) w0 |= byte << (8 * k); else w1 |= byte << (8 * (k - 4));
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < 4; ++j) MD[j] = pack2(md8[2 * j], md8[2 * j + 1]);
+            }
+            if (act) {
+              if constexpr (MK == KAON_M_4BIT) {
+                stg_u32(reinterpret_cast<unsigned char*>(d.m) + (t.e0 >> 1) + (size_t)v * 4, w0);
+                if ((v & 15) == 0) stg_f32(d.m_scale + blk0 + (v >> 4), sc);
+              } else {
+                *reinterpret_cast<uint2*>(reinterpret_cast<unsigned char*>(d.m) + t.e0 + (size_t)v * 8) = make_uint2(w0, w1);
+                if (col == 0) d.m_scale[row] = sc;
+              }
+            }
+            // ---- weights: p <- SR(p - update), then the Nekaon climb from the momentum as stored ----
+#pragma unroll
+            for (int j = 0; j < 4; ++j) F[j] = pack2(-F[j].x, -F[j].y);
+            sr_write(P, F, s_upd, q);
+            if (hp.climb) {
+              const f32x2 AC = pack2(hp.a_climb, hp.a_climb);
+              const bool wild2 = !(sc <= 3.0e38f);
+              f32x2 Dc[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                f32x2 e = mul2(MD[j], AC);
+                if (wild2) { if (e.x != e.x) e.x = 0.0f; if (e.y != e.y) e.y = 0.0f; }
+                Dc[j] = clamp2(e, hp.b_climb);
+              }
+              sr_write(P, Dc, s_clb, q);
+            }
+            if (act) {
+              const uint4 out = make_uint4(prmt(__float_as_uint(P[0].x), __float_as_uint(P[0].y), 0x7632u),
+                                           prmt(__float_as_uint(P[1].x), __float_as_uint(P[1].y), 0x7632u),
+                                           prmt(__float_as_uint(P[2].x), __float_as_uint(P[2].y), 0x7632u),
+                                           prmt(__float_as_uint(P[3].x), __float_as_uint(P[3].y), 0x7632u));
+              *reinterpret_cast<uint4*>(pbase + (size_t)v * 16) = out;
+              mirror16(&pv.peers, pbase + (size_t)v * 16, out);
+            }
+          }
+        };
+        const int nfull = nvec & ~31;
+        if (hp.small_w1) {
+          for (int v = tid; v < nfull; v += APPLY_THREADS) trip(v, std::false_type{}, std::true_type{});
+          if (nfull != nvec && tid < 32) trip(nfull + tid, std::true_type{}, std::true_type{});
+        } else {
+          for (int v = tid; v < nfull; v += APPLY_THREADS) trip(v, std::false_type{}, std::false_type{});
+          if (nfull != nvec && tid < 32) trip(nfull + tid, std::true_type{}, std::false_type{});
+        }
+      }
+      if (!fast)
       for (int v = tid; v < nvec_pad; v += APPLY_THREADS) {
         const bool act = v < nvec;
         const int vv = act ? v : 0;

@@ -55,7 +55,10 @@ __device__ __forceinline__ float quant_round(float m, float scale, float inv, fl
   return q;
 }
 
-// ----------------------------------------------------------------------------- Philox4x32-10
+// ----------------------------------------------------------------------------- Philox4x32-7
+// Round function and key schedule of Salmon et al. 2011; the stochastic-rounding stream runs seven
+// rounds (the smallest count its authors report as passing BigCrush), as the CPU oracle does.
+#define KAON_PHILOX_ROUNDS 7
 
 struct Philox {
   uint32_t k0, k1;
@@ -63,7 +66,7 @@ struct Philox {
                                              uint32_t out[4]) const {
     uint32_t a = k0, b = k1;
 #pragma unroll
-    for (int r = 0; r < 10; ++r) {
+    for (int r = 0; r < KAON_PHILOX_ROUNDS; ++r) {
       if (r) {
         a += 0x9E3779B9u;
         b += 0xBB67AE85u;

@@ -18,7 +18,8 @@ ORACLES = {"Lion": ko.OracleLion, "Adakaon": ko.OracleAdakaon, "Nekaon": ko.Orac
 
 
 def test_philox_known_answers():
-    # Random123 known-answer vectors for Philox4x32-10
+    # Random123 known-answer vectors for Philox4x32-10: they pin the round function and the key schedule;
+    # the stochastic-rounding stream runs the same function for seven rounds
     assert [hex(x) for x in ko.philox4x32([0] * 4, [0] * 2)] == ["0x6627e8d5", "0xe169c58d", "0xbc57ac4c", "0x9b00dbd8"]
     assert [hex(x) for x in ko.philox4x32([0xFFFFFFFF] * 4, [0xFFFFFFFF] * 2)] == ["0x408f276d", "0x41c83b0e", "0xa20bc7c6", "0x6d5451fd"]
     assert [hex(x) for x in ko.philox4x32([0x243F6A88, 0x85A308D3, 0x13198A2E, 0x03707344], [0xA4093822, 0x299F31D0])] == ["0xd16cfe09", "0x94fdcceb", "0x5001e420", "0x24126ea1"]
