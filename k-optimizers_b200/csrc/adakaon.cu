@@ -452,31 +452,76 @@ __device__ void ada_stats_stream(const PlanView& pv, const AdaDev& hp, const Tas
       const int row = t.row0 + r0 + r;
       const float old = d.stat_a[row];
       float mu = 0.0f;
-      if (gc) {
-        float s = 0.0f;
+      float s2 = 0.0f;
+      if constexpr (E::IS_BF16) {
+        // packed pairs, four 16-byte loads in flight per lane
+        const uint4* rowq = reinterpret_cast<const uint4*>(rowp);
+        auto pairs = [](uint32_t w) { return pack2(bf16lo(w), bf16hi(w)); };
+        if (gc) {
+          f32x2 a0 = pack2(0.0f, 0.0f), a1v = pack2(0.0f, 0.0f);
+          int v = lane;
+          for (; v + 96 < nv; v += 128) {
+            const uint4 q0 = rowq[v], q1 = rowq[v + 32], q2 = rowq[v + 64], q3 = rowq[v + 96];
+            a0 = add2(a0, add2(add2(pairs(q0.x), pairs(q0.y)), add2(pairs(q1.x), pairs(q1.y))));
+            a1v = add2(a1v, add2(add2(pairs(q0.z), pairs(q0.w)), add2(pairs(q1.z), pairs(q1.w))));
+            a0 = add2(a0, add2(add2(pairs(q2.x), pairs(q2.y)), add2(pairs(q3.x), pairs(q3.y))));
+            a1v = add2(a1v, add2(add2(pairs(q2.z), pairs(q2.w)), add2(pairs(q3.z), pairs(q3.w))));
+          }
+          for (; v < nv; v += 32) {
+            const uint4 q0 = rowq[v];
+            a0 = add2(a0, add2(pairs(q0.x), pairs(q0.y)));
+            a1v = add2(a1v, add2(pairs(q0.z), pairs(q0.w)));
+          }
+          const float s = warp_sum((a0.x + a0.y) + (a1v.x + a1v.y));
+          mu = round_bf16(__fdiv_rn(s, (float)C));
+        }
+        const uint32_t mu2 = pack_bf16_rn(mu, mu);
+        const f32x2 EPS = pack2(hp.eps1, hp.eps1);
+        auto sq2 = [&](uint32_t w) {
+          const f32x2 y = pairs(gc ? sub_bf16x2(w, mu2) : w);
+          const f32x2 q = mul2(y, y);
+          return hp.has_eps ? add2(q, EPS) : q;
+        };
+        f32x2 b0 = pack2(0.0f, 0.0f), b1 = pack2(0.0f, 0.0f);
+        int v = lane;
+        for (; v + 96 < nv; v += 128) {
+          const uint4 q0 = rowq[v], q1 = rowq[v + 32], q2 = rowq[v + 64], q3 = rowq[v + 96];
+          b0 = add2(b0, add2(add2(sq2(q0.x), sq2(q0.y)), add2(sq2(q1.x), sq2(q1.y))));
+          b1 = add2(b1, add2(add2(sq2(q0.z), sq2(q0.w)), add2(sq2(q1.z), sq2(q1.w))));
+          b0 = add2(b0, add2(add2(sq2(q2.x), sq2(q2.y)), add2(sq2(q3.x), sq2(q3.y))));
+          b1 = add2(b1, add2(add2(sq2(q2.z), sq2(q2.w)), add2(sq2(q3.z), sq2(q3.w))));
+        }
+        for (; v < nv; v += 32) {
+          const uint4 q0 = rowq[v];
+          b0 = add2(b0, add2(sq2(q0.x), sq2(q0.y)));
+          b1 = add2(b1, add2(sq2(q0.z), sq2(q0.w)));
+        }
+        s2 = warp_sum((b0.x + b0.y) + (b1.x + b1.y));
+      } else {
+        if (gc) {
+          float s = 0.0f;
+          for (int v = lane; v < nv; v += 32) {
+            float x[8];
+            E::load8(rowp + (size_t)v * 8 * E::BYTES, x);
+            s += ((x[0] + x[1]) + (x[2] + x[3])) + ((x[4] + x[5]) + (x[6] + x[7]));
+          }
+          s = warp_sum(s);
+          mu = __fdiv_rn(s, (float)C);
+        }
         for (int v = lane; v < nv; v += 32) {
           float x[8];
           E::load8(rowp + (size_t)v * 8 * E::BYTES, x);
-          s += ((x[0] + x[1]) + (x[2] + x[3])) + ((x[4] + x[5]) + (x[6] + x[7]));
-        }
-        s = warp_sum(s);
-        const float mean = __fdiv_rn(s, (float)C);
-        mu = E::IS_BF16 ? round_bf16(mean) : mean;
-      }
-      float s2 = 0.0f;
-      for (int v = lane; v < nv; v += 32) {
-        float x[8];
-        E::load8(rowp + (size_t)v * 8 * E::BYTES, x);
-        float sq[8];
+          float sq[8];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const float y = centered<PT>(x[k], mu, gc);
-          sq[k] = __fmul_rn(y, y);
-          if (hp.has_eps) sq[k] = __fadd_rn(sq[k], hp.eps1);
+          for (int k = 0; k < 8; ++k) {
+            const float y = centered<PT>(x[k], mu, gc);
+            sq[k] = __fmul_rn(y, y);
+            if (hp.has_eps) sq[k] = __fadd_rn(sq[k], hp.eps1);
+          }
+          s2 += ((sq[0] + sq[1]) + (sq[2] + sq[3])) + ((sq[4] + sq[5]) + (sq[6] + sq[7]));
         }
-        s2 += ((sq[0] + sq[1]) + (sq[2] + sq[3])) + ((sq[4] + sq[5]) + (sq[6] + sq[7]));
+        s2 = warp_sum(s2);
       }
-      s2 = warp_sum(s2);
       if (lane == 0) {
         const float mean = __fdiv_rn(s2, (float)C);
         const float rn = lerp_torch(old, mean, hp.w2, hp.w2m1, hp.small_w2 != 0);
@@ -494,6 +539,31 @@ __device__ void ada_stats_stream(const PlanView& pv, const AdaDev& hp, const Tas
       for (int j = 0; j < VPT; ++j) {
         const int v = v0 + j * AT;
         if (v < nv && (j == 0 || Q == 1)) {
+          if constexpr (E::IS_BF16) {
+            // the same per-element operations on packed pairs (a1[j][2w], a1[j][2w+1] = one pair)
+            const f32x2 EPS = pack2(hp.eps1, hp.eps1);
+            f32x2 A1[4], A2[4];
+#pragma unroll
+            for (int w = 0; w < 4; ++w) { A1[w] = pack2(a1[j][2 * w], a1[j][2 * w + 1]); A2[w] = pack2(a2[j][2 * w], a2[j][2 * w + 1]); }
+#pragma unroll 4
+            for (int r = q; r < nr; r += Q) {
+              const uint4 qv = *reinterpret_cast<const uint4*>(gitem + ((size_t)(r0 + r) * C + (size_t)v * 8) * 2);
+              const float mu = sm.mean_s[r], ri = sm.rfac_s[r];
+              const uint32_t mu2 = pack_bf16_rn(mu, mu);
+              const f32x2 RI = pack2(ri, ri);
+              const uint32_t ww[4] = {qv.x, qv.y, qv.z, qv.w};
+#pragma unroll
+              for (int w = 0; w < 4; ++w) {
+                const uint32_t yw = gc ? sub_bf16x2(ww[w], mu2) : ww[w];
+                const f32x2 y = pack2(bf16lo(yw), bf16hi(yw));
+                const f32x2 sq = mul2(y, y);
+                A1[w] = add2(A1[w], hp.has_eps ? add2(sq, EPS) : sq);
+                A2[w] = add2(A2[w], mul2(sq, RI));
+              }
+            }
+#pragma unroll
+            for (int w = 0; w < 4; ++w) { a1[j][2 * w] = A1[w].x; a1[j][2 * w + 1] = A1[w].y; a2[j][2 * w] = A2[w].x; a2[j][2 * w + 1] = A2[w].y; }
+          } else
           for (int r = q; r < nr; r += Q) {
             float x[8];
             E::load8(gitem + ((size_t)(r0 + r) * C + (size_t)v * 8) * E::BYTES, x);
@@ -551,6 +621,218 @@ __device__ void ada_stats_stream(const PlanView& pv, const AdaDev& hp, const Tas
 __device__ __forceinline__ bool stats_stream_ok(const DevTensor& d, const void* g, int ebytes) {
   return (d.cols & 7) == 0 && d.cols >= 256 && (reinterpret_cast<uintptr_t>(g) & 15) == 0 &&
          (((long long)d.cols * ebytes) & 15) == 0;
+}
+
+// ----------------------------------------------------------------------------- STATS as a launch of its own
+
+// The streaming STATS work item in small CTAs (256 threads, four per SM) for plans whose factored tensors
+// all stream bf16 rows of at least 256 elements: the same outputs as ada_stats_stream (row statistics,
+// centralization means, the item's column partial sums and row-statistic sum), taken with packed-pair
+// arithmetic.  Phase 1: one warp per row, the row streamed twice (mean, then sum of squares).  Phase 2:
+// thread-owned columns over the item's rows, which are in L2 by then; rows narrower than the CTA are
+// shared out over row groups whose partial sums are combined in a fixed order.  FINAL runs in the
+// following launch, so the order of the stream stands in for waiting on the completion counter (which
+// is still raised: the FINAL items look at it).
+constexpr int STT = 256;
+constexpr int ST_MAXROWS = 1024;   // rows of one STATS item at most
+constexpr int ST_VPT = 2;          // column vectors a thread accumulates at a time
+
+__global__ void __launch_bounds__(STT, 4) ada_stats_kernel(PlanView pv, AdaDev hp) {
+  __shared__ uint32_t mean2_s[ST_MAXROWS];  // centralization mean of each row, two bf16 copies
+  __shared__ float rinv_s[ST_MAXROWS];      // 1 / row statistic
+  __shared__ float xs[STT * 16];            // partial sums of the row groups (narrow rows)
+  __shared__ double red[STT / 32];
+  __shared__ int next_s[2];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  auto claim_next = [&](int slot) {
+    if (tid == 0) {
+      const unsigned st = *reinterpret_cast<volatile unsigned*>(pv.status);
+      next_s[slot] = st ? 0x7fffffff : (int)atomicAdd(pv.task_counter, 1u);
+    }
+  };
+  claim_next(0);
+  __syncthreads();
+  int slot_i = 0;
+  int cur = next_s[0];
+  const bool gc = hp.gc != 0 && pv.signal == nullptr;
+  const f32x2 EPS = pack2(hp.eps1, hp.eps1);
+  auto pairs = [](uint32_t w) { return pack2(bf16lo(w), bf16hi(w)); };
+  while (cur < pv.n_tasks) {
+    claim_next(slot_i ^ 1);
+    const Task t = pv.tasks[cur];
+    const DevTensor d = pv.tensors[t.tensor];
+    const unsigned char* g = reinterpret_cast<const unsigned char*>(pv.grads[t.tensor]);
+    if (g != nullptr && pv.signal != nullptr) g = reinterpret_cast<const unsigned char*>(pv.signal[t.tensor]);
+    const bool ok = g != nullptr;
+    const int C = d.cols, nv = C >> 3, nrows = t.n / C;
+    double rowsum = 0.0;
+    const uint4* gitem = reinterpret_cast<const uint4*>(g + (ok ? t.e0 * 2 : 0));
+    float* slot = pv.aux + d.aux_off + 2ll * t.slot * C;
+    // row statistics of rows [ra, rb) of the item, one warp per row
+    auto rows_phase = [&](const int ra, const int rb) {
+      for (int r = ra + warp; r < rb; r += STT / 32) {
+        const uint4* rowq = gitem + (size_t)r * nv;
+        const int row = t.row0 + r;
+        const float old = d.stat_a[row];
+        float mu = 0.0f;
+        if (gc) {
+          f32x2 a0 = pack2(0.0f, 0.0f), a1 = pack2(0.0f, 0.0f);
+          int v = lane;
+          for (; v + 96 < nv; v += 128) {
+            const uint4 q0 = rowq[v], q1 = rowq[v + 32], q2 = rowq[v + 64], q3 = rowq[v + 96];
+            a0 = add2(a0, add2(add2(pairs(q0.x), pairs(q0.y)), add2(pairs(q1.x), pairs(q1.y))));
+            a1 = add2(a1, add2(add2(pairs(q0.z), pairs(q0.w)), add2(pairs(q1.z), pairs(q1.w))));
+            a0 = add2(a0, add2(add2(pairs(q2.x), pairs(q2.y)), add2(pairs(q3.x), pairs(q3.y))));
+            a1 = add2(a1, add2(add2(pairs(q2.z), pairs(q2.w)), add2(pairs(q3.z), pairs(q3.w))));
+          }
+          for (; v < nv; v += 32) {
+            const uint4 q0 = rowq[v];
+            a0 = add2(a0, add2(pairs(q0.x), pairs(q0.y)));
+            a1 = add2(a1, add2(pairs(q0.z), pairs(q0.w)));
+          }
+          mu = round_bf16(__fdiv_rn(warp_sum((a0.x + a0.y) + (a1.x + a1.y)), (float)C));
+        }
+        const uint32_t mu2 = pack_bf16_rn(mu, mu);
+        auto sq2 = [&](uint32_t w) {
+          const f32x2 y = pairs(gc ? sub_bf16x2(w, mu2) : w);
+          const f32x2 q = mul2(y, y);
+          return hp.has_eps ? add2(q, EPS) : q;
+        };
+        f32x2 b0 = pack2(0.0f, 0.0f), b1 = pack2(0.0f, 0.0f);
+        int v = lane;
+        for (; v + 96 < nv; v += 128) {
+          const uint4 q0 = rowq[v], q1 = rowq[v + 32], q2 = rowq[v + 64], q3 = rowq[v + 96];
+          b0 = add2(b0, add2(add2(sq2(q0.x), sq2(q0.y)), add2(sq2(q1.x), sq2(q1.y))));
+          b1 = add2(b1, add2(add2(sq2(q0.z), sq2(q0.w)), add2(sq2(q1.z), sq2(q1.w))));
+          b0 = add2(b0, add2(add2(sq2(q2.x), sq2(q2.y)), add2(sq2(q3.x), sq2(q3.y))));
+          b1 = add2(b1, add2(add2(sq2(q2.z), sq2(q2.w)), add2(sq2(q3.z), sq2(q3.w))));
+        }
+        for (; v < nv; v += 32) {
+          const uint4 q0 = rowq[v];
+          b0 = add2(b0, add2(sq2(q0.x), sq2(q0.y)));
+          b1 = add2(b1, add2(sq2(q0.z), sq2(q0.w)));
+        }
+        const float s2 = warp_sum((b0.x + b0.y) + (b1.x + b1.y));
+        if (lane == 0) {
+          const float rn = lerp_torch(old, __fdiv_rn(s2, (float)C), hp.w2, hp.w2m1, hp.small_w2 != 0);
+          d.stat_a[row] = rn;
+          mean2_s[r] = mu2;
+          if (gc) pv.aux[aux_mean(d) + row] = mu;
+          rinv_s[r] = __fdiv_rn(1.0f, rn);
+          rowsum += (double)rn;
+        }
+      }
+    };
+    // one vector of four pairs from row r into the two column accumulators
+    auto accum = [&](f32x2 A1[4], f32x2 A2[4], const uint4 qv, const int r) {
+      const uint32_t mu2 = mean2_s[r];
+      const f32x2 RI = pack2(rinv_s[r], rinv_s[r]);
+      const uint32_t ww[4] = {qv.x, qv.y, qv.z, qv.w};
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const f32x2 y = pairs(gc ? sub_bf16x2(ww[w], mu2) : ww[w]);
+        const f32x2 sq = mul2(y, y);
+        A1[w] = add2(A1[w], hp.has_eps ? add2(sq, EPS) : sq);
+        A2[w] = add2(A2[w], mul2(sq, RI));
+      }
+    };
+    if (ok && nv <= STT) {
+      // Rows of at most 2048 elements: one column vector per thread, its accumulators in registers for the
+      // whole item, so rows and columns alternate over sub-groups of rows small enough (about 48 KB) for the
+      // column phase to find the rows in L2.  Rows narrower than half the CTA: Q groups of nv threads take
+      // every Q-th row and their partial sums are combined in group order.
+      const int Q = STT / nv, q = tid / nv, v = tid - q * nv;
+      int sg = (48 * 1024) / (C * 2);
+      sg = max(STT / 32, sg / (STT / 32) * (STT / 32));
+      f32x2 A1[4], A2[4];
+#pragma unroll
+      for (int w = 0; w < 4; ++w) { A1[w] = pack2(0.0f, 0.0f); A2[w] = pack2(0.0f, 0.0f); }
+      for (int ra = 0; ra < nrows; ra += sg) {
+        const int rb = min(nrows, ra + sg);
+        rows_phase(ra, rb);
+        __syncthreads();
+        if (q < Q) {
+#pragma unroll 4
+          for (int r = ra + q; r < rb; r += Q) accum(A1, A2, gitem[(size_t)r * nv + v], r);
+        }
+      }
+      if (Q == 1) {
+        if (q < Q) {
+          float4* s1 = reinterpret_cast<float4*>(slot + (size_t)v * 8);
+          float4* s2 = reinterpret_cast<float4*>(slot + C + (size_t)v * 8);
+          s1[0] = make_float4(A1[0].x, A1[0].y, A1[1].x, A1[1].y);
+          s1[1] = make_float4(A1[2].x, A1[2].y, A1[3].x, A1[3].y);
+          s2[0] = make_float4(A2[0].x, A2[0].y, A2[1].x, A2[1].y);
+          s2[1] = make_float4(A2[2].x, A2[2].y, A2[3].x, A2[3].y);
+        }
+      } else {
+        if (q < Q) {
+#pragma unroll
+          for (int w = 0; w < 4; ++w) {
+            xs[(size_t)q * 2 * C + v * 8 + 2 * w] = A1[w].x; xs[(size_t)q * 2 * C + v * 8 + 2 * w + 1] = A1[w].y;
+            xs[(size_t)q * 2 * C + C + v * 8 + 2 * w] = A2[w].x; xs[(size_t)q * 2 * C + C + v * 8 + 2 * w + 1] = A2[w].y;
+          }
+        }
+        __syncthreads();
+        for (int j = tid; j < 2 * C; j += STT) {
+          float tot = 0.0f;
+          for (int qq = 0; qq < Q; ++qq) tot += xs[(size_t)qq * 2 * C + j];
+          slot[j] = tot;
+        }
+      }
+    } else if (ok) {
+      // wider rows: all rows first, then the columns in chunks of ST_VPT vectors per thread
+      rows_phase(0, nrows);
+      __syncthreads();
+      for (int c0 = 0; c0 < nv; c0 += STT * ST_VPT) {
+        f32x2 A1[ST_VPT][4], A2[ST_VPT][4];
+#pragma unroll
+        for (int j = 0; j < ST_VPT; ++j)
+#pragma unroll
+          for (int w = 0; w < 4; ++w) { A1[j][w] = pack2(0.0f, 0.0f); A2[j][w] = pack2(0.0f, 0.0f); }
+        const int v0 = c0 + tid, v1 = v0 + STT;
+        if (v1 < nv) {
+#pragma unroll 2
+          for (int r = 0; r < nrows; ++r) {
+            const uint4 qa = gitem[(size_t)r * nv + v0], qb = gitem[(size_t)r * nv + v1];
+            accum(A1[0], A2[0], qa, r);
+            accum(A1[1], A2[1], qb, r);
+          }
+        } else if (v0 < nv) {
+#pragma unroll 4
+          for (int r = 0; r < nrows; ++r) accum(A1[0], A2[0], gitem[(size_t)r * nv + v0], r);
+        }
+#pragma unroll
+        for (int j = 0; j < ST_VPT; ++j) {
+          const int v = v0 + j * STT;
+          if (v < nv) {
+            float4* s1 = reinterpret_cast<float4*>(slot + (size_t)v * 8);
+            float4* s2 = reinterpret_cast<float4*>(slot + C + (size_t)v * 8);
+            s1[0] = make_float4(A1[j][0].x, A1[j][0].y, A1[j][1].x, A1[j][1].y);
+            s1[1] = make_float4(A1[j][2].x, A1[j][2].y, A1[j][3].x, A1[j][3].y);
+            s2[0] = make_float4(A2[j][0].x, A2[j][0].y, A2[j][1].x, A2[j][1].y);
+            s2[1] = make_float4(A2[j][2].x, A2[j][2].y, A2[j][3].x, A2[j][3].y);
+          }
+        }
+      }
+    }
+    // ---- the item's row-statistic sum, in warp order ----
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) rowsum += __shfl_xor_sync(0xffffffffu, rowsum, o);
+    if (lane == 0) red[warp] = rowsum;
+    __syncthreads();
+    if (tid == 0) {
+      if (ok) {
+        double rs = 0.0;
+        for (int w = 0; w < STT / 32; ++w) rs += red[w];
+        reinterpret_cast<double*>(pv.aux + aux_rowpart(d))[t.slot] = rs;
+      }
+      __threadfence();  // this item's stores (ordered before the barrier) go out before the signal
+      signal_counter(pv.done + 0 * pv.n_tensors + t.tensor, 1u);
+    }
+    slot_i ^= 1;
+    cur = next_s[slot_i];
+  }
 }
 
 // ----------------------------------------------------------------------------- FINAL
@@ -2282,6 +2564,32 @@ int ensure_apply2(kaon_plan* pl) {
     pl->n_tasks_main_na = (int)keep.size();
     pl->device_bytes += (int64_t)(sizeof(Task) * keep.size());
   }
+  // STATS as a launch of its own (ada_stats_kernel): bf16 rows of at least 256 elements in every factored
+  // tensor, work items of at most ST_MAXROWS rows whose slot rows are 16-byte aligned
+  {
+    bool ok = muon || pl->param_dtype == KAON_DT_BF16;
+    std::vector<Task> h((size_t)pl->n_tasks_main_na);
+    KAON_CUDA(cudaMemcpy(h.data(), pl->d_tasks_main_na, sizeof(Task) * h.size(), cudaMemcpyDeviceToHost));
+    std::vector<Task> stats, rest;
+    for (const Task& t : h) {
+      if (t.phase != PH_ADA_STATS) { rest.push_back(t); continue; }
+      const DevTensor& dt = pl->h_tensors[t.tensor];
+      if (dt.cols < 256 || (dt.cols & 7) || t.n / dt.cols > ST_MAXROWS || (dt.aux_off & 3)) ok = false;
+      stats.push_back(t);
+    }
+    if (ok && !stats.empty()) {
+      KAON_CUDA(cudaMalloc((void**)&pl->d_tasks_stats, sizeof(Task) * stats.size()));
+      KAON_CUDA(cudaMemcpy(pl->d_tasks_stats, stats.data(), sizeof(Task) * stats.size(), cudaMemcpyHostToDevice));
+      KAON_CUDA(cudaMalloc((void**)&pl->d_tasks_rest, sizeof(Task) * std::max<size_t>(rest.size(), 1)));
+      KAON_CUDA(cudaMemcpy(pl->d_tasks_rest, rest.data(), sizeof(Task) * rest.size(), cudaMemcpyHostToDevice));
+      pl->n_tasks_stats = (int)stats.size();
+      pl->n_tasks_rest = (int)rest.size();
+      int per_sm2 = 0;
+      KAON_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm2, (const void*)ada_stats_kernel, STT, 0));
+      pl->stats_grid = prop.multiProcessorCount * std::max(per_sm2, 1);
+      pl->device_bytes += (int64_t)(sizeof(Task) * (stats.size() + rest.size()));
+    }
+  }
   KAON_CUDA(cudaMalloc((void**)&pl->d_tasks_apply2, sizeof(Task) * items.size()));
   KAON_CUDA(cudaMemcpy(pl->d_tasks_apply2, items.data(), sizeof(Task) * items.size(), cudaMemcpyHostToDevice));
   KAON_CUDA(cudaMalloc((void**)&pl->d_counter2, 256));
@@ -2293,6 +2601,20 @@ int ensure_apply2(kaon_plan* pl) {
 
 // The COUNT (cautious mask on) and APPLY launches over the plan's flat items; `base` carries the
 // plan's pointers (and AdaMuon's signal column).
+// STATS as a launch of its own, when the plan has the lists for it: returns 1 after launching (the
+// caller's first kernel then walks pl->d_tasks_rest), 0 when the plan keeps STATS in the first kernel.
+int launch_stats(kaon_plan* pl, const PlanView& base, const AdaDev& hp, cudaStream_t s) {
+  if (pl->n_tasks_stats == 0) return 0;
+  PlanView vs = base;
+  vs.tasks = pl->d_tasks_stats;
+  vs.n_tasks = pl->n_tasks_stats;
+  vs.task_counter = pl->d_counter2;
+  if (cudaMemsetAsync(pl->d_counter2, 0, sizeof(unsigned), s) != cudaSuccess) return 0;
+  ada_stats_kernel<<<pl->stats_grid, STT, 0, s>>>(vs, hp);
+  pl->launches += 1;
+  return 1;
+}
+
 int launch_count_apply(kaon_plan* pl, const PlanView& base, const AdaDev& hp, cudaStream_t s) {
   const bool muon = pl->optimizer == KAON_OPT_ADAMUON;
   const int mk = muon ? KAON_M_NONE : pl->momentum_kind;
@@ -2355,6 +2677,7 @@ extern "C" int kaon_adakaon_step(kaon_plan* pl, const kaon_adakaon_hparams* h, u
   else if (hp.cautious) { v.tasks = pl->d_tasks_full; v.n_tasks = pl->n_tasks_full; }
   else { v.tasks = pl->d_tasks_main; v.n_tasks = pl->n_tasks_main; }
   KAON_CUDA(cudaMemsetAsync(v.task_counter, 0, pl->counters_bytes - sizeof(unsigned), s));
+  if (two && launch_stats(pl, pl->view, hp, s)) { v.tasks = pl->d_tasks_rest; v.n_tasks = pl->n_tasks_rest; }
   AdaKernel k = pick_ada(pl->param_dtype, pl->momentum_kind, false);
   k<<<pl->grid, AT, pl->smem_bytes, s>>>(v, hp, (int)x_offset_rows(pl) | (pl->double_buffer ? 1 : 0));
   KAON_CUDA(cudaGetLastError());

@@ -23,5 +23,6 @@ size_t x_offset_rows(const kaon_plan* pl);
 // COUNT and APPLY as launches of their own (plans whose factored tensors all stream)
 int ensure_apply2(kaon_plan* pl);
 int launch_count_apply(kaon_plan* pl, const PlanView& base, const AdaDev& hp, cudaStream_t s);
+int launch_stats(kaon_plan* pl, const PlanView& base, const AdaDev& hp, cudaStream_t s);
 
 }  // namespace kaon

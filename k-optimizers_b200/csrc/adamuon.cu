@@ -292,6 +292,7 @@ extern "C" int kaon_adamuon_step(kaon_plan* pl, const kaon_adamuon_hparams* h, v
   if (three) { v.tasks = pl->d_tasks_main_na; v.n_tasks = pl->n_tasks_main_na; }
   else if (hp.cautious) { v.tasks = pl->d_tasks_full; v.n_tasks = pl->n_tasks_full; }
   else { v.tasks = pl->d_tasks_main; v.n_tasks = pl->n_tasks_main; }
+  if (three && launch_stats(pl, v, hp, s)) { v.tasks = pl->d_tasks_rest; v.n_tasks = pl->n_tasks_rest; }
   AdaKernel k = pick_ada(pl->param_dtype, pl->momentum_kind, true);
   if (!k) return fail(KAON_E_INVALID, "no AdaMuon kernel for this dtype combination");
   k<<<pl->grid, ADA_THREADS, pl->smem_bytes, s>>>(v, hp, (int)x_offset_rows(pl) | (pl->double_buffer ? 1 : 0));

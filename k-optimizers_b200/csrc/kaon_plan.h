@@ -141,6 +141,10 @@ struct kaon_plan {
   kaon::Task* d_tasks_apply2 = nullptr;      // flat items of the factored tensors
   kaon::Task* d_tasks_main_na = nullptr;     // the first launch's work list without COUNT and APPLY items
   int n_tasks_apply2 = 0, n_tasks_main_na = 0;
+  // STATS as a launch of its own: the STATS items, and the first kernel's list without them
+  kaon::Task* d_tasks_stats = nullptr;
+  kaon::Task* d_tasks_rest = nullptr;
+  int n_tasks_stats = 0, n_tasks_rest = 0, stats_grid = 0;
   unsigned* d_counter2 = nullptr;            // claim counter of the COUNT / APPLY launches
   int apply_grid = 0;
   size_t apply_smem = 0;

@@ -322,6 +322,8 @@ int kaon_plan_destroy(kaon_plan* pl) {
   cudaFree(pl->d_tasks_ema);
   cudaFree(pl->d_tasks_apply2);
   cudaFree(pl->d_tasks_main_na);
+  cudaFree(pl->d_tasks_stats);
+  cudaFree(pl->d_tasks_rest);
   cudaFree(pl->d_counter2);
   cudaFree((void*)pl->d_signal);
   delete pl;
