@@ -851,7 +851,18 @@ __device__ void ada_final(const PlanView& pv, const AdaDev& hp, const Task& t, c
   double tl = 0.0;
   for (int j = tid; j < nc; j += AT) {
     float s1 = 0.0f, s2 = 0.0f;
-    for (int s = 0; s < d.n_stats; ++s) {
+    int s = 0;
+    for (; s + 8 <= d.n_stats; s += 8) {  // eight slots' loads in flight; the sums keep the slot order
+      float x1[8], x2[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        x1[u] = __ldcg(part + 2ll * (s + u) * C + j0 + j);
+        x2[u] = __ldcg(part + 2ll * (s + u) * C + C + j0 + j);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) { s1 += x1[u]; s2 += x2[u]; }
+    }
+    for (; s < d.n_stats; ++s) {
       s1 += __ldcg(part + 2ll * s * C + j0 + j);
       s2 += __ldcg(part + 2ll * s * C + C + j0 + j);
     }
@@ -1963,11 +1974,11 @@ __global__ void __launch_bounds__(APPLY_THREADS, 4) adakaon_apply_kernel(PlanVie
       unsigned char* pbase = reinterpret_cast<unsigned char*>(d.p) + t.e0 * E::BYTES;
       const int nvec = n >> 3;
       const int nvec_pad = (nvec + 31) & ~31;
-      // ---- fast path: bf16 weights, int8 / 4-bit momentum, stochastic-rounding write (or the COUNT stage),
-      //      no Kahan buffer.  Same arithmetic as the general loop below, element for element, on packed
+      // ---- fast path: bf16 weights, int8 / 4-bit momentum (or AdaMuon's chain, which carries none and takes
+      //      the orthogonalised matrix as its signal), stochastic-rounding write (or the COUNT stage), no Kahan buffer.  Same arithmetic as the general loop below, element for element, on packed
       //      pairs (f32x2), with the cautious mask and the quantised codes gathered by byte permutes and
       //      one exactness check per vector; the rare vectors that fail a check are redone the plain way. ----
-      constexpr bool FASTABLE = E::IS_BF16 && !MUON && (MK == KAON_M_INT8 || MK == KAON_M_4BIT);
+      constexpr bool FASTABLE = E::IS_BF16 && (MUON || MK == KAON_M_INT8 || MK == KAON_M_4BIT);
       bool fast = false;
       if constexpr (FASTABLE) fast = !hp.kahan && (!APPLY || sr);
       if constexpr (FASTABLE) if (fast) {
@@ -2032,6 +2043,9 @@ __global__ void __launch_bounds__(APPLY_THREADS, 4) adakaon_apply_kernel(PlanVie
             for (int j = 0; j < 4; ++j)
               MO[j] = mul2(add2(pack2(__uint_as_float(prmt(wl, 0x4B000000u, 0x7540u | (uint32_t)j)),
                                       __uint_as_float(prmt(wh, 0x4B000000u, 0x7540u | (uint32_t)j))), BIAS), SC);
+          } else if constexpr (MK == KAON_M_NONE) {
+            sc_old = 1.0f;
+            MO[0] = MO[1] = MO[2] = MO[3] = pack2(0.0f, 0.0f);
           } else {
             sc_old = APPLY ? __ldcg(oldsc + row) : d.m_scale[row];
             const uint2 w = reinterpret_cast<const uint2*>(m_s)[vv];
@@ -2072,10 +2086,19 @@ __global__ void __launch_bounds__(APPLY_THREADS, 4) adakaon_apply_kernel(PlanVie
             f32x2 U = mul2(mul2(G, RF), CF[j]);
             const f32x2 qq = mul2(U, RCPD);
             U = mul2(fma2(fma2(qq, DIVN, U), RCPD, qq), SCALE);
-            const f32x2 diff = sub2(U, MO[j]);
-            MN[j] = SMALL_W1 ? fma2(W1, diff, MO[j]) : fma2(W1M1, diff, U);
+            if constexpr (MK == KAON_M_NONE) {
+              MN[j] = U;  // no momentum of its own: delta = u
+            } else {
+              const f32x2 diff = sub2(U, MO[j]);
+              MN[j] = SMALL_W1 ? fma2(W1, diff, MO[j]) : fma2(W1M1, diff, U);
+            }
             DV[j] = fma2(P[j], LRWD, MN[j]);
-            unpack2(mul2(DV[j], G), a[2 * j], a[2 * j + 1]);
+            if constexpr (MUON) {  // the mask compares with the raw gradient, staged where the momentum goes otherwise
+              const uint32_t rw = reinterpret_cast<const uint32_t*>(m_s)[(size_t)vv * 4 + j];
+              unpack2(mul2(DV[j], pack2(bf16lo(rw), bf16hi(rw))), a[2 * j], a[2 * j + 1]);
+            } else {
+              unpack2(mul2(DV[j], G), a[2 * j], a[2 * j + 1]);
+            }
           }
           // ---- cautious mask: kept <=> delta * g > 0 (sign bits; a zero or underflowing product is rare
           //      and decided by the comparison itself) ----
@@ -2136,7 +2159,10 @@ __global__ void __launch_bounds__(APPLY_THREADS, 4) adakaon_apply_kernel(PlanVie
             }
             // ---- quantise and store the new momentum; MD = the momentum as stored, decoded ----
             f32x2 MD[4];
-            float sc;
+            float sc = 1.0f;
+            if constexpr (MK == KAON_M_NONE) {
+              MD[0] = MD[1] = MD[2] = MD[3] = pack2(0.0f, 0.0f);
+            } else {
             if constexpr (MK == KAON_M_4BIT) {
               const float am = fmaxf(half_warp_max(act ? amax : 0.0f, tid), 1e-12f);
               __syncwarp();  // every lane of the block has read the old scale before it is replaced
@@ -2210,11 +2236,12 @@ __global__ void __launch_bounds__(APPLY_THREADS, 4) adakaon_apply_kernel(PlanVie
                 if (col == 0) d.m_scale[row] = sc;
               }
             }
+            }  // MK != NONE
             // ---- weights: p <- SR(p - update), then the Nekaon climb from the momentum as stored ----
 #pragma unroll
             for (int j = 0; j < 4; ++j) F[j] = pack2(-F[j].x, -F[j].y);
             sr_write(P, F, s_upd, q);
-            if (hp.climb) {
+            if (hp.climb && MK != KAON_M_NONE) {
               const f32x2 AC = pack2(hp.a_climb, hp.a_climb);
               const bool wild2 = !(sc <= 3.0e38f);
               f32x2 Dc[4];

@@ -164,9 +164,15 @@ static EmaKernel pick_ema_pt(int mk) {
 
 static size_t up256(size_t x) { return (x + 255) / 256 * 256; }
 
+// Matrices are independent of each other until the second-moment stage, so their EMA pre-pass and
+// Newton-Schulz chains run round robin on NS_LANES internal streams, each with a staging matrix and a
+// Newton-Schulz scratch of its own: when the last tiles of one matrix's GEMM leave most SMs idle, the next
+// matrix's kernels start on them.
+constexpr int NS_LANES = 3;
+
 struct MuonLayout {
   std::vector<size_t> o_off;  // per tensor: byte offset of O in the workspace (factored tensors)
-  size_t x0_off = 0, ns_off = 0, total = 0;
+  size_t x0_off = 0, ns_off = 0, lane_stride = 0, total = 0;  // lane l: x0_off + l * lane_stride, ns_off + l * lane_stride
 };
 
 static MuonLayout muon_layout(const kaon_plan* pl) {
@@ -181,8 +187,10 @@ static MuonLayout muon_layout(const kaon_plan* pl) {
     max_x = std::max(max_x, up256((size_t)t.numel * 2));
     max_ns = std::max(max_ns, up256(ns_workspace_bytes(t.rows, t.cols)));
   }
-  L.x0_off = cur; cur += max_x;
-  L.ns_off = cur; cur += max_ns;
+  L.x0_off = cur;
+  L.ns_off = cur + max_x;
+  L.lane_stride = max_x + max_ns;
+  cur += (size_t)NS_LANES * L.lane_stride;
   L.total = cur + 256;
   return L;
 }
@@ -256,21 +264,39 @@ extern "C" int kaon_adamuon_step(kaon_plan* pl, const kaon_adamuon_hparams* h, v
   v.signal = pl->d_signal;
   KAON_CUDA(cudaMemsetAsync(v.task_counter, 0, pl->counters_bytes - sizeof(unsigned), s));
 
-  // (1) + (2): per factored tensor with a gradient: EMA pre-pass, then Newton-Schulz into its O slot
-  __nv_bfloat16* x0 = reinterpret_cast<__nv_bfloat16*>(ws + L.x0_off);
+  // (1) + (2): per factored tensor with a gradient: EMA pre-pass, then Newton-Schulz into its O slot,
+  // round robin over the lanes (forked from the caller's stream, joined before stage 3)
+  if (!pl->muon_lanes_ready) {
+    for (int l = 0; l < NS_LANES; ++l) {
+      KAON_CUDA(cudaStreamCreateWithFlags(&pl->muon_stream[l], cudaStreamNonBlocking));
+      KAON_CUDA(cudaEventCreateWithFlags(&pl->muon_join[l], cudaEventDisableTiming));
+    }
+    KAON_CUDA(cudaEventCreateWithFlags(&pl->muon_fork, cudaEventDisableTiming));
+    pl->muon_lanes_ready = true;
+  }
+  KAON_CUDA(cudaEventRecord(pl->muon_fork, s));
+  for (int l = 0; l < NS_LANES; ++l) KAON_CUDA(cudaStreamWaitEvent(pl->muon_stream[l], pl->muon_fork, 0));
+  int turn = 0;
   for (int i = 0; i < n; ++i) {
     const DevTensor& t = pl->h_tensors[i];
     if (t.rows <= 0 || t.numel == 0 || pl->h_grads[i] == nullptr) continue;
+    const int lane = turn++ % NS_LANES;
+    cudaStream_t sl = pl->muon_stream[lane];
+    __nv_bfloat16* x0 = reinterpret_cast<__nv_bfloat16*>(ws + L.x0_off + (size_t)lane * L.lane_stride);
     const int t0 = pl->ema_begin[i], t1 = pl->ema_begin[i + 1];
     const int grid = std::min(t1 - t0, pl->sm_count * 8);
-    ek<<<grid, ET, 0, s>>>(v, pl->d_tasks_ema, t0, t1, w1, w1 - 1.0f, w1 < 0.5f, x0);
+    ek<<<grid, ET, 0, sl>>>(v, pl->d_tasks_ema, t0, t1, w1, w1 - 1.0f, w1 < 0.5f, x0);
     KAON_CUDA(cudaGetLastError());
     pl->launches += 1;
     long long nl = 0;
     int rc = ns_run(x0, t.rows, t.cols, h->ns_steps, reinterpret_cast<__nv_bfloat16*>(ws + L.o_off[i]),
-                    ws + L.ns_off, v.status, s, &nl);
+                    ws + L.ns_off + (size_t)lane * L.lane_stride, v.status, sl, &nl);
     pl->launches += nl;
     if (rc) return rc;
+  }
+  for (int l = 0; l < NS_LANES; ++l) {
+    KAON_CUDA(cudaEventRecord(pl->muon_join[l], pl->muon_stream[l]));
+    KAON_CUDA(cudaStreamWaitEvent(s, pl->muon_join[l], 0));
   }
 
   // (3) second moment of O, clip, scale, cautious, weight write (and the whole 1-D branch)

@@ -2,6 +2,7 @@
 // Shared by the host planner (plan.cu) and the kernels.
 #pragma once
 
+#include <cuda_runtime.h>
 #include <stdint.h>
 
 #include <vector>
@@ -136,6 +137,10 @@ struct kaon_plan {
   std::vector<int> ema_begin;                // [n_tensors + 1] ranges into d_tasks_ema
   const void** d_signal = nullptr;           // per-tensor pointer to O in the caller's workspace
   const void* signal_base = nullptr;         // workspace the pointers were computed for
+  bool muon_lanes_ready = false;             // internal streams of the per-matrix Newton-Schulz chains
+  cudaStream_t muon_stream[4] = {nullptr, nullptr, nullptr, nullptr};
+  cudaEvent_t muon_join[4] = {nullptr, nullptr, nullptr, nullptr};
+  cudaEvent_t muon_fork = nullptr;
   // Adakaon / AdaMuon (built lazily by the first step): COUNT and APPLY as launches of their own
   int apply2 = 0;                            // 0 = not decided, 1 = in use, -1 = this plan is not eligible
   kaon::Task* d_tasks_apply2 = nullptr;      // flat items of the factored tensors

@@ -66,7 +66,7 @@ __global__ void ns_gemm_simple_kernel(const __nv_bfloat16* A, int a_mn, long lon
   p.out[(long long)i * p.ld_out + j] = __float2bfloat16_rn(acc * alpha + beta * x);
 }
 
-static bool g_gemm_attr_set[64] = {false};
+static int g_gemm_sms[64] = {0};  // multiprocessors per device, once the kernel's shared-memory limit is set
 
 // out[M,N] = bf16(alpha * A(m,:) . B(n,:) + beta * aux)
 int launch_ns_gemm(const __nv_bfloat16* A, bool a_mn, long long lda, const __nv_bfloat16* B, bool b_mn, long long ldb,
@@ -88,9 +88,9 @@ int launch_ns_gemm(const __nv_bfloat16* A, bool a_mn, long long lda, const __nv_
   }
   p.BN = N >= 256 ? 256 : (N > 64 ? 128 : 64);
   if (p.sym && N >= 256) {
-    // One CTA per computed tile: with 256-wide tiles a 3072-wide symmetric product has 156 of them,
-    // two waves over 148 SMs all the same; 192-wide tiles make 208 (two waves of 3/4 the work each).
-    // Take 192 when waves x width comes out clearly smaller.
+    // Persistent CTAs share the computed tiles out evenly: take the tile width whose busiest SM has the
+    // least work (tiles per SM x width); narrower tiles balance better but feed the tensor cores worse,
+    // so 256 keeps a 10 % edge.
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -109,16 +109,25 @@ int launch_ns_gemm(const __nv_bfloat16* A, bool a_mn, long long lda, const __nv_
   if (rc) return rc;
   if (b_mn) rc = make_map(&mb, B, N, K, ldb, 64); else rc = make_map(&mb, B, K, N, ldb, p.BN);
   if (rc) return rc;
-  const size_t smem = 1024 + (size_t)G_STAGES * (G_A_BYTES + (size_t)p.BN * G_BK * 2);
+  // always the shared memory of the widest tile: one CTA per SM, whose tensor-memory allocation (all 512
+  // columns) then never waits for a neighbour
+  const size_t smem = 1024 + (size_t)G2_STAGES * (G_A_BYTES + (size_t)G_MAX_BN * G_BK * 2);
   int dev = 0;
   KAON_CUDA(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && !g_gemm_attr_set[dev]) {
+  if (dev < 0 || dev >= 64) return fail(KAON_E_UNSUPPORTED, "device index %d", dev);
+  if (!g_gemm_sms[dev]) {
     KAON_CUDA(cudaFuncSetAttribute((const void*)ns_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   (int)(1024 + (size_t)G_STAGES * (G_A_BYTES + (size_t)G_MAX_BN * G_BK * 2))));
-    g_gemm_attr_set[dev] = true;
+                                   (int)(1024 + (size_t)G2_STAGES * (G_A_BYTES + (size_t)G_MAX_BN * G_BK * 2))));
+    int sms = 0;
+    KAON_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    g_gemm_sms[dev] = sms;
   }
-  dim3 grid((N + p.BN - 1) / p.BN, (M + G_BM - 1) / G_BM);
-  ns_gemm_kernel<<<grid, G_THREADS, smem, stream>>>(ma, mb, p);
+  // computed tiles: all of them, or in symmetric mode those that reach the diagonal
+  const int tm = (M + G_BM - 1) / G_BM, tn = (N + p.BN - 1) / p.BN;
+  int total = 0;
+  for (int mi = 0; mi < tm; ++mi) total += tn - (p.sym ? std::min(tn, (mi * G_BM) / p.BN) : 0);
+  const int grid = std::min(total, g_gemm_sms[dev]);
+  ns_gemm_kernel<<<grid, G2_THREADS, smem, stream>>>(ma, mb, p, total);
   KAON_CUDA(cudaGetLastError());
   return KAON_OK;
 }

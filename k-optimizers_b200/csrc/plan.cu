@@ -326,6 +326,13 @@ int kaon_plan_destroy(kaon_plan* pl) {
   cudaFree(pl->d_tasks_rest);
   cudaFree(pl->d_counter2);
   cudaFree((void*)pl->d_signal);
+  if (pl->muon_lanes_ready) {
+    for (int l = 0; l < 4; ++l) {
+      if (pl->muon_stream[l]) cudaStreamDestroy(pl->muon_stream[l]);
+      if (pl->muon_join[l]) cudaEventDestroy(pl->muon_join[l]);
+    }
+    if (pl->muon_fork) cudaEventDestroy(pl->muon_fork);
+  }
   delete pl;
   return KAON_OK;
 }
