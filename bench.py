@@ -38,17 +38,19 @@ ADAMUON_KW = dict(lr=1e-3, ns_steps=2, cautious=True, momentum_dtype="int8")
 #  Adakaon-int8 (config 3): g 2 + p 2+2 + m 1+1 + row scales, row/col stats, 1-D v; 1 % of grads x100
 #  Nekaon-4bit (config 4): as Lion-4bit + stats; climb and removal ride on the same weight access
 #  AdaMuon-int8 (config 5): the non-NS passes move 8.006 B/param; Newton-Schulz is 3.24e14 flop per step
-# traffic_bpp: DRAM bytes per parameter of one step, from the ncu capture of the *_mid workload (a list
-# of 269 M parameters, > 10x L2) summarised in profiles/; None = not captured.
+# traffic_bpp: DRAM bytes per parameter of one step (all its launches), from the ncu launch list of the
+# *_mid workload (a list of 269 M parameters with every tensor shape of the big one, 15x L2) summarised in
+# profiles/lion_kernel_bf16_4bit_unet_mid.md and profiles/adakaon_kernels_bf16_unet_mid.md.
 WORKLOADS = {
-    "lion4bit_unet2p6b": ("Lion", LION_KW, "unet_2p6b", 7.0625, {"traffic_bpp": None}),
+    "lion4bit_unet2p6b": ("Lion", LION_KW, "unet_2p6b", 7.0625, {"traffic_bpp": 7.22}),
     "lion4bit_sample": ("Lion", LION_KW, "unet_sample", 7.0625, {}),
     "lion4bit_mid": ("Lion", LION_KW, "unet_mid", 7.0625, {}),
     "lion4bit_nogc_unet2p6b": ("Lion", dict(LION_KW, gradient_centralization=False), "unet_2p6b", 7.0625, {}),
-    "adakaon_int8_unet2p6b": ("Adakaon", ADAKAON_KW, "unet_2p6b", 8.015, {"outlier": True, "traffic_bpp": None}),
+    "adakaon_int8_unet2p6b": ("Adakaon", ADAKAON_KW, "unet_2p6b", 8.015, {"outlier": True, "traffic_bpp": 13.78}),
     "adakaon_int8_sample": ("Adakaon", ADAKAON_KW, "unet_sample", 8.015, {"outlier": True}),
     "adakaon_int8_mid": ("Adakaon", ADAKAON_KW, "unet_mid", 8.015, {"outlier": True}),
-    "nekaon4bit_unet2p6b": ("Nekaon", NEKAON_KW, "unet_2p6b", 7.073, {"cosine": (1e-4, 1e-5, 50), "steps": 50}),
+    "nekaon4bit_unet2p6b": ("Nekaon", NEKAON_KW, "unet_2p6b", 7.073, {"cosine": (1e-4, 1e-5, 50), "steps": 50,
+                                                                       "traffic_bpp": 14.38}),
     "nekaon4bit_sample": ("Nekaon", NEKAON_KW, "unet_sample", 7.073, {"cosine": (1e-4, 1e-5, 50)}),
     "nekaon4bit_mid": ("Nekaon", NEKAON_KW, "unet_mid", 7.073, {"cosine": (1e-4, 1e-5, 50)}),
     "adamuon_int8_dit11b": ("AdaMuon", ADAMUON_KW, "dit_11b", 8.006, {"one_grad_set": True, "steps": 10}),
@@ -591,7 +593,10 @@ def measure(ctx: Ctx, workload: str, steps: int, warmup: int, e2e_steps: int = 0
             res["roofline"] = {"bound": "tensor", "achieved": ns_info["total"]["tflops"], "peak": tpeak,
                                "unit": "TFLOP/s", "frac": ns_info["total"]["tflops"] / tpeak, "traffic": None,
                                "peak_kind": f"{peak_kind} cuBLAS bf16 burst", "kernel": "ns_gemm_kernel",
-                               "note": "Newton-Schulz GEMM chain timed alone per shape (CUDA events); hbm_passes has the rest of the step"}
+                               "note": "Newton-Schulz GEMM chain of one matrix timed alone per shape (CUDA events); inside a step "
+                                       "the chains of different matrices overlap on three streams: newton_schulz.whole_step_tflops "
+                                       "is the same flops over the whole step time"}
+            ns_info["whole_step_tflops"] = ns_info["total"]["flop_per_step"] / (kern_ms * 1e-3) / 1e12
             res["newton_schulz"] = ns_info
     return res
 
