@@ -46,7 +46,8 @@ struct DevTensor {
   unsigned block;       // 4-bit block size in use
   int n_main;           // number of MAIN work items of this tensor (what `done` must reach)
   // Adakaon / AdaMuon only
-  int chunk_rows;       // rows staged at a time (chunk_rows * cols <= CAP, aligned)
+  int chunk_rows;       // rows staged at a time (chunk_rows * cols <= CAP, aligned); -1: a Lion tensor cut into
+                        // flat runs instead of whole rows (its row means are in `aux` at aux_off)
   int n_stats;          // STATS items (= slots of column partials)
   int n_strips;         // FINAL items
   int n_count;          // COUNT items
@@ -78,7 +79,7 @@ struct Task {
   int n;         // elements (<= CAP); whole rows for >=2-D tensors
   int row0;      // first row (>=2-D tensors); FINAL items: first column of the strip
   int slot;      // STATS items: index of the column-partial slot; otherwise 0
-  int pad;
+  int pad;       // Lion items of a tensor cut into flat runs: column of the first element (e0 - row0 * cols)
 };
 
 // Mirrors of the weight buffer on other GPUs (ZeRO-1 publish fused into the step): every weight the
@@ -159,6 +160,8 @@ struct kaon_plan {
   int64_t launches = 0;
   int grid = 0;          // persistent grid size
   int sm_count = 0;      // multiprocessors of the plan's device
+  int* d_flat_tensors = nullptr;  // Lion: indices of the tensors cut into flat runs (row means by a pre-pass)
+  int n_flat_tensors = 0;
   size_t smem_bytes = 0;
   int64_t total_elems = 0;
 };

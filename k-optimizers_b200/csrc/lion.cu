@@ -83,7 +83,7 @@ __device__ __forceinline__ unsigned lion_fast4_bf16(const PlanView& pv, const Li
       w = msrc[v];
       sc_old = sc_s[v >> 4];
       if (GC) {
-        const uint32_t mu2 = mean2_s[row_of((unsigned)v * 8u, d)];
+        const uint32_t mu2 = mean2_s[row_of((unsigned)t.pad + (unsigned)v * 8u, d)];
 #pragma unroll
         for (int j = 0; j < 4; ++j) gw[j] = sub_bf16x2(gw[j], mu2);
       }
@@ -213,7 +213,7 @@ __device__ __forceinline__ unsigned lion_fast4(const PlanView& pv, const LionDev
       w = msrc[v];
       sc_old = sc_s[v >> 4];
       if (GC) {
-        const float mu = mean_s[row_of((unsigned)v * 8u, d)];
+        const float mu = mean_s[row_of((unsigned)t.pad + (unsigned)v * 8u, d)];
 #pragma unroll
         for (int k = 0; k < 8; k += 2) {
           const float x0 = __fsub_rn(g[k], mu), x1 = __fsub_rn(g[k + 1], mu);
@@ -348,7 +348,16 @@ __device__ void lion_main(const PlanView& pv, const LionDev& hp, const Task& t, 
     fast = !hp.has_wd && hp.cautious && (n & 7) == 0 && ((d.rows <= 0) || ((C & 7) == 0));
   // the bf16 fast path subtracts the mean from packed pairs: it reads the mean as two bf16 copies
   const bool mean_packed = fast && E::IS_BF16;
-  if (do_gc) {
+  if (do_gc && d.chunk_rows < 0) {
+    // a tensor cut into flat runs (rows longer than a work item, or rows that cannot be grouped on block
+    // boundaries): the run touches parts of a few rows, whose means lion_rowmean_kernel left in the scratch
+    const int touched = (int)(((long long)t.pad + n + C - 1) / C);
+    for (int r = tid; r < touched; r += NTHREADS) {
+      const float mean = __ldcg(pv.aux + d.aux_off + t.row0 + r);
+      if (mean_packed) reinterpret_cast<uint32_t*>(mean_s)[r] = pack_bf16_rn(mean, mean);
+      else mean_s[r] = mean;
+    }
+  } else if (do_gc) {
     const int warp = tid >> 5, lane = tid & 31;
     for (int r = warp; r < nrows; r += NTHREADS / 32) {
       const unsigned char* rowp = g_s + (size_t)r * C * E::BYTES;
@@ -401,7 +410,7 @@ __device__ void lion_main(const PlanView& pv, const LionDev& hp, const Task& t, 
     load8_guard<PT>(g_s + (size_t)v * 8 * E::BYTES, cnt, gv);
     if (do_gc) {
       if (row_uniform) {
-        float mu = mean_s[row_of((unsigned)v * 8u, d)];
+        float mu = mean_s[row_of((unsigned)t.pad + (unsigned)v * 8u, d)];
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           float x = __fsub_rn(gv[k], mu);
@@ -410,7 +419,7 @@ __device__ void lion_main(const PlanView& pv, const LionDev& hp, const Task& t, 
       } else {
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          float x = __fsub_rn(gv[k], mean_s[k < cnt ? row_of((unsigned)(v * 8 + k), d) : 0]);
+          float x = __fsub_rn(gv[k], mean_s[k < cnt ? row_of((unsigned)t.pad + (unsigned)(v * 8 + k), d) : 0]);
           gv[k] = (k < cnt) ? (E::IS_BF16 ? round_bf16(x) : x) : 0.0f;
         }
       }
@@ -738,6 +747,40 @@ __global__ void __launch_bounds__(NTHREADS, 4) lion_kernel(PlanView pv, LionDev 
   }
 }
 
+// Row means (gradient centralization) of the tensors that are cut into flat runs, one warp per row, into
+// the plan's scratch: bf16-rounded for bf16 gradients, as the staged rows' means are.
+template <typename PT>
+__global__ void lion_rowmean_kernel(PlanView pv, const int* tensor_ids, int n_ids) {
+  using E = Elems<PT>;
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
+  for (int k = 0; k < n_ids; ++k) {
+    const DevTensor d = pv.tensors[tensor_ids[k]];
+    const unsigned char* g = reinterpret_cast<const unsigned char*>(pv.grads[tensor_ids[k]]);
+    if (g == nullptr) continue;
+    const int C = d.cols;
+    for (long long r = warp0; r < d.rows; r += nwarps) {
+      const unsigned char* rowp = g + (size_t)r * C * E::BYTES;
+      float s = 0.0f;
+      if ((C & 7) == 0 && ((reinterpret_cast<uintptr_t>(rowp) & 15) == 0)) {
+        for (int v = lane; v < (C >> 3); v += 32) {
+          float x[8];
+          E::load8(rowp + (size_t)v * 8 * E::BYTES, x);
+          s += ((x[0] + x[1]) + (x[2] + x[3])) + ((x[4] + x[5]) + (x[6] + x[7]));
+        }
+      } else {
+        for (int i = lane; i < C; i += 32) s += E::load1(rowp, i);
+      }
+      s = warp_sum(s);
+      if (lane == 0) {
+        const float mean = __fdiv_rn(s, (float)C);
+        pv.aux[d.aux_off + r] = E::IS_BF16 ? round_bf16(mean) : mean;
+      }
+    }
+  }
+}
+
 typedef void (*LionKernel)(PlanView, LionDev);
 
 static LionKernel pick_lion(int pdt, int mk, bool mirror) {
@@ -803,6 +846,12 @@ extern "C" int kaon_lion_step(kaon_plan* pl, const kaon_lion_hparams* h, uint64_
   if (hp.cautious) { v.tasks = pl->d_tasks_full; v.n_tasks = pl->n_tasks_full; }
   else { v.tasks = pl->d_tasks_main; v.n_tasks = pl->n_tasks_main; }
   KAON_CUDA(cudaMemsetAsync(v.task_counter, 0, pl->counters_bytes - sizeof(unsigned), s));
+  if (pl->n_flat_tensors > 0 && hp.gc) {  // row means of the tensors cut into flat runs
+    if (pl->param_dtype == KAON_DT_BF16) lion_rowmean_kernel<__nv_bfloat16><<<pl->sm_count * 4, 256, 0, s>>>(v, pl->d_flat_tensors, pl->n_flat_tensors);
+    else lion_rowmean_kernel<float><<<pl->sm_count * 4, 256, 0, s>>>(v, pl->d_flat_tensors, pl->n_flat_tensors);
+    KAON_CUDA(cudaGetLastError());
+    pl->launches += 1;
+  }
   LionKernel k = pick_lion(pl->param_dtype, pl->momentum_kind, v.peers.n > 0 || hp.kahan);
   k<<<pl->grid, NTHREADS, pl->smem_bytes, s>>>(v, hp);
   KAON_CUDA(cudaGetLastError());

@@ -48,7 +48,7 @@ size_t momentum_bytes_per_cap(int mk) {
 
 // Split one tensor into work items: runs of whole rows (>=2-D) or flat runs (1-D), each at most CAP
 // elements, each starting on the alignment unit.
-static int split_tensor(const kaon_tensor_desc& d, int ti, int mk, std::vector<Task>& out) {
+static int split_tensor(const kaon_tensor_desc& d, int ti, int mk, bool lion, std::vector<Task>& out) {
   const long long n = d.numel;
   const int A = align_unit(mk);
   if (n == 0) return 0;
@@ -62,6 +62,16 @@ static int split_tensor(const kaon_tensor_desc& d, int ti, int mk, std::vector<T
     const long long unit = A / gcd_ll(C, A);  // rows per aligned group
     long long rpt = (CAP / C) / unit * unit;   // rows per work item
     rpt = std::min<long long>(rpt, MAX_TASK_ROWS / unit * unit);
+    if (rpt <= 0 && lion && mk != KAON_M_INT8 && C >= 8) {
+      // Lion: flat runs instead of whole rows (only the row means tie a row together, and a pre-pass takes
+      // those); int8 momentum keeps whole rows (one scale per row).  Returns 1: the caller marks the tensor.
+      const long long chunk = CAP / A * A;
+      for (long long e = 0; e < n; e += chunk) {
+        const long long r0 = e / C;
+        out.push_back(Task{ti, 0, e, (int)std::min<long long>(chunk, n - e), (int)r0, 0, (int)(e - r0 * C)});
+      }
+      return 1;
+    }
     if (rpt <= 0)
       return fail(KAON_E_UNSUPPORTED,
                   "tensor %d: %lld rows of %lld elements cannot be cut into row-aligned work items of <= %d "
@@ -120,7 +130,8 @@ int kaon_plan_create(kaon_plan** out, int optimizer, int param_dtype, int moment
 
   std::vector<DevTensor> tens(n);
   std::vector<std::vector<Task>> per(n);
-  long long code_bytes = 0, total = 0;
+  long long code_bytes = 0, total = 0, lion_aux_floats = 0;
+  std::vector<int> flat_tensors;
   for (int i = 0; i < n; ++i) {
     const kaon_tensor_desc& d = descs[i];
     if (!d.p || d.numel < 0) return fail(KAON_E_INVALID, "tensor %d: null weights or negative numel", i);
@@ -147,8 +158,14 @@ int kaon_plan_create(kaon_plan** out, int optimizer, int param_dtype, int moment
     t.code_off = code_bytes;
     code_bytes += ((d.numel + 3) / 4 + 63) / 64 * 64;  // 2 bits per element, 64-byte granules
     total += d.numel;
-    int rc = split_tensor(d, i, momentum_kind, per[i]);
-    if (rc) return rc;
+    int rc = split_tensor(d, i, momentum_kind, optimizer == KAON_OPT_LION, per[i]);
+    if (rc < 0) return rc;
+    if (rc == 1) {  // cut into flat runs: row means come from a pre-pass into the scratch
+      t.chunk_rows = -1;
+      t.aux_off = lion_aux_floats;
+      lion_aux_floats += (d.rows + 63) / 64 * 64;
+      flat_tensors.push_back(i);
+    }
     t.n_main = (int)per[i].size();
   }
 
@@ -267,7 +284,14 @@ int kaon_plan_create(kaon_plan** out, int optimizer, int param_dtype, int moment
     ce = cudaMalloc((void**)&pl->d_codes, (size_t)code_bytes);
     if (ce != cudaSuccess) { cudaFree(pl->d_block); delete pl; return cuda_fail(ce, "cudaMalloc(code scratch)"); }
   }
-  if (optimizer != KAON_OPT_LION) {
+  if (optimizer == KAON_OPT_LION && !flat_tensors.empty()) {
+    aux_floats = lion_aux_floats;
+    ce = cudaMalloc((void**)&pl->d_flat_tensors, sizeof(int) * flat_tensors.size());
+    if (ce == cudaSuccess) ce = cudaMemcpy(pl->d_flat_tensors, flat_tensors.data(), sizeof(int) * flat_tensors.size(), cudaMemcpyHostToDevice);
+    if (ce != cudaSuccess) { cudaFree(pl->d_block); cudaFree(pl->d_codes); delete pl; return cuda_fail(ce, "cudaMalloc(flat-run tensor list)"); }
+    pl->n_flat_tensors = (int)flat_tensors.size();
+  }
+  if (optimizer != KAON_OPT_LION || !flat_tensors.empty()) {
     ce = cudaMalloc((void**)&pl->d_aux, sizeof(float) * (size_t)std::max<long long>(aux_floats, 64));
     if (ce != cudaSuccess) { cudaFree(pl->d_block); cudaFree(pl->d_codes); delete pl; return cuda_fail(ce, "cudaMalloc(aux scratch)"); }
   }
@@ -319,6 +343,7 @@ int kaon_plan_destroy(kaon_plan* pl) {
   cudaFree(pl->d_block);
   cudaFree(pl->d_codes);
   cudaFree(pl->d_aux);
+  cudaFree(pl->d_flat_tensors);
   cudaFree(pl->d_tasks_ema);
   cudaFree(pl->d_tasks_apply2);
   cudaFree(pl->d_tasks_main_na);
