@@ -2699,12 +2699,18 @@ extern "C" int kaon_adakaon_step(kaon_plan* pl, const kaon_adakaon_hparams* h, u
   if (int rc = ensure_apply2(pl)) return rc;
   // two launches when the plan is eligible (int8 momentum also needs the COUNT stage's row maxima)
   const bool two = pl->apply2 == 1 && (pl->momentum_kind != KAON_M_INT8 || hp.cautious);
+  if (pl->has_long_rows && !(two && pl->n_tasks_stats > 0))
+    return fail(KAON_E_UNSUPPORTED,
+                "a tensor's rows exceed a work item of %d elements: such rows are stepped by the streaming launches "
+                "only (bf16 weights, every factored tensor with rows of >= 256 elements in multiples of 8 (16 with "
+                "int8 momentum), 4-bit block 128, int8 momentum with the cautious mask on)", CAP);
   // first launch: STATS, FINAL, FLAT (the list without COUNT and APPLY items); then COUNT, then APPLY
   if (two) { v.tasks = pl->d_tasks_main_na; v.n_tasks = pl->n_tasks_main_na; }
   else if (hp.cautious) { v.tasks = pl->d_tasks_full; v.n_tasks = pl->n_tasks_full; }
   else { v.tasks = pl->d_tasks_main; v.n_tasks = pl->n_tasks_main; }
   KAON_CUDA(cudaMemsetAsync(v.task_counter, 0, pl->counters_bytes - sizeof(unsigned), s));
   if (two && launch_stats(pl, pl->view, hp, s)) { v.tasks = pl->d_tasks_rest; v.n_tasks = pl->n_tasks_rest; }
+  else if (pl->has_long_rows) return fail(KAON_E_CUDA, "the STATS launch could not be started");
   AdaKernel k = pick_ada(pl->param_dtype, pl->momentum_kind, false);
   k<<<pl->grid, AT, pl->smem_bytes, s>>>(v, hp, (int)x_offset_rows(pl) | (pl->double_buffer ? 1 : 0));
   KAON_CUDA(cudaGetLastError());

@@ -143,6 +143,7 @@ struct kaon_plan {
   cudaEvent_t muon_join[4] = {nullptr, nullptr, nullptr, nullptr};
   cudaEvent_t muon_fork = nullptr;
   // Adakaon / AdaMuon (built lazily by the first step): COUNT and APPLY as launches of their own
+  bool has_long_rows = false;                // a factored tensor's rows exceed a work item: streaming launches only
   int apply2 = 0;                            // 0 = not decided, 1 = in use, -1 = this plan is not eligible
   kaon::Task* d_tasks_apply2 = nullptr;      // flat items of the factored tensors
   kaon::Task* d_tasks_main_na = nullptr;     // the first launch's work list without COUNT and APPLY items

@@ -72,6 +72,15 @@ static int split_tensor(const kaon_tensor_desc& d, int ti, int mk, bool lion, st
       }
       return 1;
     }
+    if (rpt <= 0 && !lion && C >= 256 && (C & 7) == 0 && (mk != KAON_M_INT8 || (C & 15) == 0)) {
+      // Adakaon / Nekaon: the streaming launches (STATS, COUNT and APPLY as kernels of their own) never stage
+      // whole rows, so a longer row is fine there.  Flat runs for the climb list; returns 2: the caller marks
+      // the plan, and a step that cannot take the streaming form refuses.
+      const long long chunk = CAP / A * A;
+      for (long long e = 0; e < n; e += chunk)
+        out.push_back(Task{ti, 0, e, (int)std::min<long long>(chunk, n - e), (int)(e / C), 0, (int)(e % C)});
+      return 2;
+    }
     if (rpt <= 0)
       return fail(KAON_E_UNSUPPORTED,
                   "tensor %d: %lld rows of %lld elements cannot be cut into row-aligned work items of <= %d "
@@ -132,6 +141,7 @@ int kaon_plan_create(kaon_plan** out, int optimizer, int param_dtype, int moment
   std::vector<std::vector<Task>> per(n);
   long long code_bytes = 0, total = 0, lion_aux_floats = 0;
   std::vector<int> flat_tensors;
+  std::vector<char> long_rows(n, 0);
   for (int i = 0; i < n; ++i) {
     const kaon_tensor_desc& d = descs[i];
     if (!d.p || d.numel < 0) return fail(KAON_E_INVALID, "tensor %d: null weights or negative numel", i);
@@ -165,6 +175,11 @@ int kaon_plan_create(kaon_plan** out, int optimizer, int param_dtype, int moment
       t.aux_off = lion_aux_floats;
       lion_aux_floats += (d.rows + 63) / 64 * 64;
       flat_tensors.push_back(i);
+    }
+    if (rc == 2) {
+      if (optimizer == KAON_OPT_ADAMUON)
+        return fail(KAON_E_UNSUPPORTED, "tensor %d: rows of %d elements exceed a work item of %d (AdaMuon steps whole rows)", i, t.cols, CAP);
+      long_rows[i] = 1;
     }
     t.n_main = (int)per[i].size();
   }
@@ -209,8 +224,13 @@ int kaon_plan_create(kaon_plan** out, int optimizer, int param_dtype, int moment
         continue;
       }
       const long long C = t.cols;
-      max_cols = std::max<int>(max_cols, (int)C);
-      t.chunk_rows = (int)(per[i][0].n / C);
+      if (long_rows[i]) {  // streaming launches only: no row of it is ever staged by the persistent kernel
+        pl->has_long_rows = true;
+        t.chunk_rows = 1;
+      } else {
+        max_cols = std::max<int>(max_cols, (int)C);
+        t.chunk_rows = (int)(per[i][0].n / C);
+      }
       // rows per run: column partials (8 B per column per run) stay under ~10 % of the run's gradient
       // bytes, and a run is at least ~128 K elements
       long long run_rows = std::max<long long>(40, (131072 + C - 1) / C);

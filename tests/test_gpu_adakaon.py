@@ -163,13 +163,41 @@ BIG_STREAM = [(640, 2560), (320, 320, 4, 4), (1280,), (5120, 640), (336, 80), (3
 @pytest.mark.parametrize("dtype", ["bf16", "f32"])
 @pytest.mark.parametrize("kind", ["ragged", "stream"])
 def test_adakaon_vs_oracle_bigger_shapes(md, wd, method, dtype, kind):
+    # rows of 4100 elements cannot start every work item on a 128-element 4-bit block boundary within
+    # the shared-memory budget: the plan refuses that shape for 4-bit momentum (tested below)
+    BIG = [s for s in BIG_ALL if not (md == "4bit" and s == (96, 4100))] if kind == "ragged" else BIG_STREAM
+    _adakaon_vs_oracle(BIG, md, wd, method, dtype)
+
+
+# rows of 23040 elements exceed a work item: stepped by the streaming launches only
+LONG_ROWS = [(16, 2560, 3, 3), (640, 2560), (1280,), (9, 16640)]
+
+
+@pytest.mark.parametrize("md,wd,method", [("int8", 0.0, "stochastic_rounding"), ("4bit", 0.1, "none"),
+                                          ("bfloat16", 0.01, "stochastic_rounding")])
+def test_adakaon_vs_oracle_rows_longer_than_a_work_item(md, wd, method):
+    _adakaon_vs_oracle(LONG_ROWS, md, wd, method, "bf16")
+
+
+def test_rows_longer_than_a_work_item_need_the_streaming_form():
+    import kaon_b200
+    p = torch.nn.Parameter(torch.zeros(16, 2560, 3, 3, dtype=torch.float32, device="cuda"))
+    opt = kaon_b200.Adakaon([p], momentum_dtype="4bit")
+    p.grad = torch.zeros_like(p)
+    with pytest.raises(NotImplementedError, match="streaming launches"):
+        opt.step()
+    q = torch.nn.Parameter(torch.zeros(4, 16388, dtype=torch.bfloat16, device="cuda"))
+    opt = kaon_b200.Adakaon([q], momentum_dtype="bfloat16")
+    q.grad = torch.zeros_like(q)
+    with pytest.raises(NotImplementedError, match="cannot be cut into row-aligned work items"):
+        opt.step()
+
+
+def _adakaon_vs_oracle(BIG, md, wd, method, dtype):
     import kaon_b200
     from _gpu import state_np, to_bits
     tdt = torch.bfloat16 if dtype == "bf16" else torch.float32
     gen = torch.Generator().manual_seed(9)
-    # rows of 4100 elements cannot start every work item on a 128-element 4-bit block boundary within
-    # the shared-memory budget: the plan refuses that shape for 4-bit momentum (tested below)
-    BIG = [s for s in BIG_ALL if not (md == "4bit" and s == (96, 4100))] if kind == "ragged" else BIG_STREAM
     host = [(torch.randn(s, generator=gen) * 0.02).to(tdt) for s in BIG]
     params = [torch.nn.Parameter(h.clone().cuda()) for h in host]
     kw = dict(lr=1e-4, betas=(0.9 if md else 0.0, 0.999), weight_decay=wd, bf16_method=method)
@@ -221,11 +249,20 @@ def test_unsupported_shape_is_refused_loudly():
         opt.step()
 
 
+@pytest.mark.parametrize("md", ["4bit", "int8"])
+def test_nekaon_vs_oracle_rows_longer_than_a_work_item(md):
+    _nekaon_vs_oracle(LONG_ROWS, md, "bf16")
+
+
 @pytest.mark.parametrize("dtype", ["bf16", "f32"])
 @pytest.mark.parametrize("md", ["4bit", "int8"])
 def test_nekaon_vs_oracle_streaming_shapes(md, dtype):
     """Nekaon (removal + update + climb on one weight access) on shapes that take the streaming stages
     and the separate COUNT / APPLY launches, against the oracle with the same Philox stream."""
+    _nekaon_vs_oracle(BIG_STREAM, md, dtype)
+
+
+def _nekaon_vs_oracle(BIG_STREAM, md, dtype):
     import kaon_b200
     from _gpu import state_np, to_bits
     tdt = torch.bfloat16 if dtype == "bf16" else torch.float32

@@ -48,6 +48,8 @@ def test_wait_that_runs_out_sets_status_and_drains_the_plan():
     _step(opt, params, grads[1])           # returns: the wait gave up after 1000 polls
     with pytest.raises(L.KaonError, match="bounded wait ran out"):
         opt.check_device_status()
+    with pytest.raises(L.KaonError, match="bounded wait ran out"):
+        opt.state_dict()                   # no checkpoint from state a failed kernel left behind
     assert lib.kaon_plan_status(plan.handle, C.c_void_p(torch.cuda.current_stream().cuda_stream)) == -4
     assert torch.equal(params[0].detach().view(torch.int16), before[0].view(torch.int16))  # APPLY never ran
     # the status is sticky: later steps of this plan do nothing and keep reporting
