@@ -1594,7 +1594,10 @@ __device__ __forceinline__ bool stream_ok(const DevTensor& d, const AdaDev& hp, 
 // ----------------------------------------------------------------------------- FLAT (1-D tensors)
 
 // reference src/kaon/adakaon.py:908-966: full second moment v, no factoring, no centralization.
-// The whole tensor (<= CAP elements) is one work item, so every tensor-wide reduction is CTA-local.
+// The whole tensor is one work item, so every tensor-wide reduction is CTA-local.  Up to CAP elements
+// the gradient and the momentum are staged and the intermediate lives in shared memory; a longer
+// tensor (t.slot != 0) is streamed from global memory pass by pass, with the intermediate and the
+// block maxima in the tensor's scratch.
 template <typename PT, int MK>
 __device__ void ada_flat(const PlanView& pv, const AdaDev& hp, const Task& t, Stage& st,
                          const AdaSmem& sm, int tid) {
@@ -1603,14 +1606,19 @@ __device__ void ada_flat(const PlanView& pv, const AdaDev& hp, const Task& t, St
   const unsigned char* g = reinterpret_cast<const unsigned char*>(pv.grads[t.tensor]);
   if (g == nullptr) return;
   const int n = t.n;
-  stage_issue(st, 0, g, (unsigned)n * E::BYTES, m_ptr<MK>(d, 0), m_bytes<MK>(n), tid);
-  if (!stage_wait(st, 0, g, (unsigned)n * E::BYTES, m_ptr<MK>(d, 0), m_bytes<MK>(n), pv.status)) return;
-  float* f_s = sm.x_s;  // u, then the new momentum
+  const bool lng = t.slot != 0;
+  if (!lng) {
+    stage_issue(st, 0, g, (unsigned)n * E::BYTES, m_ptr<MK>(d, 0), m_bytes<MK>(n), tid);
+    if (!stage_wait(st, 0, g, (unsigned)n * E::BYTES, m_ptr<MK>(d, 0), m_bytes<MK>(n), pv.status)) return;
+  }
+  const unsigned char* g_src = lng ? g : st.g_s;
+  const unsigned char* m_src = lng ? reinterpret_cast<const unsigned char*>(d.m) : st.m_s;
+  float* f_s = lng ? pv.aux + d.aux_off + 8 : sm.x_s;  // u, then the new momentum
   float* v = d.stat_a;
   // 1. second moment, raw update, its rms
   double ss = 0.0;
   for (int i = tid; i < n; i += AT) {
-    const float x = E::load1(st.g_s, i);
+    const float x = E::load1(g_src, i);
     float sq = __fmul_rn(x, x);
     if (hp.has_eps) sq = __fadd_rn(sq, hp.eps1);
     const float vn = lerp_torch(v[i], sq, hp.w2, hp.w2m1, hp.small_w2 != 0);
@@ -1624,20 +1632,22 @@ __device__ void ada_flat(const PlanView& pv, const AdaDev& hp, const Task& t, St
   const float div = fmaxf(__fdiv_rn(rms, hp.clip), 1.0f);
   // 2. momentum EMA (pre-requant value kept in f_s), absmax per scale group
   const bool one_block = MK == KAON_M_4BIT && d.block != 128u;
-  unsigned* blkmax = sm.rowmax_s;  // 4bit: one entry per 128-block (<= CAP/128); int8: entry 0
-  for (int i = tid; i < MAX_TASK_ROWS; i += AT) blkmax[i] = 0u;
+  // 4bit: one entry per 128-block; int8: entry 0
+  unsigned* blkmax = lng ? reinterpret_cast<unsigned*>(f_s + flat_long_pad(n)) : sm.rowmax_s;
+  const int nblk = lng ? (n + 127) / 128 + 1 : MAX_TASK_ROWS;
+  for (int i = tid; i < nblk; i += AT) blkmax[i] = 0u;
   __syncthreads();
   auto old_m = [&](int i) -> float {
     if constexpr (MK == KAON_M_4BIT) {
-      const unsigned byte = st.m_s[i >> 1];
+      const unsigned byte = m_src[i >> 1];
       const int nib = (i & 1) ? (byte >> 4) & 0xF : byte & 0xF;
       return __fmul_rn((float)(nib - 8), d.m_scale[one_block ? 0 : (i >> 7)]);
     } else if constexpr (MK == KAON_M_INT8) {
-      return __fmul_rn((float)(signed char)st.m_s[i], d.m_scale[0]);
+      return __fmul_rn((float)(signed char)m_src[i], d.m_scale[0]);
     } else if constexpr (MK == KAON_M_BF16) {
-      return Elems<__nv_bfloat16>::load1(st.m_s, i);
+      return Elems<__nv_bfloat16>::load1(m_src, i);
     } else if constexpr (MK == KAON_M_F32) {
-      return reinterpret_cast<const float*>(st.m_s)[i];
+      return reinterpret_cast<const float*>(m_src)[i];
     } else {
       return 0.0f;
     }
@@ -1670,7 +1680,7 @@ __device__ void ada_flat(const PlanView& pv, const AdaDev& hp, const Task& t, St
   if (hp.cautious) {
     for (int i = tid; i < n; i += AT) {
       const float dv = hp.has_wd ? __fmaf_rn(p_before(i), hp.lrwd, f_s[i]) : f_s[i];
-      if (__fmul_rn(dv, E::load1(st.g_s, i)) > 0.0f) ++kept_local;
+      if (__fmul_rn(dv, E::load1(g_src, i)) > 0.0f) ++kept_local;
     }
   }
   const unsigned kept = block_sum_u(kept_local, sm.red, tid);
@@ -1689,7 +1699,7 @@ __device__ void ada_flat(const PlanView& pv, const AdaDev& hp, const Task& t, St
   for (int i = tid; i < n; i += AT) {
     const float pv0 = p_before(i);
     float dv = hp.has_wd ? __fmaf_rn(pv0, hp.lrwd, f_s[i]) : f_s[i];
-    if (hp.cautious) dv = (__fmul_rn(dv, E::load1(st.g_s, i)) > 0.0f) ? __fdiv_rn(dv, denom) : 0.0f;
+    if (hp.cautious) dv = (__fmul_rn(dv, E::load1(g_src, i)) > 0.0f) ? __fdiv_rn(dv, denom) : 0.0f;
     float pn;
     if (E::IS_BF16 && hp.kahan) {
       uint16_t* shp = reinterpret_cast<uint16_t*>(d.shift) + i;

@@ -70,6 +70,9 @@ __host__ __device__ inline long long aux_mean(const DevTensor& d) { return aux_r
 __host__ __device__ inline long long aux_oldsc(const DevTensor& d) { return aux_mean(d) + d.rows; }
 // r_i = rsqrt(row_i / mean(row)) of every row, left by the last FINAL strip for COUNT / APPLY
 __host__ __device__ inline long long aux_rfac(const DevTensor& d) { return aux_oldsc(d) + d.rows; }
+// scratch of a 1-D tensor stepped from global memory: 8 floats | n floats (padded) | one word per 128 elements
+__host__ __device__ inline long long flat_long_pad(long long n) { return (n + 63) / 64 * 64; }
+__host__ __device__ inline long long flat_long_size(long long n) { return 8 + flat_long_pad(n) + ((n + 127) / 128 + 1 + 63) / 64 * 64; }
 __host__ __device__ inline long long aux_size(const DevTensor& d) { return aux_rfac(d) + d.rows - d.aux_off; }
 
 struct Task {

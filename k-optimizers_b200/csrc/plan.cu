@@ -91,7 +91,7 @@ static int split_tensor(const kaon_tensor_desc& d, int ti, int mk, bool lion, st
     }
     return 0;
   }
-  if (mk == KAON_M_INT8 && n > CAP)
+  if (mk == KAON_M_INT8 && n > CAP && lion)
     return fail(KAON_E_UNSUPPORTED, "tensor %d: a 1-D tensor of %lld elements with int8 momentum (one scalar scale) exceeds %d", ti, n, CAP);
   const long long chunk = CAP / A * A;
   for (long long e = 0; e < n; e += chunk)
@@ -215,12 +215,13 @@ int kaon_plan_create(kaon_plan** out, int optimizer, int param_dtype, int moment
       DevTensor& t = tens[i];
       if (per[i].empty()) continue;
       if (t.rows <= 0) {
-        if (t.numel > CAP) { delete pl; return fail(KAON_E_UNSUPPORTED, "tensor %d: a 1-D tensor of %lld elements exceeds %d (Adakaon/AdaMuon step 1-D tensors in one work item)", i, t.numel, CAP); }
+        if (t.numel > 0x7fffffffll) { delete pl; return fail(KAON_E_UNSUPPORTED, "tensor %d: a 1-D tensor of %lld elements (more than 2^31)", i, t.numel); }
+        const bool lng = t.numel > CAP;  // one work item all the same, streamed from global memory
         stages[i].resize(1);
-        max_cols = std::max<int>(max_cols, (int)t.numel);  // FLAT keeps the whole tensor as fp32 in shared memory
-        Task f = per[i][0]; f.phase = PH_ADA_FLAT; stages[i][0].push_back(f);
+        if (!lng) max_cols = std::max<int>(max_cols, (int)t.numel);  // FLAT keeps the whole tensor as fp32 in shared memory
+        stages[i][0].push_back(Task{i, PH_ADA_FLAT, 0, (int)t.numel, 0, lng ? 1 : 0, 0});
         t.aux_off = aux_floats; t.n_stats = 0; t.n_strips = 0; t.chunk_rows = 0;
-        aux_floats += 8;
+        aux_floats += lng ? flat_long_size(t.numel) : 8;
         continue;
       }
       const long long C = t.cols;

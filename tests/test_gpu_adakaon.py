@@ -179,6 +179,18 @@ def test_adakaon_vs_oracle_rows_longer_than_a_work_item(md, wd, method):
     _adakaon_vs_oracle(LONG_ROWS, md, wd, method, "bf16")
 
 
+# 1-D tensors above a work item's 16384 elements: one FLAT item streamed from global memory
+LONG_FLAT = [(50000,), (640, 320), (16385,), (131, 7), (300001,)]
+
+
+@pytest.mark.parametrize("md,wd,method", [("int8", 0.0, "stochastic_rounding"), ("4bit", 0.1, "none"),
+                                          ("bfloat16", 0.01, "stochastic_rounding"), ("float32", 0.0, "none"),
+                                          (None, 0.0, "none")])
+@pytest.mark.parametrize("dtype", ["bf16", "f32"])
+def test_adakaon_vs_oracle_long_1d_tensors(md, wd, method, dtype):
+    _adakaon_vs_oracle(LONG_FLAT, md, wd, method, dtype)
+
+
 def test_rows_longer_than_a_work_item_need_the_streaming_form():
     import kaon_b200
     p = torch.nn.Parameter(torch.zeros(16, 2560, 3, 3, dtype=torch.float32, device="cuda"))
@@ -252,6 +264,11 @@ def test_unsupported_shape_is_refused_loudly():
 @pytest.mark.parametrize("md", ["4bit", "int8"])
 def test_nekaon_vs_oracle_rows_longer_than_a_work_item(md):
     _nekaon_vs_oracle(LONG_ROWS, md, "bf16")
+
+
+@pytest.mark.parametrize("md", ["4bit", "int8"])
+def test_nekaon_vs_oracle_long_1d_tensors(md):
+    _nekaon_vs_oracle(LONG_FLAT, md, "bf16")
 
 
 @pytest.mark.parametrize("dtype", ["bf16", "f32"])

@@ -36,16 +36,18 @@ SHAPES = [(256, 384), (640, 128), (96,), (16, 12, 3, 3), (200, 328), (128, 128)]
 SHAPES_RAGGED = SHAPES
 # rows that are multiples of 16 elements: the plan takes the streaming stages and the separate COUNT / APPLY launches
 SHAPES_STREAM = [(128, 256), (256, 64), (200,), (48, 16, 4, 4), (96, 1024)]
+# a 1-D tensor above a work item's 16384 elements (one FLAT item streamed from global memory)
+SHAPES_LONG_1D = [(128, 256), (40000,), (96, 1024)]
 
 
 @pytest.mark.parametrize("md,method,wd", [("int8", "none", 0.0), ("4bit", "stochastic_rounding", 0.05),
                                           ("bfloat16", "none", 0.0), (None, "none", 0.0)])
 @pytest.mark.parametrize("dtype", ["bf16", "f32"])
-@pytest.mark.parametrize("kind", ["ragged", "stream"])
+@pytest.mark.parametrize("kind", ["ragged", "stream", "long1d"])
 def test_adamuon_chain_vs_oracle_with_same_orthogonal_factor(md, method, wd, dtype, kind):
     import kaon_b200
     from _gpu import state_np, to_bits
-    SHAPES = SHAPES_RAGGED if kind == "ragged" else SHAPES_STREAM  # noqa: N806
+    SHAPES = {"ragged": SHAPES_RAGGED, "stream": SHAPES_STREAM, "long1d": SHAPES_LONG_1D}[kind]  # noqa: N806
     tdt = torch.bfloat16 if dtype == "bf16" else torch.float32
     gen = torch.Generator().manual_seed(31)
     host = [(torch.randn(s, generator=gen) * 0.02).to(tdt) for s in SHAPES]
