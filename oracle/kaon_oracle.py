@@ -176,21 +176,22 @@ class OracleTensor:
         self.cols = self.n // self.rows if self.rows else self.n
         self.state: dict = {}
 
-    def init_momentum(self, md: str, block: int) -> None:
-        """reference src/kaon/_momentum_codec.py:263-264, 295-301, 350-360"""
+    def init_momentum(self, md: str, block: int, key: str = "m") -> None:
+        """reference src/kaon/_momentum_codec.py:263-264, 295-301, 350-360 (AdaPNM's two buffers,
+        keys "m_pos" / "m_neg": src/kaon/adapnm.py:451-480)"""
         st = self.state
         if md == "int8":
-            st["m"] = np.zeros(self.n, np.int8)
-            st["m_scale"] = np.ones(max(self.rows, 1), np.float32)
+            st[key] = np.zeros(self.n, np.int8)
+            st[f"{key}_scale"] = np.ones(max(self.rows, 1), np.float32)
         elif md == "4bit":
             bs = fourbit_block(self.n, block)
-            st["m"] = np.full((self.n + 1) // 2, 0x88, np.uint8)
-            st["m_scale"] = np.ones((self.n + bs - 1) // bs, np.float32)
-            st["m_numel"], st["m_block"] = self.n, bs
+            st[key] = np.full((self.n + 1) // 2, 0x88, np.uint8)
+            st[f"{key}_scale"] = np.ones((self.n + bs - 1) // bs, np.float32)
+            st[f"{key}_numel"], st[f"{key}_block"] = self.n, bs
         elif md == "bfloat16":
-            st["m"] = np.zeros(self.n, np.uint16)
+            st[key] = np.zeros(self.n, np.uint16)
         else:
-            st["m"] = np.zeros(self.n, np.float32)
+            st[key] = np.zeros(self.n, np.float32)
 
     def init_second_moment(self) -> None:
         """reference src/kaon/adakaon.py:318-331"""
@@ -201,7 +202,7 @@ class OracleTensor:
             self.state["v"] = np.zeros(self.n, np.float32)
 
     def block(self) -> int:
-        return int(self.state.get("m_block", 128))
+        return int(self.state.get("m_block", self.state.get("m_pos_block", 128)))
 
     def decoded_m(self, md: str) -> np.ndarray:
         st = self.state
@@ -318,6 +319,52 @@ class OracleAdakaon(OracleOptimizer):
                 C.c_int(bool(hp["cautious"])), C.c_int(bool(hp["gradient_centralization"])),
                 C.c_int(method), C.c_uint64(self.seed), C.c_uint32(self.t), C.c_uint32(tid),
                 _p(noise), C.byref(kept), C.byref(rms))
+            assert rc == 0
+            self.kept.append(kept.value)
+            self.rms.append(rms.value)
+
+
+class OracleAdaPNM(OracleOptimizer):
+    """reference src/kaon/adapnm.py:344-366 (defaults), :599-620 (step), :1209-1273 (one tensor)"""
+    DEFAULTS = dict(lr=1e-3, betas=(0.8, 0.999), beta0=0.5, eps=1e-8, weight_decay=0.0,
+                    clip_threshold=1.0, cautious=True, gradient_centralization=True, ams_bound=False,
+                    momentum_dtype="bfloat16", momentum_4bit_block=128,
+                    bf16_method="stochastic_rounding")
+
+    def _lazy_init(self, t):
+        if not t.state:
+            t.init_second_moment()
+            if not t.rows and self.hp["ams_bound"]:
+                t.state["max_v"] = np.zeros(t.n, np.float32)
+            t.init_momentum(self.hp["momentum_dtype"], self.hp["momentum_4bit_block"], "m_pos")
+            t.init_momentum(self.hp["momentum_dtype"], self.hp["momentum_4bit_block"], "m_neg")
+
+    def step(self, grads, noises=None):
+        hp = self.hp
+        self.t += 1
+        pos, neg = ("m_pos", "m_neg") if self.t % 2 == 1 else ("m_neg", "m_pos")  # adapnm.py:588-596
+        self.kept, self.rms = [], []
+        for tid, (t, g) in enumerate(zip(self.tensors, grads)):
+            if g is None:
+                self.kept.append(-1)
+                self.rms.append(float("nan"))
+                continue
+            self._lazy_init(t)
+            st = t.state
+            kept, rms = C.c_int64(-1), C.c_float(0)
+            noise = None if noises is None else noises[tid]
+            method = self._method(t, noise)
+            rc = lib().ko_adapnm_step(
+                _p(t.p), _p(np.ascontiguousarray(g).reshape(-1)), _dt(t.p), C.c_int64(t.n), C.c_int64(t.rows),
+                C.c_int(MKIND[hp["momentum_dtype"]]), _p(st[pos]), _p(st.get(f"{pos}_scale")), _p(st[neg]),
+                _p(st.get(f"{neg}_scale")), C.c_int64(t.block()),
+                _p(st["row"] if t.rows else st["v"]), _p(st["col"] if t.rows else None), _p(st.get("max_v")),
+                C.c_double(hp["lr"]), C.c_double(hp["betas"][0]), C.c_double(hp["betas"][1]),
+                C.c_double(hp["beta0"]), C.c_double(hp["eps"]), C.c_double(hp["weight_decay"]),
+                C.c_double(hp["clip_threshold"]), C.c_int(bool(hp["cautious"])),
+                C.c_int(bool(hp["gradient_centralization"])), C.c_int(bool(hp["ams_bound"])), C.c_int(method),
+                C.c_uint32(self.t), C.c_uint64(self.seed), C.c_uint32(self.t), C.c_uint32(tid), _p(noise),
+                C.byref(kept), C.byref(rms))
             assert rc == 0
             self.kept.append(kept.value)
             self.rms.append(rms.value)

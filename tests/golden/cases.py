@@ -41,6 +41,13 @@ CASES = {
     # AdaMuon (C5 settings)
     "adamuon_int8_none": ("AdaMuon", dict(lr=1e-3, ns_steps=2, cautious=True, momentum_dtype="int8", bf16_method="none"), MUON, "bf16", 4, 30, {}),
     "adamuon_int8_kahan": ("AdaMuon", dict(lr=1e-3, ns_steps=2, cautious=True, momentum_dtype="int8", bf16_method="kahan"), MUON, "bf16", 3, 31, {}),
+    # AdaPNM (two momenta through the same codecs; the second-moment EMA and the clip as Adakaon's)
+    "adapnm_int8_none": ("AdaPNM", dict(lr=1e-4, momentum_dtype="int8", bf16_method="none"), SMALL, "bf16", 6, 40, {}),
+    "adapnm_4bit_wd_f32": ("AdaPNM", dict(lr=1e-4, betas=(0.9, 0.999), beta0=1.0, weight_decay=0.1, momentum_dtype="4bit"), SMALL, "f32", 5, 41, {}),
+    "adapnm_bf16m_sr": ("AdaPNM", dict(lr=1e-4), SMALL, "bf16", 4, 42, {}),
+    "adapnm_f32m_ams_nocautious": ("AdaPNM", dict(lr=1e-4, eps=1e-6, momentum_dtype="float32", ams_bound=True, cautious=False, gradient_centralization=False, weight_decay=0.05, bf16_method="none"), SMALL, "bf16", 5, 43, {}),
+    "adapnm_int8_kahan": ("AdaPNM", dict(lr=1e-4, momentum_dtype="int8", bf16_method="kahan", clip_threshold=0.5), SMALL, "bf16", 5, 44, {}),
+    "adapnm_4bit_outlier": ("AdaPNM", dict(lr=1e-4, momentum_dtype="4bit", bf16_method="none"), SMALL, "bf16", 5, 45, {"outlier": True}),
     # C1 at full size (the CPU-runnable correctness workload); big tensors stored strided
     "c1_full": ("Adakaon", dict(lr=1e-4, betas=(0.9, 0.999), momentum_dtype="int8", bf16_method="stochastic_rounding"), C1, "bf16", 10, 0, {"store_inputs": False, "sample": 257}),
 }

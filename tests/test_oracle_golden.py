@@ -14,7 +14,7 @@ from _golden import Fixture, rel_err, sr_close, ulp_diff_bf16
 from golden.cases import CASES, SCHEDULES
 
 ORACLES = {"Lion": ko.OracleLion, "Adakaon": ko.OracleAdakaon, "Nekaon": ko.OracleNekaon,
-           "AdaMuon": ko.OracleAdaMuon}
+           "AdaMuon": ko.OracleAdaMuon, "AdaPNM": ko.OracleAdaPNM}
 
 
 def test_philox_known_answers():
@@ -84,11 +84,20 @@ def _run_oracle(name):
         yield step, f, opt
 
 
-def _check_state(f, opt, step, *, exact, md):
+def _check_state(f, opt, step, *, exact, md, mkeys=("m",)):
     """Compare every tensor's state with the fixture; returns (flipped codes, total codes)."""
     flips = total = 0
+    for mk in mkeys:
+        fl, to = _check_state_one(f, opt, step, exact=exact, md=md, mk=mk)
+        flips += fl
+        total += to
+    return flips, total
+
+
+def _check_state_one(f, opt, step, *, exact, md, mk):
+    flips = total = 0
     for i, t in enumerate(opt.tensors):
-        for key in ("row", "col", "v"):
+        for key in ("row", "col", "v", "max_v"):
             want = f.state(step, i, key)
             if want is None:
                 continue
@@ -96,17 +105,17 @@ def _check_state(f, opt, step, *, exact, md):
                 assert np.array_equal(t.state[key], want), (step, i, key)
             else:
                 assert rel_err(t.state[key], want) <= 1e-5, (step, i, key, rel_err(t.state[key], want))
-        want_m = f.state(step, i, "m")
+        want_m = f.state(step, i, mk)
         if want_m is None:
             continue
-        got_m = t.state["m"]
-        want_sc = f.state(step, i, "m_scale")
+        got_m = t.state[mk]
+        want_sc = f.state(step, i, f"{mk}_scale")
         if md in ("int8", "4bit"):
             if exact:
                 assert np.array_equal(got_m.view(np.uint8), want_m.view(np.uint8)), (step, i)
-                assert np.array_equal(t.state["m_scale"], want_sc.reshape(-1)), (step, i)
+                assert np.array_equal(t.state[f"{mk}_scale"], want_sc.reshape(-1)), (step, i)
             else:
-                assert rel_err(t.state["m_scale"], want_sc.reshape(-1)) <= 1e-5
+                assert rel_err(t.state[f"{mk}_scale"], want_sc.reshape(-1)) <= 1e-5
                 if md == "int8":
                     d = np.abs(got_m.astype(np.int32) - want_m.view(np.int8).astype(np.int32))
                 else:
@@ -220,6 +229,55 @@ def test_adakaon(name):
                 np.testing.assert_allclose(t.p, want, rtol=1e-5, atol=1e-9)
     if total:
         assert flips / total < 2e-3, (flips, total)
+
+
+@pytest.mark.parametrize("name", [n for n in CASES if n.startswith("adapnm_") and "kahan" not in n])
+def test_adapnm(name):
+    """reference src/kaon/adapnm.py: two momenta (only the positive one sees the gradient, the roles
+    alternate), Adakaon's factored second moment, RMS clip of the mixed update."""
+    kw = CASES[name][1]
+    md = kw.get("momentum_dtype", "bfloat16")
+    sr = kw.get("bf16_method", "stochastic_rounding") == "stochastic_rounding"
+    exact = not kw.get("gradient_centralization", True)   # without a row mean upstream the momenta are exact
+    flips = total = 0
+    for step, f, opt in _run_oracle(name):
+        fl, to = _check_state_one(f, opt, step, exact=False, md=md, mk="m_pos")
+        fl2, to2 = _check_state_one(f, opt, step, exact=False, md=md, mk="m_neg")
+        flips += fl + fl2
+        total += to + to2
+        for i, t in enumerate(opt.tensors):
+            if exact and "v" in t.state:   # the 1-D second moment (and its running maximum) bit for bit
+                assert np.array_equal(t.state["v"], f.state(step, i, "v")), (step, i)
+                if "max_v" in t.state:
+                    assert np.array_equal(t.state["max_v"], f.state(step, i, "max_v")), (step, i)
+            if md == "float32":
+                for mk in ("m_pos", "m_neg"):
+                    want = f.state(step, i, mk)
+                    if exact:
+                        assert np.array_equal(t.state[mk], want), (step, i, mk)
+                    else:
+                        np.testing.assert_allclose(t.state[mk], want, rtol=1e-5, atol=1e-12)
+            want = f.weights(step, i)
+            if want.dtype == np.uint16:
+                if sr:
+                    assert sr_close(t.p, want, step, 1e-3), (step, i)
+                else:
+                    assert ulp_diff_bf16(t.p, want).max() <= 1, (step, i)
+            else:
+                np.testing.assert_allclose(t.p, want, rtol=1e-5, atol=1e-9)
+    if total:
+        assert flips / total < 2e-3, (flips, total)
+
+
+def test_adapnm_kahan():
+    flips = total = 0
+    for step, f, opt in _run_oracle("adapnm_int8_kahan"):
+        fl, to = _check_state(f, opt, step, exact=False, md="int8", mkeys=("m_pos", "m_neg"))
+        flips += fl
+        total += to
+        for i, t in enumerate(opt.tensors):
+            assert _kahan_close(t.p, t.state["shift"], f.weights(step, i), f.state(step, i, "shift")), (step, i)
+    assert flips / total < 2e-3
 
 
 def test_nekaon_fp32_params():
