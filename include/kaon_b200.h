@@ -41,6 +41,7 @@ extern "C" {
 #define KAON_OPT_LION 0
 #define KAON_OPT_ADAKAON 1
 #define KAON_OPT_ADAMUON 2
+#define KAON_OPT_ADAPNM 3
 
 /* error codes */
 #define KAON_OK 0
@@ -100,6 +101,15 @@ typedef struct kaon_adamuon_hparams {
   double lr, beta1, beta2, eps1, weight_decay, clip_threshold;
   int32_t ns_steps, cautious, gradient_centralization, bf16_method;
 } kaon_adamuon_hparams;
+
+/* AdaPNM (src/kaon/adapnm.py:344-366, 998-1017).  group_step is the parameter group's 1-based step count
+ * ("step" in the reference's param_groups): it sets the bias corrections and which stored momentum is the
+ * positive one (odd: "m_pos"). */
+typedef struct kaon_adapnm_hparams {
+  double lr, beta1, beta2, beta0, eps, weight_decay, clip_threshold;
+  int32_t cautious, gradient_centralization, ams_bound, bf16_method;
+  uint32_t group_step, reserved;
+} kaon_adapnm_hparams;
 
 /* ---- library ---- */
 int kaon_abi_version(void);
@@ -183,6 +193,20 @@ int kaon_lion_noalloc_status(void* stream);
  * optionally the Nekaon removal and climb (the msam_* fields of kaon_adakaon_hparams). */
 int kaon_adakaon_step(kaon_plan* plan, const kaon_adakaon_hparams* hp, uint64_t seed, uint32_t step,
                       void* stream);
+
+/* AdaPNM.  Replaces AdaPNM._step_impl / _native_dispatch / _step_foreach / _factored_bucket /
+ * _nonfactored_bucket / _pn_stacked / _step_one_param / _pn_one (src/kaon/adapnm.py:599-645, 1039-1273)
+ * with the same second-moment, codec, cautious and weight-write pieces as kaon_adakaon_step.  The plan is
+ * created with optimizer KAON_OPT_ADAPNM; each descriptor's m / m_scale name the state's "m_pos" buffers,
+ * stat_a / stat_b its row / col (or v) statistics.  kaon_adapnm_attach then names, per tensor, the
+ * "m_neg" buffer, its scales (int8 / 4-bit; else null) and, for ams_bound, the 1-D tensors' max_v (null
+ * array or null entries otherwise); it must be called once before the first step.  weight_decay is
+ * applied to the weights before the update (p *= 1 - lr*wd, rounded to the weights' dtype), as the
+ * reference does. */
+int kaon_adapnm_attach(kaon_plan* plan, const void* const* m_neg, float* const* m_neg_scale,
+                       float* const* max_v, int n);
+int kaon_adapnm_step(kaon_plan* plan, const kaon_adapnm_hparams* hp, uint64_t seed, uint32_t step,
+                     void* stream);
 
 /* One AdaMuon step.  Replaces AdaMuon._run_step / _factored_bucket / _nonfactored_bucket /
  * _step_one_param (src/kaon/adamuon.py:327-352, 434-615): per >=2-D tensor the EMA of the raw gradient

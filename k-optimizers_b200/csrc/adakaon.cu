@@ -2610,8 +2610,7 @@ int ensure_apply2(kaon_plan* pl) {
     std::vector<Task> stats, rest;
     for (const Task& t : h) {
       if (t.phase != PH_ADA_STATS) { rest.push_back(t); continue; }
-      const DevTensor& dt = pl->h_tensors[t.tensor];
-      if (dt.cols < 256 || (dt.cols & 7) || t.n / dt.cols > ST_MAXROWS || (dt.aux_off & 3)) ok = false;
+      if (!stats_item_ok(pl, t)) ok = false;
       stats.push_back(t);
     }
     if (ok && !stats.empty()) {
@@ -2650,6 +2649,32 @@ int launch_stats(kaon_plan* pl, const PlanView& base, const AdaDev& hp, cudaStre
   ada_stats_kernel<<<pl->stats_grid, STT, 0, s>>>(vs, hp);
   pl->launches += 1;
   return 1;
+}
+
+bool stats_item_ok(const kaon_plan* pl, const Task& t) {
+  const DevTensor& dt = pl->h_tensors[t.tensor];
+  return dt.cols >= 256 && (dt.cols & 7) == 0 && t.n / dt.cols <= ST_MAXROWS && (dt.aux_off & 3) == 0;
+}
+
+int launch_stats_tasks(kaon_plan* pl, const PlanView& base, const AdaDev& hp, const Task* tasks, int n, cudaStream_t s) {
+  if (pl->d_counter2 == nullptr) {
+    KAON_CUDA(cudaMalloc((void**)&pl->d_counter2, 256));
+    pl->device_bytes += 256;
+  }
+  if (pl->stats_grid == 0) {
+    int per_sm = 0;
+    KAON_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, (const void*)ada_stats_kernel, STT, 0));
+    pl->stats_grid = pl->sm_count * std::max(per_sm, 1);
+  }
+  PlanView vs = base;
+  vs.tasks = tasks;
+  vs.n_tasks = n;
+  vs.task_counter = pl->d_counter2;
+  KAON_CUDA(cudaMemsetAsync(pl->d_counter2, 0, sizeof(unsigned), s));
+  ada_stats_kernel<<<pl->stats_grid, STT, 0, s>>>(vs, hp);
+  KAON_CUDA(cudaGetLastError());
+  pl->launches += 1;
+  return KAON_OK;
 }
 
 int launch_count_apply(kaon_plan* pl, const PlanView& base, const AdaDev& hp, cudaStream_t s) {

@@ -24,5 +24,8 @@ size_t x_offset_rows(const kaon_plan* pl);
 int ensure_apply2(kaon_plan* pl);
 int launch_count_apply(kaon_plan* pl, const PlanView& base, const AdaDev& hp, cudaStream_t s);
 int launch_stats(kaon_plan* pl, const PlanView& base, const AdaDev& hp, cudaStream_t s);
+// the STATS launch over a caller's list of STATS items (all of which pass stats_item_ok); KAON_OK or an error
+bool stats_item_ok(const kaon_plan* pl, const Task& t);
+int launch_stats_tasks(kaon_plan* pl, const PlanView& base, const AdaDev& hp, const Task* tasks, int n, cudaStream_t s);
 
 }  // namespace kaon

@@ -168,4 +168,11 @@ struct kaon_plan {
   int n_flat_tensors = 0;
   size_t smem_bytes = 0;
   int64_t total_elems = 0;
+  // AdaPNM only: lists, partial sums and the second-momentum table (adapnm.cu), built by kaon_adapnm_attach
+  void* pnm = nullptr;
+  bool pnm_has_max_v = false;
 };
+
+namespace kaon {
+void pnm_free(kaon_plan* pl);
+}

@@ -7,7 +7,8 @@ through a C ABI (``libkaon_b200.so``, declared in ``include/kaon_b200.h``).  CUD
 from ._version import __version__
 from .adakaon import Adakaon
 from .adamuon import AdaMuon
+from .adapnm import AdaPNM
 from .lion import Lion
 from .nekaon import Nekaon
 
-__all__ = ["AdaMuon", "Adakaon", "Lion", "Nekaon", "__version__"]
+__all__ = ["AdaMuon", "AdaPNM", "Adakaon", "Lion", "Nekaon", "__version__"]

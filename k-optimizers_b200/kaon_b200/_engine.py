@@ -27,25 +27,26 @@ def fourbit_block_size(numel: int, block: int) -> int:
     return min(block, numel) if numel > 0 else 1
 
 
-def init_momentum_state(state: dict[str, Any], grad: torch.Tensor, md: str, block: int) -> None:
-    """Allocate the first-moment buffer in the reference's layout
-    (src/kaon/_momentum_codec.py:263-264, 295-301, 350-360; src/kaon/lion.py:210-241)."""
+def init_momentum_state(state: dict[str, Any], grad: torch.Tensor, md: str, block: int, key: str = "m") -> None:
+    """Allocate one first-moment buffer in the reference's layout
+    (src/kaon/_momentum_codec.py:263-264, 295-301, 350-360; src/kaon/lion.py:210-241); AdaPNM keeps two,
+    under the keys "m_pos" and "m_neg" (src/kaon/adapnm.py:451-480)."""
     dev = grad.device
     if md in ("bfloat16", "float32"):
-        state["m"] = torch.zeros_like(grad, dtype=torch.bfloat16 if md == "bfloat16" else torch.float32,
+        state[key] = torch.zeros_like(grad, dtype=torch.bfloat16 if md == "bfloat16" else torch.float32,
                                       memory_format=torch.contiguous_format)
     elif md == "int8":
-        state["m"] = torch.zeros_like(grad, dtype=torch.int8, memory_format=torch.contiguous_format)
+        state[key] = torch.zeros_like(grad, dtype=torch.int8, memory_format=torch.contiguous_format)
         shape = (grad.shape[0],) + (1,) * (grad.ndim - 1) if grad.ndim >= 2 else ()
-        state["m_scale"] = torch.ones(shape, dtype=torch.float32, device=dev)
+        state[f"{key}_scale"] = torch.ones(shape, dtype=torch.float32, device=dev)
     else:  # 4bit
         numel = grad.numel()
         bs = fourbit_block_size(numel, block)
         nblocks = (numel + bs - 1) // bs
-        state["m"] = torch.full(((numel + 1) // 2,), 0x88, dtype=torch.uint8, device=dev)
-        state["m_scale"] = torch.ones(nblocks, dtype=torch.float32, device=dev)
-        state["m_numel"] = numel
-        state["m_block"] = bs
+        state[key] = torch.full(((numel + 1) // 2,), 0x88, dtype=torch.uint8, device=dev)
+        state[f"{key}_scale"] = torch.ones(nblocks, dtype=torch.float32, device=dev)
+        state[f"{key}_numel"] = numel
+        state[f"{key}_block"] = bs
 
 
 def init_shift_state(p: torch.Tensor, state: dict[str, Any], group: dict[str, Any]) -> None:
@@ -59,7 +60,7 @@ class GroupPlan:
     """One C-ABI plan: the tensors of one (param group, device, dtype) bucket."""
 
     def __init__(self, optimizer_kind: int, params: list[torch.Tensor], states: list[dict[str, Any]],
-                 tensor_ids: list[int], momentum_dtype: str | None):
+                 tensor_ids: list[int], momentum_dtype: str | None, m_key: str = "m"):
         lib = L.lib()
         p0 = params[0]
         if not p0.is_cuda:
@@ -83,8 +84,8 @@ class GroupPlan:
             d.numel = p.numel()
             d.rows = p.shape[0] if p.ndim >= 2 else 0
             d.tensor_id = tid
-            d.block = int(st.get("m_block", 128))
-            for field, key in (("m", "m"), ("m_scale", "m_scale")):
+            d.block = int(st.get(f"{m_key}_block", 128))
+            for field, key in (("m", m_key), ("m_scale", f"{m_key}_scale")):
                 t = st.get(key) if mk != L.M_NONE else None
                 if t is not None:
                     if not t.is_contiguous() or t.device != p.device:
@@ -179,6 +180,10 @@ class FusedStepMixin:
     """
 
     _OPT_KIND: int
+    _M_KEY = "m"   # state key of the momentum the plan's descriptors name
+
+    def _plan_created(self, plan: GroupPlan, params: list[torch.Tensor], states: list[dict[str, Any]]) -> None:
+        """Hook for optimizers whose plan needs more than the descriptor table."""
 
     def _fused_init(self) -> None:
         self._plans: dict[tuple, GroupPlan] = {}
@@ -248,7 +253,8 @@ class FusedStepMixin:
                 if ids is None:
                     ids = self._tensor_ids()
                 pl = GroupPlan(self._OPT_KIND, plist, [state_of(p) for p in plist],
-                               [ids[id(p)] for p in plist], self._momentum_dtype(group))
+                               [ids[id(p)] for p in plist], self._momentum_dtype(group), self._M_KEY)
+                self._plan_created(pl, plist, [state_of(p) for p in plist])
                 if self._mirrors is not None:
                     pl.set_peers(*self._mirrors)
                 self._plans[key] = pl

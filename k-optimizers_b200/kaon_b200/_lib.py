@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(PKG, "libkaon_b200.so")
 DT_F32, DT_BF16 = 0, 1
 M_F32, M_BF16, M_INT8, M_4BIT, M_NONE = 0, 1, 2, 3, 4
 W_NONE, W_SR, W_KAHAN = 0, 1, 2
-OPT_LION, OPT_ADAKAON, OPT_ADAMUON = 0, 1, 2
+OPT_LION, OPT_ADAKAON, OPT_ADAMUON, OPT_ADAPNM = 0, 1, 2, 3
 TAG_UPDATE, TAG_REMOVE, TAG_CLIMB, TAG_EVAL, TAG_TRAIN = 0, 1, 2, 3, 4
 MOMENTUM_KIND = {"float32": M_F32, "bfloat16": M_BF16, "int8": M_INT8, "4bit": M_4BIT}
 BF16_METHOD = {"none": W_NONE, "stochastic_rounding": W_SR, "kahan": W_KAHAN}
@@ -48,6 +48,13 @@ class AdaMuonHParams(C.Structure):
                 ("eps1", C.c_double), ("weight_decay", C.c_double), ("clip_threshold", C.c_double),
                 ("ns_steps", C.c_int32), ("cautious", C.c_int32),
                 ("gradient_centralization", C.c_int32), ("bf16_method", C.c_int32)]
+
+
+class AdaPNMHParams(C.Structure):
+    _fields_ = [("lr", C.c_double), ("beta1", C.c_double), ("beta2", C.c_double), ("beta0", C.c_double),
+                ("eps", C.c_double), ("weight_decay", C.c_double), ("clip_threshold", C.c_double),
+                ("cautious", C.c_int32), ("gradient_centralization", C.c_int32), ("ams_bound", C.c_int32),
+                ("bf16_method", C.c_int32), ("group_step", C.c_uint32), ("reserved", C.c_uint32)]
 
 
 class KaonError(RuntimeError):
