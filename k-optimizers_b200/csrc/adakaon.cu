@@ -2555,20 +2555,26 @@ int configure_launch_adakaon(kaon_plan* pl, const cudaDeviceProp& prop, int max_
   return KAON_OK;
 }
 
-// One-time set-up of the three-launch form: eligibility, the flat COUNT/APPLY items, the first launch's
-// list without COUNT and APPLY items, the second kernel's launch configuration.
+// One-time set-up of the launches beside the persistent kernel.  Per factored tensor: its COUNT and
+// APPLY items go to the flat COUNT / APPLY launches when its rows stream (a multiple of 8 elements; 16
+// with int8 momentum; 4-bit block 128), and its STATS items to the STATS launch when they qualify
+// (stats_item_ok, bf16 gradients or AdaMuon's bf16 signal).  Everything else - FINAL, the 1-D tensors,
+// the stages of tensors that do not qualify - stays in the persistent kernel, whose two lists (with
+// COUNT items for the cautious mask, without them otherwise) are the plan's lists minus what left.
 int ensure_apply2(kaon_plan* pl) {
   if (pl->apply2 != 0) return KAON_OK;
   pl->apply2 = -1;
   const bool muon = pl->optimizer == KAON_OPT_ADAMUON;
   const int mk = muon ? KAON_M_NONE : pl->momentum_kind;
   std::vector<Task> items;
+  std::vector<char> elig((size_t)pl->n_tensors, 0);
   for (int i = 0; i < pl->n_tensors; ++i) {
     const DevTensor& t = pl->h_tensors[i];
     if (t.rows <= 0 || t.numel == 0) continue;
-    if ((t.cols & 7) != 0) return KAON_OK;
-    if (mk == KAON_M_4BIT && t.block != 128u) return KAON_OK;
-    if (mk == KAON_M_INT8 && (t.cols & 15) != 0) return KAON_OK;
+    if ((t.cols & 7) != 0) continue;
+    if (mk == KAON_M_4BIT && t.block != 128u) continue;
+    if (mk == KAON_M_INT8 && (t.cols & 15) != 0) continue;
+    elig[i] = 1;
     for (long long e = 0; e < t.numel; e += APPLY_CAP)
       items.push_back(Task{i, PH_ADA_APPLY, e, (int)std::min<long long>(APPLY_CAP, t.numel - e), 0, 0, 0});
   }
@@ -2586,69 +2592,53 @@ int ensure_apply2(kaon_plan* pl) {
   int per_sm = 0;
   KAON_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, (const void*)k, APPLY_THREADS, pl->apply_smem));
   if (per_sm < 1) return KAON_OK;
-  cudaDeviceProp prop;
-  KAON_CUDA(cudaGetDeviceProperties(&prop, pl->device));
-  pl->apply_grid = prop.multiProcessorCount * per_sm;
-  // the first launch's list without COUNT and APPLY items
-  {
-    std::vector<Task> h((size_t)pl->n_tasks_main);
-    KAON_CUDA(cudaMemcpy(h.data(), pl->d_tasks_main, sizeof(Task) * h.size(), cudaMemcpyDeviceToHost));
-    std::vector<Task> keep;
-    for (const Task& t : h)
-      if (t.phase != PH_ADA_APPLY) keep.push_back(t);
-    KAON_CUDA(cudaMalloc((void**)&pl->d_tasks_main_na, sizeof(Task) * std::max<size_t>(keep.size(), 1)));
-    KAON_CUDA(cudaMemcpy(pl->d_tasks_main_na, keep.data(), sizeof(Task) * keep.size(), cudaMemcpyHostToDevice));
-    pl->n_tasks_main_na = (int)keep.size();
+  pl->apply_grid = pl->sm_count * per_sm;
+  // the persistent kernel's lists and the STATS launch's
+  const bool stats_dtype = muon || pl->param_dtype == KAON_DT_BF16;
+  std::vector<Task> stats;
+  pl->long_rows_ok = true;
+  for (int variant = 0; variant < 2; ++variant) {   // 0: from the list without COUNT items; 1: from the full list
+    const Task* src = variant ? pl->d_tasks_full : pl->d_tasks_main;
+    const int ns = variant ? pl->n_tasks_full : pl->n_tasks_main;
+    std::vector<Task> h((size_t)ns), keep;
+    KAON_CUDA(cudaMemcpy(h.data(), src, sizeof(Task) * h.size(), cudaMemcpyDeviceToHost));
+    for (const Task& t : h) {
+      const bool el = elig[t.tensor] != 0;
+      if ((t.phase == PH_ADA_APPLY || t.phase == PH_ADA_COUNT) && el) continue;
+      if (t.phase == PH_ADA_STATS && stats_dtype && stats_item_ok(pl, t)) {
+        if (variant == 0) stats.push_back(t);
+        continue;
+      }
+      // what stays here is staged row by row: a tensor whose rows exceed a work item cannot stay
+      if (t.phase != PH_ADA_FINAL && t.phase != PH_ADA_FLAT && pl->h_tensors[t.tensor].cols > CAP) pl->long_rows_ok = false;
+      keep.push_back(t);
+    }
+    KAON_CUDA(cudaMalloc((void**)&pl->d_tasks_na[variant], sizeof(Task) * std::max<size_t>(keep.size(), 1)));
+    KAON_CUDA(cudaMemcpy(pl->d_tasks_na[variant], keep.data(), sizeof(Task) * keep.size(), cudaMemcpyHostToDevice));
+    pl->n_tasks_na[variant] = (int)keep.size();
     pl->device_bytes += (int64_t)(sizeof(Task) * keep.size());
   }
-  // STATS as a launch of its own (ada_stats_kernel): bf16 rows of at least 256 elements in every factored
-  // tensor, work items of at most ST_MAXROWS rows whose slot rows are 16-byte aligned
-  {
-    bool ok = muon || pl->param_dtype == KAON_DT_BF16;
-    std::vector<Task> h((size_t)pl->n_tasks_main_na);
-    KAON_CUDA(cudaMemcpy(h.data(), pl->d_tasks_main_na, sizeof(Task) * h.size(), cudaMemcpyDeviceToHost));
-    std::vector<Task> stats, rest;
-    for (const Task& t : h) {
-      if (t.phase != PH_ADA_STATS) { rest.push_back(t); continue; }
-      if (!stats_item_ok(pl, t)) ok = false;
-      stats.push_back(t);
-    }
-    if (ok && !stats.empty()) {
-      KAON_CUDA(cudaMalloc((void**)&pl->d_tasks_stats, sizeof(Task) * stats.size()));
-      KAON_CUDA(cudaMemcpy(pl->d_tasks_stats, stats.data(), sizeof(Task) * stats.size(), cudaMemcpyHostToDevice));
-      KAON_CUDA(cudaMalloc((void**)&pl->d_tasks_rest, sizeof(Task) * std::max<size_t>(rest.size(), 1)));
-      KAON_CUDA(cudaMemcpy(pl->d_tasks_rest, rest.data(), sizeof(Task) * rest.size(), cudaMemcpyHostToDevice));
-      pl->n_tasks_stats = (int)stats.size();
-      pl->n_tasks_rest = (int)rest.size();
-      int per_sm2 = 0;
-      KAON_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm2, (const void*)ada_stats_kernel, STT, 0));
-      pl->stats_grid = prop.multiProcessorCount * std::max(per_sm2, 1);
-      pl->device_bytes += (int64_t)(sizeof(Task) * (stats.size() + rest.size()));
-    }
+  if (!stats.empty()) {
+    KAON_CUDA(cudaMalloc((void**)&pl->d_tasks_stats, sizeof(Task) * stats.size()));
+    KAON_CUDA(cudaMemcpy(pl->d_tasks_stats, stats.data(), sizeof(Task) * stats.size(), cudaMemcpyHostToDevice));
+    pl->n_tasks_stats = (int)stats.size();
+    pl->device_bytes += (int64_t)(sizeof(Task) * stats.size());
   }
   KAON_CUDA(cudaMalloc((void**)&pl->d_tasks_apply2, sizeof(Task) * items.size()));
   KAON_CUDA(cudaMemcpy(pl->d_tasks_apply2, items.data(), sizeof(Task) * items.size(), cudaMemcpyHostToDevice));
-  KAON_CUDA(cudaMalloc((void**)&pl->d_counter2, 256));
   pl->n_tasks_apply2 = (int)items.size();
-  pl->device_bytes += (int64_t)(sizeof(Task) * items.size() + 256);
+  pl->device_bytes += (int64_t)(sizeof(Task) * items.size());
   pl->apply2 = 1;
   return KAON_OK;
 }
 
 // The COUNT (cautious mask on) and APPLY launches over the plan's flat items; `base` carries the
 // plan's pointers (and AdaMuon's signal column).
-// STATS as a launch of its own, when the plan has the lists for it: returns 1 after launching (the
-// caller's first kernel then walks pl->d_tasks_rest), 0 when the plan keeps STATS in the first kernel.
+// STATS as a launch of its own over the plan's qualifying STATS items (the persistent kernel's lists
+// do not hold them); KAON_OK also when there are none.
 int launch_stats(kaon_plan* pl, const PlanView& base, const AdaDev& hp, cudaStream_t s) {
-  if (pl->n_tasks_stats == 0) return 0;
-  PlanView vs = base;
-  vs.tasks = pl->d_tasks_stats;
-  vs.n_tasks = pl->n_tasks_stats;
-  vs.task_counter = pl->d_counter2;
-  if (cudaMemsetAsync(pl->d_counter2, 0, sizeof(unsigned), s) != cudaSuccess) return 0;
-  ada_stats_kernel<<<pl->stats_grid, STT, 0, s>>>(vs, hp);
-  pl->launches += 1;
-  return 1;
+  if (pl->n_tasks_stats == 0) return KAON_OK;
+  return launch_stats_tasks(pl, base, hp, pl->d_tasks_stats, pl->n_tasks_stats, s);
 }
 
 bool stats_item_ok(const kaon_plan* pl, const Task& t) {
@@ -2678,6 +2668,10 @@ int launch_stats_tasks(kaon_plan* pl, const PlanView& base, const AdaDev& hp, co
 }
 
 int launch_count_apply(kaon_plan* pl, const PlanView& base, const AdaDev& hp, cudaStream_t s) {
+  if (pl->d_counter2 == nullptr) {
+    KAON_CUDA(cudaMalloc((void**)&pl->d_counter2, 256));
+    pl->device_bytes += 256;
+  }
   const bool muon = pl->optimizer == KAON_OPT_ADAMUON;
   const int mk = muon ? KAON_M_NONE : pl->momentum_kind;
   PlanView va = base;
@@ -2734,18 +2728,19 @@ extern "C" int kaon_adakaon_step(kaon_plan* pl, const kaon_adakaon_hparams* h, u
   if (int rc = ensure_apply2(pl)) return rc;
   // two launches when the plan is eligible (int8 momentum also needs the COUNT stage's row maxima)
   const bool two = pl->apply2 == 1 && (pl->momentum_kind != KAON_M_INT8 || hp.cautious);
-  if (pl->has_long_rows && !(two && pl->n_tasks_stats > 0))
+  if (pl->has_long_rows && !(two && pl->long_rows_ok))
     return fail(KAON_E_UNSUPPORTED,
                 "a tensor's rows exceed a work item of %d elements: such rows are stepped by the streaming launches "
-                "only (bf16 weights, every factored tensor with rows of >= 256 elements in multiples of 8 (16 with "
-                "int8 momentum), 4-bit block 128, int8 momentum with the cautious mask on)", CAP);
-  // first launch: STATS, FINAL, FLAT (the list without COUNT and APPLY items); then COUNT, then APPLY
-  if (two) { v.tasks = pl->d_tasks_main_na; v.n_tasks = pl->n_tasks_main_na; }
+                "only (bf16 weights, a row length that is a multiple of 8 (16 with int8 momentum), 4-bit block 128, "
+                "int8 momentum with the cautious mask on)", CAP);
+  // the persistent kernel: FINAL, the 1-D tensors and the stages of tensors that do not stream; beside it
+  // the STATS launch before and the COUNT / APPLY launches after
+  if (two) { v.tasks = pl->d_tasks_na[hp.cautious ? 1 : 0]; v.n_tasks = pl->n_tasks_na[hp.cautious ? 1 : 0]; }
   else if (hp.cautious) { v.tasks = pl->d_tasks_full; v.n_tasks = pl->n_tasks_full; }
   else { v.tasks = pl->d_tasks_main; v.n_tasks = pl->n_tasks_main; }
   KAON_CUDA(cudaMemsetAsync(v.task_counter, 0, pl->counters_bytes - sizeof(unsigned), s));
-  if (two && launch_stats(pl, pl->view, hp, s)) { v.tasks = pl->d_tasks_rest; v.n_tasks = pl->n_tasks_rest; }
-  else if (pl->has_long_rows) return fail(KAON_E_CUDA, "the STATS launch could not be started");
+  if (two)
+    if (int rc = launch_stats(pl, pl->view, hp, s)) return rc;
   AdaKernel k = pick_ada(pl->param_dtype, pl->momentum_kind, false);
   k<<<pl->grid, AT, pl->smem_bytes, s>>>(v, hp, (int)x_offset_rows(pl) | (pl->double_buffer ? 1 : 0));
   KAON_CUDA(cudaGetLastError());

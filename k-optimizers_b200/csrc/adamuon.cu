@@ -315,10 +315,11 @@ extern "C" int kaon_adamuon_step(kaon_plan* pl, const kaon_adamuon_hparams* h, v
   hp.step = step; hp.k0 = (uint32_t)seed; hp.k1 = (uint32_t)(seed >> 32);
   if (int rc = ensure_apply2(pl)) return rc;
   const bool three = pl->apply2 == 1;  // STATS/FINAL/FLAT here, COUNT and APPLY as launches of their own
-  if (three) { v.tasks = pl->d_tasks_main_na; v.n_tasks = pl->n_tasks_main_na; }
+  if (three) { v.tasks = pl->d_tasks_na[hp.cautious ? 1 : 0]; v.n_tasks = pl->n_tasks_na[hp.cautious ? 1 : 0]; }
   else if (hp.cautious) { v.tasks = pl->d_tasks_full; v.n_tasks = pl->n_tasks_full; }
   else { v.tasks = pl->d_tasks_main; v.n_tasks = pl->n_tasks_main; }
-  if (three && launch_stats(pl, v, hp, s)) { v.tasks = pl->d_tasks_rest; v.n_tasks = pl->n_tasks_rest; }
+  if (three)
+    if (int rc = launch_stats(pl, v, hp, s)) return rc;
   AdaKernel k = pick_ada(pl->param_dtype, pl->momentum_kind, true);
   if (!k) return fail(KAON_E_INVALID, "no AdaMuon kernel for this dtype combination");
   k<<<pl->grid, ADA_THREADS, pl->smem_bytes, s>>>(v, hp, (int)x_offset_rows(pl) | (pl->double_buffer ? 1 : 0));

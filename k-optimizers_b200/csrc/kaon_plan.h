@@ -149,12 +149,14 @@ struct kaon_plan {
   bool has_long_rows = false;                // a factored tensor's rows exceed a work item: streaming launches only
   int apply2 = 0;                            // 0 = not decided, 1 = in use, -1 = this plan is not eligible
   kaon::Task* d_tasks_apply2 = nullptr;      // flat items of the factored tensors
-  kaon::Task* d_tasks_main_na = nullptr;     // the first launch's work list without COUNT and APPLY items
-  int n_tasks_apply2 = 0, n_tasks_main_na = 0;
-  // STATS as a launch of its own: the STATS items, and the first kernel's list without them
+  int n_tasks_apply2 = 0;
+  // the persistent kernel's lists beside those launches: [0] without COUNT items, [1] with them
+  kaon::Task* d_tasks_na[2] = {nullptr, nullptr};
+  int n_tasks_na[2] = {0, 0};
+  bool long_rows_ok = false;                 // every tensor whose rows exceed a work item left the persistent kernel
+  // STATS as a launch of its own: the STATS items that qualify
   kaon::Task* d_tasks_stats = nullptr;
-  kaon::Task* d_tasks_rest = nullptr;
-  int n_tasks_stats = 0, n_tasks_rest = 0, stats_grid = 0;
+  int n_tasks_stats = 0, stats_grid = 0;
   unsigned* d_counter2 = nullptr;            // claim counter of the COUNT / APPLY launches
   int apply_grid = 0;
   size_t apply_smem = 0;

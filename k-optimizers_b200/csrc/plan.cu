@@ -370,9 +370,9 @@ int kaon_plan_destroy(kaon_plan* pl) {
   kaon::pnm_free(pl);
   cudaFree(pl->d_tasks_ema);
   cudaFree(pl->d_tasks_apply2);
-  cudaFree(pl->d_tasks_main_na);
+  cudaFree(pl->d_tasks_na[0]);
+  cudaFree(pl->d_tasks_na[1]);
   cudaFree(pl->d_tasks_stats);
-  cudaFree(pl->d_tasks_rest);
   cudaFree(pl->d_counter2);
   cudaFree((void*)pl->d_signal);
   if (pl->muon_lanes_ready) {

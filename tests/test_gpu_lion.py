@@ -121,7 +121,7 @@ def test_lion_vs_oracle_bigger_shapes(md, gc, method, wd, dtype):
                 assert np.mean(to_bits(p) != ot.p) < 1e-2
 
 
-LONG_ROWS = [(16, 2560, 3, 3), (96, 4100), (640, 2560), (1280,)]
+LONG_ROWS = [(16, 2560, 3, 3), (96, 4100), (640, 2560), (1280,), (50000,)]
 
 
 @pytest.mark.parametrize("md,method", [("4bit", "stochastic_rounding"), ("4bit", "none"), ("bfloat16", "none")])
