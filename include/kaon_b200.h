@@ -46,7 +46,7 @@ extern "C" {
 /* error codes */
 #define KAON_OK 0
 #define KAON_E_INVALID (-1)     /* bad argument (message says which) */
-#define KAON_E_UNSUPPORTED (-2) /* a shape / option this build has no kernel for */
+#define KAON_E_UNSUPPORTED (-2) /* a shape / option the library has no kernel for */
 #define KAON_E_CUDA (-3)        /* a CUDA runtime call failed */
 #define KAON_E_DEVICE (-4)      /* the device status word reported a bounded wait that ran out */
 
@@ -71,7 +71,10 @@ typedef struct kaon_tensor_desc {
   int64_t numel;
   int64_t rows;    /* shape[0] when ndim >= 2, else 0 (1-D tensor) */
   uint32_t tensor_id; /* position in the optimizer's flattened param list: keys the SR stream */
-  uint32_t block;  /* 4-bit block size actually in use: min(momentum_4bit_block, numel) */
+  uint32_t block;  /* 4-bit block size actually in use: min(momentum_4bit_block, numel), or numel for a
+                    * non-positive setting (src/kaon/_momentum_codec.py:192-200).  Plans take a power of two
+                    * from 32 to 256, one block over a tensor of <= 128 elements, and (not under Lion) one
+                    * block over a 1-D tensor of any length; anything else is KAON_E_UNSUPPORTED. */
   void* shift;     /* bf16_method="kahan" with bf16 weights: compensation buffer state["shift"], bf16
                       [numel], 16-byte aligned; NULL otherwise */
 } kaon_tensor_desc;

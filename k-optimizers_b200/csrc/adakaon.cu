@@ -1037,9 +1037,9 @@ __device__ void ada_rows(const PlanView& pv, const AdaDev& hp, const Task& t, St
       }
     }
     float pre_blk = 1.0f;
-    if constexpr (MK == KAON_M_4BIT) {  // old block scales of the chunk (<= CAP/128 = 128 blocks)
-      const int nblk = d.block == 128u ? (n + 127) >> 7 : 1;
-      if (tid < nblk) pre_blk = d.m_scale[(d.block == 128u ? (e0 >> 7) : 0) + tid];
+    if constexpr (MK == KAON_M_4BIT) {  // old block scales of the chunk (<= CAP/32 = 512 blocks, one per thread)
+      const int nblk = d.bshift >= 31 ? 1 : (int)(blk_of(d, e0 + n - 1) - blk_of(d, e0) + 1);
+      if (tid < nblk) pre_blk = d.m_scale[blk_of(d, e0) + tid];
     }
     {
       const unsigned char *s0, *s1; unsigned b0, b1;
@@ -1060,7 +1060,7 @@ __device__ void ada_rows(const PlanView& pv, const AdaDev& hp, const Task& t, St
       }
     }
     if constexpr (MK == KAON_M_4BIT) {
-      const int nblk = d.block == 128u ? (n + 127) >> 7 : 1;
+      const int nblk = d.bshift >= 31 ? 1 : (int)(blk_of(d, e0 + n - 1) - blk_of(d, e0) + 1);
       if (tid < nblk) sm.scale_s[tid] = pre_blk;
     }
     __syncthreads();
@@ -1097,7 +1097,7 @@ __device__ void ada_rows(const PlanView& pv, const AdaDev& hp, const Task& t, St
         const float4 c0 = *reinterpret_cast<const float4*>(cfac_s + (v * 8 - r * C));
         const float4 c1 = *reinterpret_cast<const float4*>(cfac_s + (v * 8 - r * C) + 4);
         const float cf[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-        if constexpr (MK == KAON_M_4BIT) decode8<MK>(st.m_s, v, 8, sm.scale_s[v >> 4], mo);
+        if constexpr (MK == KAON_M_4BIT) decode8<MK>(st.m_s, v, 8, sm.scale_s[d.bshift >= 31 ? 0 : (v >> (d.bshift - 3))], mo);
         else if constexpr (MK == KAON_M_INT8) decode8<MK>(st.m_s, v, 8, sm.scale_s[r], mo);
         else if constexpr (MK == KAON_M_NONE) {
 #pragma unroll
@@ -1148,7 +1148,7 @@ __device__ void ada_rows(const PlanView& pv, const AdaDev& hp, const Task& t, St
       for (int k = 0; k < 8; ++k) rl[k] = row_uniform ? row_of((unsigned)v * 8u, d) : row_of((unsigned)(v * 8 + min(k, max(cnt - 1, 0))), d);
       // old momentum
       if constexpr (MK == KAON_M_4BIT) {
-        decode8<MK>(st.m_s, v, cnt, cnt > 0 ? sm.scale_s[d.block == 128u ? (v >> 4) : 0] : 1.0f, mo);
+        decode8<MK>(st.m_s, v, cnt, cnt > 0 ? sm.scale_s[d.bshift >= 31 ? 0 : (v >> (d.bshift - 3))] : 1.0f, mo);
       } else if constexpr (MK == KAON_M_INT8) {
 #pragma unroll
         for (int k = 0; k < 8; ++k)
@@ -1233,7 +1233,7 @@ __device__ void ada_rows(const PlanView& pv, const AdaDev& hp, const Task& t, St
           float a = 0.0f;
 #pragma unroll
           for (int k = 0; k < 8; ++k) a = fmaxf(a, fabsf(mn[k]));
-          a = fmaxf(group_max(a, 16), 1e-12f);
+          a = fmaxf(group_max(a, blk_lanes(d)), 1e-12f);
           const float sc = __fdiv_rn(a, 7.0f);
           const float inv = __fdividef(1.0f, sc);
           uint32_t word = 0;
@@ -1249,7 +1249,7 @@ __device__ void ada_rows(const PlanView& pv, const AdaDev& hp, const Task& t, St
             if (cnt == 8) *reinterpret_cast<uint32_t*>(mdst) = word;
             else
               for (int b = 0; b < (cnt + 1) / 2; ++b) mdst[b] = (unsigned char)(word >> (8 * b));
-            if ((v & 15) == 0) d.m_scale[(d.block == 128u) ? ((e0 >> 7) + (v >> 4)) : 0] = sc;
+            if ((v & (blk_lanes(d) - 1)) == 0) d.m_scale[blk_of(d, e0 + (long long)v * 8)] = sc;
           }
         } else if constexpr (MK == KAON_M_INT8) {
           if (cnt > 0) {
@@ -1631,17 +1631,18 @@ __device__ void ada_flat(const PlanView& pv, const AdaDev& hp, const Task& t, St
   const float rms = __fdiv_rn((float)sqrt(ss), (float)sqrt((double)n));
   const float div = fmaxf(__fdiv_rn(rms, hp.clip), 1.0f);
   // 2. momentum EMA (pre-requant value kept in f_s), absmax per scale group
-  const bool one_block = MK == KAON_M_4BIT && d.block != 128u;
+  const bool one_block = MK == KAON_M_4BIT && d.bshift >= 31;
+  const int bsh = one_block ? 0 : d.bshift;  // 4-bit: element -> block
   // 4bit: one entry per 128-block; int8: entry 0
   unsigned* blkmax = lng ? reinterpret_cast<unsigned*>(f_s + flat_long_pad(n)) : sm.rowmax_s;
-  const int nblk = lng ? (n + 127) / 128 + 1 : MAX_TASK_ROWS;
+  const int nblk = lng ? (n + 31) / 32 + 1 : MAX_TASK_ROWS;
   for (int i = tid; i < nblk; i += AT) blkmax[i] = 0u;
   __syncthreads();
   auto old_m = [&](int i) -> float {
     if constexpr (MK == KAON_M_4BIT) {
       const unsigned byte = m_src[i >> 1];
       const int nib = (i & 1) ? (byte >> 4) & 0xF : byte & 0xF;
-      return __fmul_rn((float)(nib - 8), d.m_scale[one_block ? 0 : (i >> 7)]);
+      return __fmul_rn((float)(nib - 8), d.m_scale[one_block ? 0 : (i >> bsh)]);
     } else if constexpr (MK == KAON_M_INT8) {
       return __fmul_rn((float)(signed char)m_src[i], d.m_scale[0]);
     } else if constexpr (MK == KAON_M_BF16) {
@@ -1656,7 +1657,7 @@ __device__ void ada_flat(const PlanView& pv, const AdaDev& hp, const Task& t, St
     const float u = __fmul_rn(__fdiv_rn(f_s[i], div), hp.upd_scale);
     const float mn = ema_of<MK>(old_m(i), u, hp);
     f_s[i] = mn;
-    if constexpr (MK == KAON_M_4BIT) atomicMax(blkmax + (one_block ? 0 : (i >> 7)), __float_as_uint(fabsf(mn)));
+    if constexpr (MK == KAON_M_4BIT) atomicMax(blkmax + (one_block ? 0 : (i >> bsh)), __float_as_uint(fabsf(mn)));
     if constexpr (MK == KAON_M_INT8) atomicMax(blkmax, __float_as_uint(fabsf(mn)));
   }
   __syncthreads();
@@ -1688,7 +1689,7 @@ __device__ void ada_flat(const PlanView& pv, const AdaDev& hp, const Task& t, St
   const float denom = fmaxf(__fdiv_rn((float)kept, (float)n), 1e-8f);
   // 4. encode the momentum, write the weights
   auto scale_of = [&](int i) -> float {
-    if constexpr (MK == KAON_M_4BIT) return __fdiv_rn(fmaxf(__uint_as_float(blkmax[one_block ? 0 : (i >> 7)]), 1e-12f), 7.0f);
+    if constexpr (MK == KAON_M_4BIT) return __fdiv_rn(fmaxf(__uint_as_float(blkmax[one_block ? 0 : (i >> bsh)]), 1e-12f), 7.0f);
     else if constexpr (MK == KAON_M_INT8) return __fdiv_rn(fmaxf(__uint_as_float(blkmax[0]), 1e-12f), 127.0f);
     else return 1.0f;
   };
@@ -1738,8 +1739,8 @@ __device__ void ada_flat(const PlanView& pv, const AdaDev& hp, const Task& t, St
       unsigned hi = i1 < n ? (unsigned)(code_of(i1, scale_of(i1)) + 8) : 0u;
       reinterpret_cast<unsigned char*>(d.m)[b] = (unsigned char)(lo | (hi << 4));
     }
-    const int nb = one_block ? 1 : (n + 127) >> 7;
-    for (int b = tid; b < nb; b += AT) d.m_scale[b] = scale_of(b << 7);
+    const int nb = one_block ? 1 : (int)(((long long)n + (1 << bsh) - 1) >> bsh);
+    for (int b = tid; b < nb; b += AT) d.m_scale[b] = scale_of(b << bsh);
   } else if constexpr (MK == KAON_M_INT8) {
     const float sc = scale_of(0);
     for (int i = tid; i < n; i += AT) reinterpret_cast<signed char*>(d.m)[i] = (signed char)code_of(i, sc);
@@ -1862,7 +1863,7 @@ __global__ void __launch_bounds__(256) msam_axpy_kernel(PlanView pv, float alpha
           if constexpr (MK == KAON_M_4BIT) {
             const unsigned byte = reinterpret_cast<const unsigned char*>(d.m)[i >> 1];
             const int nib = (i & 1) ? (byte >> 4) & 0xF : byte & 0xF;
-            x = __fmul_rn((float)(nib - 8), d.m_scale[d.block == 128u ? (i >> 7) : 0]);
+            x = __fmul_rn((float)(nib - 8), d.m_scale[blk_of(d, i)]);
           } else if constexpr (MK == KAON_M_INT8) {
             const int row = d.rows > 0 ? (int)(i / d.cols) : 0;
             x = __fmul_rn((float)reinterpret_cast<const signed char*>(d.m)[i], d.m_scale[row]);

@@ -41,7 +41,7 @@ __global__ void __launch_bounds__(ET) muon_ema_kernel(PlanView pv, const Task* t
       float gv[8], mo[8];
       load8_guard<PT>(g + (size_t)v * 8 * E::BYTES, cnt, gv);
       if constexpr (MK == KAON_M_4BIT) {
-        const long long blk = (d.block == 128u) ? ((t.e0 >> 7) + (v >> 4)) : 0;
+        const long long blk = blk_of(d, t.e0 + (long long)v * 8);
         decode8<MK>(mbase + (t.e0 >> 1), v, cnt, d.m_scale[blk], mo);
       } else if constexpr (MK == KAON_M_INT8) {
 #pragma unroll
@@ -93,7 +93,7 @@ __global__ void __launch_bounds__(ET) muon_ema_kernel(PlanView pv, const Task* t
         float a = 0.0f;
 #pragma unroll
         for (int k = 0; k < 8; ++k) a = fmaxf(a, fabsf(mn[k]));
-        a = fmaxf(group_max(a, 16), 1e-12f);
+        a = fmaxf(group_max(a, blk_lanes(d)), 1e-12f);
         const float sc = __fdiv_rn(a, 7.0f);
         const float inv = __fdividef(1.0f, sc);
         uint32_t word = 0;
@@ -107,7 +107,7 @@ __global__ void __launch_bounds__(ET) muon_ema_kernel(PlanView pv, const Task* t
           if (cnt == 8) *reinterpret_cast<uint32_t*>(mdst) = word;
           else
             for (int b = 0; b < (cnt + 1) / 2; ++b) mdst[b] = (unsigned char)(word >> (8 * b));
-          if ((v & 15) == 0) d.m_scale[(d.block == 128u) ? ((t.e0 >> 7) + (v >> 4)) : 0] = sc;
+          if ((v & (blk_lanes(d) - 1)) == 0) d.m_scale[blk_of(d, t.e0 + (long long)v * 8)] = sc;
         }
       } else if constexpr (MK == KAON_M_INT8) {
         if (cnt > 0) {

@@ -71,11 +71,11 @@ __device__ __forceinline__ float pnm_centered(float g, float mu, bool gc) {
 }
 
 template <int MK>
-__device__ __forceinline__ float pnm_decode(const void* m, const float* sc, long long i, int row, bool b128) {
+__device__ __forceinline__ float pnm_decode(const void* m, const float* sc, long long i, int row, int bsh) {
   if constexpr (MK == KAON_M_4BIT) {
     const unsigned byte = reinterpret_cast<const unsigned char*>(m)[i >> 1];
     const int nib = (i & 1) ? (byte >> 4) & 0xF : byte & 0xF;
-    return __fmul_rn((float)(nib - 8), sc[b128 ? (i >> 7) : 0]);
+    return __fmul_rn((float)(nib - 8), sc[bsh >= 31 ? 0 : (i >> bsh)]);
   } else if constexpr (MK == KAON_M_INT8) {
     return __fmul_rn((float)reinterpret_cast<const signed char*>(m)[i], sc[row]);
   } else if constexpr (MK == KAON_M_BF16) {
@@ -176,8 +176,8 @@ __device__ __forceinline__ void pnm_write(const PnmDev& hp, const DevTensor& d, 
 // lane with nothing).  int8: `amax_bits_of_row` gives the finished absmax of an element's row (factored)
 // or of the tensor (1-D).
 template <int MK, typename RowMax>
-__device__ __forceinline__ void pnm_store_m(void* pos, float* psc, const PnmTrip& tr, long long e, int cnt, bool b128,
-                                            int lane, RowMax amax_of_row) {
+__device__ __forceinline__ void pnm_store_m(void* pos, float* psc, const PnmTrip& tr, long long e, int cnt, int bsh,
+                                            int lane, RowMax amax_of_row, float whole_amax = -1.0f) {
   if constexpr (MK == KAON_M_F32) {
     float* dst = reinterpret_cast<float*>(pos) + e;
     for (int k = 0; k < cnt; ++k) dst[k] = tr.mp[k];
@@ -194,8 +194,11 @@ __device__ __forceinline__ void pnm_store_m(void* pos, float* psc, const PnmTrip
   } else {  // 4-bit
     float amax = 0.0f;
     for (int k = 0; k < cnt; ++k) amax = fmaxf(amax, fabsf(tr.mp[k]));
-#pragma unroll
-    for (int o = 1; o < 16; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const int lanes = bsh >= 31 ? 16 : (1 << (bsh - 3));  // threads that share a block
+    for (int o = 1; o < lanes; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    // one block over a whole 1-D tensor: its absmax was taken by the caller's first sweep
+    const bool whole = whole_amax >= 0.0f;
+    if (whole) amax = whole_amax;
     const float sc = __fdiv_rn(fmaxf(amax, 1e-12f), 7.0f);
     unsigned q[8];
 #pragma unroll
@@ -209,7 +212,7 @@ __device__ __forceinline__ void pnm_store_m(void* pos, float* psc, const PnmTrip
       for (int b = 0; 2 * b < cnt; ++b) dst[b] = (unsigned char)(q[2 * b] | (q[2 * b + 1] << 4));
     }
     __syncwarp();  // every lane of the block has decoded with the old scale
-    if ((lane & 15) == 0 && cnt > 0) psc[b128 ? (e >> 7) : 0] = sc;
+    if (!whole && (lane & (lanes - 1)) == 0 && cnt > 0) psc[bsh >= 31 ? 0 : (e >> bsh)] = sc;
   }
 }
 
@@ -241,7 +244,7 @@ __global__ void __launch_bounds__(PT_THREADS) pnm_pass_kernel(PlanView pv, PnmDe
       unsigned* rowmax = reinterpret_cast<unsigned*>(pv.aux + aux_rowmax(d));
       // int8: the positive buffer's row scales as they were before this step (its rows get new ones in APPLY)
       const float* psc_rd = MK == KAON_M_INT8 ? pv.aux + aux_oldsc(d) : psc;
-      const bool b128 = d.block == 128u;
+      const int bsh = d.bshift;  // 4-bit: element -> block shift (31: one block)
       float div = 1.0f, denom = 1.0f;
       if (APPLY) { div = x.scal[2 * t.tensor]; denom = x.scal[2 * t.tensor + 1]; }
       const int nvec = (t.n + 7) >> 3;
@@ -264,8 +267,8 @@ __global__ void __launch_bounds__(PT_THREADS) pnm_pass_kernel(PlanView pv, PnmDe
               tr.rw[k] = r;
               if (c == 0) tr.first |= 1u << k;
               const float yk = pnm_centered<PT>(gx[k], hp.gc ? mean[r] : 0.0f, hp.gc != 0);
-              const float mpo = pnm_decode<MK>(pos, psc_rd, e + k, r, b128);
-              const float mno = pnm_decode<MK>(neg, nsc, e + k, r, b128);
+              const float mpo = pnm_decode<MK>(pos, psc_rd, e + k, r, bsh);
+              const float mno = pnm_decode<MK>(neg, nsc, e + k, r, bsh);
               const float mpn = __fmaf_rn(yk, hp.fw, __fmul_rn(mpo, hp.fb));
               const float pn = __fmul_rn(__fmaf_rn(mno, hp.c2, __fmul_rn(mpn, hp.c1)), hp.c3);
               const float inv = __fmul_rn(__fmul_rn(rfac[r], cfac[c]), hp.bc2);
@@ -294,7 +297,7 @@ __global__ void __launch_bounds__(PT_THREADS) pnm_pass_kernel(PlanView pv, PnmDe
           }
         } else {
           if (cnt > 0) pnm_write<PT>(hp, d, tr, e, cnt, div, denom, s_upd, &pv.peers);
-          pnm_store_m<MK>(pos, psc, tr, e, cnt, b128, lane,
+          pnm_store_m<MK>(pos, psc, tr, e, cnt, bsh, lane,
                           [&](int r) { return __uint_as_float(__ldcg(rowmax + r)); });
         }
       }
@@ -380,7 +383,7 @@ __global__ void __launch_bounds__(PT_THREADS) pnm_flat_kernel(PlanView pv, PnmDe
   float* psc = b.sc[hp.swap];
   const void* neg = b.m[hp.swap ^ 1];
   const float* nsc = b.sc[hp.swap ^ 1];
-  const bool b128 = d.block == 128u;
+  const int bsh = d.bshift;  // 4-bit: element -> block shift (31: one block)
   const long long n = d.numel;
   const long long nvec = (n + 7) >> 3;
   float* v = d.stat_a;
@@ -388,10 +391,11 @@ __global__ void __launch_bounds__(PT_THREADS) pnm_flat_kernel(PlanView pv, PnmDe
   const SrStream s_upd{Philox{hp.k0, hp.k1}, hp.step, KAON_TAG_UPDATE};
   // int8: one scalar scale; every thread keeps the old one before anything is written
   __shared__ float old_sc_s;
-  if (tid == 0) old_sc_s = MK == KAON_M_INT8 ? psc[0] : 0.0f;
+  const bool one_scale = MK == KAON_M_INT8 || (MK == KAON_M_4BIT && bsh >= 31);
+  if (tid == 0) old_sc_s = one_scale ? psc[0] : 0.0f;
   __syncthreads();
   const float old_sc = old_sc_s;
-  const float* psc_rd = MK == KAON_M_INT8 ? &old_sc : psc;
+  const float* psc_rd = one_scale ? &old_sc : psc;
 
   auto chain = [&](long long e, int cnt, bool first_sweep, PnmTrip& tr) {
     float gx[8];
@@ -410,8 +414,8 @@ __global__ void __launch_bounds__(PT_THREADS) pnm_flat_kernel(PlanView pv, PnmDe
           vv = max_v != nullptr ? max_v[e + k] : v[e + k];
         }
         const float den = __fdiv_rn(__fadd_rn(__fsqrt_rn(__fadd_rn(vv, 1e-15f)), hp.eps), hp.bc2);
-        const float mpo = pnm_decode<MK>(pos, psc_rd, e + k, 0, b128);
-        const float mno = pnm_decode<MK>(neg, nsc, e + k, 0, b128);
+        const float mpo = pnm_decode<MK>(pos, psc_rd, e + k, 0, bsh);
+        const float mno = pnm_decode<MK>(neg, nsc, e + k, 0, bsh);
         const float mpn = __fmaf_rn(yk, hp.fw, __fmul_rn(mpo, hp.fb));
         const float pn = __fmul_rn(__fmaf_rn(mno, hp.c2, __fmul_rn(mpn, hp.c1)), hp.c3);
         tr.y[k] = yk; tr.mp[k] = mpn; tr.u[k] = __fdiv_rn(pn, den);
@@ -467,11 +471,13 @@ __global__ void __launch_bounds__(PT_THREADS) pnm_flat_kernel(PlanView pv, PnmDe
       chain(e, cnt, false, tr);
       pnm_write<PT>(hp, d, tr, e, cnt, div, denom, s_upd, &pv.peers);
     }
-    pnm_store_m<MK>(pos, psc, tr, e, cnt, b128, lane, [&](int) { return tmax; });
+    pnm_store_m<MK>(pos, psc, tr, e, cnt, bsh, lane, [&](int) { return tmax; },
+                    (MK == KAON_M_4BIT && bsh >= 31) ? tmax : -1.0f);
   }
-  if constexpr (MK == KAON_M_INT8) {
+  if constexpr (MK == KAON_M_INT8 || MK == KAON_M_4BIT) {
+    // the one scale of the tensor (int8, or a 4-bit block that covers it), once every thread has decoded with the old one
     __syncthreads();
-    if (tid == 0) psc[0] = __fdiv_rn(fmaxf(tmax, 1e-12f), 127.0f);
+    if (tid == 0 && (MK == KAON_M_INT8 || bsh >= 31)) psc[0] = __fdiv_rn(fmaxf(tmax, 1e-12f), MK == KAON_M_INT8 ? 127.0f : 7.0f);
   }
 }
 

@@ -44,6 +44,8 @@ struct DevTensor {
   unsigned row_magic;   // ceil(2^32 / cols): floor(i / cols) == umulhi(i, row_magic) for i*cols < 2^32
   unsigned tensor_id;
   unsigned block;       // 4-bit block size in use
+  int bshift;           // 4-bit: log2(block) for a power-of-two block of 32..256 elements; 31 when one block
+                        // covers the whole tensor
   int n_main;           // number of MAIN work items of this tensor (what `done` must reach)
   // Adakaon / AdaMuon only
   int chunk_rows;       // rows staged at a time (chunk_rows * cols <= CAP, aligned); -1: a Lion tensor cut into
@@ -56,6 +58,10 @@ struct DevTensor {
                         //   tpart[n_strips] (double) | scal[4] = {rowmean, divisor, rms, -} | rowmax[rows] | mean[rows]
   void* shift;          // Kahan compensation buffer (bf16 [numel]) or null
 };
+
+// 4-bit block geometry: the block an element belongs to, and how many threads (eight elements each) share one
+__host__ __device__ inline long long blk_of(const DevTensor& d, long long i) { return d.bshift >= 31 ? 0 : (i >> d.bshift); }
+__host__ __device__ inline int blk_lanes(const DevTensor& d) { return d.bshift >= 31 ? 16 : (1 << (d.bshift - 3)); }
 
 // float offsets inside a tensor's aux block
 __host__ __device__ inline long long aux_cfac(const DevTensor& d) { return d.aux_off + 2ll * d.n_stats * d.cols; }
@@ -70,9 +76,9 @@ __host__ __device__ inline long long aux_mean(const DevTensor& d) { return aux_r
 __host__ __device__ inline long long aux_oldsc(const DevTensor& d) { return aux_mean(d) + d.rows; }
 // r_i = rsqrt(row_i / mean(row)) of every row, left by the last FINAL strip for COUNT / APPLY
 __host__ __device__ inline long long aux_rfac(const DevTensor& d) { return aux_oldsc(d) + d.rows; }
-// scratch of a 1-D tensor stepped from global memory: 8 floats | n floats (padded) | one word per 128 elements
+// scratch of a 1-D tensor stepped from global memory: 8 floats | n floats (padded) | one word per 4-bit block (>= 32 elements)
 __host__ __device__ inline long long flat_long_pad(long long n) { return (n + 63) / 64 * 64; }
-__host__ __device__ inline long long flat_long_size(long long n) { return 8 + flat_long_pad(n) + ((n + 127) / 128 + 1 + 63) / 64 * 64; }
+__host__ __device__ inline long long flat_long_size(long long n) { return 8 + flat_long_pad(n) + ((n + 31) / 32 + 1 + 63) / 64 * 64; }
 __host__ __device__ inline long long aux_size(const DevTensor& d) { return aux_rfac(d) + d.rows - d.aux_off; }
 
 struct Task {

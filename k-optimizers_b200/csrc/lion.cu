@@ -344,8 +344,8 @@ __device__ void lion_main(const PlanView& pv, const LionDev& hp, const Task& t, 
   const int C = d.cols;
   const int nrows = d.rows > 0 ? n / C : 1;
   bool fast = false;
-  if constexpr (MK == KAON_M_4BIT)
-    fast = !hp.has_wd && hp.cautious && (n & 7) == 0 && ((d.rows <= 0) || ((C & 7) == 0));
+  if constexpr (MK == KAON_M_4BIT)  // the fast paths know blocks of 128 (or one block in the first 16 lanes)
+    fast = !hp.has_wd && hp.cautious && (n & 7) == 0 && ((d.rows <= 0) || ((C & 7) == 0)) && (d.bshift == 7 || d.bshift >= 31);
   // the bf16 fast path subtracts the mean from packed pairs: it reads the mean as two bf16 copies
   const bool mean_packed = fast && E::IS_BF16;
   if (do_gc && d.chunk_rows < 0) {
@@ -391,9 +391,11 @@ __device__ void lion_main(const PlanView& pv, const LionDev& hp, const Task& t, 
     }
   }
   if constexpr (MK == KAON_M_4BIT) {  // old block scales of the chunk (the fast path reads them from here)
-    const int nblk = d.block == 128u ? (n + 127) >> 7 : 1;
-    const long long b0 = d.block == 128u ? (t.e0 >> 7) : 0;
-    for (int b = tid; b < nblk; b += NTHREADS) sc_s[b] = d.m_scale[b0 + b];
+    if (fast) {
+      const int nblk = d.block == 128u ? (n + 127) >> 7 : 1;
+      const long long b0 = d.block == 128u ? (t.e0 >> 7) : 0;
+      for (int b = tid; b < nblk; b += NTHREADS) sc_s[b] = d.m_scale[b0 + b];
+    }
   }
   if constexpr (MK == KAON_M_INT8) {
     for (int r = tid; r < nrows; r += NTHREADS) {
@@ -479,7 +481,7 @@ __device__ void lion_main(const PlanView& pv, const LionDev& hp, const Task& t, 
     float sc_old = 1.0f;
     long long blk = 0;
     if constexpr (MK == KAON_M_4BIT) {
-      blk = (d.block == 128u) ? ((t.e0 >> 7) + (v >> 4)) : 0;
+      blk = blk_of(d, t.e0 + (long long)v * 8);
       if (cnt > 0) sc_old = d.m_scale[blk];
     }
     if constexpr (MK == KAON_M_INT8) {
@@ -511,7 +513,8 @@ __device__ void lion_main(const PlanView& pv, const LionDev& hp, const Task& t, 
       float a = 0.0f;
 #pragma unroll
       for (int k = 0; k < 8; ++k) a = fmaxf(a, fabsf(mv[k]));
-      a = group_max(a, 16);
+      const int lanes = blk_lanes(d);  // threads that share a block: consecutive lanes of one warp
+      a = group_max(a, lanes);
       a = fmaxf(a, 1e-12f);
       const float sc = __fdiv_rn(a, 7.0f);
       const float inv = __fdividef(1.0f, sc);
@@ -527,7 +530,7 @@ __device__ void lion_main(const PlanView& pv, const LionDev& hp, const Task& t, 
         if (cnt == 8) *reinterpret_cast<uint32_t*>(mdst) = word;
         else
           for (int b = 0; b < (cnt + 1) / 2; ++b) mdst[b] = (unsigned char)(word >> (8 * b));
-        if ((v & 15) == 0) d.m_scale[blk] = sc;
+        if ((v & (lanes - 1)) == 0) d.m_scale[blk] = sc;
       }
     } else if constexpr (MK == KAON_M_INT8) {
       if (cnt > 0) {
@@ -1019,7 +1022,7 @@ extern "C" int kaon_lion_step_noalloc(const kaon_tensor_desc* t, int param_dtype
   d.rows = (int)t->rows;
   d.cols = (int)std::min<long long>(C, 0x7fffffff);
   d.row_magic = d.cols > 1 ? (unsigned)((0x100000000ull + (unsigned)d.cols - 1) / (unsigned)d.cols) : 0u;
-  d.tensor_id = t->tensor_id; d.block = t->block;
+  d.tensor_id = t->tensor_id; d.block = t->block; d.bshift = t->block == 128 ? 7 : 31;
   d.n_main = (int)n_items;
 
   LionDev hp;

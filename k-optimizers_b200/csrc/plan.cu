@@ -34,7 +34,10 @@ static long long gcd_ll(long long a, long long b) { return b ? gcd_ll(b, a % b) 
 
 // Element alignment every work item must start on so that vector loads, the bulk copies of the
 // momentum bytes and the 4-bit blocks line up.
-static int align_unit(int momentum_kind) { return momentum_kind == KAON_M_4BIT ? 128 : 8; }
+static int align_unit(int momentum_kind, unsigned block) {
+  if (momentum_kind != KAON_M_4BIT) return 8;
+  return block == 256u ? 256 : 128;  // smaller power-of-two blocks divide 128
+}
 
 size_t momentum_bytes_per_cap(int mk) {
   switch (mk) {
@@ -50,7 +53,7 @@ size_t momentum_bytes_per_cap(int mk) {
 // elements, each starting on the alignment unit.
 static int split_tensor(const kaon_tensor_desc& d, int ti, int mk, bool lion, std::vector<Task>& out) {
   const long long n = d.numel;
-  const int A = align_unit(mk);
+  const int A = align_unit(mk, d.block);
   if (n == 0) return 0;
   if (d.rows > 0) {
     const long long C = n / d.rows;
@@ -152,9 +155,16 @@ int kaon_plan_create(kaon_plan** out, int optimizer, int param_dtype, int moment
     if ((uintptr_t)d.m & 15) return fail(KAON_E_INVALID, "tensor %d: momentum not 16-byte aligned", i);
     if ((momentum_kind == KAON_M_INT8 || momentum_kind == KAON_M_4BIT) && !d.m_scale && d.numel) return fail(KAON_E_INVALID, "tensor %d: m_scale missing", i);
     if (d.numel >= (1ll << 40)) return fail(KAON_E_UNSUPPORTED, "tensor %d: more than 2^40 elements", i);
+    int bshift = 7;
     if (momentum_kind == KAON_M_4BIT && d.numel) {
-      bool ok = d.block == 128 || ((long long)d.block == d.numel && d.numel <= 128);
-      if (!ok) return fail(KAON_E_UNSUPPORTED, "tensor %d: 4-bit block size %u (numel %lld): this build handles block 128, or one block covering a tensor of <= 128 elements", i, d.block, (long long)d.numel);
+      // reference src/kaon/_momentum_codec.py:192-200: the block in use is min(block, numel), or numel for
+      // a non-positive setting; the caller passes that value
+      const long long b = d.block;
+      const bool pow2 = b >= 32 && b <= 256 && (b & (b - 1)) == 0;
+      const bool whole = b == d.numel && (d.numel <= 128 || (d.rows <= 0 && optimizer != KAON_OPT_LION));
+      if (pow2 && b < d.numel) { bshift = 0; while ((1ll << bshift) < b) ++bshift; }
+      else if (whole || (pow2 && b == d.numel && d.numel <= 128)) bshift = 31;
+      else return fail(KAON_E_UNSUPPORTED, "tensor %d: 4-bit block size %u (numel %lld): the library handles power-of-two blocks of 32..256 elements, one block covering a tensor of <= 128 elements, and one block covering a 1-D tensor of any length (not under Lion)", i, d.block, (long long)d.numel);
     }
     DevTensor& t = tens[i];
     t.p = d.p; t.m = d.m; t.m_scale = d.m_scale; t.stat_a = d.stat_a; t.stat_b = d.stat_b;
@@ -167,6 +177,7 @@ int kaon_plan_create(kaon_plan** out, int optimizer, int param_dtype, int moment
     t.row_magic = t.cols > 1 ? (unsigned)((0x100000000ull + (unsigned)t.cols - 1) / (unsigned)t.cols) : 0u;
     t.tensor_id = d.tensor_id;
     t.block = d.block;
+    t.bshift = bshift;
     t.code_off = code_bytes;
     code_bytes += ((d.numel + 3) / 4 + 63) / 64 * 64;  // 2 bits per element, 64-byte granules
     total += d.numel;

@@ -274,7 +274,7 @@ class FusedStepMixin:
 
     # ---- checkpoint extras: the stochastic-rounding stream position ----
     def _extra_state(self, sd: dict[str, Any]) -> dict[str, Any]:
-        """Adds the one top-level key this build needs for bit-exact resume under stochastic rounding
+        """Adds the one top-level key the fused step needs for bit-exact resume under stochastic rounding
         (the step index and seed that key the noise).  torch's and the reference's loaders ignore it.
         A checkpoint is not written from state a failed kernel left behind: the device status is checked
         first (one stream synchronisation, which reading the state out needs anyway)."""

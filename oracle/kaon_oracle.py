@@ -370,6 +370,109 @@ class OracleAdaPNM(OracleOptimizer):
             self.rms.append(rms.value)
 
 
+class OracleKProdigy(OracleOptimizer):
+    """reference src/kaon/kprodigy.py:151-236 (defaults), :299-404 (step: the distance estimate d between two
+    passes over the tensors), :417-478 (pass 1), :800-840 (pass 2).  One parameter group."""
+    DEFAULTS = dict(lr=1.0, betas=(0.9, 0.999), beta3=None, eps=1e-8, weight_decay=0.0, decouple=True,
+                    use_bias_correction=False, safeguard_warmup=False, d0=1e-6, d_coef=1.0,
+                    growth_rate=float("inf"), d_update_freq=1, slice_p=1, momentum_dtype="bfloat16",
+                    momentum_4bit_block=128, second_moment="full", eps_factored=1e-30, cautious=False,
+                    gradient_centralization=True, bf16_method="stochastic_rounding")
+
+    def __init__(self, params, shapes, *, seed: int = 0, **hp):
+        super().__init__(params, shapes, seed=seed, **hp)
+        d0 = self.hp["d0"]
+        self.group = {"d": d0, "d0": d0, "d_max": d0, "d_numerator": 0.0, "k": 0, "d_hat": None}
+
+    def _lazy_init(self, t):
+        if t.state:
+            return
+        hp = self.hp
+        sp = hp["slice_p"]
+        sliced = as_f32(t.p)[::sp].astype(np.float32)
+        t.state["step"] = 0
+        t.state["s"] = np.zeros(sliced.size, np.float32)
+        # the reference keeps a 0-dim zero when the sliced weights are all zero (kprodigy.py:277-280)
+        t.state["p0"] = sliced.copy() if float(np.linalg.norm(sliced.astype(np.float64))) > 0 else np.zeros((), np.float32)
+        if hp["betas"][0] > 0:
+            t.init_momentum(hp["momentum_dtype"], hp["momentum_4bit_block"])
+        if hp["second_moment"] == "factored" and t.rows:
+            t.state["row"] = np.zeros(t.rows, np.float32)
+            t.state["col"] = np.zeros(t.cols, np.float32)
+        else:
+            t.state["v"] = np.zeros(t.n, np.float32)
+
+    def step(self, grads, noises=None):
+        hp, grp = self.hp, self.group
+        self.t += 1
+        beta1, beta2 = hp["betas"]
+        beta3 = hp["beta3"] if hp["beta3"] is not None else math.sqrt(beta2)
+        k, d, d0, lr = grp["k"], grp["d"], grp["d0"], hp["lr"]
+        bc = ((1 - beta2 ** (k + 1)) ** 0.5) / (1 - beta1 ** (k + 1)) if hp["use_bias_correction"] else 1.0
+        dlr = d * lr * bc
+        should = (k % hp["d_update_freq"]) == 0
+        d_over_d0 = d / d0
+        d_numerator = grp["d_numerator"] * beta3
+        alpha_s = (d_over_d0 * d) if hp["safeguard_warmup"] else (d_over_d0 * dlr)
+        factored = hp["second_moment"] == "factored"
+        wd = hp["weight_decay"]
+        mk = MKIND[hp["momentum_dtype"]] if beta1 > 0 else MKIND["float32"]
+        do_d = bool(lr > 0.0 and should)
+        delta_num = np.float32(0.0)
+        d_den = np.float32(0.0)
+        const = d_over_d0 * dlr
+        active = []
+        for tid, (t, g) in enumerate(zip(self.tensors, grads)):
+            if g is None:
+                continue
+            self._lazy_init(t)
+            st = t.state
+            active.append((tid, t, g))
+            num, den = C.c_float(0), C.c_float(0)
+            fac = factored and bool(t.rows)
+            p0 = st["p0"] if st["p0"].ndim else None
+            rc = lib().ko_kprodigy_pass1(
+                _p(t.p), _p(np.ascontiguousarray(g).reshape(-1)), _dt(t.p), C.c_int64(t.n), C.c_int64(t.rows),
+                C.c_int(mk), _p(st.get("m")), _p(st.get("m_scale")), C.c_int64(t.block()),
+                _p(st["row"] if fac else st["v"]), _p(st["col"] if fac else None), C.c_int(fac), _p(st["s"]), _p(p0),
+                C.c_int64(hp["slice_p"]), C.c_int(do_d), C.c_double(beta1), C.c_double(beta2), C.c_double(beta3),
+                C.c_double(d), C.c_double(alpha_s), C.c_double(wd if (wd != 0 and not hp["decouple"]) else 0.0),
+                C.c_double(hp["eps_factored"]), C.c_int(bool(hp["gradient_centralization"])),
+                C.byref(num), C.byref(den))
+            assert rc == 0
+            if do_d:   # the fp32 left fold of the reference (kprodigy.py:451, 455, 580-588)
+                delta_num = np.float32(delta_num + np.float32(np.float32(num.value) * np.float32(const)))
+                d_den = np.float32(d_den + np.float32(den.value))
+        if should and lr > 0.0 and active and float(d_den) > 0.0:
+            global_num = d_numerator + float(delta_num)
+            d_hat = hp["d_coef"] * global_num / float(d_den)
+            d_new, d_max = d, grp["d_max"]
+            if d_new == d0:
+                d_new = max(d_new, d_hat)
+            d_max = max(d_max, d_hat)
+            d_new = min(d_max, d_new * hp["growth_rate"])
+            grp.update(d_numerator=global_num, d=d_new, d_max=d_max, d_hat=d_hat)
+        self.kept = [-1] * len(self.tensors)
+        for tid, t, g in active:
+            st = t.state
+            st["step"] += 1
+            fac = factored and bool(t.rows)
+            kept = C.c_int64(-1)
+            noise = None if noises is None else noises[tid]
+            method = self._method(t, noise)
+            rc = lib().ko_kprodigy_pass2(
+                _p(t.p), _p(np.ascontiguousarray(g).reshape(-1)), _dt(t.p), C.c_int64(t.n), C.c_int64(t.rows),
+                C.c_int(mk), _p(st.get("m")), _p(st.get("m_scale")), C.c_int64(t.block()),
+                _p(st["row"] if fac else st["v"]), _p(st["col"] if fac else None), C.c_int(fac), C.c_int(beta1 > 0),
+                C.c_double(d), C.c_double(dlr), C.c_double(hp["eps"]),
+                C.c_double(wd * dlr if (wd != 0 and hp["decouple"]) else 0.0), C.c_int(bool(hp["cautious"])),
+                C.c_int(bool(hp["gradient_centralization"])), C.c_int(method), C.c_uint64(self.seed),
+                C.c_uint32(self.t), C.c_uint32(tid), _p(noise), C.byref(kept))
+            assert rc == 0
+            self.kept[tid] = kept.value
+        grp["k"] += 1
+
+
 class OracleNekaon(OracleAdakaon):
     """reference src/kaon/nekaon.py:122-185 over src/kaon/msam.py:374-406 with norm="none".
 

@@ -1,7 +1,6 @@
 """Generate the golden vectors under tests/golden/ by running the REFERENCE implementation on CPU.
 
-Run in a container that has the reference checked out (it cannot travel to the GPU box, the
-vectors can):
+Needs the reference's source tree (only this script imports it; the tests read the vectors):
 
     python tests/golden/make_golden.py [--ref /path/to/reference/src]
 
@@ -34,11 +33,14 @@ def make_params(shapes, dtype, seed):
     return [torch.nn.Parameter((torch.randn(s, generator=g) * 0.02).to(dtype)) for s in shapes]
 
 
-def make_grads(shapes, dtype, seed, step, outlier=False):
+def make_grads(shapes, dtype, seed, step, outlier=False, correlated=False):
     g = torch.Generator().manual_seed(seed + step)
+    base = torch.Generator().manual_seed(seed + 7919)
     out = []
     for s in shapes:
         t = torch.randn(s, generator=g) * 1e-3
+        if correlated:   # a steady direction under the noise, so that a distance estimate has something to find
+            t = t * 0.3 + torch.randn(s, generator=base) * 1e-3
         if outlier:
             mask = torch.rand(s, generator=g) < 0.01
             t = torch.where(mask, t * 100.0, t)
@@ -55,7 +57,7 @@ def dump_state(out, prefix, st):
 
 
 def run_optimizer(kaon, name, kwargs, shapes, dtype, steps, seed, *, lr_sched=None, outlier=False,
-                  store_inputs=True, sample=None, nekaon_eval=False):
+                  store_inputs=True, sample=None, nekaon_eval=False, correlated=False):
     """Step the reference; returns the fixture dict."""
     torch.manual_seed(1234)  # the reference draws SR noise from the global RNG
     cls = getattr(kaon, name)
@@ -73,12 +75,15 @@ def run_optimizer(kaon, name, kwargs, shapes, dtype, steps, seed, *, lr_sched=No
             lr = lr_sched(step - 1)
             for grp in opt.param_groups:
                 grp["lr"] = lr
-        grads = make_grads(shapes, dtype, seed, step, outlier)
+        grads = make_grads(shapes, dtype, seed, step, outlier, correlated)
         for i, (p, g) in enumerate(zip(params, grads)):
             if store_inputs:
                 out[f"g_s{step}_t{i}"] = bits(g).reshape(-1)
             p.grad = g.clone()
         opt.step()
+        for key in ("d", "d_max", "d_numerator", "d_hat", "k", "step"):
+            if key in opt.param_groups[0]:
+                out[f"grp_s{step}_{key}"] = np.asarray(opt.param_groups[0][key], dtype=np.float64)
         for i, p in enumerate(params):
             st = inner.state[p]
             if sample is None:
@@ -196,7 +201,8 @@ def main():
                                       lr_sched=SCHEDULES.get(o.get("lr_sched")),
                                       outlier=o.get("outlier", False),
                                       store_inputs=o.get("store_inputs", True),
-                                      sample=o.get("sample"), nekaon_eval=o.get("nekaon_eval", False)))
+                                      sample=o.get("sample"), nekaon_eval=o.get("nekaon_eval", False),
+                                      correlated=o.get("correlated", False)))
     for name, fn in cases.items():
         if args.only and name != args.only:
             continue

@@ -60,7 +60,8 @@ def _check_against_fixture(name, writes_per_step=1):
 
 
 @pytest.mark.parametrize("name", ["adakaon_int8_none", "adakaon_int8_sr", "adakaon_int8_outlier",
-                                  "adakaon_4bit_wd_f32", "adakaon_bf16m_none"])
+                                  "adakaon_4bit_wd_f32", "adakaon_bf16m_none", "adakaon_4bit_block256_wd",
+                                  "adakaon_4bit_block32_f32"])
 def test_adakaon_matches_reference(name):
     _check_against_fixture(name)
 
@@ -191,6 +192,27 @@ def test_adakaon_vs_oracle_long_1d_tensors(md, wd, method, dtype):
     _adakaon_vs_oracle(LONG_FLAT, md, wd, method, dtype)
 
 
+@pytest.mark.parametrize("block", [32, 64, 256, 0])
+@pytest.mark.parametrize("dtype", ["bf16", "f32"])
+def test_adakaon_vs_oracle_other_4bit_block_sizes(block, dtype):
+    """momentum_4bit_block other than 128 (reference src/kaon/_momentum_codec.py:192-200): powers of two, and
+    0 = one block per tensor, which the library takes for 1-D tensors of any length and for tensors of at
+    most 128 elements."""
+    shapes = BIG_ALL[:-1] if block else [(1280,), (7,), (50000,), (8, 16), (100,)]
+    if block == 256:   # rows of 77 elements cannot be grouped on 256-element block boundaries within a work item
+        shapes = [s for s in shapes if s != (333, 77)]
+    _adakaon_vs_oracle(shapes, "4bit", 0.01, "stochastic_rounding", dtype, momentum_4bit_block=block)
+
+
+def test_one_4bit_block_over_a_big_matrix_is_refused():
+    import kaon_b200
+    p = torch.nn.Parameter(torch.zeros(64, 128, dtype=torch.bfloat16, device="cuda"))
+    opt = kaon_b200.Adakaon([p], momentum_dtype="4bit", momentum_4bit_block=0)
+    p.grad = torch.zeros_like(p)
+    with pytest.raises(NotImplementedError, match="4-bit block size"):
+        opt.step()
+
+
 def test_rows_longer_than_a_work_item_need_the_streaming_form():
     import kaon_b200
     p = torch.nn.Parameter(torch.zeros(16, 2560, 3, 3, dtype=torch.float32, device="cuda"))
@@ -205,7 +227,7 @@ def test_rows_longer_than_a_work_item_need_the_streaming_form():
         opt.step()
 
 
-def _adakaon_vs_oracle(BIG, md, wd, method, dtype):
+def _adakaon_vs_oracle(BIG, md, wd, method, dtype, **more):
     import kaon_b200
     from _gpu import state_np, to_bits
     tdt = torch.bfloat16 if dtype == "bf16" else torch.float32
@@ -215,6 +237,7 @@ def _adakaon_vs_oracle(BIG, md, wd, method, dtype):
     kw = dict(lr=1e-4, betas=(0.9 if md else 0.0, 0.999), weight_decay=wd, bf16_method=method)
     if md:
         kw["momentum_dtype"] = md
+    kw.update(more)
     opt = kaon_b200.Adakaon(params, **kw)
     opt.sr_seed = 4
     orc = ko.OracleAdakaon([to_bits(h) for h in host], BIG, seed=4, **kw)

@@ -41,7 +41,7 @@ SHAPES_LONG_1D = [(128, 256), (40000,), (96, 1024)]
 
 
 @pytest.mark.parametrize("md,method,wd", [("int8", "none", 0.0), ("4bit", "stochastic_rounding", 0.05),
-                                          ("bfloat16", "none", 0.0), (None, "none", 0.0)])
+                                          ("bfloat16", "none", 0.0), (None, "none", 0.0), ("4bit/64", "none", 0.0)])
 @pytest.mark.parametrize("dtype", ["bf16", "f32"])
 @pytest.mark.parametrize("kind", ["ragged", "stream", "long1d"])
 def test_adamuon_chain_vs_oracle_with_same_orthogonal_factor(md, method, wd, dtype, kind):
@@ -53,6 +53,9 @@ def test_adamuon_chain_vs_oracle_with_same_orthogonal_factor(md, method, wd, dty
     host = [(torch.randn(s, generator=gen) * 0.02).to(tdt) for s in SHAPES]
     params = [torch.nn.Parameter(h.clone().cuda()) for h in host]
     kw = dict(lr=1e-3, betas=(0.95 if md else 0.0, 0.999), weight_decay=wd, ns_steps=2, bf16_method=method)
+    if md and "/" in md:   # the 4-bit codec with another block size
+        md, blk = md.split("/")
+        kw["momentum_4bit_block"] = int(blk)
     if md:
         kw["momentum_dtype"] = md
     opt = kaon_b200.AdaMuon(params, **kw)

@@ -17,7 +17,7 @@ def _inner_state(opt, p):
 
 
 @pytest.mark.parametrize("name", ["lion_4bit_nogc_wd", "lion_4bit_none", "lion_int8_none",
-                                  "lion_bf16_nocautious"])
+                                  "lion_bf16_nocautious", "lion_4bit_block64"])
 def test_lion_matches_reference_bit_exact(name):
     from _gpu import run_case_gpu, state_np, to_bits
     for step, f, opt, params in run_case_gpu(name):
@@ -80,7 +80,9 @@ SHAPES_BIG = [(640, 2560), (320, 320, 3, 3), (1280,), (5120, 640), (333, 77), (1
 
 @pytest.mark.parametrize("md,gc,method,wd", [("4bit", False, "none", 0.0), ("4bit", True, "stochastic_rounding", 0.0),
                                              ("int8", True, "none", 0.05), ("bfloat16", True, "stochastic_rounding", 0.0),
-                                             ("float32", False, "none", 0.0), ("4bit", True, "none", 0.1)])
+                                             ("float32", False, "none", 0.0), ("4bit", True, "none", 0.1),
+                                             ("4bit/32", False, "none", 0.0), ("4bit/64", True, "stochastic_rounding", 0.0),
+                                             ("4bit/256", True, "none", 0.1)])
 @pytest.mark.parametrize("dtype", ["bf16", "f32"])
 def test_lion_vs_oracle_bigger_shapes(md, gc, method, wd, dtype):
     """Shapes with ragged tails, rows that straddle 4-bit blocks (C = 2880, 77), a row of exactly CAP
@@ -93,6 +95,9 @@ def test_lion_vs_oracle_bigger_shapes(md, gc, method, wd, dtype):
     host = [(torch.randn(s, generator=gen) * 0.02).to(tdt) for s in shapes]
     params = [torch.nn.Parameter(h.clone().cuda()) for h in host]
     kw = dict(lr=2e-4, betas=(0.95, 0.98), weight_decay=wd, momentum_dtype=md, gradient_centralization=gc, bf16_method=method)
+    if "/" in md:   # "4bit/64": the 4-bit codec with another block size (reference src/kaon/_momentum_codec.py:192-200)
+        md, blk = md.split("/")
+        kw.update(momentum_dtype=md, momentum_4bit_block=int(blk))
     opt = kaon_b200.Lion(params, **kw)
     opt.sr_seed = 3
     orc = ko.OracleLion([to_bits(h) for h in host], shapes, seed=3, **kw)

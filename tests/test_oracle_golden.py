@@ -14,7 +14,7 @@ from _golden import Fixture, rel_err, sr_close, ulp_diff_bf16
 from golden.cases import CASES, SCHEDULES
 
 ORACLES = {"Lion": ko.OracleLion, "Adakaon": ko.OracleAdakaon, "Nekaon": ko.OracleNekaon,
-           "AdaMuon": ko.OracleAdaMuon, "AdaPNM": ko.OracleAdaPNM}
+           "AdaMuon": ko.OracleAdaMuon, "AdaPNM": ko.OracleAdaPNM, "KProdigy": ko.OracleKProdigy}
 
 
 def test_philox_known_answers():
@@ -144,7 +144,7 @@ def test_lion_fp32_grads_with_gc():
 
 
 @pytest.mark.parametrize("name", ["lion_4bit_nogc_wd", "lion_4bit_none", "lion_int8_none",
-                                  "lion_bf16_nocautious"])
+                                  "lion_bf16_nocautious", "lion_4bit_block64"])
 def test_lion_bit_exact(name):
     """Lion has no order-dependent reduction except the GC row mean; on these vectors the oracle's
     double-accumulated mean rounds to the same bf16 as torch's, so everything is bit-exact."""
@@ -209,7 +209,8 @@ def test_lion_sr_state_is_weight_independent():
 
 
 @pytest.mark.parametrize("name", ["adakaon_int8_none", "adakaon_int8_sr", "adakaon_int8_outlier",
-                                  "adakaon_4bit_wd_f32", "adakaon_bf16m_none"])
+                                  "adakaon_4bit_wd_f32", "adakaon_bf16m_none", "adakaon_4bit_block256_wd",
+                                  "adakaon_4bit_block32_f32"])
 def test_adakaon(name):
     md = CASES[name][1]["momentum_dtype"]
     sr = CASES[name][1].get("bf16_method", "stochastic_rounding") == "stochastic_rounding"
@@ -278,6 +279,83 @@ def test_adapnm_kahan():
         for i, t in enumerate(opt.tensors):
             assert _kahan_close(t.p, t.state["shift"], f.weights(step, i), f.state(step, i, "shift")), (step, i)
     assert flips / total < 2e-3
+
+
+def _kprodigy_check(name, steps_of, group_of, tensor_state, weights_of, shift_of):
+    """Shared by the oracle test here and the CUDA test: compare a KProdigy run with its fixture.
+
+    Under stochastic rounding with bf16 weights only the first step is comparable: from the second step on
+    the distance estimate d feeds on p0 - p, which one step of stochastic rounding dominates (the update
+    is far below a bf16 ulp), so the reference's own trajectory depends on its noise."""
+    kw = CASES[name][1]
+    md = kw.get("momentum_dtype", "bfloat16") if kw.get("betas", (0.9, 0.999))[0] > 0 else None
+    method = kw.get("bf16_method", "stochastic_rounding")
+    bf16_weights = CASES[name][3] == "bf16"
+    flips = total = 0
+    for step, f in steps_of():
+        if bf16_weights and method == "stochastic_rounding" and step > 1:
+            break
+        grp = group_of()
+        for key in ("d", "d_max", "d_numerator"):
+            want = float(f[f"grp_s{step}_{key}"])
+            assert abs(grp[key] - want) <= 5e-5 * abs(want) + 1e-30, (step, key, grp[key], want)
+        assert grp["k"] == int(f[f"grp_s{step}_k"])
+        for i in range(len(f.shapes)):
+            st = tensor_state(i)
+            for key in ("s", "v", "row", "col"):
+                want = f.state(step, i, key)
+                if want is not None:
+                    # d itself is only good to ~1e-5 (a sum over all tensors), s mixes terms of both signs, and
+                    # a centralised fp32 gradient close to zero carries the row mean's rounding
+                    np.testing.assert_allclose(st[key], want.reshape(-1), rtol=5e-5,
+                                               atol=5e-5 * float(np.abs(want).max()), err_msg=f"{step} {i} {key}")
+            assert np.array_equal(np.asarray(st["p0"]).reshape(-1), f.state(step, i, "p0").reshape(-1))
+            assert int(st["step"]) == int(f.state(step, i, "step"))
+            if md in ("int8", "4bit"):
+                want_m, got_m = f.state(step, i, "m"), st["m"]
+                assert rel_err(st["m_scale"], f.state(step, i, "m_scale").reshape(-1)) <= 5e-5, (step, i)
+                if md == "int8":
+                    dd = np.abs(got_m.view(np.int8).astype(np.int32) - want_m.view(np.int8).astype(np.int32))
+                else:
+                    g8, w8 = got_m.view(np.uint8), want_m.view(np.uint8)
+                    dd = np.maximum(np.abs((g8 & 15).astype(np.int32) - (w8 & 15)),
+                                    np.abs((g8 >> 4).astype(np.int32) - (w8 >> 4)))
+                assert dd.max() <= 1, (step, i, int(dd.max()))
+                flips += int((dd != 0).sum())
+                total += dd.size
+            elif md == "bfloat16":
+                assert np.mean(ulp_diff_bf16(st["m"], f.state(step, i, "m")) > 1) < 1e-3, (step, i)
+            elif md == "float32":
+                want_m = f.state(step, i, "m").reshape(-1)
+                np.testing.assert_allclose(st["m"], want_m, rtol=5e-5, atol=5e-5 * float(np.abs(want_m).max()))
+            got, want = weights_of(i), f.weights(step, i)
+            if want.dtype == np.uint16:
+                if method == "stochastic_rounding":
+                    assert sr_close(got, want, step, 1e-3), (step, i)
+                elif method == "kahan":
+                    assert _kahan_close(got, shift_of(i), want, f.state(step, i, "shift"), tol_ulp=2.0), (step, i)
+                else:
+                    ud = ulp_diff_bf16(got, want)
+                    assert ud.max() <= 1 and np.mean(ud > 0) < 3e-2, (step, i, float(np.mean(ud > 0)))
+            else:
+                np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-9)
+    if total:
+        assert flips / total < 5e-3, (flips, total)
+
+
+@pytest.mark.parametrize("name", [n for n in CASES if n.startswith("kprodigy_")])
+def test_kprodigy(name):
+    """reference src/kaon/kprodigy.py: the distance estimate d (a scalar over all tensors) between a pass that
+    updates the statistics and the moments and a pass that writes the weights."""
+    holder = {}
+
+    def steps_of():
+        for step, f, opt in _run_oracle(name):
+            holder["opt"] = opt
+            yield step, f
+
+    _kprodigy_check(name, steps_of, lambda: holder["opt"].group, lambda i: holder["opt"].tensors[i].state,
+                    lambda i: holder["opt"].tensors[i].p, lambda i: holder["opt"].tensors[i].state["shift"])
 
 
 def test_nekaon_fp32_params():
