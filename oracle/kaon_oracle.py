@@ -452,6 +452,7 @@ class OracleKProdigy(OracleOptimizer):
             d_max = max(d_max, d_hat)
             d_new = min(d_max, d_new * hp["growth_rate"])
             grp.update(d_numerator=global_num, d=d_new, d_max=d_max, d_hat=d_hat)
+            d = d_new   # pass 2 takes the NEW d for its denominator with the OLD dlr (kprodigy.py:379-403)
         self.kept = [-1] * len(self.tensors)
         for tid, t, g in active:
             st = t.state

@@ -282,19 +282,13 @@ def test_adapnm_kahan():
 
 
 def _kprodigy_check(name, steps_of, group_of, tensor_state, weights_of, shift_of):
-    """Shared by the oracle test here and the CUDA test: compare a KProdigy run with its fixture.
-
-    Under stochastic rounding with bf16 weights only the first step is comparable: from the second step on
-    the distance estimate d feeds on p0 - p, which one step of stochastic rounding dominates (the update
-    is far below a bf16 ulp), so the reference's own trajectory depends on its noise."""
+    """Shared by the oracle test here and the CUDA test: compare a KProdigy run, every step of which starts
+    from the reference's state (kprodigy_force), with its fixture."""
     kw = CASES[name][1]
     md = kw.get("momentum_dtype", "bfloat16") if kw.get("betas", (0.9, 0.999))[0] > 0 else None
     method = kw.get("bf16_method", "stochastic_rounding")
-    bf16_weights = CASES[name][3] == "bf16"
     flips = total = 0
     for step, f in steps_of():
-        if bf16_weights and method == "stochastic_rounding" and step > 1:
-            break
         grp = group_of()
         for key in ("d", "d_max", "d_numerator"):
             want = float(f[f"grp_s{step}_{key}"])
@@ -331,31 +325,65 @@ def _kprodigy_check(name, steps_of, group_of, tensor_state, weights_of, shift_of
             got, want = weights_of(i), f.weights(step, i)
             if want.dtype == np.uint16:
                 if method == "stochastic_rounding":
-                    assert sr_close(got, want, step, 1e-3), (step, i)
+                    assert sr_close(got, want, 1, 1e-3), (step, i)   # one write since the forced state
                 elif method == "kahan":
                     assert _kahan_close(got, shift_of(i), want, f.state(step, i, "shift"), tol_ulp=2.0), (step, i)
                 else:
+                    # one ulp, except where a cautious-mask bit flipped (terms of both signs that all but
+                    # cancel): such an element is off by one masked update, far below 1e-4; a 4-bit code one level off does the same
                     ud = ulp_diff_bf16(got, want)
-                    assert ud.max() <= 1 and np.mean(ud > 0) < 3e-2, (step, i, float(np.mean(ud > 0)))
+                    assert (ud > 1).sum() <= max(2, 5e-3 * ud.size) and (ud > 0).sum() <= max(3, 3e-2 * ud.size), (step, i)
+                    assert np.abs(ko.as_f32(got).astype(np.float64) - ko.as_f32(want)).max() < 1e-4, (step, i)
             else:
-                np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-9)
+                np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-8)
     if total:
         assert flips / total < 5e-3, (flips, total)
+
+
+def kprodigy_force(f, step, group, n_tensors, set_weights, set_state):
+    """Put an implementation into the reference's state after `step` (weights, per-tensor state, the group's
+    scalars), so that every step is compared on its own: the distance estimate feeds on p0 - p, so a single
+    cautious-mask bit or stochastic rounding draw that differs moves every later step by a per cent or so -
+    in the reference's own trajectory as much as here."""
+    for key in ("d", "d_max", "d_numerator"):
+        group[key] = float(f[f"grp_s{step}_{key}"])
+    group["k"] = int(f[f"grp_s{step}_k"])
+    for i in range(n_tensors):
+        set_weights(i, f.weights(step, i))
+        for key in ("s", "p0", "m", "m_scale", "v", "row", "col", "shift"):
+            want = f.state(step, i, key)
+            if want is not None:
+                set_state(i, key, want)
 
 
 @pytest.mark.parametrize("name", [n for n in CASES if n.startswith("kprodigy_")])
 def test_kprodigy(name):
     """reference src/kaon/kprodigy.py: the distance estimate d (a scalar over all tensors) between a pass that
-    updates the statistics and the moments and a pass that writes the weights."""
-    holder = {}
+    updates the statistics and the moments and a pass that writes the weights.  Every step starts from the
+    reference's state after the step before."""
+    opt_name, kw, shapes, dtype, steps, seed, o = CASES[name]
+    f = Fixture(name)
+    opt = ko.OracleKProdigy(f.params(), shapes, **kw)
+
+    def set_weights(i, bits):
+        opt.tensors[i].p[...] = bits
+
+    def set_state(i, key, want):
+        st = opt.tensors[i].state
+        if key == "p0" and want.ndim == 0:
+            st[key] = np.zeros((), np.float32)
+        else:
+            st[key][...] = want.reshape(st[key].shape).view(st[key].dtype)
 
     def steps_of():
-        for step, f, opt in _run_oracle(name):
-            holder["opt"] = opt
+        for step in range(1, steps + 1):
+            if step > 1:
+                kprodigy_force(f, step - 1, opt.group, len(shapes), set_weights, set_state)
+            opt.step(f.grads(step))
             yield step, f
 
-    _kprodigy_check(name, steps_of, lambda: holder["opt"].group, lambda i: holder["opt"].tensors[i].state,
-                    lambda i: holder["opt"].tensors[i].p, lambda i: holder["opt"].tensors[i].state["shift"])
+    _kprodigy_check(name, steps_of, lambda: opt.group, lambda i: opt.tensors[i].state,
+                    lambda i: opt.tensors[i].p, lambda i: opt.tensors[i].state["shift"])
 
 
 def test_nekaon_fp32_params():
