@@ -42,6 +42,7 @@ extern "C" {
 #define KAON_OPT_ADAKAON 1
 #define KAON_OPT_ADAMUON 2
 #define KAON_OPT_ADAPNM 3
+#define KAON_OPT_KPRODIGY 4
 
 /* error codes */
 #define KAON_OK 0
@@ -113,6 +114,21 @@ typedef struct kaon_adapnm_hparams {
   int32_t cautious, gradient_centralization, ams_bound, bf16_method;
   uint32_t group_step, reserved;
 } kaon_adapnm_hparams;
+
+/* KProdigy (src/kaon/kprodigy.py:329-404).  The distance estimate d is a host scalar of the caller (the
+ * reference keeps it in param_groups); the two passes take the values the reference computes around it:
+ * pass 1 the d of the top of the step, alpha_s = (d/d0)*d or (d/d0)*dlr, the coupled weight decay (0 when
+ * decoupled); pass 2 the d as just updated, the dlr of the top of the step, decay_dlr = weight_decay*dlr
+ * (0 unless decoupled). */
+typedef struct kaon_kprodigy_pass1_hparams {
+  double beta1, beta2, beta3, d, alpha_s, weight_decay_coupled, eps_factored;
+  int32_t do_d, gradient_centralization, factored, reserved;
+} kaon_kprodigy_pass1_hparams;
+
+typedef struct kaon_kprodigy_pass2_hparams {
+  double d, dlr, eps, decay_dlr;
+  int32_t cautious, gradient_centralization, factored, bf16_method;
+} kaon_kprodigy_pass2_hparams;
 
 /* ---- library ---- */
 int kaon_abi_version(void);
@@ -210,6 +226,21 @@ int kaon_adapnm_attach(kaon_plan* plan, const void* const* m_neg, float* const* 
                        float* const* max_v, int n);
 int kaon_adapnm_step(kaon_plan* plan, const kaon_adapnm_hparams* hp, uint64_t seed, uint32_t step,
                      void* stream);
+
+/* KProdigy.  Replaces KProdigy._pass1_per_param / _pass1_foreach / _pass1_momentum_foreach /
+ * _pass1_second_moment_foreach / _update_momentum (src/kaon/kprodigy.py:417-703, 762-782) and _apply_updates /
+ * _update_one_param / _update_foreach / _factored_bucket / _full_bucket (:706-949); the D update between
+ * them (:371-391) stays with the caller.  The plan is created with optimizer KAON_OPT_KPRODIGY (momentum kind
+ * KAON_M_NONE for betas[0] == 0); stat_a / stat_b name "row" / "col" of a factored tensor, stat_a alone the
+ * full "v".  kaon_kprodigy_attach names each tensor's "s" buffer and "p0" reference point (a null entry for
+ * the reference's zero-dimensional zero) with the slice_p they were built for.
+ * kaon_kprodigy_pass1: statistics and moments; with do_d it synchronises `stream` and leaves, per tensor i,
+ * sums_host[2i] = sum over the sliced elements of g*(p0 - p) and sums_host[2i+1] = sum |s| (zeros for a
+ * tensor without a gradient); the caller folds them in tensor order.  kaon_kprodigy_pass2: the weights. */
+int kaon_kprodigy_attach(kaon_plan* plan, float* const* s, const float* const* p0, int n, int64_t slice_p);
+int kaon_kprodigy_pass1(kaon_plan* plan, const kaon_kprodigy_pass1_hparams* hp, float* sums_host, void* stream);
+int kaon_kprodigy_pass2(kaon_plan* plan, const kaon_kprodigy_pass2_hparams* hp, uint64_t seed, uint32_t step,
+                        void* stream);
 
 /* One AdaMuon step.  Replaces AdaMuon._run_step / _factored_bucket / _nonfactored_bucket /
  * _step_one_param (src/kaon/adamuon.py:327-352, 434-615): per >=2-D tensor the EMA of the raw gradient

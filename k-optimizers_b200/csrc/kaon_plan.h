@@ -179,8 +179,11 @@ struct kaon_plan {
   // AdaPNM only: lists, partial sums and the second-momentum table (adapnm.cu), built by kaon_adapnm_attach
   void* pnm = nullptr;
   bool pnm_has_max_v = false;
+  // KProdigy only: item lists, partial sums and the s / p0 table (kprodigy.cu), built by kaon_kprodigy_attach
+  void* kp = nullptr;
 };
 
 namespace kaon {
 void pnm_free(kaon_plan* pl);
+void kp_free(kaon_plan* pl);
 }

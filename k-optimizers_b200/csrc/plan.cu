@@ -137,7 +137,7 @@ int kaon_plan_create(kaon_plan** out, int optimizer, int param_dtype, int moment
   if (!out || !descs || n <= 0) return fail(KAON_E_INVALID, "kaon_plan_create: null argument or n <= 0");
   if (param_dtype != KAON_DT_F32 && param_dtype != KAON_DT_BF16) return fail(KAON_E_INVALID, "param_dtype %d", param_dtype);
   if (momentum_kind < KAON_M_F32 || momentum_kind > KAON_M_NONE) return fail(KAON_E_INVALID, "momentum_kind %d", momentum_kind);
-  if (optimizer < KAON_OPT_LION || optimizer > KAON_OPT_ADAPNM) return fail(KAON_E_INVALID, "optimizer %d", optimizer);
+  if (optimizer < KAON_OPT_LION || optimizer > KAON_OPT_KPRODIGY) return fail(KAON_E_INVALID, "optimizer %d", optimizer);
   if (optimizer == KAON_OPT_LION && momentum_kind == KAON_M_NONE) return fail(KAON_E_INVALID, "Lion needs a momentum");
   if (optimizer == KAON_OPT_ADAPNM && momentum_kind == KAON_M_NONE) return fail(KAON_E_INVALID, "AdaPNM needs its two momenta");
   *out = nullptr;
@@ -379,6 +379,7 @@ int kaon_plan_destroy(kaon_plan* pl) {
   cudaFree(pl->d_aux);
   cudaFree(pl->d_flat_tensors);
   kaon::pnm_free(pl);
+  kaon::kp_free(pl);
   cudaFree(pl->d_tasks_ema);
   cudaFree(pl->d_tasks_apply2);
   cudaFree(pl->d_tasks_na[0]);

@@ -8,7 +8,8 @@ from ._version import __version__
 from .adakaon import Adakaon
 from .adamuon import AdaMuon
 from .adapnm import AdaPNM
+from .kprodigy import KProdigy
 from .lion import Lion
 from .nekaon import Nekaon
 
-__all__ = ["AdaMuon", "AdaPNM", "Adakaon", "Lion", "Nekaon", "__version__"]
+__all__ = ["AdaMuon", "AdaPNM", "Adakaon", "KProdigy", "Lion", "Nekaon", "__version__"]

@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(PKG, "libkaon_b200.so")
 DT_F32, DT_BF16 = 0, 1
 M_F32, M_BF16, M_INT8, M_4BIT, M_NONE = 0, 1, 2, 3, 4
 W_NONE, W_SR, W_KAHAN = 0, 1, 2
-OPT_LION, OPT_ADAKAON, OPT_ADAMUON, OPT_ADAPNM = 0, 1, 2, 3
+OPT_LION, OPT_ADAKAON, OPT_ADAMUON, OPT_ADAPNM, OPT_KPRODIGY = 0, 1, 2, 3, 4
 TAG_UPDATE, TAG_REMOVE, TAG_CLIMB, TAG_EVAL, TAG_TRAIN = 0, 1, 2, 3, 4
 MOMENTUM_KIND = {"float32": M_F32, "bfloat16": M_BF16, "int8": M_INT8, "4bit": M_4BIT}
 BF16_METHOD = {"none": W_NONE, "stochastic_rounding": W_SR, "kahan": W_KAHAN}
@@ -55,6 +55,19 @@ class AdaPNMHParams(C.Structure):
                 ("eps", C.c_double), ("weight_decay", C.c_double), ("clip_threshold", C.c_double),
                 ("cautious", C.c_int32), ("gradient_centralization", C.c_int32), ("ams_bound", C.c_int32),
                 ("bf16_method", C.c_int32), ("group_step", C.c_uint32), ("reserved", C.c_uint32)]
+
+
+class KProdigyPass1(C.Structure):
+    _fields_ = [("beta1", C.c_double), ("beta2", C.c_double), ("beta3", C.c_double), ("d", C.c_double),
+                ("alpha_s", C.c_double), ("weight_decay_coupled", C.c_double), ("eps_factored", C.c_double),
+                ("do_d", C.c_int32), ("gradient_centralization", C.c_int32), ("factored", C.c_int32),
+                ("reserved", C.c_int32)]
+
+
+class KProdigyPass2(C.Structure):
+    _fields_ = [("d", C.c_double), ("dlr", C.c_double), ("eps", C.c_double), ("decay_dlr", C.c_double),
+                ("cautious", C.c_int32), ("gradient_centralization", C.c_int32), ("factored", C.c_int32),
+                ("bf16_method", C.c_int32)]
 
 
 class KaonError(RuntimeError):

@@ -56,7 +56,7 @@ CASES = {
     "kprodigy_4bit_factored_slice_cautious": ("KProdigy", dict(momentum_dtype="4bit", second_moment="factored", slice_p=3, cautious=True, weight_decay=0.01, bf16_method="none"), SMALL, "bf16", 10, 51, {"correlated": True}),
     "kprodigy_int8_wd_f32": ("KProdigy", dict(momentum_dtype="int8", weight_decay=0.05, d_coef=2.0), SMALL, "f32", 10, 52, {"correlated": True}),
     "kprodigy_f32m_nogc_bias_safeguard": ("KProdigy", dict(momentum_dtype="float32", gradient_centralization=False, use_bias_correction=True, safeguard_warmup=True, growth_rate=1.5, d0=1e-5, bf16_method="none"), SMALL, "bf16", 10, 53, {"correlated": True}),
-    "kprodigy_nomomentum_coupled_wd": ("KProdigy", dict(betas=(0.0, 0.99), weight_decay=0.02, decouple=False, second_moment="factored", d_update_freq=2, bf16_method="none"), SMALL, "bf16", 10, 54, {"correlated": True}),
+    "kprodigy_nomomentum_coupled_wd": ("KProdigy", dict(betas=(0.0, 0.99), weight_decay=0.02, decouple=False, d_update_freq=2, bf16_method="none"), SMALL, "bf16", 10, 54, {"correlated": True}),
     "kprodigy_int8_kahan": ("KProdigy", dict(momentum_dtype="int8", bf16_method="kahan", cautious=True), SMALL, "bf16", 10, 55, {"correlated": True}),
     # C1 at full size (the CPU-runnable correctness workload); big tensors stored strided
     "c1_full": ("Adakaon", dict(lr=1e-4, betas=(0.9, 0.999), momentum_dtype="int8", bf16_method="stochastic_rounding"), C1, "bf16", 10, 0, {"store_inputs": False, "sample": 257}),
