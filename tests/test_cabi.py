@@ -56,7 +56,7 @@ def test_integration_doc_structs_match_the_header():
     from kaon_b200 import _lib
     text = open(os.path.join(ROOT, "INTEGRATION.md")).read()
     ns = {"C": C}
-    for name in ("TensorDesc", "LionHParams", "AdaPNMHParams"):
+    for name in ("TensorDesc", "LionHParams", "AdaPNMHParams", "KProdigyPass1", "KProdigyPass2"):
         m = re.search(r"class %s\(C\.Structure\):.*?\n    _fields_ = \[(.*?)\]" % name, text, flags=re.S)
         assert m, name
         exec("class %s(C.Structure):\n    _fields_ = [%s]" % (name, m.group(1)), ns)  # noqa: S102
@@ -64,4 +64,5 @@ def test_integration_doc_structs_match_the_header():
         assert C.sizeof(doc) == C.sizeof(ours), (name, C.sizeof(doc), C.sizeof(ours))
         assert [f[0] for f in doc._fields_] == [f[0] for f in ours._fields_]
     assert C.sizeof(ns["TensorDesc"]) == 80 and C.sizeof(ns["AdaPNMHParams"]) == 80
+    assert C.sizeof(ns["KProdigyPass1"]) == 72 and C.sizeof(ns["KProdigyPass2"]) == 48
     assert '"kahan": 2' in text
