@@ -148,7 +148,7 @@ def test_kprodigy_vs_oracle_bigger_shapes(kw, dtype):
                 # an element whose second moment sits at the d*eps floor moves by g*lr/eps: the fp32 noise of a
                 # centralised gradient near zero shows there and nowhere else
                 bad = np.abs(got - want) > 1e-5 * np.abs(want) + 1e-5 * float(np.abs(want).mean())
-                assert bad.mean() < 5e-4, (step, i, BIG[i], int(bad.sum()))
+                assert bad.sum() <= max(16, 5e-4 * bad.size), (step, i, BIG[i], int(bad.sum()))
                 np.testing.assert_allclose(got, want, rtol=1e-3, atol=1e-5 * float(np.abs(want).max()))
 
 
