@@ -55,11 +55,17 @@ WORKLOADS = {
     "nekaon4bit_mid": ("Nekaon", NEKAON_KW, "unet_mid", 7.073, {"cosine": (1e-4, 1e-5, 50)}),
     "adamuon_int8_dit11b": ("AdaMuon", ADAMUON_KW, "dit_11b", 8.006, {"one_grad_set": True, "steps": 10}),
     "adamuon_int8_ditblock": ("AdaMuon", ADAMUON_KW, "dit_block", 8.006, {}),
+    # the two optimizers beyond the benchmark configurations (not tuned; sized for a quick figure)
+    #  AdaPNM-4bit: g 2 + p 2+2 + m_pos 0.5+0.5 + m_neg 0.5 + scales;  KProdigy defaults: g 2 + p 2+2 + bf16 m 2+2
+    #  + fp32 v 4+4 + fp32 s 4+4 + p0 4 (slice_p = 1)
+    "adapnm_4bit_mid": ("AdaPNM", dict(lr=1e-4, momentum_dtype="4bit"), "unet_mid", 7.6, {}),
+    "kprodigy_default_mid": ("KProdigy", dict(), "unet_mid", 30.0, {}),
 }
 HEADLINE = "lion4bit_unet2p6b"
 RECORD = ["adakaon_int8_unet2p6b", "nekaon4bit_unet2p6b", "adamuon_int8_dit11b"]
 KERNEL_NAME = {"AdaMuon": "ns_gemm_kernel", "Lion": "lion_kernel<bf16,4bit>", "Adakaon": "adakaon_kernel<bf16,int8>",
-               "Nekaon": "adakaon_kernel<bf16,4bit>"}
+               "Nekaon": "adakaon_kernel<bf16,4bit>", "AdaPNM": "pnm_pass_kernel<bf16,4bit>",
+               "KProdigy": "kp_sweep_kernel<bf16,bf16>"}
 
 
 def host_cores() -> int:

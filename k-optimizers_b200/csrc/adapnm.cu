@@ -75,16 +75,17 @@ __device__ __forceinline__ void pnm_write(const PnmDev& hp, const DevTensor& d, 
   uint32_t nz[4] = {0u, 0u, 0u, 0u};
   if (hp.sr) s_upd.draw8(d.tensor_id, (uint64_t)(e >> 3), nz);
   const bool kahan = E::IS_BF16 && hp.kahan;
+  const float rdiv = __frcp_rn(div), rdenom = __frcp_rn(denom);
   unsigned char* she = kahan ? reinterpret_cast<unsigned char*>(d.shift) + e * 2 : nullptr;
   if (kahan) load8_guard<__nv_bfloat16>(she, cnt, sh);
 #pragma unroll
   for (int k = 0; k < 8; ++k) {
-    if (k >= cnt) break;
+    if (k >= cnt) continue;
     float p0 = pw[k];
     if (hp.has_wd) p0 = E::IS_BF16 ? round_bf16(__fmul_rn(p0, hp.wdsc)) : __fmul_rn(p0, hp.wdsc);
-    float dl = hp.clip_on ? __fdiv_rn(tr.u[k], div) : tr.u[k];
+    float dl = hp.clip_on ? div_by(tr.u[k], div, rdiv) : tr.u[k];
     dl = __fmul_rn(dl, hp.fstep);
-    if (hp.cautious) dl = (__fmul_rn(dl, tr.y[k]) > 0.0f) ? __fdiv_rn(dl, denom) : 0.0f;
+    if (hp.cautious) dl = (__fmul_rn(dl, tr.y[k]) > 0.0f) ? div_by(dl, denom, rdenom) : 0.0f;
     if (kahan) kahan_step(p0, sh[k], dl);
     else p0 = write_step_pnm<PT>(p0, dl, hp.sr != 0, noise_lane_pnm(nz, k));
     pw[k] = p0;
@@ -105,7 +106,8 @@ __device__ __forceinline__ void pnm_write(const PnmDev& hp, const DevTensor& d, 
                        (__float_as_uint(sh[4]) >> 16) | (__float_as_uint(sh[5]) & 0xFFFF0000u),
                        (__float_as_uint(sh[6]) >> 16) | (__float_as_uint(sh[7]) & 0xFFFF0000u));
     } else {
-      for (int k = 0; k < cnt; ++k) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) if (k < cnt) {
         reinterpret_cast<uint16_t*>(pe)[k] = (uint16_t)(__float_as_uint(pw[k]) >> 16);
         if (kahan) reinterpret_cast<uint16_t*>(she)[k] = (uint16_t)(__float_as_uint(sh[k]) >> 16);
       }
@@ -119,7 +121,8 @@ __device__ __forceinline__ void pnm_write(const PnmDev& hp, const DevTensor& d, 
       mirror16(peers, pf, make_uint4(__float_as_uint(pw[0]), __float_as_uint(pw[1]), __float_as_uint(pw[2]), __float_as_uint(pw[3])));
       mirror16(peers, pf + 4, make_uint4(__float_as_uint(pw[4]), __float_as_uint(pw[5]), __float_as_uint(pw[6]), __float_as_uint(pw[7])));
     } else {
-      for (int k = 0; k < cnt; ++k) pf[k] = pw[k];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) if (k < cnt) pf[k] = pw[k];
       mirror_copy(peers, pf, cnt * 4);
     }
   }
@@ -164,37 +167,65 @@ __global__ void __launch_bounds__(PT_THREADS) pnm_pass_kernel(PlanView pv, PnmDe
         PnmTrip tr;
         tr.first = 0u;
         if (cnt > 0) {
-          float gx[8];
+          float gx[8], mpo[8], mno[8];
+          int cl[8];
           load8_guard<PT>(g + e * E::BYTES, cnt, gx);
-          int r = (int)(e / C);
+          int r = e < 0x100000000ll ? (int)((unsigned)e / (unsigned)C) : (int)(e / C);
           int c = (int)(e - (long long)r * C);
+          // the common trip: eight elements of one row (no row bookkeeping, one row factor, one mean)
+          const bool one_row = cnt == 8 && c + 8 <= C;
+          if (one_row) {
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            tr.y[k] = 0.0f; tr.mp[k] = 0.0f; tr.u[k] = 0.0f; tr.rw[k] = 0;
-            if (k < cnt) {
-              while (c >= C) { c -= C; ++r; }
-              tr.rw[k] = r;
-              if (c == 0) tr.first |= 1u << k;
-              const float yk = pnm_centered<PT>(gx[k], hp.gc ? mean[r] : 0.0f, hp.gc != 0);
-              const float mpo = pnm_decode<MK>(pos, psc_rd, e + k, r, bsh);
-              const float mno = pnm_decode<MK>(neg, nsc, e + k, r, bsh);
-              const float mpn = __fmaf_rn(yk, hp.fw, __fmul_rn(mpo, hp.fb));
-              const float pn = __fmul_rn(__fmaf_rn(mno, hp.c2, __fmul_rn(mpn, hp.c1)), hp.c3);
-              const float inv = __fmul_rn(__fmul_rn(rfac[r], cfac[c]), hp.bc2);
-              tr.y[k] = yk; tr.mp[k] = mpn; tr.u[k] = __fmul_rn(pn, inv);
-              ++c;
+            for (int k = 0; k < 8; ++k) { tr.rw[k] = r; cl[k] = c + k; }
+            if (c == 0) tr.first = 1u;
+          } else {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              tr.rw[k] = 0; cl[k] = 0;
+              if (k < cnt) {
+                while (c >= C) { c -= C; ++r; }
+                tr.rw[k] = r;
+                cl[k] = c;
+                if (c == 0) tr.first |= 1u << k;
+                ++c;
+              }
             }
           }
+          pnm_decode8<MK>(pos, psc_rd, e, cnt, tr.rw, bsh, mpo);
+          pnm_decode8<MK>(neg, nsc, e, cnt, tr.rw, bsh, mno);
+          auto chain = [&](int k, float rf, float mu) {
+            const float yk = pnm_centered<PT>(gx[k], mu, hp.gc != 0);
+            const float mpn = __fmaf_rn(yk, hp.fw, __fmul_rn(mpo[k], hp.fb));
+            const float pn = __fmul_rn(__fmaf_rn(mno[k], hp.c2, __fmul_rn(mpn, hp.c1)), hp.c3);
+            const float inv = __fmul_rn(__fmul_rn(rf, cfac[cl[k]]), hp.bc2);
+            tr.y[k] = yk; tr.mp[k] = mpn; tr.u[k] = __fmul_rn(pn, inv);
+          };
+          if (one_row) {
+            const float rf = rfac[tr.rw[0]], mu = hp.gc ? mean[tr.rw[0]] : 0.0f;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) chain(k, rf, mu);
+          } else {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              tr.y[k] = 0.0f; tr.mp[k] = 0.0f; tr.u[k] = 0.0f;
+              if (k < cnt) chain(k, rfac[tr.rw[k]], hp.gc ? mean[tr.rw[k]] : 0.0f);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) { tr.y[k] = 0.0f; tr.mp[k] = 0.0f; tr.u[k] = 0.0f; tr.rw[k] = 0; }
         }
         if constexpr (!APPLY) {
-          for (int k = 0; k < cnt; ++k) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) if (k < cnt) {
             ss += (double)tr.u[k] * (double)tr.u[k];
             kept += (__fmul_rn(tr.u[k], tr.y[k]) > 0.0f) ? 1u : 0u;
           }
           if constexpr (MK == KAON_M_INT8) {
             int cr = -1;
             float mx = 0.0f;
-            for (int k = 0; k < cnt; ++k) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) if (k < cnt) {
               if (tr.rw[k] != cr) {
                 if (cr >= 0) atomicMax(rowmax + cr, __float_as_uint(mx));
                 cr = tr.rw[k];
@@ -307,28 +338,33 @@ __global__ void __launch_bounds__(PT_THREADS) pnm_flat_kernel(PlanView pv, PnmDe
   const float* psc_rd = one_scale ? &old_sc : psc;
 
   auto chain = [&](long long e, int cnt, bool first_sweep, PnmTrip& tr) {
-    float gx[8];
+    float gx[8], vv[8], mx[8], mpo[8], mno[8];
     load8_guard<PT>(g + e * E::BYTES, cnt, gx);
+    ld8f(v + e, cnt, vv);
+    if (max_v != nullptr) ld8f(max_v + e, cnt, mx);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) tr.rw[k] = 0;
+    pnm_decode8<MK>(pos, psc_rd, e, cnt, tr.rw, bsh, mpo);
+    pnm_decode8<MK>(neg, nsc, e, cnt, tr.rw, bsh, mno);
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
-      tr.y[k] = 0.0f; tr.mp[k] = 0.0f; tr.u[k] = 0.0f; tr.rw[k] = 0;
+      tr.y[k] = 0.0f; tr.mp[k] = 0.0f; tr.u[k] = 0.0f;
       if (k < cnt) {
         const float yk = gx[k];
-        float vv;
         if (first_sweep) {
-          vv = __fmaf_rn(__fmul_rn(hp.fw2, yk), yk, __fmul_rn(v[e + k], hp.fb2));
-          v[e + k] = vv;
-          if (max_v != nullptr) { vv = fmaxf(max_v[e + k], vv); max_v[e + k] = vv; }
-        } else {
-          vv = max_v != nullptr ? max_v[e + k] : v[e + k];
+          vv[k] = __fmaf_rn(__fmul_rn(hp.fw2, yk), yk, __fmul_rn(vv[k], hp.fb2));
+          if (max_v != nullptr) mx[k] = fmaxf(mx[k], vv[k]);
         }
-        const float den = __fdiv_rn(__fadd_rn(__fsqrt_rn(__fadd_rn(vv, 1e-15f)), hp.eps), hp.bc2);
-        const float mpo = pnm_decode<MK>(pos, psc_rd, e + k, 0, bsh);
-        const float mno = pnm_decode<MK>(neg, nsc, e + k, 0, bsh);
-        const float mpn = __fmaf_rn(yk, hp.fw, __fmul_rn(mpo, hp.fb));
-        const float pn = __fmul_rn(__fmaf_rn(mno, hp.c2, __fmul_rn(mpn, hp.c1)), hp.c3);
+        const float vd = max_v != nullptr ? mx[k] : vv[k];
+        const float den = __fdiv_rn(__fadd_rn(__fsqrt_rn(__fadd_rn(vd, 1e-15f)), hp.eps), hp.bc2);
+        const float mpn = __fmaf_rn(yk, hp.fw, __fmul_rn(mpo[k], hp.fb));
+        const float pn = __fmul_rn(__fmaf_rn(mno[k], hp.c2, __fmul_rn(mpn, hp.c1)), hp.c3);
         tr.y[k] = yk; tr.mp[k] = mpn; tr.u[k] = __fdiv_rn(pn, den);
       }
+    }
+    if (first_sweep) {
+      st8f(v + e, cnt, vv);
+      if (max_v != nullptr) st8f(max_v + e, cnt, mx);
     }
   };
 
@@ -342,7 +378,8 @@ __global__ void __launch_bounds__(PT_THREADS) pnm_flat_kernel(PlanView pv, PnmDe
     if (cnt > 0) {
       PnmTrip tr;
       chain(e, cnt, true, tr);
-      for (int k = 0; k < cnt; ++k) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) if (k < cnt) {
         ss += (double)tr.u[k] * (double)tr.u[k];
         kept += (__fmul_rn(tr.u[k], tr.y[k]) > 0.0f) ? 1u : 0u;
         amax = fmaxf(amax, fabsf(tr.mp[k]));

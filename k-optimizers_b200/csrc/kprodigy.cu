@@ -141,6 +141,7 @@ __global__ void __launch_bounds__(KP_THREADS) kp_sweep_kernel(PlanView pv, KpDev
       const int bsh = d.bshift;
       float denom = 1.0f;
       if (MODE == 3 && hp.cautious) denom = x.sums[t.tensor];
+      const float rdenom = __frcp_rn(denom), rfd = __frcp_rn(hp.fd);
       const int nvec = (t.n + 7) >> 3;
       for (int v0 = 0; v0 < nvec; v0 += KP_THREADS) {
         const int v = v0 + tid;
@@ -152,71 +153,117 @@ __global__ void __launch_bounds__(KP_THREADS) kp_sweep_kernel(PlanView pv, KpDev
         for (int k = 0; k < 8; ++k) { tr.y[k] = 0.0f; tr.mp[k] = 0.0f; tr.u[k] = 0.0f; tr.rw[k] = 0; }
         float pw[8];
         if (cnt > 0) {
-          float gx[8];
+          float gx[8], mo[8], vv[8], sv[8], p0v[8];
+          int cl[8];
           load8_guard<PT>(g + e * E::BYTES, cnt, gx);
           const bool need_p = MODE == 0 ? (hp.do_d || hp.has_wdc) : (MODE >= 2);
           if (need_p) load8_guard<PT>(reinterpret_cast<const unsigned char*>(d.p) + e * E::BYTES, cnt, pw);
-          int r = two_d ? (int)(e / C) : 0;
-          int c = two_d ? (int)(e - (long long)r * C) : 0;
+          int r = 0, c = 0;
+          if (two_d) {
+            r = e < 0x100000000ll ? (int)((unsigned)e / (unsigned)C) : (int)(e / C);
+            c = (int)(e - (long long)r * C);
+          }
+          // the common trip: eight elements of one row (or of a 1-D tensor)
+          const bool one_row = cnt == 8 && (!two_d || c + 8 <= C);
+          const int r0 = r;
+          if (one_row) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) { tr.rw[k] = r; cl[k] = c + k; }
+            if (two_d ? c == 0 : e == 0) tr.first = 1u;
+          } else {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              cl[k] = 0;
+              if (k < cnt) {
+                if (two_d) {
+                  while (c >= C) { c -= C; ++r; }
+                  if (c == 0) tr.first |= 1u << k;
+                } else if (e + k == 0) {
+                  tr.first |= 1u << k;
+                }
+                tr.rw[k] = r;
+                cl[k] = c;
+                ++c;
+              }
+            }
+          }
+          // the momentum: before the EMA in pass 1, as stored in pass 2
+          const bool read_m = hp.has_m && MK != KAON_M_NONE;
+          if (read_m) pnm_decode8<MK>(d.m, (MODE <= 1 && MK == KAON_M_INT8) ? msc_rd : d.m_scale, e, cnt, tr.rw, bsh, mo);
+          const bool full_v = !fac;
+          if (full_v && (MODE == 0 || MODE >= 2)) ld8f(d.stat_a + e, cnt, vv);
+          const bool dstat = MODE == 0 && hp.do_d;
+          const bool dense = hp.slice_p == 1;
+          if (dstat && dense) {
+            ld8f(b.s + e, cnt, sv);
+            if (b.p0) ld8f(b.p0 + e, cnt, p0v);
+          }
+          int rp = -1;
+          float rf = 0.0f, mu = 0.0f;
+          if (one_row) {
+            rp = r0;
+            mu = gc ? mean[rp] : 0.0f;
+            if (MODE >= 2 && fac) rf = rfac[rp];
+          }
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
-            if (k >= cnt) break;
-            if (two_d) {
-              while (c >= C) { c -= C; ++r; }
-              if (c == 0) tr.first |= 1u << k;
-            } else if (e + k == 0) {
-              tr.first |= 1u << k;
+            if (k >= cnt) continue;
+            if (!one_row && tr.rw[k] != rp) {
+              rp = tr.rw[k];
+              mu = gc ? mean[rp] : 0.0f;
+              if (MODE >= 2 && fac) rf = rfac[rp];
             }
-            tr.rw[k] = r;
-            const float yraw = pnm_centered<PT>(gx[k], gc ? mean[r] : 0.0f, gc);
+            const float yraw = pnm_centered<PT>(gx[k], mu, gc);
             if constexpr (MODE <= 1) {
               const float y = hp.has_wdc ? __fmaf_rn(pw[k], hp.fwd, yraw) : yraw;
               tr.y[k] = y;
-              if (MODE == 0 && hp.do_d && ((e + k) % hp.slice_p) == 0) {
-                const long long j = (e + k) / hp.slice_p;
-                const float pr = b.p0 ? b.p0[j] : 0.0f;
-                acc_a += (double)__fmul_rn(y, __fsub_rn(pr, pw[k]));
-                const float sn = __fmaf_rn(y, hp.fa, __fmul_rn(b.s[j], hp.fb3));
-                b.s[j] = sn;
-                acc_b += (double)fabsf(sn);
+              if (dstat) {
+                if (dense) {
+                  const float pr = b.p0 ? p0v[k] : 0.0f;
+                  acc_a += (double)__fmul_rn(y, __fsub_rn(pr, pw[k]));
+                  sv[k] = __fmaf_rn(y, hp.fa, __fmul_rn(sv[k], hp.fb3));
+                  acc_b += (double)fabsf(sv[k]);
+                } else if (((e + k) % hp.slice_p) == 0) {
+                  const long long j = (e + k) / hp.slice_p;
+                  const float pr = b.p0 ? b.p0[j] : 0.0f;
+                  acc_a += (double)__fmul_rn(y, __fsub_rn(pr, pw[k]));
+                  const float sn = __fmaf_rn(y, hp.fa, __fmul_rn(b.s[j], hp.fb3));
+                  b.s[j] = sn;
+                  acc_b += (double)fabsf(sn);
+                }
               }
               if (hp.has_m) {
                 if constexpr (MK == KAON_M_BF16) {
-                  const float mo = pnm_decode<MK>(d.m, nullptr, e + k, r, bsh);
-                  tr.mp[k] = round_bf16(__fmaf_rn(round_bf16(y), hp.ftb, round_bf16(__fmul_rn(mo, hp.fb1))));
+                  tr.mp[k] = round_bf16(__fmaf_rn(round_bf16(y), hp.ftb, round_bf16(__fmul_rn(mo[k], hp.fb1))));
                 } else if constexpr (MK == KAON_M_4BIT) {
-                  const float mo = pnm_decode<MK>(d.m, d.m_scale, e + k, r, bsh);
-                  tr.mp[k] = lerp_torch(mo, hp.d_is_one ? y : __fmul_rn(y, hp.fd), hp.w1, hp.w1m1, hp.small_w1 != 0);
+                  tr.mp[k] = lerp_torch(mo[k], hp.d_is_one ? y : __fmul_rn(y, hp.fd), hp.w1, hp.w1m1, hp.small_w1 != 0);
                 } else if constexpr (MK == KAON_M_INT8 || MK == KAON_M_F32) {
-                  const float mo = pnm_decode<MK>(d.m, msc_rd, e + k, r, bsh);
-                  tr.mp[k] = __fmaf_rn(y, hp.ft, __fmul_rn(mo, hp.fb1));
+                  tr.mp[k] = __fmaf_rn(y, hp.ft, __fmul_rn(mo[k], hp.fb1));
                 }
               }
-              if (MODE == 0 && !fac) {   // the full second moment (also every 1-D tensor)
-                float* vv = d.stat_a + e + k;
-                *vv = __fmaf_rn(__fmul_rn(hp.fv, y), y, __fmul_rn(*vv, hp.fb2));
-              }
+              if (MODE == 0 && full_v)   // the full second moment (also every 1-D tensor)
+                vv[k] = __fmaf_rn(__fmul_rn(hp.fv, y), y, __fmul_rn(vv[k], hp.fb2));
             } else {
               tr.y[k] = yraw;
-              float numer = yraw;
-              if (hp.has_m) {
-                if constexpr (MK != KAON_M_NONE) numer = pnm_decode<MK>(d.m, d.m_scale, e + k, r, bsh);
-              }
+              const float numer = read_m ? mo[k] : yraw;
               float dl;
               if (fac) {
-                const float inv = fminf(__fdiv_rn(__fmul_rn(rfac[r], cfac[c]), hp.fd), hp.cap);
+                const float inv = fminf(div_by(__fmul_rn(rf, cfac[cl[k]]), hp.fd, rfd), hp.cap);
                 dl = __fmul_rn(numer, inv);
               } else {
-                dl = __fdiv_rn(numer, fmaxf(__fsqrt_rn(d.stat_a[e + k]), hp.floor_));
+                dl = __fdiv_rn(numer, fmaxf(__fsqrt_rn(vv[k]), hp.floor_));
               }
               dl = __fmul_rn(dl, hp.fdlr);
               if (hp.has_decay) dl = __fmaf_rn(pw[k], hp.fdecay, dl);
               const bool keep = __fmul_rn(dl, yraw) > 0.0f;
               if (MODE == 2) { if (keep) acc_a += 1.0; }
-              else if (hp.cautious) dl = keep ? __fdiv_rn(dl, denom) : 0.0f;
+              else if (hp.cautious) dl = keep ? div_by(dl, denom, rdenom) : 0.0f;
               tr.u[k] = dl;
             }
-            ++c;
+          }
+          if (MODE == 0) {
+            if (full_v) st8f(d.stat_a + e, cnt, vv);
+            if (dstat && dense) st8f(b.s + e, cnt, sv);
           }
         }
         if constexpr (MODE == 0) {
@@ -224,7 +271,8 @@ __global__ void __launch_bounds__(KP_THREADS) kp_sweep_kernel(PlanView pv, KpDev
             if constexpr (MK == KAON_M_INT8) {  // the row maxima first; the codes in the second sweep
               int cr = -1;
               float mx = 0.0f;
-              for (int k = 0; k < cnt; ++k) {
+#pragma unroll
+              for (int k = 0; k < 8; ++k) if (k < cnt) {
                 if (tr.rw[k] != cr) {
                   if (cr >= 0) atomicMax(rowmax + cr, __float_as_uint(mx));
                   cr = tr.rw[k];
@@ -247,7 +295,8 @@ __global__ void __launch_bounds__(KP_THREADS) kp_sweep_kernel(PlanView pv, KpDev
             const bool kahan = E::IS_BF16 && hp.kahan;
             unsigned char* pe = reinterpret_cast<unsigned char*>(d.p) + e * E::BYTES;
             uint16_t* she = kahan ? reinterpret_cast<uint16_t*>(d.shift) + e : nullptr;
-            for (int k = 0; k < cnt; ++k) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) if (k < cnt) {
               float p0 = pw[k];
               if (kahan) {
                 float sh = __uint_as_float((uint32_t)she[k] << 16);
@@ -267,12 +316,14 @@ __global__ void __launch_bounds__(KP_THREADS) kp_sweep_kernel(PlanView pv, KpDev
                 *reinterpret_cast<uint4*>(pe) = out;
                 mirror16(&pv.peers, pe, out);
               } else {
-                for (int k = 0; k < cnt; ++k) reinterpret_cast<uint16_t*>(pe)[k] = (uint16_t)(__float_as_uint(pw[k]) >> 16);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) if (k < cnt) reinterpret_cast<uint16_t*>(pe)[k] = (uint16_t)(__float_as_uint(pw[k]) >> 16);
                 mirror_copy(&pv.peers, pe, cnt * 2);
               }
             } else {
               float* pf = reinterpret_cast<float*>(pe);
-              for (int k = 0; k < cnt; ++k) pf[k] = pw[k];
+#pragma unroll
+              for (int k = 0; k < 8; ++k) if (k < cnt) pf[k] = pw[k];
               mirror_copy(&pv.peers, pf, cnt * 4);
             }
           }
