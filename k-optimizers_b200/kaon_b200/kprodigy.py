@@ -120,6 +120,13 @@ class KProdigy(FusedStepMixin, Optimizer):
         self._foreach_batch_cutoff = foreach_batch_cutoff
         self._foreach_stack_budget = foreach_stack_budget
         self._fused_init()
+        self._shard_group: Any = None
+
+    def set_shard_group(self, group: Any = True) -> None:
+        """ZeRO-1: this optimizer steps only the tensors its rank owns.  The distance estimate is one scalar
+        over ALL tensors, so the two sums behind it are added over the ranks of ``group`` (``True``: the default
+        process group) before every update of d - one all-reduce of three floats per scope and step."""
+        self._shard_group = group
 
     def get_d(self) -> float:
         """Current D estimate (effective learning rate) of the first group."""
@@ -241,6 +248,13 @@ class KProdigy(FusedStepMixin, Optimizer):
                                 continue
                             delta_numerator = np.float32(delta_numerator + np.float32(sums[2 * i] * const))
                             d_denom = np.float32(d_denom + sums[2 * i + 1])
+        if self._shard_group is not None and should_update_d and lr > 0.0:
+            import torch.distributed as dist
+            dev = self.param_groups[0]["params"][0].device
+            red = torch.tensor([float(delta_numerator), float(d_denom), 1.0 if seen else 0.0], dtype=torch.float32, device=dev)
+            dist.all_reduce(red, group=None if self._shard_group is True else self._shard_group)
+            vals = red.tolist()
+            delta_numerator, d_denom, seen = np.float32(vals[0]), np.float32(vals[1]), vals[2] > 0.0
         if should_update_d and lr > 0.0 and seen:
             denom_val = float(d_denom)
             if denom_val > 0.0:

@@ -41,7 +41,11 @@ def main():
         p.kaon_tensor_id = i
         params.append(p)
     kw = dict(lr=2e-4, momentum_dtype="4bit") if opt_name == "Lion" else dict(lr=1e-4, momentum_dtype="int8")
+    if opt_name == "KProdigy":   # the one optimizer with a scalar over all tensors: its sums are all-reduced
+        kw = dict(momentum_dtype="4bit", second_moment="factored", growth_rate=3.0)
     opt = getattr(kaon_b200, opt_name)(params, **kw)
+    if opt_name == "KProdigy" and world > 1:
+        opt.set_shard_group(True)
     opt.sr_seed = 3
     sw.attach(opt)
     torch.cuda.synchronize()
@@ -50,8 +54,10 @@ def main():
     sg = ShardedGrads(sw, SHAPES)
     for p, g in zip(params, sg.owned):
         p.grad = g                                   # the reduce-scatter's output buffer, for good
-    for step in range(4):
-        grads = [(torch.randn(s, generator=gen) * 1e-3).bfloat16() for s in SHAPES]
+    base = [torch.randn(s, generator=gen) * 1e-3 for s in SHAPES]   # a steady direction: KProdigy's d has something to find
+    for step in range(8 if opt_name == "KProdigy" else 4):
+        grads = [((b if opt_name == "KProdigy" else 0.0) + torch.randn(s, generator=gen) * (3e-4 if opt_name == "KProdigy" else 1e-3)).bfloat16()
+                 for b, s in zip(base, SHAPES)]
         for v, g in zip(sg.views, grads):            # "backward": every rank holds the same local gradient,
             v.copy_(g)                               # so the average is exact in bf16
         sg.reduce_scatter(average=True)

@@ -112,3 +112,29 @@ def test_two_ranks_fused_publish_equals_single_gpu(opt_name, tmp_path):
         for key, v in s1["state"][k].items():
             w = s2["state"][k][key]
             assert torch.equal(v, w) if torch.is_tensor(v) else v == w, (k, key)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_ranks_kprodigy_share_one_distance_estimate(tmp_path):
+    """KProdigy under ZeRO-1: each rank steps its own tensors, the two sums behind d are all-reduced, so both
+    ranks hold the same d as a single-GPU run (to the order of the fp32 additions) and the same weights."""
+    script = os.path.join(os.path.dirname(__file__), "_zero1_rank.py")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    out = str(tmp_path / "k")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+           "--master-addr", "127.0.0.1", "--master-port", "29534", script, "KProdigy", out]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    ref = subprocess.run([sys.executable, script, "KProdigy", out], env=dict(env, WORLD_SIZE="1", RANK="0", LOCAL_RANK="0"),
+                         capture_output=True, text=True, timeout=600)
+    assert ref.returncode == 0, ref.stdout[-3000:] + ref.stderr[-3000:]
+    s1, s2 = torch.load(out + ".w1.state.pt"), torch.load(out + ".w2.state.pt")
+    g1, g2 = s1["param_groups"][0], s2["param_groups"][0]
+    assert g1["k"] == g2["k"] == 8 and g1["d"] > g1["d0"]
+    for key in ("d", "d_max", "d_numerator"):
+        assert abs(g1[key] - g2[key]) <= 1e-5 * abs(g1[key]), (key, g1[key], g2[key])
+    single = torch.load(out + ".w1.r0.pt")
+    for r_ in range(2):
+        got = torch.load(out + f".w2.r{r_}.pt")
+        for i, (a, b) in enumerate(zip(single, got)):
+            assert (a.view(torch.int16) != b.view(torch.int16)).float().mean() < 2e-3, (r_, i)
