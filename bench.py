@@ -397,13 +397,26 @@ def measure(ctx: Ctx, workload: str, steps: int, warmup: int, e2e_steps: int = 0
         p = torch.nn.Parameter(sw.views[i], requires_grad=True)
         p.kaon_tensor_id = i  # global list position keys the SR stream: same weights for any N
         params.append(p)
-    opt = getattr(kaon_b200, opt_name)(params, **kw)
-    opt.sr_seed = 0
     sg = None
+    group_wave = None
     if args.reduce_scatter and world > 1:
         from kaon_b200.zero1 import ShardedGrads
-        sg = ShardedGrads(sw, shapes)              # full-list local gradients + the owner's reduced shard
+        # full-list local gradients + the owner's reduced shard, cut into waves: one collective and one
+        # parameter group per wave, so that wave w is stepped while wave w+1 is still being reduced
+        sg = ShardedGrads(sw, shapes, waves=max(1, args.waves))
         fill_normal(sg.flat, 1e-3, outlier=bool(wopt.get("outlier")))
+        by_wave = {}
+        for p, i in zip(params, owned):
+            by_wave.setdefault(sg.wave_of[i], []).append(p)
+        group_wave = sorted(by_wave)
+        opt = getattr(kaon_b200, opt_name)([{"params": by_wave[w]} for w in group_wave], **kw)
+    else:
+        opt = getattr(kaon_b200, opt_name)(params, **kw)
+    opt.sr_seed = 0
+    if sg is not None and sg.waves > 1 and args.comm_sms > 0:
+        # the step kernels are persistent: leave the collective's CTAs somewhere to run beside them
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        getattr(opt, "inner", opt).sm_limit = max(1, sms - args.comm_sms)
     cos = wopt.get("cosine")
     state = {"k": 0}
 
@@ -416,10 +429,16 @@ def measure(ctx: Ctx, workload: str, steps: int, warmup: int, e2e_steps: int = 0
                 grp["lr"] = cos[1] + 0.5 * (cos[0] - cos[1]) * (1.0 + math.cos(math.pi * (k % cos[2]) / cos[2]))
         for p, g in zip(params, gv):
             p.grad = g
-        if sg is not None:
-            sg.reduce_scatter(average=True)
         if ev:
             ev[0].record()
+        if sg is not None:
+            works = sg.reduce_scatter_waves(average=True)      # asynchronous, back to back on NCCL's stream
+            stepper = getattr(opt, "inner", opt)
+
+            def wait_for_wave(gi, works=works):
+                if works[group_wave[gi]] is not None:
+                    works[group_wave[gi]].wait()                # orders this stream after wave gi's collective
+            stepper.before_group = wait_for_wave
         opt.step()
         if ev:
             ev[1].record()
@@ -570,7 +589,8 @@ def measure(ctx: Ctx, workload: str, steps: int, warmup: int, e2e_steps: int = 0
                                    "nccl all_gather_into_tensor after the step"),
                        "lr_schedule": "cosine 1e-4 -> 1e-5 over 50 steps" if cos else "constant",
                        "l2": f"inputs ({alg_bytes / 1e9:.1f} GB per step per GPU) larger than L2; no flush needed"},
-            "gradient_reduce_scatter": "inside every step" if sg is not None else "not part of the step",
+            "gradient_reduce_scatter": (f"inside every step, {sg.waves} waves overlapped with the step" if sg is not None
+                                        else "not part of the step"),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "frac_of_nominal_8TBs": achieved / 8000.0,
                          "peak_kind": f"{peak_kind} copy bandwidth",
@@ -681,6 +701,12 @@ def main():
     ap.add_argument("--no-gpu-bar", action="store_true")
     ap.add_argument("--gpu-bar", action="store_true", help="time the reference's own CUDA paths (needs baseline/_ref)")
     ap.add_argument("--gpu-bar-fused", action="store_true", help="with --gpu-bar: also the reference's Triton path")
+    ap.add_argument("--comm-sms", type=int, default=24,
+                    help="with --reduce-scatter in waves: multiprocessors left free of the (persistent) step kernels "
+                         "for the collective that runs beside them")
+    ap.add_argument("--waves", type=int, default=4,
+                    help="with --reduce-scatter: cut every rank's tensors into this many waves, each one collective "
+                         "and one parameter group, so the step of a wave overlaps the next wave's reduce-scatter")
     ap.add_argument("--reduce-scatter", action="store_true",
                     help="N>1: put the gradient reduce-scatter (NCCL, bf16 average) inside every step; the step "
                          "kernels then read the collective's output buffer")

@@ -421,6 +421,23 @@ int kaon_plan_debug_stall(kaon_plan* pl, int tensor, uint32_t spin_limit) {
 int64_t kaon_plan_device_bytes(const kaon_plan* pl) { return pl ? pl->device_bytes : 0; }
 int64_t kaon_plan_launch_count(const kaon_plan* pl) { return pl ? pl->launches : 0; }
 
+int kaon_plan_set_sm_limit(kaon_plan* pl, int sms) {
+  if (!pl || sms < 1) return fail(KAON_E_INVALID, "kaon_plan_set_sm_limit: null plan or sms < 1");
+  cudaDeviceProp prop;
+  cudaError_t ce = cudaGetDeviceProperties(&prop, pl->device);
+  if (ce != cudaSuccess) return cuda_fail(ce, "cudaGetDeviceProperties");
+  const int now = std::min(sms, prop.multiProcessorCount);
+  const int was = pl->sm_count;
+  if (now == was) return KAON_OK;
+  // every launch of the plan is sized in CTAs per multiprocessor: rescale what has been sized already
+  auto rescale = [&](int g) { return g > 0 ? std::max(1, (int)((long long)g * now / was)) : g; };
+  pl->grid = rescale(pl->grid);
+  pl->apply_grid = rescale(pl->apply_grid);
+  pl->stats_grid = rescale(pl->stats_grid);
+  pl->sm_count = now;
+  return KAON_OK;
+}
+
 int kaon_plan_set_peers(kaon_plan* pl, const int64_t* byte_delta, int n_peers) {
   if (!pl || n_peers < 0 || n_peers > KAON_MAX_PEERS || (n_peers > 0 && !byte_delta))
     return fail(KAON_E_INVALID, "kaon_plan_set_peers: bad arguments (at most 7 peers)");

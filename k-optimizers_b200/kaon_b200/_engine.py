@@ -191,6 +191,11 @@ class FusedStepMixin:
         self._t = 0                 # completed steps; the SR stream uses the 1-based index
         self.sr_seed: int | None = None  # None -> torch.initial_seed() at the first step
         self._mirrors: tuple[int, int, list[int]] | None = None
+        # called with the group index before that group's launches: lets a caller order the stream after
+        # whatever produces the group's gradients (a per-wave gradient reduce-scatter)
+        self.before_group = None
+        # multiprocessors the step launches are sized for (None: all); see kaon_plan_set_sm_limit
+        self.sm_limit: int | None = None
 
     def set_weight_mirrors(self, base_ptr: int, nbytes: int, byte_deltas: list[int]) -> None:
         """Fuse the ZeRO-1 publish into the step: every weight written inside
@@ -257,6 +262,8 @@ class FusedStepMixin:
                 self._plan_created(pl, plist, [state_of(p) for p in plist])
                 if self._mirrors is not None:
                     pl.set_peers(*self._mirrors)
+                if self.sm_limit is not None:
+                    L.check(L.lib().kaon_plan_set_sm_limit(pl.handle, int(self.sm_limit)))
                 self._plans[key] = pl
                 self._plan_members[key] = sig
             plans.append(pl)
@@ -266,6 +273,8 @@ class FusedStepMixin:
         state_of = state_of or (lambda p: self.state[p])
         self._t += 1
         for gi, group in enumerate(self.param_groups):
+            if self.before_group is not None:
+                self.before_group(gi)
             for pl in self._group_plans(gi, group, state_of):
                 with torch.cuda.device(pl.device):
                     stream = torch.cuda.current_stream(pl.device).cuda_stream

@@ -107,41 +107,90 @@ class ShardedWeights:
 
 
 class ShardedGrads:
-    """Gradients of the whole list in the weights' layout, and their reduce-scatter into this rank's
-    shard: the front half of the sharded step.  ``views[i]`` is where backward leaves tensor i's local
-    gradient; after ``reduce_scatter()`` ``owned[k]`` holds the reduced gradient of the k-th owned
-    tensor, inside the collective's own output buffer, which is what the step kernels read (the
-    gradient pointers never change, so the plan's pointer column is uploaded once)."""
+    """Gradients of the whole list and their reduce-scatter into this rank's shard: the front half of the
+    sharded step.  ``views[i]`` is where backward leaves tensor i's local gradient; after the reduce-scatter
+    ``owned[k]`` holds the reduced gradient of the k-th owned tensor, inside the collective's own output
+    buffer, which is what the step kernels read (the gradient pointers never change, so the plan's pointer
+    column is uploaded once).
 
-    def __init__(self, weights: ShardedWeights, shapes, dtype=None):
+    ``waves > 1`` cuts every rank's tensors (in list order) into that many consecutive waves of about equal
+    size and lays the buffers out wave by wave (wave w: ``[rank 0's part | rank 1's part | ...]``, parts
+    padded to the longest), so that each wave is ONE contiguous reduce-scatter.  ``wave_of[i]`` names tensor
+    i's wave; ``reduce_scatter_waves()`` issues them back to back and returns their handles, so a step
+    that waits per wave (one parameter group per wave) runs wave w while wave w+1 is still on the wire."""
+
+    def __init__(self, weights: ShardedWeights, shapes, dtype=None, waves: int = 1):
         import torch
         sw = self.weights = weights
         dtype = dtype or sw.flat.dtype
-        self.flat = torch.zeros(sw.world * sw.part.shard_len, dtype=dtype, device=sw.flat.device)
-        self.shard = (self.flat if sw.world == 1 else
-                      torch.zeros(sw.part.shard_len, dtype=dtype, device=sw.flat.device))
+        world, W = sw.world, max(1, int(waves))
+        sizes = [math.prod(s) for s in shapes]
+        pad = lambda n: (n + ALIGN - 1) // ALIGN * ALIGN  # noqa: E731
+        # waves per rank: consecutive owned tensors, cut where the running size passes w/W of the rank's load
+        self.wave_of = [0] * len(shapes)
+        wave_len = [0] * W                      # longest part of each wave over the ranks
+        off_in_wave = [0] * len(shapes)
+        for r in range(world):
+            owned = sw.part.owned(r)
+            total = sum(pad(sizes[i]) for i in owned)
+            run, cur = 0, [0] * W
+            for i in owned:
+                w = min(W - 1, run * W // total) if total else 0
+                self.wave_of[i] = w
+                off_in_wave[i] = cur[w]
+                cur[w] += pad(sizes[i])
+                run += pad(sizes[i])
+            wave_len = [max(a, b) for a, b in zip(wave_len, cur)]
+        self.waves = W
+        self.wave_len = wave_len
+        wave_base = [0] * (W + 1)               # offset of each wave inside a shard
+        for w in range(W):
+            wave_base[w + 1] = wave_base[w] + wave_len[w]
+        self._wave_base = wave_base
+        shard_len = wave_base[W]
+        self.flat = torch.zeros(world * shard_len, dtype=dtype, device=sw.flat.device)
+        self.shard = (self.flat if world == 1 else torch.zeros(shard_len, dtype=dtype, device=sw.flat.device))
         self.views, self.owned = [], []
         for i, s in enumerate(shapes):
-            n = math.prod(s)
-            start = sw.part.owner[i] * sw.part.shard_len + sw.part.offset[i]
+            n, w, r = sizes[i], self.wave_of[i], sw.part.owner[i]
+            start = world * wave_base[w] + r * wave_len[w] + off_in_wave[i]
             self.views.append(self.flat[start:start + n].view(s))
-            if sw.part.owner[i] == sw.rank:
-                self.owned.append(self.shard[sw.part.offset[i]:sw.part.offset[i] + n].view(s))
+            if r == sw.rank:
+                o = (start if world == 1 else wave_base[w] + off_in_wave[i])
+                self.owned.append(self.shard[o:o + n].view(s))
 
-    def reduce_scatter(self, average: bool = True, async_op: bool = False):
+    def _wave_buffers(self, w: int):
+        world, b, n = self.weights.world, self._wave_base[w], self.wave_len[w]
+        return self.shard[b:b + n], self.flat[world * b:world * (b + n)]
+
+    def reduce_scatter_wave(self, w: int, average: bool = True, async_op: bool = False):
         import torch.distributed as dist
         sw = self.weights
-        if sw.world == 1:
+        if sw.world == 1 or self.wave_len[w] == 0:
             return None
+        out, inp = self._wave_buffers(w)
         if dist.get_backend(sw.group) == "gloo":
-            # gloo (CPU tests of the host flow) has no reduce-scatter: all-reduce, keep this rank's slice
-            dist.all_reduce(self.flat, group=sw.group)
-            self.shard.copy_(self.flat[sw.rank * sw.part.shard_len:(sw.rank + 1) * sw.part.shard_len])
+            # gloo (CPU tests of the host flow) has no reduce-scatter: all-reduce, keep this rank's part
+            dist.all_reduce(inp, group=sw.group)
+            n = self.wave_len[w]
+            out.copy_(inp[sw.rank * n:(sw.rank + 1) * n])
             if average:
-                self.shard.div_(sw.world)
+                out.div_(sw.world)
             return None
         op = dist.ReduceOp.AVG if average else dist.ReduceOp.SUM
-        return dist.reduce_scatter_tensor(self.shard, self.flat, op=op, group=sw.group, async_op=async_op)
+        return dist.reduce_scatter_tensor(out, inp, op=op, group=sw.group, async_op=async_op)
+
+    def reduce_scatter(self, average: bool = True, async_op: bool = False):
+        """All waves, in order; with one wave (the default) this is a single collective."""
+        last = None
+        for w in range(self.waves):
+            last = self.reduce_scatter_wave(w, average=average, async_op=async_op)
+        return last
+
+    def reduce_scatter_waves(self, average: bool = True):
+        """Issue every wave's collective asynchronously; ``handles[w].wait()`` orders the current stream after
+        wave w (``None`` for an empty wave or a single rank)."""
+        return [self.reduce_scatter_wave(w, average=average, async_op=True) for w in range(self.waves)]
 
 
 # ---- checkpoints of a sharded optimizer in the single-process layout ----

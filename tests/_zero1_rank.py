@@ -22,8 +22,11 @@ SHAPES_STREAM = [(640, 256), (64, 32, 4, 4), (1280,), (512, 640), (336, 80), (3,
 def main():
     global SHAPES
     opt_name, out = sys.argv[1], sys.argv[2]
+    waves = 1
     if opt_name.endswith("-stream"):
         opt_name, SHAPES = opt_name[:-len("-stream")], SHAPES_STREAM
+    if opt_name.endswith("-waves"):   # the gradient reduce-scatter in three waves, one parameter group per wave
+        opt_name, waves = opt_name[:-len("-waves")], 3
     world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
@@ -43,7 +46,12 @@ def main():
     kw = dict(lr=2e-4, momentum_dtype="4bit") if opt_name == "Lion" else dict(lr=1e-4, momentum_dtype="int8")
     if opt_name == "KProdigy":   # the one optimizer with a scalar over all tensors: its sums are all-reduced
         kw = dict(momentum_dtype="4bit", second_moment="factored", growth_rate=3.0)
-    opt = getattr(kaon_b200, opt_name)(params, **kw)
+    sg = ShardedGrads(sw, SHAPES, waves=waves)
+    by_wave = {}
+    for p, i in zip(params, owned):
+        by_wave.setdefault(sg.wave_of[i], []).append(p)
+    group_wave = sorted(by_wave)
+    opt = getattr(kaon_b200, opt_name)([{"params": by_wave[w]} for w in group_wave] if waves > 1 else params, **kw)
     if opt_name == "KProdigy" and world > 1:
         opt.set_shard_group(True)
     opt.sr_seed = 3
@@ -51,7 +59,6 @@ def main():
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    sg = ShardedGrads(sw, SHAPES)
     for p, g in zip(params, sg.owned):
         p.grad = g                                   # the reduce-scatter's output buffer, for good
     base = [torch.randn(s, generator=gen) * 1e-3 for s in SHAPES]   # a steady direction: KProdigy's d has something to find
@@ -60,7 +67,11 @@ def main():
                  for b, s in zip(base, SHAPES)]
         for v, g in zip(sg.views, grads):            # "backward": every rank holds the same local gradient,
             v.copy_(g)                               # so the average is exact in bf16
-        sg.reduce_scatter(average=True)
+        if waves > 1:
+            works = sg.reduce_scatter_waves(average=True)
+            opt.before_group = lambda gi, works=works: works[group_wave[gi]].wait() if works[group_wave[gi]] is not None else None
+        else:
+            sg.reduce_scatter(average=True)
         opt.step()
         sw.publish()
     torch.cuda.synchronize()

@@ -102,6 +102,43 @@ def test_reduce_scatter_feeds_owned_gradients_gloo_world2():
     mp.spawn(_grads_worker, args=(2, _free_port(), shapes), nprocs=2, join=True)
 
 
+def _waves_worker(rank, world, port, shapes, waves):
+    from kaon_b200.zero1 import ShardedGrads
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        sw = ShardedWeights(shapes, world, rank, torch.float32, torch.device("cpu"))
+        sg = ShardedGrads(sw, shapes, waves=waves)
+        assert sg.waves == waves and len(sg.wave_of) == len(shapes) and set(sg.wave_of) <= set(range(waves))
+        # every rank's owned tensors are cut into consecutive waves
+        for r in range(world):
+            ws = [sg.wave_of[i] for i in sw.part.owned(r)]
+            assert ws == sorted(ws), (r, ws)
+        # no two gradient views overlap
+        spans = sorted((v.data_ptr(), v.data_ptr() + v.numel() * 4) for v in sg.views)
+        assert all(a[1] <= b[0] for a, b in zip(spans, spans[1:]))
+        for i, v in enumerate(sg.views):
+            v.fill_(float((rank + 1) * (i + 1)))
+        mean_factor = sum(r + 1 for r in range(world)) / world
+        owned = sw.part.owned(rank)
+        done = set()
+        for w in range(waves):                     # wave by wave: only that wave's tensors are reduced
+            sg.reduce_scatter_wave(w, average=True)
+            done.add(w)
+            for g, i in zip(sg.owned, owned):
+                if sg.wave_of[i] in done:
+                    assert torch.all(g == mean_factor * (i + 1)), (rank, w, i)
+                else:
+                    assert torch.all(g == 0.0), (rank, w, i)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_reduce_scatter_in_waves_gloo_world2():
+    shapes = [(7, 5), (300,), (64, 64), (3,), (128, 2), (33, 9), (40, 40), (17,), (256, 8), (5, 5, 3, 3)]
+    mp.spawn(_waves_worker, args=(2, _free_port(), shapes, 3), nprocs=2, join=True)
+
+
 def _fake_state(i, shape):
     """What a quantised-momentum optimizer keeps for tensor i (values recognisable by i)."""
     n = math.prod(shape)
