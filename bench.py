@@ -701,7 +701,7 @@ def main():
     ap.add_argument("--no-gpu-bar", action="store_true")
     ap.add_argument("--gpu-bar", action="store_true", help="time the reference's own CUDA paths (needs baseline/_ref)")
     ap.add_argument("--gpu-bar-fused", action="store_true", help="with --gpu-bar: also the reference's Triton path")
-    ap.add_argument("--comm-sms", type=int, default=24,
+    ap.add_argument("--comm-sms", type=int, default=48,
                     help="with --reduce-scatter in waves: multiprocessors left free of the (persistent) step kernels "
                          "for the collective that runs beside them")
     ap.add_argument("--waves", type=int, default=4,

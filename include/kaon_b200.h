@@ -173,9 +173,11 @@ int kaon_plan_kept_counts(kaon_plan* plan, uint32_t* host_out, int n, void* stre
  * before a barrier that follows this step on every rank's stream.  n_peers = 0 switches mirroring off. */
 #define KAON_MAX_PEERS 7
 int kaon_plan_set_peers(kaon_plan* plan, const int64_t* byte_delta, int n_peers);
-/* Size every launch of the plan for `sms` multiprocessors instead of all of the device's (clamped to the
- * device).  The step kernels are persistent - their CTAs hold a multiprocessor until the launch ends - so a
- * collective that should run beside a step (the next wave's gradient reduce-scatter) needs some left free. */
+/* Keep the step kernels of the plan off all but `sms` multiprocessors (at least half of the device's; the Lion
+ * and Adakaon step kernels honour it).  They are persistent - their CTAs hold every register of a
+ * multiprocessor until the launch ends - so a collective that should run beside a step (the next wave's
+ * gradient reduce-scatter) finds no room unless some multiprocessors are left empty: CTAs that land on the
+ * others leave before claiming work. */
 int kaon_plan_set_sm_limit(kaon_plan* plan, int sms);
 
 /* ---- optimizer steps ---- */

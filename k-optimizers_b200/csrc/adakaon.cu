@@ -644,6 +644,7 @@ __global__ void __launch_bounds__(STT, 4) ada_stats_kernel(PlanView pv, AdaDev h
   __shared__ double red[STT / 32];
   __shared__ int next_s[2];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (on_reserved_sm(pv.sm_reserve)) return;
   auto claim_next = [&](int slot) {
     if (tid == 0) {
       const unsigned st = *reinterpret_cast<volatile unsigned*>(pv.status);
@@ -1790,6 +1791,7 @@ __global__ void __launch_bounds__(AT, 1) adakaon_kernel(PlanView pv, AdaDev hp, 
   // COUNT/APPLY/FLAT put cfac / the flat buffer after them.
   AdaSmem sm_stats{mean_s, rfac_s, rowmax_s, scale_s, reinterpret_cast<float*>(mbase), red, part_s};
   AdaSmem sm_rows{mean_s, rfac_s, rowmax_s, scale_s, reinterpret_cast<float*>(mbase + (size_t)nbuf * mcap), red, part_s};
+  if (on_reserved_sm(pv.sm_reserve)) return;
   auto claim_next = [&](int slot) {
     if (tid == 0) {
       const unsigned s = *reinterpret_cast<volatile unsigned*>(pv.status);
@@ -1914,6 +1916,7 @@ __global__ void __launch_bounds__(APPLY_THREADS, 4) adakaon_apply_kernel(PlanVie
   unsigned char* p_s = dyn + (size_t)APPLY_CAP * E::BYTES;
   unsigned char* m_s = dyn + (size_t)2 * APPLY_CAP * E::BYTES;
   const int tid = threadIdx.x;
+  if (on_reserved_sm(pv.sm_reserve)) return;
   auto claim_next = [&](int slot) {
     if (tid == 0) {
       const unsigned st = *reinterpret_cast<volatile unsigned*>(pv.status);

@@ -149,6 +149,16 @@ __device__ __forceinline__ float group_max(float v, int width) {
   return v;
 }
 
+// True for a CTA that landed on one of the `reserve` multiprocessors with the highest ids: it should leave
+// before claiming work (work is claimed from a counter, so the CTAs that stay do all of it).
+__device__ __forceinline__ bool on_reserved_sm(unsigned reserve) {
+  if (reserve == 0u) return false;
+  unsigned smid, nsm;
+  asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+  asm volatile("mov.u32 %0, %%nsmid;" : "=r"(nsm));
+  return reserve * 2u <= nsm && smid + reserve >= nsm;
+}
+
 // ----------------------------------------------------------------------------- bounded wait
 
 // Spin until *flag >= target or the limit runs out; on timeout records `code` in the status word.

@@ -117,6 +117,8 @@ struct PlanView {
   unsigned char* codes;    // 2 bits per element
   Peers peers;             // n == 0: no mirrors
   unsigned spin_limit;     // polls a completion-counter wait makes before it gives up (0: the default)
+  unsigned sm_reserve;     // multiprocessors (the highest ids) whose CTAs leave at once, so that a collective's
+                           // CTAs find them empty beside the persistent step (0: none)
 };
 
 }  // namespace kaon

@@ -724,6 +724,7 @@ __global__ void __launch_bounds__(NTHREADS, 4) lion_kernel(PlanView pv, LionDev 
   unsigned char* g_s = dyn;
   unsigned char* m_s = dyn + (size_t)CAP * Elems<PT>::BYTES;
   const int tid = threadIdx.x;
+  if (on_reserved_sm(pv.sm_reserve)) return;
   auto claim_next = [&](int slot) {
     if (tid == 0) {
       const unsigned st = *reinterpret_cast<volatile unsigned*>(pv.status);

@@ -423,18 +423,9 @@ int64_t kaon_plan_launch_count(const kaon_plan* pl) { return pl ? pl->launches :
 
 int kaon_plan_set_sm_limit(kaon_plan* pl, int sms) {
   if (!pl || sms < 1) return fail(KAON_E_INVALID, "kaon_plan_set_sm_limit: null plan or sms < 1");
-  cudaDeviceProp prop;
-  cudaError_t ce = cudaGetDeviceProperties(&prop, pl->device);
-  if (ce != cudaSuccess) return cuda_fail(ce, "cudaGetDeviceProperties");
-  const int now = std::min(sms, prop.multiProcessorCount);
-  const int was = pl->sm_count;
-  if (now == was) return KAON_OK;
-  // every launch of the plan is sized in CTAs per multiprocessor: rescale what has been sized already
-  auto rescale = [&](int g) { return g > 0 ? std::max(1, (int)((long long)g * now / was)) : g; };
-  pl->grid = rescale(pl->grid);
-  pl->apply_grid = rescale(pl->apply_grid);
-  pl->stats_grid = rescale(pl->stats_grid);
-  pl->sm_count = now;
+  // Launches keep their size; the CTAs that land on the multiprocessors with the highest ids leave at once
+  // (work is claimed from a counter, so the others do all of it) and those multiprocessors stay empty.
+  pl->view.sm_reserve = sms < pl->sm_count ? (unsigned)(pl->sm_count - sms) : 0u;
   return KAON_OK;
 }
 
