@@ -131,7 +131,7 @@ __device__ __forceinline__ void pnm_write(const PnmDev& hp, const DevTensor& d, 
 // ----------------------------------------------------------------------------- factored tensors
 
 template <typename PT, int MK, bool APPLY>
-__global__ void __launch_bounds__(PT_THREADS) pnm_pass_kernel(PlanView pv, PnmDev hp, PnmView x) {
+__global__ void __launch_bounds__(PT_THREADS, 3) pnm_pass_kernel(PlanView pv, PnmDev hp, PnmView x) {
   using E = Elems<PT>;
   __shared__ double red_d[PT_THREADS / 32];
   __shared__ unsigned red_u[PT_THREADS / 32];

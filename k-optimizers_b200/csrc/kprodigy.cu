@@ -116,7 +116,7 @@ __global__ void __launch_bounds__(KP_THREADS) kp_prep_kernel(PlanView pv, KpView
 // MODE 0: pass 1 (statistics, moments).  MODE 1: pass 1's second sweep for int8 (codes and scales).
 // MODE 2: pass 2 COUNT (cautious kept count).  MODE 3: pass 2 weight write.
 template <typename PT, int MK, int MODE>
-__global__ void __launch_bounds__(KP_THREADS) kp_sweep_kernel(PlanView pv, KpDev hp, KpView x) {
+__global__ void __launch_bounds__(KP_THREADS, 4) kp_sweep_kernel(PlanView pv, KpDev hp, KpView x) {
   using E = Elems<PT>;
   __shared__ double red_a[KP_THREADS / 32], red_b[KP_THREADS / 32];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
