@@ -49,6 +49,7 @@ WORKLOADS = {
     "adakaon_int8_unet2p6b": ("Adakaon", ADAKAON_KW, "unet_2p6b", 8.015, {"outlier": True, "traffic_bpp": 13.78}),
     "adakaon_int8_sample": ("Adakaon", ADAKAON_KW, "unet_sample", 8.015, {"outlier": True}),
     "adakaon_int8_mid": ("Adakaon", ADAKAON_KW, "unet_mid", 8.015, {"outlier": True}),
+    "adakaon_int8_mid_odd": ("Adakaon", ADAKAON_KW, "unet_mid_odd", 8.015, {"outlier": True}),
     "nekaon4bit_unet2p6b": ("Nekaon", NEKAON_KW, "unet_2p6b", 7.073, {"cosine": (1e-4, 1e-5, 50), "steps": 50,
                                                                        "traffic_bpp": 14.38}),
     "nekaon4bit_sample": ("Nekaon", NEKAON_KW, "unet_sample", 7.073, {"cosine": (1e-4, 1e-5, 50)}),

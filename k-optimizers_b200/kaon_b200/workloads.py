@@ -52,9 +52,16 @@ def unet_mid() -> list[tuple[int, ...]]:
     return shapes + [(1280, 1280, 3, 3)] * 4
 
 
+def unet_mid_odd() -> list[tuple[int, ...]]:
+    """``unet_mid`` plus the odd tensors a real UNet has at its ends: a [320,4,3,3] input convolution (rows
+    of 36 elements), a [4,320,3,3] output convolution, a [333,77] table - shapes that cannot take the
+    streaming launches and must not take the rest of the list off them."""
+    return unet_mid() + [(320, 4, 3, 3), (4, 320, 3, 3), (333, 77)]
+
+
 def numel(shapes) -> int:
     return sum(math.prod(s) for s in shapes)
 
 
 WORKLOADS = {"unet_2p6b": unet_2p6b, "dit_11b": dit_11b, "dit_block": dit_block, "unet_sample": unet_sample,
-             "unet_mid": unet_mid}
+             "unet_mid": unet_mid, "unet_mid_odd": unet_mid_odd}
