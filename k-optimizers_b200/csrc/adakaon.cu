@@ -973,6 +973,9 @@ __device__ void ada_rows(const PlanView& pv, const AdaDev& hp, const Task& t, St
   const int C = d.cols;
   const int nrows = t.n / C;
   const bool gc = hp.gc != 0 && !MUON;
+  // AdaMuon with gradient centralization: the statistics run on the orthogonalised matrix, which is not
+  // centralised; the cautious mask compares with the CENTRALISED raw gradient (row means in the scratch)
+  const bool gcr = hp.gc != 0 && MUON;
   const float* scal = pv.aux + aux_scal(d);
   const float rowmean = __ldcg(scal + 0);
   Chain ch;
@@ -1028,7 +1031,7 @@ __device__ void ada_rows(const PlanView& pv, const AdaDev& hp, const Task& t, St
       const int r = tid + j * AT;
       if (r < nrc) {
         const int row = t.row0 + c0 + r;
-        if (gc) pre_mu[j] = __ldcg(pv.aux + aux_mean(d) + row);
+        if (gc || gcr) pre_mu[j] = __ldcg(pv.aux + aux_mean(d) + row);
         pre_row[j] = __ldcg(d.stat_a + row);
         if constexpr (MK == KAON_M_INT8) {
           pre_sc[j] = d.m_scale[row];
@@ -1095,6 +1098,10 @@ __device__ void ada_rows(const PlanView& pv, const AdaDev& hp, const Task& t, St
         if (MUON) E::load8(st.m_s + (size_t)v * 8 * E::BYTES, raw);
         const int r = row_of((unsigned)v * 8u, d);
         const float rf = sm.rfac_s[r], mu = sm.mean_s[r];
+        if (MUON && gcr) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) raw[k] = centered<PT>(raw[k], mu, true);
+        }
         const float4 c0 = *reinterpret_cast<const float4*>(cfac_s + (v * 8 - r * C));
         const float4 c1 = *reinterpret_cast<const float4*>(cfac_s + (v * 8 - r * C) + 4);
         const float cf[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
@@ -1147,6 +1154,10 @@ __device__ void ada_rows(const PlanView& pv, const AdaDev& hp, const Task& t, St
       int rl[8];
 #pragma unroll
       for (int k = 0; k < 8; ++k) rl[k] = row_uniform ? row_of((unsigned)v * 8u, d) : row_of((unsigned)(v * 8 + min(k, max(cnt - 1, 0))), d);
+      if (MUON && gcr) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) raw[k] = (k < cnt) ? centered<PT>(raw[k], sm.mean_s[rl[k]], true) : 0.0f;
+      }
       // old momentum
       if constexpr (MK == KAON_M_4BIT) {
         decode8<MK>(st.m_s, v, cnt, cnt > 0 ? sm.scale_s[d.bshift >= 31 ? 0 : (v >> (d.bshift - 3))] : 1.0f, mo);
@@ -1376,6 +1387,9 @@ __device__ void ada_stream(const PlanView& pv, const AdaDev& hp, const Task& t, 
   const int C = d.cols;
   const int nrows = t.n / C;
   const bool gc = hp.gc != 0 && !MUON;
+  // AdaMuon with gradient centralization: the statistics run on the orthogonalised matrix, which is not
+  // centralised; the cautious mask compares with the CENTRALISED raw gradient (row means in the scratch)
+  const bool gcr = hp.gc != 0 && MUON;
   // AdaMuon: the chain runs on the orthogonalised momentum, the cautious mask on the raw gradient
   const unsigned char* sig = MUON ? reinterpret_cast<const unsigned char*>(pv.signal[t.tensor]) : g;
   const float* scal = pv.aux + aux_scal(d);
@@ -1428,7 +1442,11 @@ __device__ void ada_stream(const PlanView& pv, const AdaDev& hp, const Task& t, 
 #pragma unroll
         for (int k = 0; k < 8; ++k) pc[k] = 0.0f;
       }
-      const float mu = gc ? __ldcg(mean + row) : 0.0f;
+      const float mu = (gc || gcr) ? __ldcg(mean + row) : 0.0f;
+      if (MUON && gcr) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) raw[k] = centered<PT>(raw[k], mu, true);
+      }
       const float rf = __ldcg(rfac + row);
       const float4 c0v = __ldcg(reinterpret_cast<const float4*>(cfac + col));
       const float4 c1v = __ldcg(reinterpret_cast<const float4*>(cfac + col + 4));
@@ -1934,6 +1952,9 @@ __global__ void __launch_bounds__(APPLY_THREADS, 4) adakaon_apply_kernel(PlanVie
   SrStream s_clb{Philox{hp.k0, hp.k1}, hp.step, KAON_TAG_CLIMB};
   const bool sr = hp.sr != 0;
   const bool gc = hp.gc != 0 && !MUON;
+  // AdaMuon with gradient centralization: the statistics run on the orthogonalised matrix, which is not
+  // centralised; the cautious mask compares with the CENTRALISED raw gradient (row means in the scratch)
+  const bool gcr = hp.gc != 0 && MUON;
   while (cur < pv.n_tasks) {
     claim_next(slot ^ 1);
     const Task t = pv.tasks[cur];
@@ -2037,6 +2058,11 @@ __global__ void __launch_bounds__(APPLY_THREADS, 4) adakaon_apply_kernel(PlanVie
 #pragma unroll
             for (int j = 0; j < 4; ++j) gw[j] = sub_bf16x2(gw[j], mu2);
           }
+          uint32_t mu2r = 0u;   // AdaMuon: the centralization mean of the raw gradient's row, two bf16 copies
+          if (MUON && gcr) {
+            const float mur = __ldcg(mean + row);
+            mu2r = pack_bf16_rn(mur, mur);
+          }
           f32x2 P[4];
           if (need_p) {
             const uint4 pq = *reinterpret_cast<const uint4*>(psm + (size_t)vv * 4);
@@ -2108,7 +2134,8 @@ __global__ void __launch_bounds__(APPLY_THREADS, 4) adakaon_apply_kernel(PlanVie
             }
             DV[j] = fma2(P[j], LRWD, MN[j]);
             if constexpr (MUON) {  // the mask compares with the raw gradient, staged where the momentum goes otherwise
-              const uint32_t rw = reinterpret_cast<const uint32_t*>(m_s)[(size_t)vv * 4 + j];
+              uint32_t rw = reinterpret_cast<const uint32_t*>(m_s)[(size_t)vv * 4 + j];
+              if (gcr) rw = sub_bf16x2(rw, mu2r);
               unpack2(mul2(DV[j], pack2(bf16lo(rw), bf16hi(rw))), a[2 * j], a[2 * j + 1]);
             } else {
               unpack2(mul2(DV[j], G), a[2 * j], a[2 * j + 1]);
@@ -2295,7 +2322,7 @@ __global__ void __launch_bounds__(APPLY_THREADS, 4) adakaon_apply_kernel(PlanVie
         const int row = (int)row0 + r;
         const int col = (int)i - r * C;
         float gv[8], mo[8], mn[8], pc[8], dl[8];
-        const float mu = gc ? __ldcg(mean + row) : 0.0f;
+        const float mu = (gc || gcr) ? __ldcg(mean + row) : 0.0f;
         const float rf = __ldcg(rfac + row);
         const float4 c0v = __ldcg(reinterpret_cast<const float4*>(cfac + col));
         const float4 c1v = __ldcg(reinterpret_cast<const float4*>(cfac + col + 4));
@@ -2303,6 +2330,10 @@ __global__ void __launch_bounds__(APPLY_THREADS, 4) adakaon_apply_kernel(PlanVie
         S::load8(g_s + (size_t)vv * SB, gv);
         float raw[8];
         if (MUON) E::load8(m_s + (size_t)vv * GB, raw);
+        if (MUON && gcr) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) raw[k] = centered<PT>(raw[k], mu, true);
+        }
         if (need_p) E::load8(p_s + (size_t)vv * GB, pc);
         else {
 #pragma unroll

@@ -1,7 +1,8 @@
 // AdaMuon step for sm_100a (reference src/kaon/adamuon.py:327-352, 434-615).
 //
-// Per >=2-D tensor:  (1) EMA pre-pass: m <- lerp(decode(m), g, 1-b1), re-encode and store m, write the
-// fp32 pre-requant momentum as bf16 into the workspace;  (2) Newton-Schulz of that matrix on the tensor
+// Per >=2-D tensor:  (1) EMA pre-pass: m <- lerp(decode(m), g, 1-b1) with g optionally centralised (each
+// row less its mean, adamuon.py:334-335), re-encode and store m, write the fp32 pre-requant momentum as
+// bf16 into the workspace;  (2) Newton-Schulz of that matrix on the tensor
 // cores (ns.cu);  (3) the Adakaon STATS/FINAL/COUNT/APPLY work items with the orthogonalised matrix O as
 // the signal, no further momentum, scale 0.2*lr, and the cautious mask taken against the raw gradient.
 // 1-D tensors run the FLAT work item (Adam-style, momentum of the update) inside step (3)'s kernel.
@@ -22,11 +23,12 @@ constexpr int ET = 256;
 // Row-chunk items [t0, t1) of ONE tensor: gradient and momentum straight from global memory.
 template <typename PT, int MK>
 __global__ void __launch_bounds__(ET) muon_ema_kernel(PlanView pv, const Task* tasks, int t0, int t1,
-                                                      float w1, float w1m1, int small_w1,
+                                                      float w1, float w1m1, int small_w1, int gc,
                                                       __nv_bfloat16* x_out) {
   using E = Elems<PT>;
   __shared__ unsigned rowmax_s[MAX_TASK_ROWS];
   __shared__ float scale_s[MAX_TASK_ROWS];
+  __shared__ float mean_s[MAX_TASK_ROWS];  // centralization mean of each row of the item
   const int tid = threadIdx.x;
   for (int ti = t0 + blockIdx.x; ti < t1; ti += gridDim.x) {
     const Task t = tasks[ti];
@@ -37,9 +39,38 @@ __global__ void __launch_bounds__(ET) muon_ema_kernel(PlanView pv, const Task* t
     const int nvec = (n + 7) >> 3, nvec_pad = (nvec + 31) & ~31;
     const bool row_uniform = (C & 7) == 0;
     const unsigned char* mbase = reinterpret_cast<const unsigned char*>(d.m);
+    if (gc) {
+      // one warp per row; the mean also goes to the scratch, where the cautious mask of the weight stage
+      // finds it (the mask compares with the centralised gradient)
+      for (int r = tid >> 5; r < nrows; r += ET / 32) {
+        const unsigned char* rowp = g + (size_t)r * C * E::BYTES;
+        float sum = 0.0f;
+        if (row_uniform) {
+          for (int v = tid & 31; v < (C >> 3); v += 32) {
+            float x[8];
+            E::load8(rowp + (size_t)v * 8 * E::BYTES, x);
+            sum += ((x[0] + x[1]) + (x[2] + x[3])) + ((x[4] + x[5]) + (x[6] + x[7]));
+          }
+        } else {
+          for (int i = tid & 31; i < C; i += 32) sum += E::load1(rowp, i);
+        }
+        sum = warp_sum(sum);
+        const float mean = __fdiv_rn(sum, (float)C);
+        const float mu = E::IS_BF16 ? round_bf16(mean) : mean;
+        if ((tid & 31) == 0) { mean_s[r] = mu; pv.aux[aux_mean(d) + t.row0 + r] = mu; }
+      }
+      __syncthreads();
+    }
     auto m_new8 = [&](int v, int cnt, float mn[8]) {
       float gv[8], mo[8];
       load8_guard<PT>(g + (size_t)v * 8 * E::BYTES, cnt, gv);
+      if (gc) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float x = __fsub_rn(gv[k], mean_s[row_uniform ? row_of((unsigned)v * 8u, d) : row_of((unsigned)(v * 8 + min(k, max(cnt - 1, 0))), d)]);
+          gv[k] = E::IS_BF16 ? round_bf16(x) : x;
+        }
+      }
       if constexpr (MK == KAON_M_4BIT) {
         const long long blk = blk_of(d, t.e0 + (long long)v * 8);
         decode8<MK>(mbase + (t.e0 >> 1), v, cnt, d.m_scale[blk], mo);
@@ -148,7 +179,7 @@ __global__ void __launch_bounds__(ET) muon_ema_kernel(PlanView pv, const Task* t
   }
 }
 
-typedef void (*EmaKernel)(PlanView, const Task*, int, int, float, float, int, __nv_bfloat16*);
+typedef void (*EmaKernel)(PlanView, const Task*, int, int, float, float, int, int, __nv_bfloat16*);
 
 template <typename PT>
 static EmaKernel pick_ema_pt(int mk) {
@@ -217,7 +248,6 @@ extern "C" int kaon_adamuon_step(kaon_plan* pl, const kaon_adamuon_hparams* h, v
   if (int rc = check_device(pl)) return rc;
   if (h->bf16_method < KAON_W_NONE || h->bf16_method > KAON_W_KAHAN) return fail(KAON_E_UNSUPPORTED, "bf16_method %d", h->bf16_method);
   if (int rc = check_kahan(pl, h->bf16_method)) return rc;
-  if (h->gradient_centralization) return fail(KAON_E_UNSUPPORTED, "AdaMuon with gradient_centralization=True is not built (its default is off)");
   if (!(h->clip_threshold > 0.0)) return fail(KAON_E_INVALID, "clip_threshold must be > 0");
   if (h->ns_steps < 1) return fail(KAON_E_INVALID, "ns_steps must be >= 1");
   const bool has_m = pl->momentum_kind != KAON_M_NONE;
@@ -285,7 +315,7 @@ extern "C" int kaon_adamuon_step(kaon_plan* pl, const kaon_adamuon_hparams* h, v
     __nv_bfloat16* x0 = reinterpret_cast<__nv_bfloat16*>(ws + L.x0_off + (size_t)lane * L.lane_stride);
     const int t0 = pl->ema_begin[i], t1 = pl->ema_begin[i + 1];
     const int grid = std::min(t1 - t0, pl->sm_count * 8);
-    ek<<<grid, ET, 0, sl>>>(v, pl->d_tasks_ema, t0, t1, w1, w1 - 1.0f, w1 < 0.5f, x0);
+    ek<<<grid, ET, 0, sl>>>(v, pl->d_tasks_ema, t0, t1, w1, w1 - 1.0f, w1 < 0.5f, h->gradient_centralization != 0, x0);
     KAON_CUDA(cudaGetLastError());
     pl->launches += 1;
     long long nl = 0;
@@ -308,7 +338,7 @@ extern "C" int kaon_adamuon_step(kaon_plan* pl, const kaon_adamuon_hparams* h, v
   hp.lrwd = (float)(h->lr * h->weight_decay); hp.has_wd = h->weight_decay != 0.0;
   hp.upd_scale = (float)(0.2 * h->lr);  // _UPDATE_RMS * lr, product taken in double (adamuon.py:88, 489)
   hp.cautious = h->cautious != 0;
-  hp.gc = 0;
+  hp.gc = h->gradient_centralization != 0;  // the statistics of O ignore it; the mask centres the raw gradient
   hp.sr = h->bf16_method == KAON_W_SR && pl->param_dtype == KAON_DT_BF16;
   hp.kahan = h->bf16_method == KAON_W_KAHAN && pl->param_dtype == KAON_DT_BF16;
   hp.has_m = has_m;

@@ -45,6 +45,20 @@ SHAPES_LONG_1D = [(128, 256), (40000,), (96, 1024)]
 @pytest.mark.parametrize("dtype", ["bf16", "f32"])
 @pytest.mark.parametrize("kind", ["ragged", "stream", "long1d"])
 def test_adamuon_chain_vs_oracle_with_same_orthogonal_factor(md, method, wd, dtype, kind):
+    _chain_vs_oracle(md, method, wd, dtype, kind, False)
+
+
+@pytest.mark.parametrize("md,method,wd", [("int8", "none", 0.0), ("4bit", "stochastic_rounding", 0.05),
+                                          ("bfloat16", "none", 0.01), (None, "none", 0.0)])
+@pytest.mark.parametrize("dtype", ["bf16", "f32"])
+@pytest.mark.parametrize("kind", ["ragged", "stream"])
+def test_adamuon_with_gradient_centralization(md, method, wd, dtype, kind):
+    """Rows of the gradient less their mean go into the momentum (reference src/kaon/adamuon.py:334-335), and
+    the cautious mask compares with that centralised gradient; the statistics of O are untouched."""
+    _chain_vs_oracle(md, method, wd, dtype, kind, True)
+
+
+def _chain_vs_oracle(md, method, wd, dtype, kind, gc):
     import kaon_b200
     from _gpu import state_np, to_bits
     SHAPES = {"ragged": SHAPES_RAGGED, "stream": SHAPES_STREAM, "long1d": SHAPES_LONG_1D}[kind]  # noqa: N806
@@ -52,7 +66,8 @@ def test_adamuon_chain_vs_oracle_with_same_orthogonal_factor(md, method, wd, dty
     gen = torch.Generator().manual_seed(31)
     host = [(torch.randn(s, generator=gen) * 0.02).to(tdt) for s in SHAPES]
     params = [torch.nn.Parameter(h.clone().cuda()) for h in host]
-    kw = dict(lr=1e-3, betas=(0.95 if md else 0.0, 0.999), weight_decay=wd, ns_steps=2, bf16_method=method)
+    kw = dict(lr=1e-3, betas=(0.95 if md else 0.0, 0.999), weight_decay=wd, ns_steps=2, bf16_method=method,
+              gradient_centralization=gc)
     if md and "/" in md:   # the 4-bit codec with another block size
         md, blk = md.split("/")
         kw["momentum_4bit_block"] = int(blk)
@@ -62,7 +77,9 @@ def test_adamuon_chain_vs_oracle_with_same_orthogonal_factor(md, method, wd, dty
     opt.sr_seed = 8
     orc = ko.OracleAdaMuon([to_bits(h) for h in host], SHAPES, seed=8, **kw)
     for step in range(1, 4):
-        grads = [(torch.randn(s, generator=gen) * 1e-3).to(tdt) for s in SHAPES]
+        # with centralization on, a row offset of the size of the noise: means that matter
+        grads = [((torch.randn(s, generator=gen) + (torch.randn(s[0], *([1] * (len(s) - 1)), generator=gen) if gc else 0.0))
+                  * 1e-3).to(tdt) for s in SHAPES]
         for p, g in zip(params, grads):
             p.grad = g.clone().cuda()
         opt.step()
@@ -82,9 +99,25 @@ def test_adamuon_chain_vs_oracle_with_same_orthogonal_factor(md, method, wd, dty
                     assert rel_err(state_np(st, key), ot.state[key]) <= 1e-5, (step, i, key, SHAPES[i])
             if md in ("int8", "4bit"):
                 # >=2-D: EMA of the raw gradient, no reduction upstream -> identical codes and scales
-                if ot.rows:
+                if ot.rows and not gc:
                     assert np.array_equal(state_np(st, "m").view(np.uint8), ot.state["m"].view(np.uint8)), (step, i)
                     assert np.array_equal(state_np(st, "m_scale"), ot.state["m_scale"]), (step, i)
+                elif ot.rows:
+                    # the row mean is a sum in another order: a rare code one step off, and where that element
+                    # later carries its row's (or block's) absmax, the scale and with it more codes of that row
+                    a, b = state_np(st, "m"), ot.state["m"]
+                    if md == "4bit":
+                        unpack = lambda x: np.stack([x.view(np.uint8) & 15, x.view(np.uint8) >> 4], -1).astype(int)  # noqa: E731
+                        a, b = unpack(a), unpack(b)
+                    else:
+                        a, b = a.view(np.int8).astype(int), b.view(np.int8).astype(int)
+                    assert np.abs(a - b).max() <= 1, (step, i)
+                    units = ot.rows if md == "int8" else max(1, a.size // 128)
+                    bad_units = np.unique(np.nonzero((a != b).reshape(-1))[0] // (a.size // units)).size
+                    assert bad_units <= max(2, units // 50), (step, i, bad_units, units)
+                    sa, sb = state_np(st, "m_scale").reshape(-1), ot.state["m_scale"].reshape(-1)
+                    off = np.abs(sa - sb) > 2e-5 * np.abs(sb)
+                    assert off.sum() <= max(2, sa.size // 50) and np.abs(sa - sb).max() <= 0.2 * np.abs(sb).max(), (step, i)
                 else:
                     assert rel_err(state_np(st, "m_scale"), ot.state["m_scale"]) <= 2e-5
             got, want = to_bits(p), ot.p
