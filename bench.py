@@ -62,6 +62,7 @@ WORKLOADS = {
     "adapnm_4bit_mid": ("AdaPNM", dict(lr=1e-4, momentum_dtype="4bit"), "unet_mid", 7.6, {}),
     "kprodigy_default_mid": ("KProdigy", dict(), "unet_mid", 30.0, {}),
 }
+E2E_GROUPS = 16   # parameter groups of the end-to-end pipeline
 HEADLINE = "lion4bit_unet2p6b"
 RECORD = ["adakaon_int8_unet2p6b", "nekaon4bit_unet2p6b", "adamuon_int8_dit11b"]
 KERNEL_NAME = {"AdaMuon": "ns_gemm_kernel", "Lion": "lion_kernel<bf16,4bit>", "Adakaon": "adakaon_kernel<bf16,int8>",
@@ -488,44 +489,79 @@ def measure(ctx: Ctx, workload: str, steps: int, warmup: int, e2e_steps: int = 0
         host_w = torch.empty(sw.part.shard_len, dtype=torch.bfloat16, pin_memory=True)
         host_g.copy_(gsets[0][0])
         torch.cuda.synchronize()
-        # Three streams, as a training loop with a host-side gradient source would run it: the copy of
-        # step k+1's gradients to the device (s_in) and the read-back of step k's weights (s_out) travel in
-        # opposite directions over PCIe and overlap; the step itself waits for its gradients and for the
-        # previous read-back (which reads the weights the step is about to overwrite).
+        # Three streams, as a training loop with a host-side gradient source would run it, pipelined by
+        # parameter group: the owned tensors are cut into E2E_GROUPS contiguous slices of the shard, one
+        # parameter group each; slice j of step k+1's gradients goes up (s_in) while slice j of step k's
+        # weights comes down (s_out), in opposite directions over PCIe, and group j is stepped as soon as
+        # its gradients have landed and the previous read-back of its weights has finished.
         cur_s = torch.cuda.current_stream()
         s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
         nset = len(gsets)
-        ev_in = [torch.cuda.Event() for _ in range(nset)]
+        ngrp = max(1, min(E2E_GROUPS, len(params)))
+        bounds, chunks, acc, nxt = [], [[]], 0, 1
+        own_total = sum(p.numel() for p in params)
+        for p, i in zip(params, owned):
+            if acc >= nxt * own_total / ngrp and chunks[-1]:
+                chunks.append([])
+                nxt += 1
+            chunks[-1].append((p, i))
+            acc += p.numel()
+        for ch in chunks:
+            lo = min(sw.part.offset[i] for _, i in ch)
+            hi = max(sw.part.offset[i] + p.numel() for p, i in ch)
+            assert not bounds or lo >= bounds[-1][1], "the owned tensors are laid out in list order"
+            bounds.append((lo, hi))
+        bounds[0] = (0, bounds[0][1])
+        bounds[-1] = (bounds[-1][0], sw.part.shard_len)
+        ngrp = len(chunks)
+        opt_e = getattr(kaon_b200, opt_name)([{"params": [p for p, _ in ch]} for ch in chunks], **kw)
+        opt_e.sr_seed = 0
+        if world > 1 and fused_publish:
+            sw.attach(opt_e)
+        stepper = getattr(opt_e, "inner", opt_e)
+        ev_in = [[torch.cuda.Event() for _ in range(ngrp)] for _ in range(nset)]
         ev_step = [torch.cuda.Event() for _ in range(nset)]
-        ev_out = torch.cuda.Event()
+        ev_grp = [torch.cuda.Event() for _ in range(ngrp)]
+        ev_out = [torch.cuda.Event() for _ in range(ngrp)]
+        cur_buf = {"b": 0}
 
         def h2d(k):
             b_ = k % nset
             with torch.cuda.stream(s_in):
                 s_in.wait_event(ev_step[b_])      # the step that last read this gradient buffer has finished
-                gsets[b_][0].copy_(host_g, non_blocking=True)
-                ev_in[b_].record(s_in)
+                for j, (lo, hi) in enumerate(bounds):
+                    gsets[b_][0][lo:hi].copy_(host_g[lo:hi], non_blocking=True)
+                    ev_in[b_][j].record(s_in)
+
+        def group_ready(j):
+            cur_s.wait_event(ev_in[cur_buf["b"]][j])   # its gradients are on the device
+            cur_s.wait_event(ev_out[j])                # the weights it overwrites have been read back
+
+        def group_done(j):
+            ev_grp[j].record(cur_s)
+            lo, hi = bounds[j]
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_grp[j])
+                host_w[lo:hi].copy_(sw.shard[lo:hi], non_blocking=True)
+                ev_out[j].record(s_out)
+
+        stepper.before_group, stepper.after_group = group_ready, group_done
 
         def e2e_run(nsteps):
             h2d(0)
             for k in range(nsteps):
-                b_ = k % nset
+                b_ = cur_buf["b"] = k % nset
                 if k + 1 < nsteps and nset > 1:
                     h2d(k + 1)
-                cur_s.wait_event(ev_in[b_])
-                cur_s.wait_event(ev_out)
                 for p, g in zip(params, gsets[b_][1]):
                     p.grad = g
-                opt.step()
+                opt_e.step()
                 sw.publish()
                 ev_step[b_].record(cur_s)
-                with torch.cuda.stream(s_out):
-                    s_out.wait_event(ev_step[b_])
-                    host_w.copy_(sw.shard, non_blocking=True)
-                    ev_out.record(s_out)
                 if k + 1 < nsteps and nset == 1:
                     h2d(k + 1)
-            cur_s.wait_event(ev_out)
+            for j in range(ngrp):
+                cur_s.wait_event(ev_out[j])
 
         e2e_run(1)
         ctx.fence()
@@ -539,9 +575,12 @@ def measure(ctx: Ctx, workload: str, steps: int, warmup: int, e2e_steps: int = 0
         nbytes = sw.part.shard_len * 2 * world
         e2e = {"value": total / (ems * 1e-3), "unit": "params/s", "ms_per_step": ems, "steps": e2e_steps,
                "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes,
-               "pipeline": "gradients of step k+1 go up while the weights of step k come down (3 streams); "
-                           "the first upload and the last download are inside the timed region"}
-        del host_g, host_w
+               "pipeline": f"{ngrp} parameter groups: slice j of step k+1's gradients goes up while slice j of "
+                           "step k's weights comes down (3 streams); the first upload and the last download "
+                           "are inside the timed region"}
+        opt_e.check_device_status()
+        stepper.before_group = stepper.after_group = None
+        del host_g, host_w, opt_e
 
     ns_info = None
     if opt_name == "AdaMuon":

@@ -131,7 +131,7 @@ __device__ __forceinline__ void pnm_write(const PnmDev& hp, const DevTensor& d, 
 // ----------------------------------------------------------------------------- factored tensors
 
 template <typename PT, int MK, bool APPLY>
-__global__ void __launch_bounds__(PT_THREADS, 3) pnm_pass_kernel(PlanView pv, PnmDev hp, PnmView x) {
+__global__ void __launch_bounds__(PT_THREADS, 4) pnm_pass_kernel(PlanView pv, PnmDev hp, PnmView x) {
   using E = Elems<PT>;
   __shared__ double red_d[PT_THREADS / 32];
   __shared__ unsigned red_u[PT_THREADS / 32];
@@ -193,22 +193,24 @@ __global__ void __launch_bounds__(PT_THREADS, 3) pnm_pass_kernel(PlanView pv, Pn
           }
           pnm_decode8<MK>(pos, psc_rd, e, cnt, tr.rw, bsh, mpo);
           pnm_decode8<MK>(neg, nsc, e, cnt, tr.rw, bsh, mno);
-          auto chain = [&](int k, float rf, float mu) {
+          auto chain = [&](int k, float rf, float mu, float cf) {
             const float yk = pnm_centered<PT>(gx[k], mu, hp.gc != 0);
             const float mpn = __fmaf_rn(yk, hp.fw, __fmul_rn(mpo[k], hp.fb));
             const float pn = __fmul_rn(__fmaf_rn(mno[k], hp.c2, __fmul_rn(mpn, hp.c1)), hp.c3);
-            const float inv = __fmul_rn(__fmul_rn(rf, cfac[cl[k]]), hp.bc2);
+            const float inv = __fmul_rn(__fmul_rn(rf, cf), hp.bc2);
             tr.y[k] = yk; tr.mp[k] = mpn; tr.u[k] = __fmul_rn(pn, inv);
           };
           if (one_row) {
             const float rf = rfac[tr.rw[0]], mu = hp.gc ? mean[tr.rw[0]] : 0.0f;
+            float cf[8];
+            ld8f(cfac + cl[0], 8, cf);  // the eight column factors: two vector loads where the address allows
 #pragma unroll
-            for (int k = 0; k < 8; ++k) chain(k, rf, mu);
+            for (int k = 0; k < 8; ++k) chain(k, rf, mu, cf[k]);
           } else {
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
               tr.y[k] = 0.0f; tr.mp[k] = 0.0f; tr.u[k] = 0.0f;
-              if (k < cnt) chain(k, rfac[tr.rw[k]], hp.gc ? mean[tr.rw[k]] : 0.0f);
+              if (k < cnt) chain(k, rfac[tr.rw[k]], hp.gc ? mean[tr.rw[k]] : 0.0f, cfac[cl[k]]);
             }
           }
         } else {
@@ -216,11 +218,13 @@ __global__ void __launch_bounds__(PT_THREADS, 3) pnm_pass_kernel(PlanView pv, Pn
           for (int k = 0; k < 8; ++k) { tr.y[k] = 0.0f; tr.mp[k] = 0.0f; tr.u[k] = 0.0f; tr.rw[k] = 0; }
         }
         if constexpr (!APPLY) {
+          float s8 = 0.0f;  // the trip's eight squares in fp32, then one wide addition
 #pragma unroll
           for (int k = 0; k < 8; ++k) if (k < cnt) {
-            ss += (double)tr.u[k] * (double)tr.u[k];
+            s8 = __fmaf_rn(tr.u[k], tr.u[k], s8);
             kept += (__fmul_rn(tr.u[k], tr.y[k]) > 0.0f) ? 1u : 0u;
           }
+          ss += (double)s8;
           if constexpr (MK == KAON_M_INT8) {
             int cr = -1;
             float mx = 0.0f;

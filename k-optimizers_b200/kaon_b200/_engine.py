@@ -194,6 +194,9 @@ class FusedStepMixin:
         # called with the group index before that group's launches: lets a caller order the stream after
         # whatever produces the group's gradients (a per-wave gradient reduce-scatter)
         self.before_group = None
+        # called with the group index after that group's launches are enqueued: lets a caller record an
+        # event there (the group's weights are final on the stream) and start reading them back
+        self.after_group = None
         # multiprocessors the step launches are sized for (None: all); see kaon_plan_set_sm_limit
         self.sm_limit: int | None = None
 
@@ -280,6 +283,8 @@ class FusedStepMixin:
                     stream = torch.cuda.current_stream(pl.device).cuda_stream
                     if pl.set_grads(stream):
                         self._launch(pl, group, self._t, stream)
+            if self.after_group is not None:
+                self.after_group(gi)
 
     # ---- checkpoint extras: the stochastic-rounding stream position ----
     def _extra_state(self, sd: dict[str, Any]) -> dict[str, Any]:

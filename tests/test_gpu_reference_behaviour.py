@@ -296,3 +296,35 @@ def test_checkpoint_through_torch_save_keeps_dtypes_and_resumes_exactly(cls_name
     run(pc, oc, range(3, 5))
     for a, c in zip(pa, pc):
         assert torch.equal(a.detach(), c.detach())
+
+
+# ---- this package's own: the per-group hooks a pipelined caller hangs its events on ----
+
+def test_group_hooks_run_around_each_groups_launches_and_change_no_result():
+    """`before_group(i)` / `after_group(i)` are called once per parameter group and step, in order, around
+    that group's launches; a step cut into groups writes the same weights as the same list in one group
+    (the stochastic-rounding stream is keyed by the tensor's position in the whole list)."""
+    import kaon_b200
+    gen = torch.Generator().manual_seed(77)
+    host = [(torch.randn(s, generator=gen) * 0.02).bfloat16() for s in [(96, 128), (64,), (48, 16, 3, 3), (200, 40)]]
+    grads = [(torch.randn(h.shape, generator=gen) * 1e-3).bfloat16() for h in host]
+    out = []
+    for grouped in (False, True):
+        ps = [torch.nn.Parameter(h.clone().to(DEV)) for h in host]
+        arg = [{"params": ps[:1]}, {"params": ps[1:3]}, {"params": ps[3:]}] if grouped else ps
+        opt = kaon_b200.Lion(arg, lr=1e-3, momentum_dtype="4bit")
+        opt.sr_seed = 5
+        calls = []
+        opt.before_group = lambda gi: calls.append(("before", gi))
+        opt.after_group = lambda gi: calls.append(("after", gi))
+        for _ in range(2):
+            for p, g in zip(ps, grads):
+                p.grad = g.clone().to(DEV)
+            opt.step()
+        torch.cuda.synchronize()
+        opt.check_device_status()
+        n = 3 if grouped else 1
+        assert calls == [(w, gi) for gi in range(n) for w in ("before", "after")] * 2
+        out.append([p.detach().cpu() for p in ps])
+    for a, b in zip(*out):
+        assert torch.equal(a, b)
