@@ -30,7 +30,7 @@
 
 namespace kaon {
 
-constexpr int PNM_ITEM = 8192;
+constexpr int PNM_ITEM = 16384;
 constexpr int PT_THREADS = 256;
 
 struct PnmDev {
@@ -204,8 +204,28 @@ __global__ void __launch_bounds__(PT_THREADS, 4) pnm_pass_kernel(PlanView pv, Pn
             const float rf = rfac[tr.rw[0]], mu = hp.gc ? mean[tr.rw[0]] : 0.0f;
             float cf[8];
             ld8f(cfac + cl[0], 8, cf);  // the eight column factors: two vector loads where the address allows
+            // the same chain on pairs (each lane of a packed instruction is the scalar IEEE operation)
+            const f32x2 FW = pack2(hp.fw, hp.fw), FB = pack2(hp.fb, hp.fb), C1 = pack2(hp.c1, hp.c1);
+            const f32x2 C2 = pack2(hp.c2, hp.c2), C3 = pack2(hp.c3, hp.c3), BC2 = pack2(hp.bc2, hp.bc2);
+            const f32x2 RF = pack2(rf, rf), MUN = pack2(-mu, -mu);
 #pragma unroll
-            for (int k = 0; k < 8; ++k) chain(k, rf, mu, cf[k]);
+            for (int j = 0; j < 4; ++j) {
+              f32x2 y2 = pack2(gx[2 * j], gx[2 * j + 1]);
+              if (hp.gc) {
+                y2 = add2(y2, MUN);
+                if constexpr (E::IS_BF16) {
+                  const uint32_t w = pack_bf16_rn(y2.x, y2.y);
+                  y2 = pack2(bf16lo(w), bf16hi(w));
+                }
+              }
+              const f32x2 mp2 = fma2(y2, FW, mul2(pack2(mpo[2 * j], mpo[2 * j + 1]), FB));
+              const f32x2 pn2 = mul2(fma2(pack2(mno[2 * j], mno[2 * j + 1]), C2, mul2(mp2, C1)), C3);
+              const f32x2 inv2 = mul2(mul2(RF, pack2(cf[2 * j], cf[2 * j + 1])), BC2);
+              const f32x2 u2 = mul2(pn2, inv2);
+              tr.y[2 * j] = y2.x; tr.y[2 * j + 1] = y2.y;
+              tr.mp[2 * j] = mp2.x; tr.mp[2 * j + 1] = mp2.y;
+              tr.u[2 * j] = u2.x; tr.u[2 * j + 1] = u2.y;
+            }
           } else {
 #pragma unroll
             for (int k = 0; k < 8; ++k) {

@@ -6,6 +6,7 @@
 
 #include "kaon_device.cuh"
 #include "kaon_ops.cuh"
+#include "kaon_packed.cuh"
 
 namespace kaon {
 
@@ -69,8 +70,17 @@ __device__ __forceinline__ void pnm_decode8(const void* m, const float* sc, long
     if constexpr (MK == KAON_M_4BIT) {
       const uint32_t w = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const unsigned char*>(m) + (e >> 1));
       const float s = sc[bsh >= 31 ? 0 : (e >> bsh)];   // blocks hold at least 32 elements: one scale per trip
+      // nibble n -> the float 2^23 + n by a byte permute into the mantissa of 0x4B000000, less 2^23 + 8: the
+      // exact integer n - 8 without a conversion; pairs go through the packed adder and multiplier
+      const uint32_t lo = w & 0x0F0F0F0Fu, hi = (w >> 4) & 0x0F0F0F0Fu;
+      const f32x2 OFF = pack2(-8388616.0f, -8388616.0f), S2 = pack2(s, s);
 #pragma unroll
-      for (int k = 0; k < 8; ++k) o[k] = __fmul_rn((float)((int)((w >> (4 * k)) & 15u) - 8), s);
+      for (int j = 0; j < 4; ++j) {
+        const f32x2 v = pack2(__uint_as_float(__byte_perm(lo, 0x4B000000u, 0x7540u + j)),
+                              __uint_as_float(__byte_perm(hi, 0x4B000000u, 0x7540u + j)));
+        const f32x2 r = mul2(add2(v, OFF), S2);
+        o[2 * j] = r.x; o[2 * j + 1] = r.y;
+      }
       return;
     } else if constexpr (MK == KAON_M_INT8) {
       const uint2 w = *reinterpret_cast<const uint2*>(reinterpret_cast<const signed char*>(m) + e);

@@ -28,7 +28,7 @@
 
 namespace kaon {
 
-constexpr int KP_ITEM = 8192;
+constexpr int KP_ITEM = 16384;
 constexpr int KP_THREADS = 256;
 
 struct KpDev {
