@@ -10,6 +10,8 @@ import math
 SMALL = [(48, 64), (16, 20, 3, 3), (96,), (5, 7), (130,)]
 MUON = [(48, 32), (32, 64), (40,), (8, 4, 3, 3)]
 C1 = [(1024, 1024), (320, 320, 3, 3), (1024,)]
+# rows of 16 640 elements (longer than a work item's 16 384) and a 1-D tensor above a work item
+LONG = [(2, 2080, 2, 4), (50000,), (24, 16)]
 
 
 def cosine5(t):
@@ -29,6 +31,7 @@ CASES = {
     "lion_4bit_kahan": ("Lion", dict(lr=2e-4, betas=(0.95, 0.98), momentum_dtype="4bit", bf16_method="kahan"), SMALL, "bf16", 6, 6, {}),
     "lion_int8_kahan_wd_nocautious": ("Lion", dict(lr=2e-4, momentum_dtype="int8", weight_decay=0.1, cautious=False, bf16_method="kahan"), SMALL, "bf16", 4, 7, {}),
     "lion_4bit_block64": ("Lion", dict(lr=2e-4, betas=(0.95, 0.98), momentum_dtype="4bit", momentum_4bit_block=64, bf16_method="none"), SMALL, "bf16", 5, 8, {}),
+    "lion_4bit_long": ("Lion", dict(lr=2e-4, betas=(0.95, 0.98), momentum_dtype="4bit", cautious=True, bf16_method="none"), LONG, "bf16", 3, 9, {}),
     # Adakaon, the C1 settings on small shapes
     "adakaon_int8_none": ("Adakaon", dict(lr=1e-4, betas=(0.9, 0.999), momentum_dtype="int8", bf16_method="none"), SMALL, "bf16", 6, 10, {}),
     "adakaon_int8_sr": ("Adakaon", dict(lr=1e-4, betas=(0.9, 0.999), momentum_dtype="int8"), SMALL, "bf16", 6, 11, {}),
@@ -38,12 +41,14 @@ CASES = {
     "adakaon_int8_kahan": ("Adakaon", dict(lr=1e-4, betas=(0.9, 0.999), momentum_dtype="int8", bf16_method="kahan"), SMALL, "bf16", 6, 15, {}),
     "adakaon_4bit_block256_wd": ("Adakaon", dict(lr=1e-4, betas=(0.9, 0.999), weight_decay=0.05, momentum_dtype="4bit", momentum_4bit_block=256, bf16_method="none"), SMALL, "bf16", 5, 16, {}),
     "adakaon_4bit_block32_f32": ("Adakaon", dict(lr=1e-4, betas=(0.9, 0.999), momentum_dtype="4bit", momentum_4bit_block=32), SMALL, "f32", 4, 17, {}),
+    "adakaon_int8_long": ("Adakaon", dict(lr=1e-4, betas=(0.9, 0.999), momentum_dtype="int8", bf16_method="none"), LONG, "bf16", 3, 18, {}),
     # Nekaon (C4 settings; fp32 params make the three writes deterministic) under a cosine LR
     "nekaon_f32": ("Nekaon", dict(lr=1e-4, betas=(0.2, 0.999)), SMALL, "f32", 5, 20, {"lr_sched": "cosine5", "nekaon_eval": True}),
     "nekaon_bf16": ("Nekaon", dict(lr=1e-4, betas=(0.2, 0.999)), SMALL, "bf16", 5, 21, {"lr_sched": "cosine5"}),
     # AdaMuon (C5 settings)
     "adamuon_int8_none": ("AdaMuon", dict(lr=1e-3, ns_steps=2, cautious=True, momentum_dtype="int8", bf16_method="none"), MUON, "bf16", 4, 30, {}),
     "adamuon_int8_kahan": ("AdaMuon", dict(lr=1e-3, ns_steps=2, cautious=True, momentum_dtype="int8", bf16_method="kahan"), MUON, "bf16", 3, 31, {}),
+    "adamuon_int8_gc": ("AdaMuon", dict(lr=1e-3, ns_steps=2, cautious=True, momentum_dtype="int8", gradient_centralization=True, bf16_method="none"), MUON, "bf16", 4, 32, {}),
     # AdaPNM (two momenta through the same codecs; the second-moment EMA and the clip as Adakaon's)
     "adapnm_int8_none": ("AdaPNM", dict(lr=1e-4, momentum_dtype="int8", bf16_method="none"), SMALL, "bf16", 6, 40, {}),
     "adapnm_4bit_wd_f32": ("AdaPNM", dict(lr=1e-4, betas=(0.9, 0.999), beta0=1.0, weight_decay=0.1, momentum_dtype="4bit"), SMALL, "f32", 5, 41, {}),

@@ -61,7 +61,7 @@ def _check_against_fixture(name, writes_per_step=1):
 
 @pytest.mark.parametrize("name", ["adakaon_int8_none", "adakaon_int8_sr", "adakaon_int8_outlier",
                                   "adakaon_4bit_wd_f32", "adakaon_bf16m_none", "adakaon_4bit_block256_wd",
-                                  "adakaon_4bit_block32_f32"])
+                                  "adakaon_4bit_block32_f32", "adakaon_int8_long"])
 def test_adakaon_matches_reference(name):
     _check_against_fixture(name)
 

@@ -16,9 +16,10 @@ from _golden import rel_err
 pytestmark = pytest.mark.gpu
 
 
-def test_adamuon_matches_reference_golden():
+@pytest.mark.parametrize("name", ["adamuon_int8_none", "adamuon_int8_gc"])
+def test_adamuon_matches_reference_golden(name):
     from _gpu import run_case_gpu, state_np, to_bits
-    for step, f, opt, params in run_case_gpu("adamuon_int8_none"):
+    for step, f, opt, params in run_case_gpu(name):
         for i, p in enumerate(params):
             st = opt.state[p]
             got, want = ko.as_f32(to_bits(p)), ko.as_f32(f.weights(step, i))
@@ -26,8 +27,12 @@ def test_adamuon_matches_reference_golden():
             if p.ndim >= 2:
                 assert np.array_equal(state_np(st, "m").view(np.int8), f.state(step, i, "m").view(np.int8)), (step, i)
                 assert np.array_equal(state_np(st, "m_scale"), f.state(step, i, "m_scale").reshape(-1)), (step, i)
-                assert rel_err(state_np(st, "row"), f.state(step, i, "row")) < 5e-2
-                assert rel_err(state_np(st, "col"), f.state(step, i, "col")) < 5e-2
+                # statistics of O: two bf16 Newton-Schulz implementations agree to the reference's own test
+                # tolerance per element (2e-2 absolute on entries of about 0.2), i.e. several per cent on a
+                # row's mean square; the centralised gradient's 8 x 36 matrix is the least well conditioned
+                tol = 1e-1 if name.endswith("_gc") else 5e-2
+                assert rel_err(state_np(st, "row"), f.state(step, i, "row")) < tol
+                assert rel_err(state_np(st, "col"), f.state(step, i, "col")) < tol
             else:
                 assert rel_err(state_np(st, "v"), f.state(step, i, "v")) <= 1e-5
 

@@ -17,7 +17,7 @@ def _inner_state(opt, p):
 
 
 @pytest.mark.parametrize("name", ["lion_4bit_nogc_wd", "lion_4bit_none", "lion_int8_none",
-                                  "lion_bf16_nocautious", "lion_4bit_block64"])
+                                  "lion_bf16_nocautious", "lion_4bit_block64", "lion_4bit_long"])
 def test_lion_matches_reference_bit_exact(name):
     from _gpu import run_case_gpu, state_np, to_bits
     for step, f, opt, params in run_case_gpu(name):

@@ -144,7 +144,7 @@ def test_lion_fp32_grads_with_gc():
 
 
 @pytest.mark.parametrize("name", ["lion_4bit_nogc_wd", "lion_4bit_none", "lion_int8_none",
-                                  "lion_bf16_nocautious", "lion_4bit_block64"])
+                                  "lion_bf16_nocautious", "lion_4bit_block64", "lion_4bit_long"])
 def test_lion_bit_exact(name):
     """Lion has no order-dependent reduction except the GC row mean; on these vectors the oracle's
     double-accumulated mean rounds to the same bf16 as torch's, so everything is bit-exact."""
@@ -210,7 +210,7 @@ def test_lion_sr_state_is_weight_independent():
 
 @pytest.mark.parametrize("name", ["adakaon_int8_none", "adakaon_int8_sr", "adakaon_int8_outlier",
                                   "adakaon_4bit_wd_f32", "adakaon_bf16m_none", "adakaon_4bit_block256_wd",
-                                  "adakaon_4bit_block32_f32"])
+                                  "adakaon_4bit_block32_f32", "adakaon_int8_long"])
 def test_adakaon(name):
     md = CASES[name][1]["momentum_dtype"]
     sr = CASES[name][1].get("bf16_method", "stochastic_rounding") == "stochastic_rounding"
@@ -404,13 +404,14 @@ def test_nekaon_bf16_state():
             assert sr_close(t.p, f.weights(step, i), 3 * step, 1e-3)
 
 
-def test_adamuon():
-    for step, f, opt in _run_oracle("adamuon_int8_none"):
+@pytest.mark.parametrize("name", ["adamuon_int8_none", "adamuon_int8_gc"])
+def test_adamuon(name):
+    for step, f, opt in _run_oracle(name):
         for i, t in enumerate(opt.tensors):
             got = ko.as_f32(t.p)
             want = ko.as_f32(f.weights(step, i))
             np.testing.assert_allclose(got, want, rtol=2e-2, atol=2e-3)
-            if t.rows:  # the EMA of the raw grad has no reduction in it: bit-exact
+            if t.rows:  # the EMA of the raw (or centralised: bf16 row means agree) grad: bit-exact
                 assert np.array_equal(t.state["m"], f.state(step, i, "m").view(np.int8))
                 assert np.array_equal(t.state["m_scale"], f.state(step, i, "m_scale").reshape(-1))
                 assert rel_err(t.state["row"], f.state(step, i, "row")) < 5e-2
