@@ -405,7 +405,7 @@ def measure(ctx: Ctx, workload: str, steps: int, warmup: int, e2e_steps: int = 0
         from kaon_b200.zero1 import ShardedGrads
         # full-list local gradients + the owner's reduced shard, cut into waves: one collective and one
         # parameter group per wave, so that wave w is stepped while wave w+1 is still being reduced
-        sg = ShardedGrads(sw, shapes, waves=max(1, args.waves))
+        sg = ShardedGrads(sw, shapes, waves=args.waves if args.waves > 0 else (4 if world <= 2 else 1))
         fill_normal(sg.flat, 1e-3, outlier=bool(wopt.get("outlier")))
         by_wave = {}
         for p, i in zip(params, owned):
@@ -744,9 +744,10 @@ def main():
     ap.add_argument("--comm-sms", type=int, default=48,
                     help="with --reduce-scatter in waves: multiprocessors left free of the (persistent) step kernels "
                          "for the collective that runs beside them")
-    ap.add_argument("--waves", type=int, default=4,
+    ap.add_argument("--waves", type=int, default=0,
                     help="with --reduce-scatter: cut every rank's tensors into this many waves, each one collective "
-                         "and one parameter group, so the step of a wave overlaps the next wave's reduce-scatter")
+                         "and one parameter group, so the step of a wave overlaps the next wave's reduce-scatter "
+                         "(0: 4 waves on 2 GPUs, where the step is long enough to hide; 1 beyond, where the links are the floor)")
     ap.add_argument("--reduce-scatter", action="store_true",
                     help="N>1: put the gradient reduce-scatter (NCCL, bf16 average) inside every step; the step "
                          "kernels then read the collective's output buffer")
