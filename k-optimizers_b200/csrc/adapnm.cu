@@ -22,6 +22,8 @@
 #include <cmath>
 #include <vector>
 
+#include <type_traits>
+
 #include "adakaon_dev.h"
 #include "kaon_device.cuh"
 #include "kaon_host.h"
@@ -163,107 +165,120 @@ __global__ void __launch_bounds__(PT_THREADS, 4) pnm_pass_kernel(PlanView pv, Pn
       for (int v0 = 0; v0 < nvec; v0 += PT_THREADS) {
         const int v = v0 + tid;
         const long long e = t.e0 + (long long)v * 8;
-        const int cnt = v < nvec ? min(8, (int)(t.e0 + t.n - e)) : 0;
-        PnmTrip tr;
-        tr.first = 0u;
-        if (cnt > 0) {
-          float gx[8], mpo[8], mno[8];
-          int cl[8];
-          load8_guard<PT>(g + e * E::BYTES, cnt, gx);
-          int r = e < 0x100000000ll ? (int)((unsigned)e / (unsigned)C) : (int)(e / C);
-          int c = (int)(e - (long long)r * C);
-          // the common trip: eight elements of one row (no row bookkeeping, one row factor, one mean)
-          const bool one_row = cnt == 8 && c + 8 <= C;
-          if (one_row) {
-#pragma unroll
-            for (int k = 0; k < 8; ++k) { tr.rw[k] = r; cl[k] = c + k; }
-            if (c == 0) tr.first = 1u;
-          } else {
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-              tr.rw[k] = 0; cl[k] = 0;
-              if (k < cnt) {
-                while (c >= C) { c -= C; ++r; }
-                tr.rw[k] = r;
-                cl[k] = c;
-                if (c == 0) tr.first |= 1u << k;
-                ++c;
-              }
-            }
-          }
-          pnm_decode8<MK>(pos, psc_rd, e, cnt, tr.rw, bsh, mpo);
-          pnm_decode8<MK>(neg, nsc, e, cnt, tr.rw, bsh, mno);
-          auto chain = [&](int k, float rf, float mu, float cf) {
-            const float yk = pnm_centered<PT>(gx[k], mu, hp.gc != 0);
-            const float mpn = __fmaf_rn(yk, hp.fw, __fmul_rn(mpo[k], hp.fb));
-            const float pn = __fmul_rn(__fmaf_rn(mno[k], hp.c2, __fmul_rn(mpn, hp.c1)), hp.c3);
-            const float inv = __fmul_rn(__fmul_rn(rf, cf), hp.bc2);
-            tr.y[k] = yk; tr.mp[k] = mpn; tr.u[k] = __fmul_rn(pn, inv);
-          };
-          if (one_row) {
-            const float rf = rfac[tr.rw[0]], mu = hp.gc ? mean[tr.rw[0]] : 0.0f;
-            float cf[8];
-            ld8f(cfac + cl[0], 8, cf);  // the eight column factors: two vector loads where the address allows
-            // the same chain on pairs (each lane of a packed instruction is the scalar IEEE operation)
-            const f32x2 FW = pack2(hp.fw, hp.fw), FB = pack2(hp.fb, hp.fb), C1 = pack2(hp.c1, hp.c1);
-            const f32x2 C2 = pack2(hp.c2, hp.c2), C3 = pack2(hp.c3, hp.c3), BC2 = pack2(hp.bc2, hp.bc2);
-            const f32x2 RF = pack2(rf, rf), MUN = pack2(-mu, -mu);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              f32x2 y2 = pack2(gx[2 * j], gx[2 * j + 1]);
-              if (hp.gc) {
-                y2 = add2(y2, MUN);
-                if constexpr (E::IS_BF16) {
-                  const uint32_t w = pack_bf16_rn(y2.x, y2.y);
-                  y2 = pack2(bf16lo(w), bf16hi(w));
+        const int cnt_rt = v < nvec ? min(8, (int)(t.e0 + t.n - e)) : 0;
+        int r0 = 0, c0 = 0;
+        if (cnt_rt > 0) {
+          r0 = e < 0x100000000ll ? (int)((unsigned)e / (unsigned)C) : (int)(e / C);
+          c0 = (int)(e - (long long)r0 * C);
+        }
+        // FULL: every lane of the warp has eight elements inside one row, so the element guards and the
+        // row bookkeeping fold away at compile time; anything else (a row end, a tensor's tail) takes
+        // the guarded form.  The choice is per warp: the 4-bit store shuffles block maxima across lanes.
+        auto trip = [&](auto full_tag) {
+          constexpr bool FULL = decltype(full_tag)::value;
+          const int cnt = FULL ? 8 : cnt_rt;
+          PnmTrip tr;
+          tr.first = 0u;
+          if (cnt > 0) {
+            float gx[8], mpo[8], mno[8];
+            int cl[8];
+            load8_guard<PT>(g + e * E::BYTES, cnt, gx);
+            int r = r0, c = c0;
+            // the common trip: eight elements of one row (no row bookkeeping, one row factor, one mean)
+            const bool one_row = FULL || (cnt == 8 && c + 8 <= C);
+            if (one_row) {
+  #pragma unroll
+              for (int k = 0; k < 8; ++k) { tr.rw[k] = r; cl[k] = c + k; }
+              if (c == 0) tr.first = 1u;
+            } else {
+  #pragma unroll
+              for (int k = 0; k < 8; ++k) {
+                tr.rw[k] = 0; cl[k] = 0;
+                if (k < cnt) {
+                  while (c >= C) { c -= C; ++r; }
+                  tr.rw[k] = r;
+                  cl[k] = c;
+                  if (c == 0) tr.first |= 1u << k;
+                  ++c;
                 }
               }
-              const f32x2 mp2 = fma2(y2, FW, mul2(pack2(mpo[2 * j], mpo[2 * j + 1]), FB));
-              const f32x2 pn2 = mul2(fma2(pack2(mno[2 * j], mno[2 * j + 1]), C2, mul2(mp2, C1)), C3);
-              const f32x2 inv2 = mul2(mul2(RF, pack2(cf[2 * j], cf[2 * j + 1])), BC2);
-              const f32x2 u2 = mul2(pn2, inv2);
-              tr.y[2 * j] = y2.x; tr.y[2 * j + 1] = y2.y;
-              tr.mp[2 * j] = mp2.x; tr.mp[2 * j + 1] = mp2.y;
-              tr.u[2 * j] = u2.x; tr.u[2 * j + 1] = u2.y;
+            }
+            pnm_decode8<MK>(pos, psc_rd, e, cnt, tr.rw, bsh, mpo);
+            pnm_decode8<MK>(neg, nsc, e, cnt, tr.rw, bsh, mno);
+            auto chain = [&](int k, float rf, float mu, float cf) {
+              const float yk = pnm_centered<PT>(gx[k], mu, hp.gc != 0);
+              const float mpn = __fmaf_rn(yk, hp.fw, __fmul_rn(mpo[k], hp.fb));
+              const float pn = __fmul_rn(__fmaf_rn(mno[k], hp.c2, __fmul_rn(mpn, hp.c1)), hp.c3);
+              const float inv = __fmul_rn(__fmul_rn(rf, cf), hp.bc2);
+              tr.y[k] = yk; tr.mp[k] = mpn; tr.u[k] = __fmul_rn(pn, inv);
+            };
+            if (one_row) {
+              const float rf = rfac[tr.rw[0]], mu = hp.gc ? mean[tr.rw[0]] : 0.0f;
+              float cf[8];
+              ld8f(cfac + cl[0], 8, cf);  // the eight column factors: two vector loads where the address allows
+              // the same chain on pairs (each lane of a packed instruction is the scalar IEEE operation)
+              const f32x2 FW = pack2(hp.fw, hp.fw), FB = pack2(hp.fb, hp.fb), C1 = pack2(hp.c1, hp.c1);
+              const f32x2 C2 = pack2(hp.c2, hp.c2), C3 = pack2(hp.c3, hp.c3), BC2 = pack2(hp.bc2, hp.bc2);
+              const f32x2 RF = pack2(rf, rf), MUN = pack2(-mu, -mu);
+  #pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                f32x2 y2 = pack2(gx[2 * j], gx[2 * j + 1]);
+                if (hp.gc) {
+                  y2 = add2(y2, MUN);
+                  if constexpr (E::IS_BF16) {
+                    const uint32_t w = pack_bf16_rn(y2.x, y2.y);
+                    y2 = pack2(bf16lo(w), bf16hi(w));
+                  }
+                }
+                const f32x2 mp2 = fma2(y2, FW, mul2(pack2(mpo[2 * j], mpo[2 * j + 1]), FB));
+                const f32x2 pn2 = mul2(fma2(pack2(mno[2 * j], mno[2 * j + 1]), C2, mul2(mp2, C1)), C3);
+                const f32x2 inv2 = mul2(mul2(RF, pack2(cf[2 * j], cf[2 * j + 1])), BC2);
+                const f32x2 u2 = mul2(pn2, inv2);
+                tr.y[2 * j] = y2.x; tr.y[2 * j + 1] = y2.y;
+                tr.mp[2 * j] = mp2.x; tr.mp[2 * j + 1] = mp2.y;
+                tr.u[2 * j] = u2.x; tr.u[2 * j + 1] = u2.y;
+              }
+            } else {
+  #pragma unroll
+              for (int k = 0; k < 8; ++k) {
+                tr.y[k] = 0.0f; tr.mp[k] = 0.0f; tr.u[k] = 0.0f;
+                if (k < cnt) chain(k, rfac[tr.rw[k]], hp.gc ? mean[tr.rw[k]] : 0.0f, cfac[cl[k]]);
+              }
             }
           } else {
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-              tr.y[k] = 0.0f; tr.mp[k] = 0.0f; tr.u[k] = 0.0f;
-              if (k < cnt) chain(k, rfac[tr.rw[k]], hp.gc ? mean[tr.rw[k]] : 0.0f, cfac[cl[k]]);
-            }
+  #pragma unroll
+            for (int k = 0; k < 8; ++k) { tr.y[k] = 0.0f; tr.mp[k] = 0.0f; tr.u[k] = 0.0f; tr.rw[k] = 0; }
           }
-        } else {
-#pragma unroll
-          for (int k = 0; k < 8; ++k) { tr.y[k] = 0.0f; tr.mp[k] = 0.0f; tr.u[k] = 0.0f; tr.rw[k] = 0; }
-        }
-        if constexpr (!APPLY) {
-          float s8 = 0.0f;  // the trip's eight squares in fp32, then one wide addition
-#pragma unroll
-          for (int k = 0; k < 8; ++k) if (k < cnt) {
-            s8 = __fmaf_rn(tr.u[k], tr.u[k], s8);
-            kept += (__fmul_rn(tr.u[k], tr.y[k]) > 0.0f) ? 1u : 0u;
-          }
-          ss += (double)s8;
-          if constexpr (MK == KAON_M_INT8) {
-            int cr = -1;
-            float mx = 0.0f;
-#pragma unroll
+          if constexpr (!APPLY) {
+            float s8 = 0.0f;  // the trip's eight squares in fp32, then one wide addition
+  #pragma unroll
             for (int k = 0; k < 8; ++k) if (k < cnt) {
-              if (tr.rw[k] != cr) {
-                if (cr >= 0) atomicMax(rowmax + cr, __float_as_uint(mx));
-                cr = tr.rw[k];
-                mx = 0.0f;
-              }
-              mx = fmaxf(mx, fabsf(tr.mp[k]));
+              s8 = __fmaf_rn(tr.u[k], tr.u[k], s8);
+              kept += (__fmul_rn(tr.u[k], tr.y[k]) > 0.0f) ? 1u : 0u;
             }
-            if (cr >= 0) atomicMax(rowmax + cr, __float_as_uint(mx));
+            ss += (double)s8;
+            if constexpr (MK == KAON_M_INT8) {
+              int cr = -1;
+              float mx = 0.0f;
+  #pragma unroll
+              for (int k = 0; k < 8; ++k) if (k < cnt) {
+                if (tr.rw[k] != cr) {
+                  if (cr >= 0) atomicMax(rowmax + cr, __float_as_uint(mx));
+                  cr = tr.rw[k];
+                  mx = 0.0f;
+                }
+                mx = fmaxf(mx, fabsf(tr.mp[k]));
+              }
+              if (cr >= 0) atomicMax(rowmax + cr, __float_as_uint(mx));
+            }
+          } else {
+            if (cnt > 0) pnm_write<PT>(hp, d, tr, e, cnt, div, denom, s_upd, &pv.peers);
+            pnm_store_m<MK>(pos, psc, tr, e, cnt, bsh, lane,
+                            [&](int r) { return __uint_as_float(__ldcg(rowmax + r)); });
           }
-        } else {
-          if (cnt > 0) pnm_write<PT>(hp, d, tr, e, cnt, div, denom, s_upd, &pv.peers);
-          pnm_store_m<MK>(pos, psc, tr, e, cnt, bsh, lane,
-                          [&](int r) { return __uint_as_float(__ldcg(rowmax + r)); });
-        }
+        };
+        if (__all_sync(0xffffffffu, cnt_rt == 8 && c0 + 8 <= C)) trip(std::true_type{});
+        else trip(std::false_type{});
       }
     }
     if constexpr (!APPLY) {
