@@ -188,6 +188,7 @@ class FusedStepMixin:
     def _fused_init(self) -> None:
         self._plans: dict[tuple, GroupPlan] = {}
         self._plan_members: dict[tuple, tuple[int, ...]] = {}
+        self._group_buckets: dict[int, tuple] = {}   # per group: (params list, its length, momentum dtype, buckets)
         self._t = 0                 # completed steps; the SR stream uses the 1-based index
         self.sr_seed: int | None = None  # None -> torch.initial_seed() at the first step
         self._mirrors: tuple[int, int, list[int]] | None = None
@@ -212,6 +213,7 @@ class FusedStepMixin:
             pl.destroy()
         self._plans.clear()
         self._plan_members.clear()
+        self._group_buckets.clear()
 
     def _seed(self) -> int:
         if self.sr_seed is None:
@@ -233,27 +235,40 @@ class FusedStepMixin:
 
     def _group_plans(self, gi: int, group: dict[str, Any], state_of) -> list[GroupPlan]:
         """Plans covering every parameter of the group that has a gradient now or had one before."""
-        active = [p for p in group["params"] if p.grad is not None]
-        if not active:
-            return []
-        fresh = False
-        for p in active:
-            if p.grad.is_sparse:
+        params = group["params"]
+        fresh = active = False
+        for p in params:
+            g = p.grad
+            if g is None:
+                continue
+            active = True
+            if g.is_sparse:
                 raise RuntimeError(f"{type(self).__name__} does not support sparse gradients")
             st = state_of(p)
             if not st:
                 self._init_state(p, st, group)
                 fresh = True
-        # tensors stepped now or before (a lookup must not create state for the others); an empty tensor
-        # has state, as in the reference, but nothing to step and no address
-        members = [p for p in group["params"] if p in self.state and state_of(p) and p.numel() > 0]
-        buckets: dict[tuple, list[torch.Tensor]] = {}
-        for p in members:
-            buckets.setdefault((gi, p.device, p.dtype), []).append(p)
+        if not active:
+            return []
+        # The buckets of the group (which tensors, in which plan) change only when a tensor gets its first
+        # state, the group's list is replaced or resized, the momentum dtype changes or the plans are
+        # dropped (load_state_dict, new mirrors): kept between steps, so a step of an unchanged group
+        # costs one pass over the gradients.
+        md = self._momentum_dtype(group)
+        cached = self._group_buckets.get(gi)
+        if cached is None or fresh or cached[0] is not params or cached[1] != len(params) or cached[2] != md:
+            # tensors stepped now or before (a lookup must not create state for the others); an empty tensor
+            # has state, as in the reference, but nothing to step and no address
+            members = [p for p in params if p in self.state and state_of(p) and p.numel() > 0]
+            buckets: dict[tuple, list[torch.Tensor]] = {}
+            for p in members:
+                buckets.setdefault((gi, p.device, p.dtype), []).append(p)
+            cached = (params, len(params), md,
+                      [(key, plist, tuple(id(p) for p in plist) + (md,)) for key, plist in buckets.items()])
+            self._group_buckets[gi] = cached
         plans = []
         ids = None
-        for key, plist in buckets.items():
-            sig = tuple(id(p) for p in plist) + (self._momentum_dtype(group),)
+        for key, plist, sig in cached[3]:
             pl = self._plans.get(key)
             if pl is None or fresh or self._plan_members.get(key) != sig or pl.params_moved():
                 if pl is not None:
@@ -261,7 +276,7 @@ class FusedStepMixin:
                 if ids is None:
                     ids = self._tensor_ids()
                 pl = GroupPlan(self._OPT_KIND, plist, [state_of(p) for p in plist],
-                               [ids[id(p)] for p in plist], self._momentum_dtype(group), self._M_KEY)
+                               [ids[id(p)] for p in plist], md, self._M_KEY)
                 self._plan_created(pl, plist, [state_of(p) for p in plist])
                 if self._mirrors is not None:
                     pl.set_peers(*self._mirrors)
