@@ -360,6 +360,34 @@ class Ctx:
         return t.tolist()
 
 
+def e2e_groups(sizes, offsets, shard_len, ngroups):
+    """Cut a rank's tensors (element counts `sizes` at element `offsets` of its shard, in list order) into at
+    most `ngroups` runs of consecutive tensors of about equal size.  Returns (the tensor positions of each
+    run, the [lo, hi) slice of the shard each run covers); the slices tile [0, shard_len) in order, so that
+    per-run copies move every byte of the shard exactly once."""
+    n = len(sizes)
+    ngroups = max(1, min(ngroups, n))
+    total = sum(sizes)
+    chunks, acc, nxt = [[]], 0, 1
+    for k in range(n):
+        if acc >= nxt * total / ngroups and chunks[-1]:
+            chunks.append([])
+            nxt += 1
+        chunks[-1].append(k)
+        acc += sizes[k]
+    bounds = []
+    for ch in chunks:
+        lo = min(offsets[k] for k in ch)
+        hi = max(offsets[k] + sizes[k] for k in ch)
+        if bounds and lo < bounds[-1][1]:
+            raise ValueError("the owned tensors are not laid out in list order")
+        bounds.append((lo, hi))
+    # padding between runs and at either end travels with the run before it (the first run: before it)
+    bounds = [(0 if j == 0 else bounds[j][0], bounds[j + 1][0] if j + 1 < len(bounds) else shard_len)
+              for j in range(len(bounds))]
+    return chunks, bounds
+
+
 def measure(ctx: Ctx, workload: str, steps: int, warmup: int, e2e_steps: int = 0):
     """One workload at ctx.world GPUs: device-timed steps (max over ranks), clocks, roofline."""
     import torch
@@ -497,23 +525,10 @@ def measure(ctx: Ctx, workload: str, steps: int, warmup: int, e2e_steps: int = 0
         cur_s = torch.cuda.current_stream()
         s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
         nset = len(gsets)
-        ngrp = max(1, min(E2E_GROUPS, len(params)))
-        bounds, chunks, acc, nxt = [], [[]], 0, 1
-        own_total = sum(p.numel() for p in params)
-        for p, i in zip(params, owned):
-            if acc >= nxt * own_total / ngrp and chunks[-1]:
-                chunks.append([])
-                nxt += 1
-            chunks[-1].append((p, i))
-            acc += p.numel()
-        for ch in chunks:
-            lo = min(sw.part.offset[i] for _, i in ch)
-            hi = max(sw.part.offset[i] + p.numel() for p, i in ch)
-            assert not bounds or lo >= bounds[-1][1], "the owned tensors are laid out in list order"
-            bounds.append((lo, hi))
-        bounds[0] = (0, bounds[0][1])
-        bounds[-1] = (bounds[-1][0], sw.part.shard_len)
+        chunks, bounds = e2e_groups([p.numel() for p in params], [sw.part.offset[i] for i in owned],
+                                    sw.part.shard_len, E2E_GROUPS)
         ngrp = len(chunks)
+        chunks = [[(params[k], owned[k]) for k in ch] for ch in chunks]
         opt_e = getattr(kaon_b200, opt_name)([{"params": [p for p, _ in ch]} for ch in chunks], **kw)
         opt_e.sr_seed = 0
         if world > 1 and fused_publish:

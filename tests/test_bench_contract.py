@@ -57,3 +57,29 @@ def test_reference_arm_uses_the_host_cores_under_a_launcher():
     assert r.returncode == 0, r.stderr[-2000:]
     d = json.loads([ln for ln in r.stdout.splitlines() if ln.startswith("{")][0])
     assert d["cpu_baseline"]["cores"] == len(os.sched_getaffinity(0))
+
+
+def test_end_to_end_groups_tile_the_shard():
+    """The end-to-end loop copies a rank's shard slice by slice, one slice per parameter group: the slices
+    must cover every element exactly once, in order, whatever the padding between tensors, and hold the
+    tensors of their group."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("bench_module", os.path.join(ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    sizes = [1000, 24, 5000, 8, 8, 3000, 700, 64, 12000, 16]
+    offsets, cur = [], 0
+    for s in sizes:
+        offsets.append(cur)
+        cur += (s + 127) // 128 * 128        # every tensor starts on an aligned boundary: padding between them
+    shard_len = cur + 256
+    for ng in (1, 3, 4, 16, 100):
+        chunks, bounds = bench.e2e_groups(sizes, offsets, shard_len, ng)
+        assert 1 <= len(chunks) <= min(ng, len(sizes)) and len(chunks) == len(bounds)
+        assert [k for ch in chunks for k in ch] == list(range(len(sizes)))       # every tensor once, in order
+        assert bounds[0][0] == 0 and bounds[-1][1] == shard_len
+        assert all(bounds[j][1] == bounds[j + 1][0] for j in range(len(bounds) - 1))
+        for ch, (lo, hi) in zip(chunks, bounds):
+            assert all(lo <= offsets[k] and offsets[k] + sizes[k] <= hi for k in ch)
+    with pytest.raises(ValueError):
+        bench.e2e_groups([10, 10, 10, 10], [0, 256, 128, 384], 512, 4)           # not in list order
