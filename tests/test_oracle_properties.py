@@ -92,3 +92,108 @@ def test_stochastic_rounding_write_is_unbiased_and_one_level_wide():
     level = np.abs(ko.as_f32(p)).astype(np.float64) * 2.0 ** -8
     z = ((acc / steps - exact) / (level / np.sqrt(steps)))[big]
     assert abs(z.mean()) < 0.05 and z.std() < 1.5
+
+
+# ---- whole steps: properties the reference's tests hold its optimizers to, asked of the oracle ----
+
+SHAPES = [(64, 96), (16, 8, 3, 3), (300,), (5, 7)]
+
+
+def _f32(rng, shapes, scale):
+    return [(rng.standard_normal(int(np.prod(s))) * scale).astype(np.float32) for s in shapes]
+
+
+def test_lion_moves_every_weight_by_exactly_lr_against_the_sign():
+    """reference tests/test_lion.py: without mask, decay and centralization the first update is
+    -lr * sign(g) on every element with a non-zero gradient."""
+    rng = np.random.default_rng(1)
+    p0 = _f32(rng, SHAPES, 0.02)
+    g = _f32(rng, SHAPES, 1e-3)
+    opt = ko.OracleLion([p.copy() for p in p0], SHAPES, lr=1e-3, betas=(0.9, 0.99), momentum_dtype="float32",
+                        cautious=False, gradient_centralization=False, bf16_method="none")
+    opt.step(g)
+    for t, a, gi in zip(opt.tensors, p0, g):
+        want = a - np.float32(1e-3) * np.sign(gi)
+        assert np.array_equal(t.p, want.astype(np.float32))
+        assert np.allclose(t.state["m"], np.float32(0.01) * gi, rtol=1e-6, atol=0)      # (1 - beta2) * g
+
+
+def test_lion_cautious_mask_rescales_by_the_kept_fraction():
+    """With the mask on, weights whose update sign disagrees with the gradient stay, the others move by
+    lr * numel / kept (reference src/kaon/lion.py:344-348)."""
+    rng = np.random.default_rng(2)
+    shapes = [(128, 64)]
+    p0 = _f32(rng, shapes, 0.02)
+    opt = ko.OracleLion([p.copy() for p in p0], shapes, lr=1e-3, betas=(0.9, 0.5), momentum_dtype="float32",
+                        cautious=True, gradient_centralization=False, bf16_method="none")
+    opt.step(_f32(rng, shapes, 1e-3))              # momentum = half the first gradient: it decides the next sign
+    before = opt.tensors[0].p.copy()
+    g2 = _f32(rng, shapes, 1e-3)                   # an independent gradient: about half the signs disagree
+    opt.step(g2)
+    moved = opt.tensors[0].p != before
+    frac = moved.mean()
+    assert 0.3 < frac < 0.9
+    step = np.abs(opt.tensors[0].p - before)[moved]
+    assert np.allclose(step, 1e-3 / frac, rtol=2e-3)
+
+
+@pytest.mark.parametrize("md", ["float32", "int8", "4bit"])
+def test_adakaon_first_step_does_not_depend_on_the_gradients_scale(md):
+    """The factored second moment normalises the gradient: scaling every gradient by 64 leaves the first
+    update unchanged (up to eps1 = 1e-30 and rounding)."""
+    rng = np.random.default_rng(3)
+    p0 = _f32(rng, SHAPES, 0.02)
+    g = _f32(rng, SHAPES, 1e-3)
+    outs = []
+    for k in (1.0, 64.0):
+        opt = ko.OracleAdakaon([p.copy() for p in p0], SHAPES, lr=1e-3, betas=(0.9, 0.999), momentum_dtype=md,
+                               cautious=True, gradient_centralization=True, bf16_method="none")
+        opt.step([gi * np.float32(k) for gi in g])
+        outs.append([t.p.copy() for t in opt.tensors])
+    for a, b, base in zip(outs[0], outs[1], p0):
+        assert np.abs(a - base).max() > 0
+        assert np.allclose(a - base, b - base, rtol=2e-2, atol=2e-6)
+
+
+def test_zero_gradient_changes_nothing_but_decay():
+    rng = np.random.default_rng(4)
+    p0 = _f32(rng, SHAPES, 0.02)
+    z = [np.zeros_like(p) for p in p0]
+    for cls, kw in ((ko.OracleLion, dict(lr=1e-3, momentum_dtype="4bit")),
+                    (ko.OracleAdakaon, dict(lr=1e-3, momentum_dtype="int8")),
+                    (ko.OracleAdaPNM, dict(lr=1e-3, momentum_dtype="int8"))):
+        opt = cls([p.copy() for p in p0], SHAPES, bf16_method="none", **kw)
+        opt.step(z)
+        opt.step(z)
+        for t, a in zip(opt.tensors, p0):
+            assert np.array_equal(t.p, a), cls.__name__
+
+
+def test_nekaon_eval_removes_the_climb_exactly_for_fp32_weights():
+    """reference tests/test_nekaon.py: after eval() the weights are the ones an Adakaon without the climb
+    would hold; train() puts the climb back."""
+    rng = np.random.default_rng(6)
+    p0 = _f32(rng, SHAPES, 0.02)
+    opt = ko.OracleNekaon([p.copy() for p in p0], SHAPES, lr=1e-3, betas=(0.2, 0.999))
+    for _ in range(3):
+        opt.step(_f32(rng, SHAPES, 1e-3))
+    climbed = [t.p.copy() for t in opt.tensors]
+    opt.eval()
+    flat = [t.p.copy() for t in opt.tensors]
+    assert any(np.abs(a - b).max() > 0 for a, b in zip(climbed, flat))
+    opt.train()
+    for t, a in zip(opt.tensors, climbed):
+        assert np.allclose(t.p, a, rtol=0, atol=1e-9)
+
+
+def test_kprodigy_distance_estimate_never_shrinks_and_grows_on_a_steady_direction():
+    rng = np.random.default_rng(7)
+    p0 = _f32(rng, SHAPES, 0.02)
+    base = _f32(rng, SHAPES, 1e-3)
+    opt = ko.OracleKProdigy([p.copy() for p in p0], SHAPES, bf16_method="none")
+    ds = []
+    for _ in range(12):
+        opt.step([b + n for b, n in zip(base, _f32(rng, SHAPES, 3e-4))])
+        ds.append(float(opt.group["d"]))
+    assert all(b >= a for a, b in zip(ds, ds[1:]))
+    assert ds[-1] > ds[0]
