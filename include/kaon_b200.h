@@ -250,7 +250,8 @@ int kaon_kprodigy_pass2(kaon_plan* plan, const kaon_kprodigy_pass2_hparams* hp, 
 
 /* One AdaMuon step.  Replaces AdaMuon._run_step / _factored_bucket / _nonfactored_bucket /
  * _step_one_param (src/kaon/adamuon.py:327-352, 434-615): per >=2-D tensor the EMA of the raw gradient
- * through the codec, Newton-Schulz of the fp32 momentum (tcgen05 GEMMs), factored second moment of the
+ * (less its row means when gradient_centralization is set, :334-335; the mask then compares with that
+ * centralised gradient) through the codec, Newton-Schulz of the fp32 momentum (tcgen05 GEMMs), factored second moment of the
  * orthogonalised signal, clip, 0.2*lr scale, weight decay, cautious mask against the raw gradient,
  * weight write; 1-D tensors take the Adam-style branch.  `workspace` (device, 256-byte aligned, at least
  * kaon_adamuon_workspace_bytes(plan)) holds the orthogonalised matrices between the kernels; the caller
